@@ -1,0 +1,243 @@
+// Memory-bound kernels of the decoder: embedding gather, RMSNorm (alone and fused with the
+// residual add), rotate-half position encoding fused with the write of K and V into cache pages,
+// SwiGLU, and a row gather.  Each is templated on the storage type (float or bfloat16); all
+// arithmetic is float32.  Any width is accepted (no power-of-two or vector-width assumption).
+//
+// Formulas follow the reference's torch code (src/mini_llm_runtime/qwen_model_runner.py):
+// RMSNorm :22-26, RoPE :34-61, SwiGLU :215-217, K/V written after RoPE :105-109.
+#include "common.cuh"
+
+namespace mlr {
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 T* __restrict__ out, int width, int vocab) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  // Host code validates ids; clamp so a bad id can never read outside the table.
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const T* src = table + (size_t)id * width;
+  T* dst = out + (size_t)row * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------- gather rows
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows,
+                                   T* __restrict__ out, int width) {
+  const T* src = x + (size_t)rows[blockIdx.x] * width;
+  T* dst = out + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------- RMSNorm (+ residual add)
+// One block per row.  If `delta` is given the row becomes residual + delta (added in float32,
+// rounded once to T and stored back to `residual`); the norm is then taken of the stored value,
+// so the fused kernel equals "add, then norm" exactly.  The row is staged in shared memory as
+// float32 so that global memory is read once.
+template <typename T, typename W>
+__global__ void rms_norm_kernel(T* __restrict__ residual, const T* __restrict__ delta,
+                                const W* __restrict__ weight, T* __restrict__ out, int width,
+                                float eps) {
+  extern __shared__ float row_cache[];
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * width;
+  float partial = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = to_float(residual[base + i]);
+    if (delta != nullptr) {
+      T stored = from_float<T>(v + to_float(delta[base + i]));
+      residual[base + i] = stored;
+      v = to_float(stored);
+    }
+    row_cache[i] = v;
+    partial += v * v;
+  }
+  const float total = block_sum(partial, scratch);
+  const float scale = rsqrtf(total / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    out[base + i] = from_float<T>(to_float(weight[i]) * (row_cache[i] * scale));
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// in: [rows, 2*inner] holding gate in the first half of each row and up in the second.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner,
+                              size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / inner;
+    const int col = (int)(idx - row * inner);
+    const float g = to_float(gate_up[row * 2 * inner + col]);
+    const float u = to_float(gate_up[row * 2 * inner + inner + col]);
+    out[idx] = from_float<T>((g / (1.f + expf(-g))) * u);
+  }
+}
+
+// ---------------------------------------------------------------- RoPE + paged K/V write
+// qkv: [tokens, (heads + 2*kv_heads) * head_dim] = q heads, then k heads, then v heads.
+// Writes rotated q to q_out [tokens, heads*head_dim]; rotated k and raw v to the page pools
+// [pages, kv_heads, page_size, head_dim] at slot = page * page_size + offset (slot < 0: the
+// token is padding, nothing is stored).  angle = position * inv_freq[i] in float32; element i
+// pairs with element i + head_dim/2.
+template <typename T>
+__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const float* __restrict__ inv_freq,
+                                     const long long* __restrict__ slots, T* __restrict__ q_out,
+                                     T* __restrict__ k_pool, T* __restrict__ v_pool, int heads,
+                                     int kv_heads, int head_dim, int page_size, int write_kv) {
+  const int token = blockIdx.x;
+  const int half = head_dim >> 1;
+  const int row_width = (heads + 2 * kv_heads) * head_dim;
+  const T* row = qkv + (size_t)token * row_width;
+  const float position = (float)positions[token];
+  const long long slot = slots[token];
+  const long long page = slot >= 0 ? slot / page_size : 0;
+  const int offset = slot >= 0 ? (int)(slot - page * page_size) : 0;
+  const bool store = write_kv != 0 && slot >= 0;
+
+  const int rotated_heads = heads + kv_heads;
+  for (int item = threadIdx.x; item < rotated_heads * half; item += blockDim.x) {
+    const int head = item / half, i = item - head * half;
+    float sine, cosine;
+    sincosf(position * inv_freq[i], &sine, &cosine);
+    const float x1 = to_float(row[head * head_dim + i]);
+    const float x2 = to_float(row[head * head_dim + i + half]);
+    const float y1 = x1 * cosine - x2 * sine;
+    const float y2 = x2 * cosine + x1 * sine;
+    if (head < heads) {
+      T* dst = q_out + ((size_t)token * heads + head) * head_dim;
+      dst[i] = from_float<T>(y1);
+      dst[i + half] = from_float<T>(y2);
+    } else if (store) {
+      const int kv_head = head - heads;
+      T* dst = k_pool + (((size_t)page * kv_heads + kv_head) * page_size + offset) * head_dim;
+      dst[i] = from_float<T>(y1);
+      dst[i + half] = from_float<T>(y2);
+    }
+  }
+  if (store) {
+    const T* v_row = row + (size_t)(heads + kv_heads) * head_dim;
+    for (int item = threadIdx.x; item < kv_heads * head_dim; item += blockDim.x) {
+      const int kv_head = item / head_dim, i = item - kv_head * head_dim;
+      v_pool[(((size_t)page * kv_heads + kv_head) * page_size + offset) * head_dim + i] = v_row[item];
+    }
+  }
+}
+
+template <typename T>
+int rope_kv_write_launch(const void* qkv, const int* positions, const float* inv_freq,
+                         const long long* slots, void* q_out, void* k_pool, void* v_pool,
+                         int tokens, int heads, int kv_heads, int head_dim, int page_size,
+                         int write_kv, cudaStream_t stream) {
+  int work = (heads + kv_heads) * (head_dim / 2);
+  int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+  rope_kv_write_kernel<T><<<tokens, threads, 0, stream>>>(
+      (const T*)qkv, positions, inv_freq, slots, (T*)q_out, (T*)k_pool, (T*)v_pool, heads,
+      kv_heads, head_dim, page_size, write_kv);
+  return launch_status();
+}
+
+static int row_threads(int width) {
+  if (width >= 2048) return 512;
+  if (width >= 512) return 256;
+  if (width >= 128) return 128;
+  return 64;
+}
+
+}  // namespace mlr
+
+using namespace mlr;
+
+MLR_EXPORT int mlr_embedding(const int* ids, const void* table, void* out, int rows, int width,
+                             int vocab, int dtype, cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || width <= 0 || vocab <= 0) return MLR_BAD_SIZE;
+  const int threads = row_threads(width);
+  if (dtype == MLR_F32)
+    embedding_kernel<float><<<rows, threads, 0, stream>>>(ids, (const float*)table, (float*)out, width, vocab);
+  else if (dtype == MLR_BF16)
+    embedding_kernel<bf16><<<rows, threads, 0, stream>>>(ids, (const bf16*)table, (bf16*)out, width, vocab);
+  else
+    return MLR_BAD_DTYPE;
+  return launch_status();
+}
+
+MLR_EXPORT int mlr_gather_rows(const void* x, const int* rows, void* out, int count, int width,
+                               int dtype, cudaStream_t stream) {
+  if (count == 0) return MLR_OK;
+  if (count < 0 || width <= 0) return MLR_BAD_SIZE;
+  const int threads = row_threads(width);
+  if (dtype == MLR_F32)
+    gather_rows_kernel<float><<<count, threads, 0, stream>>>((const float*)x, rows, (float*)out, width);
+  else if (dtype == MLR_BF16)
+    gather_rows_kernel<bf16><<<count, threads, 0, stream>>>((const bf16*)x, rows, (bf16*)out, width);
+  else
+    return MLR_BAD_DTYPE;
+  return launch_status();
+}
+
+template <typename T, typename W>
+static int rms_norm_launch(void* residual, const void* delta, const void* weight, void* out, int rows,
+                           int width, float eps, cudaStream_t stream) {
+  const size_t shared = (size_t)width * sizeof(float);
+  if (shared > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(rms_norm_kernel<T, W>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return (int)err;
+  }
+  rms_norm_kernel<T, W><<<rows, row_threads(width), shared, stream>>>(
+      (T*)residual, (const T*)delta, (const W*)weight, (T*)out, width, eps);
+  return launch_status();
+}
+
+// residual is updated in place when delta != nullptr; out may alias neither.  The weight may be
+// stored in float32 while the rows are bfloat16 (a checkpoint's 32-bit tensor stays 32-bit).
+MLR_EXPORT int mlr_rms_norm(void* residual, const void* delta, const void* weight, void* out,
+                            int rows, int width, float eps, int dtype, int weight_dtype,
+                            cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || width <= 0) return MLR_BAD_SIZE;
+  if ((size_t)width * sizeof(float) > 200 * 1024) return MLR_TOO_LARGE;
+  if (dtype == MLR_F32 && weight_dtype == MLR_F32)
+    return rms_norm_launch<float, float>(residual, delta, weight, out, rows, width, eps, stream);
+  if (dtype == MLR_BF16 && weight_dtype == MLR_BF16)
+    return rms_norm_launch<bf16, bf16>(residual, delta, weight, out, rows, width, eps, stream);
+  if (dtype == MLR_BF16 && weight_dtype == MLR_F32)
+    return rms_norm_launch<bf16, float>(residual, delta, weight, out, rows, width, eps, stream);
+  return MLR_BAD_DTYPE;
+}
+
+MLR_EXPORT int mlr_swiglu(const void* gate_up, void* out, long long rows, int inner, int dtype,
+                          cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || inner <= 0) return MLR_BAD_SIZE;
+  const size_t total = (size_t)rows * inner;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == MLR_F32)
+    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inner, total);
+  else if (dtype == MLR_BF16)
+    swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inner, total);
+  else
+    return MLR_BAD_DTYPE;
+  return launch_status();
+}
+
+MLR_EXPORT int mlr_rope_kv_write(const void* qkv, const int* positions, const float* inv_freq,
+                                 const long long* slots, void* q_out, void* k_pool, void* v_pool,
+                                 int tokens, int heads, int kv_heads, int head_dim, int page_size,
+                                 int write_kv, int dtype, cudaStream_t stream) {
+  if (tokens == 0) return MLR_OK;
+  if (tokens < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || page_size <= 0)
+    return MLR_BAD_SIZE;
+  if (dtype == MLR_F32)
+    return rope_kv_write_launch<float>(qkv, positions, inv_freq, slots, q_out, k_pool, v_pool, tokens,
+                                       heads, kv_heads, head_dim, page_size, write_kv, stream);
+  if (dtype == MLR_BF16)
+    return rope_kv_write_launch<bf16>(qkv, positions, inv_freq, slots, q_out, k_pool, v_pool, tokens,
+                                      heads, kv_heads, head_dim, page_size, write_kv, stream);
+  return MLR_BAD_DTYPE;
+}

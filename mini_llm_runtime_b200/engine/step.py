@@ -1,0 +1,266 @@
+"""The step function: one ragged batch of (request, its next tokens) through the model.
+
+A step brings, for every request in it, the tokens that follow what the cache already holds for
+that request: a portion of a prompt of any length, or one decoded token.  All of them run as one
+batch, reading earlier tokens from the cache only, and the logits at the wanted places come back.
+
+The reference needs two model calls for this, a packed prefill that only works on empty caches
+and a batched one-token decode (src/mini_llm_runtime/engine.py:186-248,
+qwen_model_runner.py:296-376,447-508); row order here follows the order of the entries, as the
+reference's result rows follow scheduler item order (engine.py:256-261).  The step is atomic like
+the reference's: pages are taken for all requests or none, and a failure anywhere leaves every
+request's visible length unchanged (paged_batch.py:89-114, engine.py:249-254).
+
+Host-side work per step is one packed metadata buffer (token ids, positions, segment table,
+attention tiles, per-group slot mapping and block tables) written into pinned memory and sent
+with a single host-to-device copy.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.manager import CacheGroup, CacheManager, RequestCache
+from ..models.decoder import DecoderModel
+from ..ops.cuda_ops import AttentionBatch
+
+ROWS_PER_TILE = 16  # rows one CTA of the generic attention kernel handles
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places whose logits are wanted."""
+
+    request_id: str
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class Segment:
+    request_id: str
+    slot: int
+    row_start: int
+    length: int
+    position_start: int
+
+
+@dataclass
+class CacheView:
+    """What a mixer sees of its cache entry during one step."""
+
+    entry: int
+    k_pool: torch.Tensor | None = None     # [pages, kv_heads, page_size, head_dim]
+    v_pool: torch.Tensor | None = None
+    slots: torch.Tensor | None = None      # int64 [rows]: where each row's k and v go
+    batch: AttentionBatch | None = None
+    page_size: int = 0
+    window: int | None = None
+    state: torch.Tensor | None = None      # [max_requests, ...] for a fixed-size-state entry
+
+
+@dataclass
+class StepContext:
+    """Everything the parts may read about the running step."""
+
+    ops: object
+    num_rows: int
+    num_wanted: int
+    segments: list[Segment]
+    token_ids: torch.Tensor          # int32 [rows]
+    positions: torch.Tensor          # int32 [rows]
+    wanted_rows: torch.Tensor        # int32 [wanted]
+    segment_slots: torch.Tensor      # int32 [segments]: each request's state slot
+    views: dict[int, CacheView] = field(default_factory=dict)
+
+    def cache_view(self, entry: int) -> CacheView:
+        return self.views[entry]
+
+
+class _PinnedRing:
+    """A few pinned staging buffers used in turn; a buffer is reused only after the copy that
+    read it has finished."""
+
+    def __init__(self, device: torch.device, depth: int = 4) -> None:
+        self.device = device
+        self.depth = depth
+        self.buffers: list[torch.Tensor | None] = [None] * depth
+        self.events: list[torch.cuda.Event | None] = [None] * depth
+        self.cursor = 0
+        self.pinned = device.type == "cuda"
+
+    def stage(self, nbytes: int) -> tuple[torch.Tensor, int]:
+        index = self.cursor
+        self.cursor = (self.cursor + 1) % self.depth
+        if self.events[index] is not None:
+            self.events[index].synchronize()
+        buffer = self.buffers[index]
+        if buffer is None or buffer.numel() < nbytes:
+            size = max(1 << 16, 1 << (nbytes - 1).bit_length())
+            buffer = torch.empty(size, dtype=torch.uint8, pin_memory=self.pinned)
+            self.buffers[index] = buffer
+        return buffer, index
+
+    def sent(self, index: int) -> None:
+        if self.pinned:
+            event = self.events[index] or torch.cuda.Event()
+            event.record()
+            self.events[index] = event
+
+
+class _Packer:
+    """Lays numpy arrays out in one byte buffer at 16-byte aligned offsets."""
+
+    def __init__(self) -> None:
+        self.items: list[tuple[str, np.ndarray, int]] = []
+        self.size = 0
+
+    def add(self, name: str, array: np.ndarray) -> None:
+        array = np.ascontiguousarray(array)
+        self.items.append((name, array, self.size))
+        self.size += (array.nbytes + 15) // 16 * 16
+
+
+_TORCH_OF = {np.dtype(np.int32): torch.int32, np.dtype(np.int64): torch.int64,
+             np.dtype(np.float32): torch.float32}
+
+
+class ModelRunner:
+    """Owns the model and its cache; ``step`` is the only way tokens reach the model."""
+
+    def __init__(self, model: DecoderModel, cache: CacheManager) -> None:
+        if model.device is None:
+            raise ValueError("load the model's weights before building a runner")
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.vocab_size = model.spec.vocab_size
+        self.max_positions = model.spec.max_positions
+        self._ring = _PinnedRing(self.device)
+        self._device_meta: torch.Tensor | None = None
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ metadata
+    def _upload(self, packer: _Packer) -> dict[str, torch.Tensor]:
+        nbytes = max(packer.size, 16)
+        staging, index = self._ring.stage(nbytes)
+        host = staging.numpy()
+        for _, array, offset in packer.items:
+            host[offset:offset + array.nbytes] = array.view(np.uint8).reshape(-1)
+        if self._device_meta is None or self._device_meta.numel() < nbytes:
+            size = max(1 << 16, 1 << (nbytes - 1).bit_length())
+            self._device_meta = torch.empty(size, dtype=torch.uint8, device=self.device)
+        device_buffer = self._device_meta
+        device_buffer[:nbytes].copy_(staging[:nbytes], non_blocking=True)
+        self._ring.sent(index)
+        out = {}
+        for name, array, offset in packer.items:
+            flat = device_buffer[offset:offset + array.nbytes].view(_TORCH_OF[array.dtype])
+            out[name] = flat.view(array.shape)
+        return out
+
+    def _build_context(self, entries: Sequence[StepEntry], requests: list[RequestCache]) -> StepContext:
+        cache = self.cache
+        lengths = np.array([len(e.tokens) for e in entries], dtype=np.int32)
+        row_start = np.zeros(len(entries), dtype=np.int32)
+        np.cumsum(lengths[:-1], out=row_start[1:])
+        position_start = np.array([r.pending[0] for r in requests], dtype=np.int32)
+        total = int(lengths.sum())
+
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        segment_of_row = np.repeat(np.arange(len(entries), dtype=np.int32), lengths)
+        positions = (np.arange(total, dtype=np.int32) - row_start[segment_of_row]
+                     + position_start[segment_of_row]).astype(np.int32)
+        wanted = [row_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
+        wanted_rows = np.concatenate(wanted).astype(np.int32) if wanted else np.zeros(0, dtype=np.int32)
+
+        tiles_per_segment = (lengths + ROWS_PER_TILE - 1) // ROWS_PER_TILE
+        tile_seg = np.repeat(np.arange(len(entries), dtype=np.int32), tiles_per_segment)
+        tile_first = np.zeros(len(entries), dtype=np.int32)
+        np.cumsum(tiles_per_segment[:-1], out=tile_first[1:])
+        tile_row0 = ((np.arange(len(tile_seg), dtype=np.int32) - tile_first[tile_seg]) * ROWS_PER_TILE).astype(np.int32)
+
+        slots = np.array([r.slot for r in requests], dtype=np.int32)
+        kv_end = position_start + lengths
+        table_width = max(1, int(-(-int(kv_end.max()) // cache.page_size)))
+
+        packer = _Packer()
+        packer.add("token_ids", token_ids)
+        packer.add("positions", positions)
+        packer.add("wanted_rows", wanted_rows)
+        packer.add("seg_q_start", row_start)
+        packer.add("seg_q_len", lengths)
+        packer.add("seg_pos0", position_start)
+        packer.add("seg_slots", slots)
+        packer.add("tile_seg", tile_seg)
+        packer.add("tile_row0", tile_row0)
+        for group in cache.groups:
+            rows_slots = np.concatenate([
+                cache.slot_mapping(group, request, int(position_start[i]), int(lengths[i]))
+                for i, request in enumerate(requests)])
+            packer.add(f"slots{group.index}", rows_slots.astype(np.int64))
+            packer.add(f"table{group.index}", group.table[slots, :table_width])
+        dev = self._upload(packer)
+
+        segments = [Segment(e.request_id, int(slots[i]), int(row_start[i]), int(lengths[i]),
+                            int(position_start[i])) for i, e in enumerate(entries)]
+        ctx = StepContext(ops=ops.current(), num_rows=total, num_wanted=int(wanted_rows.shape[0]),
+                          segments=segments, token_ids=dev["token_ids"], positions=dev["positions"],
+                          wanted_rows=dev["wanted_rows"], segment_slots=dev["seg_slots"])
+        batches = {}
+        for group in cache.groups:
+            batches[group.index] = AttentionBatch(
+                seg_q_start=dev["seg_q_start"], seg_q_len=dev["seg_q_len"], seg_pos0=dev["seg_pos0"],
+                block_table=dev[f"table{group.index}"], tile_seg=dev["tile_seg"], tile_row0=dev["tile_row0"],
+                num_segments=len(entries), num_tiles=int(tile_seg.shape[0]),
+                max_q_len=int(lengths.max()), max_kv_len=int(kv_end.max()))
+        for entry, need in enumerate(cache.needs):
+            if entry in cache.entry_group:
+                k_pool, v_pool, group = cache.entry_pools(entry)
+                ctx.views[entry] = CacheView(entry, k_pool, v_pool, dev[f"slots{group.index}"],
+                                             batches[group.index], cache.page_size, group.window)
+            else:
+                ctx.views[entry] = CacheView(entry, state=cache.state.get(entry))
+        return ctx
+
+    # ------------------------------------------------------------------ the step
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        for entry in entries:
+            count = len(entry.tokens)
+            if count == 0:
+                raise ValueError(f"request {entry.request_id!r}: a step must bring at least one token")
+            tokens = np.asarray(entry.tokens)
+            if tokens.dtype.kind not in "iu" or tokens.min() < 0 or tokens.max() >= self.vocab_size:
+                raise ValueError(f"request {entry.request_id!r}: token ids must be integers in "
+                                 f"[0, {self.vocab_size})")
+            for place in entry.want:
+                if not 0 <= int(place) < count:
+                    raise ValueError(f"request {entry.request_id!r}: wanted place {place} is outside "
+                                     f"its {count} tokens")
+            held = self.cache.get(entry.request_id).committed
+            if held + count > self.max_positions:
+                raise ValueError(f"request {entry.request_id!r} would reach {held + count} positions, "
+                                 f"the model allows {self.max_positions}")
+
+    @torch.inference_mode()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries as one batch.  Returns float32 logits [wanted places, vocab] on the
+        device, in the order of the entries and of each entry's ``want``."""
+        self._validate(entries)
+        requests = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
+        try:
+            ctx = self._build_context(entries, requests)
+            logits = self.model.forward(ctx)
+        except BaseException:
+            self.cache.abort_step()
+            raise
+        self.cache.commit_step()
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,244 @@
+"""Python face of the hand-written sm_100a kernels.
+
+Each method checks its arguments (device, dtype, contiguity, shapes), allocates the output with
+torch, and calls one ``extern "C"`` entry point on torch's current CUDA stream.  There is no CPU
+path and no other backend: tensors that are not on a CUDA device, a library that cannot be
+built, or a size a kernel refuses raise an exception.
+
+The reference reaches its one kernel through a similar checked wrapper
+(src/mini_llm_runtime/paged_attention_cuda.py:10-73); everything else there is a torch call.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import build
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_STATUS_TEXT = {
+    -1: "unsupported dtype",
+    -2: "a size is zero, negative or inconsistent",
+    -3: "a pointer or stride is not aligned as the kernel needs",
+    -4: "a size exceeds what this kernel supports",
+    -5: "the kernel reported an error through its device flag",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: refused ({_STATUS_TEXT.get(status, status)})")
+    raise KernelError(f"{what}: the launch failed with cudaError_t {status}")
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}") from None
+
+
+def _need(tensor: torch.Tensor, name: str, dtype: torch.dtype | None = None, dims: int | None = None) -> None:
+    if not isinstance(tensor, torch.Tensor) or not tensor.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor; this engine has no CPU path")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    if dims is not None and tensor.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, got shape {tuple(tensor.shape)}")
+
+
+def _ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+@dataclass
+class AttentionBatch:
+    """Device-side description of one step's ragged batch for one cache group.
+
+    ``seg_*`` have one entry per request in the step; ``tile_*`` cut every segment into tiles
+    of at most 16 rows (the unit one CTA of the generic kernel works on).  ``block_table`` is
+    int32 [segments, table_width] with -1 where the request holds no page.
+    """
+
+    seg_q_start: torch.Tensor
+    seg_q_len: torch.Tensor
+    seg_pos0: torch.Tensor
+    block_table: torch.Tensor
+    tile_seg: torch.Tensor
+    tile_row0: torch.Tensor
+    num_segments: int
+    num_tiles: int
+    max_q_len: int
+    max_kv_len: int
+
+
+class CudaOps:
+    """The kernels, as methods.  One instance per process is enough."""
+
+    name = "cuda"
+
+    # ------------------------------------------------------------------ elementwise
+    def embedding(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        _need(ids, "ids", torch.int32, 1)
+        _need(table, "table", dims=2)
+        out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
+        lib = build.load_library("elementwise")
+        _check(lib.mlr_embedding(_ptr(ids), _ptr(table), _ptr(out), ids.shape[0], table.shape[1],
+                                 table.shape[0], _code(table.dtype), _stream()), "embedding")
+        return out
+
+    def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        _need(x, "x", dims=2)
+        _need(rows, "rows", torch.int32, 1)
+        out = torch.empty((rows.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+        lib = build.load_library("elementwise")
+        _check(lib.mlr_gather_rows(_ptr(x), _ptr(rows), _ptr(out), rows.shape[0], x.shape[1],
+                                   _code(x.dtype), _stream()), "gather_rows")
+        return out
+
+    def rms_norm(self, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """weight * x * rsqrt(mean(x^2) + eps), row by row."""
+        return self._rms_norm(x, None, weight, eps)
+
+    def add_rms_norm(self, residual: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor,
+                     eps: float) -> torch.Tensor:
+        """residual += delta (in place), then the norm of the new residual."""
+        _need(delta, "delta", residual.dtype, 2)
+        if delta.shape != residual.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} and residual {tuple(residual.shape)} differ")
+        return self._rms_norm(residual, delta, weight, eps)
+
+    def _rms_norm(self, x, delta, weight, eps):
+        _need(x, "x", dims=2)
+        _need(weight, "weight", None, 1)
+        if weight.dtype != x.dtype and weight.dtype != torch.float32:
+            raise KernelError(f"norm weight must be {x.dtype} or float32, got {weight.dtype}")
+        if weight.shape[0] != x.shape[1]:
+            raise KernelError(f"norm weight has {weight.shape[0]} entries, rows have {x.shape[1]}")
+        out = torch.empty_like(x)
+        lib = build.load_library("elementwise")
+        _check(lib.mlr_rms_norm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), x.shape[0], x.shape[1],
+                                ctypes.c_float(eps), _code(x.dtype), _code(weight.dtype), _stream()), "rms_norm")
+        return out
+
+    def swiglu(self, gate_up: torch.Tensor) -> torch.Tensor:
+        """silu(gate) * up for rows laid out as [gate | up]."""
+        _need(gate_up, "gate_up", dims=2)
+        if gate_up.shape[1] % 2 != 0:
+            raise KernelError("gate_up rows must hold gate and up halves of equal width")
+        inner = gate_up.shape[1] // 2
+        out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
+        lib = build.load_library("elementwise")
+        _check(lib.mlr_swiglu(_ptr(gate_up), _ptr(out), ctypes.c_longlong(gate_up.shape[0]), inner,
+                              _code(gate_up.dtype), _stream()), "swiglu")
+        return out
+
+    def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                      slots: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, num_heads: int,
+                      num_kv_heads: int, head_dim: int, write_kv: bool = True) -> torch.Tensor:
+        """Rotate q and k by position (rotate-half pairs, angle = position * inv_freq), return
+        q [tokens, heads*head_dim] and store rotated k and raw v at ``slots`` of the page pools
+        [pages, kv_heads, page_size, head_dim]."""
+        _need(qkv, "qkv", dims=2)
+        _need(positions, "positions", torch.int32, 1)
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        _need(slots, "slots", torch.int64, 1)
+        _need(k_pool, "k_pool", qkv.dtype, 4)
+        _need(v_pool, "v_pool", qkv.dtype, 4)
+        tokens = qkv.shape[0]
+        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+            raise KernelError(f"qkv rows have {qkv.shape[1]} entries, expected "
+                              f"{(num_heads + 2 * num_kv_heads) * head_dim}")
+        if inv_freq.shape[0] != head_dim // 2 or head_dim % 2:
+            raise KernelError("inv_freq must hold head_dim/2 entries and head_dim must be even")
+        if positions.shape[0] != tokens or slots.shape[0] != tokens:
+            raise KernelError("positions and slots need one entry per token")
+        if k_pool.shape != v_pool.shape or k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim:
+            raise KernelError(f"page pools have shape {tuple(k_pool.shape)}, expected "
+                              f"[pages, {num_kv_heads}, page_size, {head_dim}]")
+        q = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        lib = build.load_library("elementwise")
+        _check(lib.mlr_rope_kv_write(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(q),
+                                     _ptr(k_pool), _ptr(v_pool), tokens, num_heads, num_kv_heads,
+                                     head_dim, k_pool.shape[2], int(bool(write_kv)), _code(qkv.dtype),
+                                     _stream()), "rope_kv_write")
+        return q
+
+    # ------------------------------------------------------------------ matrix product
+    def linear(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+               out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """x [M,K] times weight [N,K] transposed, plus bias [N]."""
+        _need(x, "x", dims=2)
+        _need(weight, "weight", x.dtype, 2)
+        if bias is not None:
+            _need(bias, "bias", x.dtype, 1)
+            if bias.shape[0] != weight.shape[0]:
+                raise KernelError("bias length differs from the weight's output rows")
+        if x.shape[1] != weight.shape[1]:
+            raise KernelError(f"x has {x.shape[1]} columns, weight expects {weight.shape[1]}")
+        out_dtype = out_dtype or x.dtype
+        return self._linear_simt(x, weight, bias, out_dtype)
+
+    def _linear_simt(self, x, weight, bias, out_dtype):
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+        lib = build.load_library("linear_simt")
+        _check(lib.mlr_linear_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), x.shape[0],
+                                   weight.shape[0], x.shape[1], _code(x.dtype), _code(out_dtype),
+                                   _stream()), "linear")
+        return out
+
+    # ------------------------------------------------------------------ attention
+    def paged_attention(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                        batch: AttentionBatch, num_heads: int, num_kv_heads: int, head_dim: int,
+                        scale: float, window: int | None) -> torch.Tensor:
+        """Causal attention of every row of the step over its request's cached keys."""
+        _need(q, "q", dims=2)
+        _need(k_pool, "k_pool", q.dtype, 4)
+        _need(v_pool, "v_pool", q.dtype, 4)
+        if q.shape[1] != num_heads * head_dim:
+            raise KernelError(f"q rows have {q.shape[1]} entries, expected {num_heads * head_dim}")
+        if k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim or k_pool.shape != v_pool.shape:
+            raise KernelError(f"page pools have shape {tuple(k_pool.shape)}, expected "
+                              f"[pages, {num_kv_heads}, page_size, {head_dim}]")
+        out = torch.empty_like(q)
+        lib = build.load_library("attention_generic")
+        _check(lib.mlr_attention_generic(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.tile_seg), _ptr(batch.tile_row0),
+            _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
+            batch.block_table.shape[1], batch.num_tiles, num_heads, num_kv_heads, head_dim,
+            k_pool.shape[2], int(window or 0), ctypes.c_float(scale), _code(q.dtype), _stream()),
+            "paged_attention")
+        return out
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,
+               counters: torch.Tensor) -> torch.Tensor:
+        """One token per row of float32 logits: argmax where temperature <= 0, else a draw from
+        softmax(logits / temperature) with the uniform number of (seed, counter)."""
+        _need(logits, "logits", torch.float32, 2)
+        _need(temperatures, "temperatures", torch.float32, 1)
+        _need(seeds, "seeds", torch.int64, 1)
+        _need(counters, "counters", torch.int64, 1)
+        rows = logits.shape[0]
+        if not (temperatures.shape[0] == seeds.shape[0] == counters.shape[0] == rows):
+            raise KernelError("temperatures, seeds and counters need one entry per logits row")
+        tokens = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+        lib = build.load_library("sampling")
+        _check(lib.mlr_sample(_ptr(logits), _ptr(temperatures), _ptr(seeds), _ptr(counters), _ptr(tokens),
+                              rows, logits.shape[1], _stream()), "sample")
+        return tokens

@@ -1,0 +1,82 @@
+"""Grouped-query causal self-attention over the paged cache.
+
+q = x Wq^T + bq, k = x Wk^T + bk, v = x Wv^T + bv (one fused product on the concatenated
+weights), position encoding on q and k, k and v stored to the cache, every row attends to its
+request's cached keys (optionally only the last ``window`` of them) with query head h reading kv
+head h // (heads / kv_heads), then o = attn Wo^T.  Reference: the ``_attention`` function of
+src/mini_llm_runtime/qwen_model_runner.py:75-183 and the decode kernel
+csrc/paged_attention_cuda.cu:25-106; the reference keeps q/k/v as three products and has no window.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import KVCacheNeed, Mixer, TensorSpec, build_part, register_part
+
+
+class GQAAttention(Mixer):
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        a = self.args
+        self.hidden_size = int(a["hidden_size"])
+        self.num_heads = int(a["num_heads"])
+        self.num_kv_heads = int(a["num_kv_heads"])
+        self.head_dim = int(a["head_dim"])
+        self.qkv_bias = bool(a.get("qkv_bias", False))
+        self.out_bias = bool(a.get("out_bias", False))
+        self.window = a.get("window")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be divisible by num_kv_heads")
+        if self.window is not None and int(self.window) <= 0:
+            raise ValueError("an attention window must be positive")
+        self.scale = float(self.head_dim) ** -0.5
+        self.position = build_part("position", a["position"], compute_dtype)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    def cache_need(self):
+        return KVCacheNeed(self.num_kv_heads, self.head_dim, None if self.window is None else int(self.window))
+
+    def tensors(self):
+        q_rows = self.num_heads * self.head_dim
+        kv_rows = self.num_kv_heads * self.head_dim
+        p = self.prefix
+        out = {
+            p + "q_proj.weight": TensorSpec((q_rows, self.hidden_size)),
+            p + "k_proj.weight": TensorSpec((kv_rows, self.hidden_size)),
+            p + "v_proj.weight": TensorSpec((kv_rows, self.hidden_size)),
+            p + "o_proj.weight": TensorSpec((self.hidden_size, q_rows)),
+        }
+        if self.qkv_bias:
+            out[p + "q_proj.bias"] = TensorSpec((q_rows,), init="bias")
+            out[p + "k_proj.bias"] = TensorSpec((kv_rows,), init="bias")
+            out[p + "v_proj.bias"] = TensorSpec((kv_rows,), init="bias")
+        if self.out_bias:
+            out[p + "o_proj.bias"] = TensorSpec((self.hidden_size,), init="bias")
+        return out
+
+    def load(self, tensors, device):
+        p = self.prefix
+        # q, k and v rows stacked so that one product yields [q heads | k heads | v heads].
+        self.w_qkv = self._to_compute(
+            torch.cat([tensors[p + f"{n}_proj.weight"] for n in "qkv"], dim=0), device)
+        if self.qkv_bias:
+            self.b_qkv = self._to_compute(
+                torch.cat([tensors[p + f"{n}_proj.bias"] for n in "qkv"], dim=0), device)
+        self.w_o = self._to_compute(tensors[p + "o_proj.weight"], device)
+        if self.out_bias:
+            self.b_o = self._to_compute(tensors[p + "o_proj.bias"], device)
+        self.position.load({}, device)
+
+    def forward(self, x, ctx, view, writes_cache):
+        k = ops.current()
+        qkv = k.linear(x, self.w_qkv, self.b_qkv)
+        q = self.position.rotate_and_store(qkv, ctx, view, self.num_heads, self.num_kv_heads,
+                                           self.head_dim, writes_cache)
+        mixed = k.paged_attention(q, view.k_pool, view.v_pool, view.batch, self.num_heads,
+                                  self.num_kv_heads, self.head_dim, self.scale, self.window)
+        return k.linear(mixed, self.w_o, self.b_o)
+
+
+register_part("mixer", "gqa_attention", GQAAttention)

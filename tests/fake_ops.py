@@ -1,0 +1,105 @@
+"""Stand-in for the CUDA kernels, in plain torch on the CPU, with the kernels' exact calling
+contracts.  Tests install it with ``ops.use(FakeOps())`` to exercise everything above the kernels
+(parts, model, cache manager, step function, scheduler, replay program) on a machine without a
+GPU, the way the reference's own tests replace its kernel by a Python oracle
+(tests/test_engine.py:82-101 there).  It is test equipment only: the package never selects it, and
+the GPU tests do not use it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+class FakeOps:
+    name = "fake-cpu"
+
+    def embedding(self, ids, table):
+        return table[ids.long()].clone()
+
+    def gather_rows(self, x, rows):
+        return x[rows.long()].clone()
+
+    def rms_norm(self, x, weight, eps):
+        x32 = x.float()
+        out = weight.float() * (x32 * torch.rsqrt((x32 * x32).mean(-1, keepdim=True) + eps))
+        return out.to(x.dtype)
+
+    def add_rms_norm(self, residual, delta, weight, eps):
+        residual.copy_((residual.float() + delta.float()).to(residual.dtype))
+        return self.rms_norm(residual, weight, eps)
+
+    def swiglu(self, gate_up):
+        inner = gate_up.shape[1] // 2
+        gate, up = gate_up[:, :inner].float(), gate_up[:, inner:].float()
+        return (torch.nn.functional.silu(gate) * up).to(gate_up.dtype)
+
+    def linear(self, x, weight, bias=None, out_dtype=None):
+        out = x.float() @ weight.float().T
+        if bias is not None:
+            out = out + bias.float()
+        return out.to(out_dtype or x.dtype)
+
+    def rope_kv_write(self, qkv, positions, inv_freq, slots, k_pool, v_pool, num_heads, num_kv_heads,
+                      head_dim, write_kv=True):
+        tokens = qkv.shape[0]
+        page_size = k_pool.shape[2]
+        x = qkv.float().view(tokens, num_heads + 2 * num_kv_heads, head_dim)
+        angles = positions.float()[:, None] * inv_freq[None, :]
+        cos = torch.cat((angles, angles), -1).cos()[:, None, :]
+        sin = torch.cat((angles, angles), -1).sin()[:, None, :]
+        half = head_dim // 2
+
+        def rotate(t):
+            return t * cos + torch.cat((-t[..., half:], t[..., :half]), -1) * sin
+
+        q = rotate(x[:, :num_heads])
+        k = rotate(x[:, num_heads:num_heads + num_kv_heads])
+        v = x[:, num_heads + num_kv_heads:]
+        if write_kv:
+            for t in range(tokens):
+                slot = int(slots[t])
+                if slot < 0:
+                    continue
+                page, offset = divmod(slot, page_size)
+                k_pool[page, :, offset, :] = k[t].to(k_pool.dtype)
+                v_pool[page, :, offset, :] = v[t].to(v_pool.dtype)
+        return q.reshape(tokens, num_heads * head_dim).to(qkv.dtype)
+
+    def paged_attention(self, q, k_pool, v_pool, batch, num_heads, num_kv_heads, head_dim, scale, window):
+        page_size = k_pool.shape[2]
+        group = num_heads // num_kv_heads
+        out = torch.empty_like(q)
+        q3 = q.float().view(-1, num_heads, head_dim)
+        for seg in range(batch.num_segments):
+            start, length, pos0 = (int(batch.seg_q_start[seg]), int(batch.seg_q_len[seg]),
+                                   int(batch.seg_pos0[seg]))
+            table = batch.block_table[seg]
+            for r in range(length):
+                p = pos0 + r
+                low = max(0, p - window + 1) if window else 0
+                keys = torch.arange(low, p + 1)
+                pages = table[(keys // page_size).long()].long()
+                assert (pages >= 0).all(), "attention reads a page the request does not hold"
+                offsets = (keys % page_size).long()
+                k = k_pool[pages, :, offsets, :].float()   # [keys, kv_heads, D]
+                v = v_pool[pages, :, offsets, :].float()
+                k = k.repeat_interleave(group, dim=1)
+                v = v.repeat_interleave(group, dim=1)
+                scores = torch.einsum("hd,khd->hk", q3[start + r], k) * scale
+                probabilities = torch.softmax(scores, dim=-1)
+                out[start + r] = torch.einsum("hk,khd->hd", probabilities, v).reshape(-1).to(q.dtype)
+        return out
+
+    def sample(self, logits, temperatures, seeds, counters):
+        from plain_qwen2 import temperature_sample, uniform_from_seed
+
+        tokens = torch.empty(logits.shape[0], dtype=torch.int32)
+        for row in range(logits.shape[0]):
+            temperature = float(temperatures[row])
+            if temperature <= 0:
+                tokens[row] = int(torch.argmax(logits[row]))
+            else:
+                u = uniform_from_seed(int(seeds[row]) & ((1 << 64) - 1), int(counters[row]))
+                tokens[row] = temperature_sample(logits[row], temperature, u)[0]
+        return tokens

@@ -1,0 +1,278 @@
+"""Each CUDA kernel alone against a plain float32 torch restatement of the same operation
+(``fake_ops.FakeOps`` on the CPU), at sizes other than the tiny engines': widths and vocabularies
+that are no power of two, head sizes in steps of 16, odd head counts and page sizes.  Where random
+data would hide a fault the inputs are constructed so that it shows (one far key that dominates,
+the edge of a window, the last slot of a page)."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+from fake_ops import FakeOps
+from harness import assert_close
+from mini_llm_runtime_b200 import ops
+from mini_llm_runtime_b200.ops.cuda_ops import AttentionBatch
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+FAKE = FakeOps()
+
+
+def cuda():
+    return ops.current()
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    generator = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=generator) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,width", [(1000, 100), (77, 896), (5, 3)])
+def test_embedding(dtype, vocab, width):
+    table = rnd((vocab, width), dtype, 1)
+    ids = torch.randint(0, vocab, (37,), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
+    got = cuda().embedding(ids.to(DEVICE), table.to(DEVICE))
+    assert torch.equal(got.cpu(), FAKE.embedding(ids, table))
+    rows = torch.tensor([36, 0, 5, 5], dtype=torch.int32)
+    assert torch.equal(cuda().gather_rows(got, rows.to(DEVICE)).cpu(), got.cpu()[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,eps", [(100, 1e-6), (896, 1e-5), (5120, 1e-6), (7, 1e-3)])
+def test_rms_norm_and_fused_add(dtype, width, eps):
+    x = rnd((9, width), dtype, 3, 2.0)
+    delta = rnd((9, width), dtype, 4, 0.5)
+    weight = (1 + rnd((width,), torch.float32, 5, 0.1)).to(dtype)
+    got = cuda().rms_norm(x.to(DEVICE), weight.to(DEVICE), eps)
+    assert_close(got, plain.rms_norm(x, weight, eps), dtype, "rms_norm")
+    residual = x.clone().to(DEVICE)
+    got = cuda().add_rms_norm(residual, delta.to(DEVICE), weight.to(DEVICE), eps)
+    summed = (x.float() + delta.float()).to(dtype)
+    assert torch.equal(residual.cpu(), summed), "the residual must hold the once-rounded sum"
+    assert_close(got, plain.rms_norm(summed, weight, eps), dtype, "add_rms_norm")
+
+
+def test_rms_norm_keeps_a_float32_weight_with_bfloat16_rows():
+    x = rnd((5, 200), torch.bfloat16, 6)
+    weight = 1 + rnd((200,), torch.float32, 7, 0.1)
+    got = cuda().rms_norm(x.to(DEVICE), weight.to(DEVICE), 1e-6)
+    assert_close(got, plain.rms_norm(x, weight, 1e-6), torch.bfloat16, "rms_norm f32 weight")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    gate_up = rnd((13, 2 * 203), dtype, 8, 3.0)
+    got = cuda().swiglu(gate_up.to(DEVICE))
+    assert_close(got, FAKE.swiglu(gate_up.float()), dtype, "swiglu")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 50, 17), (7, 130, 96), (33, 64, 300), (200, 203, 129), (16, 1, 1)])
+def test_linear(dtype, m, n, k):
+    x = rnd((m, k), dtype, 9)
+    w = rnd((n, k), dtype, 10, 0.2)
+    b = rnd((n,), dtype, 11)
+    want = x.double() @ w.double().T + b.double()
+    got = cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE))
+    assert_close(got, want, dtype, "linear+bias")
+    got32 = cuda().linear(x.to(DEVICE), w.to(DEVICE), None, out_dtype=torch.float32)
+    assert got32.dtype == torch.float32
+    assert_close(got32, x.double() @ w.double().T, torch.float32 if dtype == torch.float32 else dtype, "linear f32 out")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_rows_do_not_depend_on_the_batch(dtype):
+    x = rnd((70, 150), dtype, 12).to(DEVICE)
+    w = rnd((90, 150), dtype, 13, 0.2).to(DEVICE)
+    whole = cuda().linear(x, w)
+    for start, stop in [(0, 1), (5, 22), (69, 70), (16, 70)]:
+        assert torch.equal(cuda().linear(x[start:stop].contiguous(), w), whole[start:stop])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(5, 1, 16, 4), (6, 3, 48, 16), (4, 4, 128, 8), (2, 1, 256, 3)])
+def test_rope_and_cache_write(dtype, heads, kv_heads, head_dim, page):
+    tokens, pages = 11, 9
+    theta = 1000000.0
+    qkv = rnd((tokens, (heads + 2 * kv_heads) * head_dim), dtype, 14)
+    positions = torch.tensor([0, 1, 2, 3, 500, 4095, 7, 31999, 8, 9, 10], dtype=torch.int32)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    # last slot of a page, first slot of a page, one padding row (-1), scattered pages
+    slots = torch.tensor([page - 1, page, -1, 5 * page + 1, 0, 8 * page + page - 1, 2 * page, 3 * page + 1,
+                          4 * page, 6 * page, 7 * page], dtype=torch.int64)
+    k_ref = torch.full((pages, kv_heads, page, head_dim), 7.0).to(dtype)
+    v_ref = torch.full((pages, kv_heads, page, head_dim), -7.0).to(dtype)
+    k_dev, v_dev = k_ref.clone().to(DEVICE), v_ref.clone().to(DEVICE)
+    q_ref = FAKE.rope_kv_write(qkv.float(), positions, inv_freq, slots, k_ref, v_ref, heads, kv_heads, head_dim)
+    q_dev = cuda().rope_kv_write(qkv.to(DEVICE), positions.to(DEVICE), inv_freq.to(DEVICE), slots.to(DEVICE),
+                                 k_dev, v_dev, heads, kv_heads, head_dim)
+    assert_close(q_dev, q_ref, dtype, "rotated q")
+    assert_close(k_dev.reshape(pages, -1), k_ref.reshape(pages, -1), dtype, "k pages (untouched slots included)")
+    assert torch.equal(v_dev.cpu(), v_ref), "v is copied unrotated and bit-exact"
+    # write_kv=False leaves the pages alone
+    k_before = k_dev.clone()
+    cuda().rope_kv_write(qkv.to(DEVICE), positions.to(DEVICE), inv_freq.to(DEVICE), slots.to(DEVICE),
+                         k_dev, v_dev, heads, kv_heads, head_dim, write_kv=False)
+    assert torch.equal(k_dev, k_before)
+
+
+def make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, seed, pages_total=None):
+    """segments: list of (pos0, q_len).  Pages are handed out in a scrambled order; every slot
+    that no request owns is poisoned with NaN so that a stray read shows."""
+    generator = torch.Generator().manual_seed(seed)
+    need = [-(-(pos0 + q_len) // page) for pos0, q_len in segments]
+    pages_total = pages_total or sum(need) + 3
+    order = torch.randperm(pages_total, generator=generator).tolist()
+    width = max(need)
+    table = torch.full((len(segments), width), -1, dtype=torch.int32)
+    k_pool = torch.full((pages_total, kv_heads, page, head_dim), float("nan"))
+    v_pool = torch.full((pages_total, kv_heads, page, head_dim), float("nan"))
+    cursor = 0
+    for s, (pos0, q_len) in enumerate(segments):
+        for logical in range(need[s]):
+            table[s, logical] = order[cursor]
+            cursor += 1
+        for t in range(pos0 + q_len):
+            pg, off = table[s, t // page], t % page
+            k_pool[pg, :, off] = torch.randn(kv_heads, head_dim, generator=generator)
+            v_pool[pg, :, off] = torch.randn(kv_heads, head_dim, generator=generator)
+    rows = sum(q for _, q in segments)
+    q = torch.randn(rows, heads * head_dim, generator=generator)
+    q_start, tile_seg, tile_row0, row = [], [], [], 0
+    for s, (pos0, q_len) in enumerate(segments):
+        q_start.append(row)
+        row += q_len
+        for r0 in range(0, q_len, 16):
+            tile_seg.append(s)
+            tile_row0.append(r0)
+
+    def ints(values, device):
+        return torch.tensor(values, dtype=torch.int32, device=device)
+
+    def batch(device):
+        return AttentionBatch(
+            seg_q_start=ints(q_start, device), seg_q_len=ints([q for _, q in segments], device),
+            seg_pos0=ints([p for p, _ in segments], device), block_table=table.to(device),
+            tile_seg=ints(tile_seg, device), tile_row0=ints(tile_row0, device),
+            num_segments=len(segments), num_tiles=len(tile_seg),
+            max_q_len=max(q for _, q in segments), max_kv_len=max(p + q for p, q in segments))
+
+    return q.to(dtype), k_pool.to(dtype), v_pool.to(dtype), batch, table
+
+
+def run_attention_both(dtype, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window):
+    scale = head_dim ** -0.5
+    want = FAKE.paged_attention(q.float(), k_pool.float(), v_pool.float(), batch("cpu"), heads, kv_heads,
+                                head_dim, scale, window)
+    got = cuda().paged_attention(q.to(DEVICE), k_pool.to(DEVICE), v_pool.to(DEVICE), batch(DEVICE), heads,
+                                 kv_heads, head_dim, scale, window)
+    return got, want
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [
+    (14, 2, 64, 16), (3, 1, 32, 8), (6, 3, 48, 16), (8, 8, 128, 16), (2, 1, 256, 3), (5, 5, 16, 4), (4, 2, 80, 32)])
+def test_attention_ragged_batch(dtype, heads, kv_heads, head_dim, page):
+    # a whole prompt, a portion in the middle of a request, two single decoded tokens, a 2-token portion
+    segments = [(0, 37), (50, 19), (130, 1), (0, 1), (63, 2)]
+    q, k_pool, v_pool, batch, _ = make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, 21)
+    got, want = run_attention_both(dtype, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+    assert_close(got, want, dtype, "attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 33, 1000])
+def test_attention_window_edge(dtype, window):
+    heads, kv_heads, head_dim, page = 4, 2, 32, 8
+    segments = [(0, 40), (70, 3), (99, 1)]
+    q, k_pool, v_pool, batch, _ = make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, 22)
+    got, want = run_attention_both(dtype, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+    assert_close(got, want, dtype, f"attention window={window}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far_key", [0, 15, 16, 255, 256, 511, 700])
+def test_attention_finds_one_far_key(dtype, far_key):
+    """One key among hundreds is made to dominate (its k equals the scaled query); the output
+    must then be that key's value, which no other value resembles."""
+    heads, kv_heads, head_dim, page = 2, 1, 64, 16
+    segments = [(700, 1), (690, 11)]
+    q, k_pool, v_pool, batch, table = make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, 23)
+    # row 0 is the decode row at position 700; rows 1.. are the portion; take its last row (position 700)
+    for seg, row in ((0, 0), (1, 11)):
+        direction = q[row, :head_dim].float()
+        pg, off = table[seg, far_key // page], far_key % page
+        k_pool[pg, 0, off] = (direction * (40.0 / direction.norm() ** 2 * math.sqrt(head_dim))).to(dtype)
+        v_pool[pg, 0, off] = torch.full((head_dim,), 100.0).to(dtype)
+    got, want = run_attention_both(dtype, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+    assert_close(got, want, dtype, "attention with a dominant far key")
+    for row in (0, 11):
+        assert float(got[row, :head_dim].float().mean()) > 90.0, "the dominant key's value was lost"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_rows_do_not_depend_on_the_cut(dtype):
+    """The same request as one portion, as two portions and as single rows: identical bits."""
+    heads, kv_heads, head_dim, page = 6, 2, 64, 16
+    q, k_pool, v_pool, batch, table = make_attention_case(dtype, heads, kv_heads, head_dim, page, [(0, 45)], 24)
+    scale = head_dim ** -0.5
+    qd, kd, vd = q.to(DEVICE), k_pool.to(DEVICE), v_pool.to(DEVICE)
+    whole = cuda().paged_attention(qd, kd, vd, batch(DEVICE), heads, kv_heads, head_dim, scale, None)
+
+    def piece(pos0, count):
+        tiles = list(range(0, count, 16))
+        ints = lambda v: torch.tensor(v, dtype=torch.int32, device=DEVICE)
+        b = AttentionBatch(ints([0]), ints([count]), ints([pos0]), table.to(DEVICE), ints([0] * len(tiles)),
+                           ints(tiles), 1, len(tiles), count, pos0 + count)
+        return cuda().paged_attention(qd[pos0:pos0 + count].contiguous(), kd, vd, b, heads, kv_heads, head_dim, scale, None)
+
+    assert torch.equal(torch.cat([piece(0, 17), piece(17, 28)]), whole)
+    assert torch.equal(torch.cat([piece(p, 1) for p in range(45)]), whole)
+
+
+def test_sampling_greedy_takes_the_lowest_index_on_ties():
+    logits = torch.zeros(3, 1000)
+    logits[0, [17, 400, 999]] = 5.0
+    logits[1, 999] = 1.0
+    logits[2] = -1.0
+    zeros = torch.zeros(3)
+    ids = torch.zeros(3, dtype=torch.int64)
+    got = cuda().sample(logits.to(DEVICE), zeros.to(DEVICE), ids.to(DEVICE), ids.to(DEVICE))
+    assert got.cpu().tolist() == [17, 999, 0]
+
+
+@pytest.mark.parametrize("vocab", [384, 1000, 151936])
+def test_sampling_temperature_matches_the_plain_sampler(vocab):
+    rows = 48
+    logits = rnd((rows, vocab), torch.float32, 31, 3.0)
+    temperatures = torch.linspace(0.3, 1.5, rows)
+    seeds = torch.arange(rows, dtype=torch.int64) * 7919 + 11
+    counters = torch.arange(rows, dtype=torch.int64) % 5
+    got = cuda().sample(logits.to(DEVICE), temperatures.to(DEVICE), seeds.to(DEVICE), counters.to(DEVICE)).cpu()
+    for row in range(rows):
+        u = plain.uniform_from_seed(int(seeds[row]), int(counters[row]))
+        token, cdf = plain.temperature_sample(logits[row], float(temperatures[row]), u)
+        chosen = int(got[row])
+        if chosen != token:
+            # float32 summation order may move a boundary by rounding: u must then sit on it
+            low = float(cdf[chosen - 1]) if chosen > 0 else 0.0
+            assert low - 1e-5 <= u <= float(cdf[chosen]) + 1e-5, (row, chosen, token, u)
+
+
+def test_sampling_follows_the_distribution():
+    vocab, rows = 11, 4000
+    logits = torch.tensor([0.0, 1.0, 2.0, -1.0, 0.5, 3.0, -2.0, 0.0, 1.5, 2.5, -0.5]).repeat(rows, 1)
+    temperatures = torch.full((rows,), 0.8)
+    seeds = torch.full((rows,), 1234, dtype=torch.int64)
+    counters = torch.arange(rows, dtype=torch.int64)
+    got = cuda().sample(logits.to(DEVICE), temperatures.to(DEVICE), seeds.to(DEVICE), counters.to(DEVICE)).cpu()
+    observed = torch.bincount(got.long(), minlength=vocab).float() / rows
+    expected = torch.softmax(logits[0] / 0.8, dim=-1)
+    assert float((observed - expected).abs().max()) < 0.03
