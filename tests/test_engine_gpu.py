@@ -1,0 +1,150 @@
+"""The engine against the plain implementation, in float32 and bfloat16, for three tiny
+configurations: each request alone and whole; most of it in one step and the last 32 tokens one by
+one; in portions of changing size down to two tokens; mixed with other requests in a pool so small
+that pages are used again; long decoding; the first tokens of a sequence.  Every position's logits
+are compared with the plain implementation run on that request alone and whole."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import scenarios
+from harness import TinyEngine, assert_close, random_prompt
+from mini_llm_runtime_b200.engine import StepEntry
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+LENGTHS = {"A": (5, 17, 33, 150), "B": (1, 9, 24, 40, 131), "C": (3, 70, 45, 97, 160)}
+
+
+def make_requests(name, vocab):
+    return {f"{name}{i}": random_prompt(vocab, length, 100 + i) for i, length in enumerate(LENGTHS[name])}
+
+
+def replay(engine: TinyEngine, requests, steps):
+    """Run ``steps`` through the runner; returns request id -> logits of all its positions."""
+    pieces = {rid: [] for rid in requests}
+    for step in steps:
+        entries = []
+        for rid, start, end in step["entries"]:
+            if rid not in engine.cache.requests:
+                engine.cache.create_request(rid)
+            entries.append(StepEntry(rid, requests[rid][start:end], list(range(end - start))))
+        logits = engine.runner.step(entries)
+        row = 0
+        for rid, start, end in step["entries"]:
+            pieces[rid].append(logits[row:row + end - start])
+            row += end - start
+        for rid in step["end"]:
+            engine.cache.release(rid)
+        engine.cache.check_consistency()
+    return {rid: torch.cat(parts) for rid, parts in pieces.items()}
+
+
+def check_all(engine, requests, results, dtype, what):
+    for rid, tokens in requests.items():
+        assert results[rid].shape[0] == len(tokens)
+        assert_close(results[rid], engine.plain_logits(tokens), dtype, f"{what}, request {rid}")
+
+
+@pytest.fixture(scope="module", params=[(n, d) for n in TINY for d in DTYPES],
+                ids=lambda p: f"{p[0]}-{'f32' if p[1] == torch.float32 else 'bf16'}")
+def setup(request):
+    name, dtype = request.param
+    config, page = TINY[name]
+    engine = TinyEngine(config, page, dtype, DEVICE, num_pages=64, max_requests=4, max_tokens=512, seed=7)
+    return name, dtype, engine, make_requests(name, config.vocab_size)
+
+
+def test_whole(setup):
+    name, dtype, engine, requests = setup
+    check_all(engine, requests, replay(engine, requests, scenarios.whole(requests)), dtype, "whole")
+
+
+def test_tail_one_by_one(setup):
+    name, dtype, engine, requests = setup
+    check_all(engine, requests, replay(engine, requests, scenarios.tail_one_by_one(requests)), dtype,
+              "last 32 one by one")
+
+
+def test_changing_portions(setup):
+    name, dtype, engine, requests = setup
+    check_all(engine, requests, replay(engine, requests, scenarios.changing_portions(requests)), dtype,
+              "changing portions")
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_mixed_with_reused_pages(setup, seed):
+    name, dtype, engine, requests = setup
+    config, page = TINY[name]
+    steps = scenarios.mixed(requests, seed)
+    tokens = scenarios.pool_tokens(requests, steps)
+    tight = TinyEngine(config, page, dtype, DEVICE, num_pages=-(-tokens // page), max_requests=4,
+                       max_tokens=512, tensors=engine.tensors)
+    handed_out = set()
+    reused = False
+    original_allocate = [g.allocator.allocate for g in tight.cache.groups]
+
+    def watch(group_index):
+        def allocate(count):
+            nonlocal reused
+            ids = original_allocate[group_index](count)
+            reused = reused or any((group_index, i) in handed_out for i in ids)
+            handed_out.update((group_index, i) for i in ids)
+            return ids
+        return allocate
+
+    for index, group in enumerate(tight.cache.groups):
+        group.allocator.allocate = watch(index)
+    results = replay(tight, requests, steps)
+    assert reused, "the scenario must hand out some page a second time"
+    assert all(g.allocator.held_count == 0 for g in tight.cache.groups)
+    check_all(tight, requests, results, dtype, f"mixed seed {seed}")
+
+
+def test_long_decoding(setup):
+    name, dtype, engine, requests = setup
+    config, page = TINY[name]
+    tokens = random_prompt(config.vocab_size, 300, 55)
+    steps = [{"entries": [("long", 0, 4)], "end": []}]
+    steps += [{"entries": [("long", p, p + 1)], "end": ["long"] if p == 299 else []} for p in range(4, 300)]
+    results = replay(engine, {"long": tokens}, steps)
+    assert_close(results["long"], engine.plain_logits(tokens), dtype, "long decoding")
+
+
+def test_first_tokens(setup):
+    name, dtype, engine, requests = setup
+    config, page = TINY[name]
+    for length in (1, 2, 3):
+        tokens = random_prompt(config.vocab_size, length, 60 + length)
+        got = engine.run_whole(f"first{length}", tokens)
+        engine.cache.release(f"first{length}")
+        assert_close(got, engine.plain_logits(tokens), dtype, f"first tokens, length {length}")
+        one_by_one = engine.run_cuts(f"single{length}", tokens, list(range(1, length)))
+        engine.cache.release(f"single{length}")
+        assert_close(one_by_one, engine.plain_logits(tokens), dtype, f"first tokens one by one, length {length}")
+
+
+def test_failed_step_leaves_no_trace(setup):
+    """Out of pages: the step raises, nothing is held, and the same step succeeds once pages are free."""
+    name, dtype, engine, requests = setup
+    config, page = TINY[name]
+    from mini_llm_runtime_b200.cache import OutOfPages
+    small = TinyEngine(config, page, dtype, DEVICE, num_pages=3, max_requests=4, max_tokens=512,
+                       tensors=engine.tensors)
+    tokens = random_prompt(config.vocab_size, 3 * page, 70)
+    small.cache.create_request("x")
+    small.cache.create_request("y")
+    first = small.runner.step([StepEntry("x", tokens[:2 * page], [2 * page - 1])])
+    with pytest.raises(OutOfPages):
+        small.runner.step([StepEntry("x", tokens[2 * page:], [0]), StepEntry("y", tokens[:page + 1], [page])])
+    small.cache.check_consistency()
+    assert small.cache.get("x").committed == 2 * page and small.cache.get("y").committed == 0
+    rest = small.runner.step([StepEntry("x", tokens[2 * page:], list(range(page)))])
+    want = small.plain_logits(tokens)
+    assert_close(first, want[2 * page - 1:2 * page], dtype, "before the failed step")
+    assert_close(rest, want[2 * page:], dtype, "after the failed step")
