@@ -42,6 +42,16 @@ class StepEntry:
 
 
 @dataclass
+class SamplingRows:
+    """Per wanted row: temperature (0 = greedy), the request's seed, and the index of the token
+    being produced (the counter of the request's random stream)."""
+
+    temperatures: Sequence[float]
+    seeds: Sequence[int]
+    token_indices: Sequence[int]
+
+
+@dataclass
 class Segment:
     request_id: str
     slot: int
@@ -77,6 +87,7 @@ class StepContext:
     wanted_rows: torch.Tensor        # int32 [wanted]
     segment_slots: torch.Tensor      # int32 [segments]: each request's state slot
     views: dict[int, CacheView] = field(default_factory=dict)
+    sampling: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None
 
     def cache_view(self, entry: int) -> CacheView:
         return self.views[entry]
@@ -164,7 +175,8 @@ class ModelRunner:
             out[name] = flat.view(array.shape)
         return out
 
-    def _build_context(self, entries: Sequence[StepEntry], requests: list[RequestCache]) -> StepContext:
+    def _build_context(self, entries: Sequence[StepEntry], requests: list[RequestCache],
+                       sampling: SamplingRows | None = None) -> StepContext:
         cache = self.cache
         lengths = np.array([len(e.tokens) for e in entries], dtype=np.int32)
         row_start = np.zeros(len(entries), dtype=np.int32)
@@ -205,6 +217,13 @@ class ModelRunner:
                 for i, request in enumerate(requests)])
             packer.add(f"slots{group.index}", rows_slots.astype(np.int64))
             packer.add(f"table{group.index}", group.table[slots, :table_width])
+        if sampling is not None:
+            if not (len(sampling.temperatures) == len(sampling.seeds) == len(sampling.token_indices)
+                    == wanted_rows.shape[0]):
+                raise ValueError("sampling needs one temperature, seed and token index per wanted row")
+            packer.add("temperatures", np.asarray(sampling.temperatures, dtype=np.float32))
+            packer.add("seeds", np.asarray(sampling.seeds, dtype=np.int64))
+            packer.add("token_indices", np.asarray(sampling.token_indices, dtype=np.int64))
         dev = self._upload(packer)
 
         segments = [Segment(e.request_id, int(slots[i]), int(row_start[i]), int(lengths[i]),
@@ -212,6 +231,8 @@ class ModelRunner:
         ctx = StepContext(ops=ops.current(), num_rows=total, num_wanted=int(wanted_rows.shape[0]),
                           segments=segments, token_ids=dev["token_ids"], positions=dev["positions"],
                           wanted_rows=dev["wanted_rows"], segment_slots=dev["seg_slots"])
+        if sampling is not None:
+            ctx.sampling = (dev["temperatures"], dev["seeds"], dev["token_indices"])
         batches = {}
         for group in cache.groups:
             batches[group.index] = AttentionBatch(
@@ -250,17 +271,21 @@ class ModelRunner:
                                  f"the model allows {self.max_positions}")
 
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], sampling: SamplingRows | None = None):
         """Run the entries as one batch.  Returns float32 logits [wanted places, vocab] on the
-        device, in the order of the entries and of each entry's ``want``."""
+        device, in the order of the entries and of each entry's ``want``.  With ``sampling`` it
+        returns ``(logits, tokens)``: one int32 token per wanted place, chosen on the device."""
         self._validate(entries)
         requests = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
         try:
-            ctx = self._build_context(entries, requests)
+            ctx = self._build_context(entries, requests, sampling)
             logits = self.model.forward(ctx)
+            tokens = None
+            if sampling is not None:
+                tokens = ctx.ops.sample(logits, *ctx.sampling)
         except BaseException:
             self.cache.abort_step()
             raise
         self.cache.commit_step()
         self.steps_run += 1
-        return logits
+        return logits if sampling is None else (logits, tokens)

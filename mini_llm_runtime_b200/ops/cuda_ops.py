@@ -32,8 +32,13 @@ class KernelError(RuntimeError):
     pass
 
 
+launches = 0  # kernels launched through this module since import (bench.py reports the count)
+
+
 def _check(status: int, what: str) -> None:
+    global launches
     if status == 0:
+        launches += 1
         return
     if status < 0:
         raise KernelError(f"{what}: refused ({_STATUS_TEXT.get(status, status)})")

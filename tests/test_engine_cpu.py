@@ -1,0 +1,218 @@
+"""Everything above the kernels on the CPU, with the kernels replaced by their plain stand-ins
+(``fake_ops.FakeOps``): the step function under several cuts, the engine loop with greedy and
+temperature sampling, failure roll-back, and toy parts registered from outside the package."""
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import scenarios
+from fake_ops import FakeOps
+from harness import TinyEngine, assert_close, random_prompt
+from mini_llm_runtime_b200 import ops
+from mini_llm_runtime_b200.cache import CacheManager
+from mini_llm_runtime_b200.config import register_architecture, unregister_architecture
+from mini_llm_runtime_b200.engine import (ContinuousBatchEngine, ModelRunner, StepEntry, greedy_generate)
+from mini_llm_runtime_b200.models import build_model
+from mini_llm_runtime_b200.weights import random_tensors
+from tiny_configs import TINY
+
+
+@pytest.fixture(autouse=True)
+def stand_in_kernels():
+    with ops.use(FakeOps()):
+        yield
+
+
+def test_the_package_never_computes_on_the_cpu_by_itself():
+    config, page = TINY["A"]
+    with ops.use(ops.CudaOps()):
+        engine = TinyEngine(config, page, torch.float32, "cpu")
+        with pytest.raises(ops.KernelError):
+            engine.run_whole("a", [1, 2, 3])
+        assert engine.cache.get("a").committed == 0 and not engine.cache.step_in_flight
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_step_function_under_mixed_cuts(name):
+    config, page = TINY[name]
+    engine = TinyEngine(config, page, torch.float32, "cpu", num_pages=24)
+    requests = {f"r{i}": random_prompt(config.vocab_size, n, i) for i, n in enumerate((3, 41, 18, 57, 9))}
+    steps = scenarios.mixed(requests, seed=3)
+    pieces = {rid: [] for rid in requests}
+    for step in steps:
+        entries = []
+        for rid, start, end in step["entries"]:
+            if rid not in engine.cache.requests:
+                engine.cache.create_request(rid)
+            entries.append(StepEntry(rid, requests[rid][start:end], list(range(end - start))))
+        logits = engine.runner.step(entries)
+        row = 0
+        for rid, start, end in step["entries"]:
+            pieces[rid].append(logits[row:row + end - start])
+            row += end - start
+        for rid in step["end"]:
+            engine.cache.release(rid)
+        engine.cache.check_consistency()
+    for rid, tokens in requests.items():
+        assert_close(torch.cat(pieces[rid]), engine.plain_logits(tokens), torch.float32, rid)
+
+
+def test_step_validation():
+    config, page = TINY["A"]
+    engine = TinyEngine(config, page, torch.float32, "cpu", max_tokens=32)
+    engine.cache.create_request("a")
+    for bad in ([StepEntry("a", [], [])], [StepEntry("a", [config.vocab_size], [0])], [StepEntry("a", [-1], [0])],
+                [StepEntry("a", [1, 2], [2])], [StepEntry("a", [1.5], [0])], []):
+        with pytest.raises(ValueError):
+            engine.runner.step(bad)
+    with pytest.raises(KeyError):
+        engine.runner.step([StepEntry("nobody", [1], [0])])
+    assert engine.runner.step([StepEntry("a", [1, 2, 3], [])]).shape == (0, config.vocab_size)
+    assert engine.cache.get("a").committed == 3
+
+
+def build_engine(name, **options):
+    config, page = TINY[name]
+    model = build_model(config, torch.float32)
+    tensors = random_tensors(model.expected_tensors(), 21)
+    model.load(tensors, "cpu")
+    defaults = dict(block_size=page, max_running_requests=4, max_batch_tokens=24, max_model_len=128)
+    defaults.update(options)
+    return config, tensors, ContinuousBatchEngine.from_model(model, **defaults)
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_continuous_batching_reproduces_plain_greedy_generation(name):
+    config, tensors, engine = build_engine(name)
+    prompts = {f"p{i}": random_prompt(config.vocab_size, n, 40 + i) for i, n in enumerate((5, 17, 33, 1, 50, 9))}
+    for i, (rid, prompt) in enumerate(prompts.items()):
+        engine.submit(rid, prompt, max_new_tokens=3 + i % 4)
+    results = engine.run()
+    assert any(len(r.batch.prefill_request_ids) and len(r.batch.decode_request_ids) for r in results)
+    assert any(not item.emits_token for r in results for item in r.batch.items)     # some prompt was cut
+    for i, (rid, prompt) in enumerate(prompts.items()):
+        want = plain.greedy_tokens(tensors, config.to_dict(), prompt, 3 + i % 4)
+        assert list(engine.scheduler.get_request(rid).generated_token_ids) == want, rid
+    stats = engine.manager.stats()
+    assert stats.live_requests == 0 and all(h == 0 for h in stats.held_pages) and all(p == 0 for p in stats.promised_pages)
+    assert engine.metrics.summary()["tokens"] == sum(3 + i % 4 for i in range(6))
+
+
+def test_eos_stops_a_request_and_frees_its_pages():
+    config, tensors, engine = build_engine("A")
+    prompt = random_prompt(config.vocab_size, 12, 5)
+    want = plain.greedy_tokens(tensors, config.to_dict(), prompt, 6)
+    engine.submit("e", prompt, max_new_tokens=6, eos_token_ids=[want[2]])
+    engine.run()
+    stop = want.index(want[2])
+    assert list(engine.scheduler.get_request("e").generated_token_ids) == want[:stop + 1]
+    assert engine.manager.stats().live_requests == 0
+
+
+def test_temperature_sampling_does_not_depend_on_the_batch():
+    config, tensors, _ = build_engine("B")
+    prompts = [random_prompt(config.vocab_size, n, 60 + n) for n in (1, 9, 24, 40)]
+
+    def run(order, budget):
+        _, _, engine = build_engine("B", max_batch_tokens=budget)
+        for i in order:
+            engine.submit(f"t{i}", prompts[i], max_new_tokens=12, temperature=0.7, seed=1000 + i)
+        engine.run()
+        return {i: engine.scheduler.get_request(f"t{i}").generated_token_ids for i in order}
+
+    together = run([0, 1, 2, 3], 64)
+    assert together == run([3, 2, 1, 0], 7)
+    assert {2: together[2]} == run([2], 64)
+    # and the tokens are the plain sampler's, fed with the plain model's logits
+    sequence = list(prompts[1])
+    for index, token in enumerate(together[1]):
+        logits = plain.forward_logits(tensors, config.to_dict(), sequence)[-1]
+        u = plain.uniform_from_seed(1001, index)
+        assert token == plain.temperature_sample(logits, 0.7, u)[0]
+        sequence.append(token)
+    assert len(set(together[1])) > 1
+
+
+def test_a_failed_step_rolls_back_scheduler_and_cache_and_can_be_retried():
+    config, tensors, engine = build_engine("A")
+    engine.submit("a", random_prompt(config.vocab_size, 6, 1), max_new_tokens=3)
+    engine.step()
+    engine.submit("b", random_prompt(config.vocab_size, 4, 2), max_new_tokens=2)
+    forward = engine.runner.model.forward
+    calls = {"n": 0}
+
+    def failing(ctx):
+        calls["n"] += 1
+        raise RuntimeError("injected failure between layers")
+
+    engine.runner.model.forward = failing
+    with pytest.raises(RuntimeError, match="injected"):
+        engine.step()
+    engine.runner.model.forward = forward
+    assert calls["n"] == 1
+    assert engine.scheduler.waiting_request_ids == ("b",) and engine.scheduler.running_request_ids == ("a",)
+    assert "b" not in engine.manager.requests and engine.manager.get("a").committed == 6
+    assert not engine.manager.step_in_flight
+    engine.manager.check_consistency()
+    result = engine.step()
+    assert result.batch.step_index == 1 and set(result.batch.admitted_request_ids) == {"b"}
+    engine.run()
+    for rid, seed, length, count in (("a", 1, 6, 3), ("b", 2, 4, 2)):
+        want = plain.greedy_tokens(tensors, config.to_dict(), random_prompt(config.vocab_size, length, seed), count)
+        assert list(engine.scheduler.get_request(rid).generated_token_ids) == want
+
+
+def test_greedy_generate_and_generate_entry_points():
+    config, tensors, engine = build_engine("B")
+    prompt = random_prompt(config.vocab_size, 24, 9)
+    want = plain.greedy_tokens(tensors, config.to_dict(), prompt, 5)
+    output = greedy_generate(engine.runner, prompt, max_new_tokens=5, return_step_logits=True)
+    assert output.generated_token_ids == want and output.decode_steps == 4
+    assert output.cache_length == len(prompt) + 4 and len(output.step_logits) == 5
+    assert engine.manager.stats().live_requests == 0
+    assert engine.generate([prompt, prompt[:3]], max_new_tokens=5)[0] == want
+    with pytest.raises(ValueError):
+        engine.submit("bad", [config.vocab_size], max_new_tokens=1)
+    with pytest.raises(ValueError):
+        engine.submit("long", [1] * 120, max_new_tokens=20)
+
+
+def test_toy_parts_register_build_and_step_without_touching_the_package():
+    import toy_parts
+
+    toy_parts.register_toys()
+    register_architecture("ToyForCausalLM", toy_parts.ToyConfig.from_dict, toy_parts.toy_model_spec, replace=True)
+    try:
+        config = toy_parts.ToyConfig()
+        model = build_model(config, torch.float32)
+        tensors = random_tensors(model.expected_tensors(), 4, torch.float32)
+        for name in tensors:                      # larger weights so that routing and mixing matter
+            if "router" in name or "mix.weight" in name:
+                tensors[name] = tensors[name] * 20
+        model.load(tensors, "cpu")
+        needs = model.cache_needs()
+        assert len(needs) == 3 and type(needs[1]).__name__ == "StateNeed"
+        cache = CacheManager(needs, page_size=8, num_pages=16, max_requests=3, max_tokens_per_request=128,
+                             dtype=torch.float32, device="cpu")
+        runner = ModelRunner(model, cache)
+        requests = {"x": random_prompt(97, 45, 1), "y": random_prompt(97, 30, 2), "z": random_prompt(97, 7, 3)}
+        pieces = {rid: [] for rid in requests}
+        for step in scenarios.mixed(requests, seed=8, max_live=3, decode_tail=5):
+            entries = []
+            for rid, start, end in step["entries"]:
+                if rid not in cache.requests:
+                    cache.create_request(rid)
+                entries.append(StepEntry(rid, requests[rid][start:end], list(range(end - start))))
+            logits = runner.step(entries)
+            row = 0
+            for rid, start, end in step["entries"]:
+                pieces[rid].append(logits[row:row + end - start])
+                row += end - start
+            for rid in step["end"]:
+                cache.release(rid)
+        for rid, tokens in requests.items():
+            assert_close(torch.cat(pieces[rid]), toy_parts.plain_toy_logits(tensors, config, tokens),
+                         torch.float32, f"toy {rid}")
+    finally:
+        unregister_architecture("ToyForCausalLM")
