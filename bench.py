@@ -233,10 +233,13 @@ def time_e2e(layers, batch, steps, warmup):
     model = random_model(config, seed=0, dtype=torch.bfloat16, device="cuda:0")
     prefix = CONTEXT_MEAN - (steps + warmup) // 2
     engine = ContinuousBatchEngine.from_model(model, block_size=BLOCK_SIZE, max_running_requests=batch,
-                                              max_batch_tokens=PREFILL_TOKENS, max_model_len=CONTEXT)
+                                              max_batch_tokens=PREFILL_TOKENS, max_model_len=CONTEXT + 1024)
+    # Requests that finish their prompt early decode while the others still prefill; leave room
+    # for those extra tokens so that all of them are alive through the timed steps.
+    slack = batch * (-(-prefix // PREFILL_TOKENS) + 1)
     for index in range(batch):
         engine.submit(f"e{index}", random_tokens(prefix, config.vocab_size, 2000 + index),
-                      max_new_tokens=steps + warmup + 1)
+                      max_new_tokens=steps + warmup + 1 + slack)
     while any(not engine.scheduler.get_request(f"e{i}").prefilled for i in range(batch)):
         engine.step()
     for _ in range(warmup):
