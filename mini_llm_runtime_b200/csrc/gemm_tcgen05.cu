@@ -1,0 +1,402 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: y[M,N] = x[M,K] * W[N,K]^T (+ bias),
+// float32 accumulation in tensor memory, output bfloat16 or float32.
+//
+// One CTA computes one 128 x BN accumulator tile:
+//   warp 0 (one lane)  TMA producer: cp.async.bulk.tensor loads of 128B-swizzled [rows x 64] tiles
+//                      of both operands into a ring of shared-memory stages, signalled by mbarriers
+//   warp 1             allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=16) on
+//                      shared-memory descriptors and commits each stage back to the producer
+//   warps 2..5         epilogue: tcgen05.ld the accumulator (one TMEM lane = one tile row per
+//                      thread), add bias, convert, store
+// Both operands are K-major, as activations [M,K] and checkpoint weights [N,K] are stored.
+//
+// Orientation.  With many rows (prefill) x is the 128-row operand and 128 weight rows form the
+// N side.  With few rows (decode) the roles swap: 128 weight rows fill the MMA's M side and the
+// BN = 16..128 token rows its N side, so that a step streams every weight byte exactly once through
+// full-width tiles.  K may be split over gridDim.z CTAs; partial tiles go to a float32 scratch
+// buffer and the CTA that arrives last for a tile adds them in split order (deterministic) and
+// writes the output.  No CTA waits for another CTA.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out stores a code into the error word
+// (host-visible memory), the CTA stops issuing work, frees its tensor memory and returns.
+// TMA loads use no cluster multicast.  Requirements: K % 8 == 0 (16-byte row pitch for TMA) and
+// 16-byte aligned base pointers; the caller falls back to the SIMT kernel otherwise.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+namespace mlr {
+
+constexpr int TILE_ROWS = 128;      // MMA M
+constexpr int TILE_K = 64;          // one 128-byte swizzle atom of bfloat16
+constexpr int MMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;   // a wait gives up after one second
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false (and an error code in *error_word) if the phase does not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error_word, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer_ns();
+  do {
+    for (int i = 0; i < 128; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+  } while (global_timer_ns() - start < WAIT_LIMIT_NS);
+  *((volatile int*)error_word) = code;
+  __threadfence_system();
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups of
+// 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((address & 0x3FFFFu) >> 4);
+  desc |= (uint64_t)1 << 16;            // leading byte offset (unused with swizzled K-major)
+  desc |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
+  desc |= (uint64_t)1 << 46;            // version
+  desc |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return desc;
+}
+
+// Instruction descriptor of kind::f16: float32 accumulator, bfloat16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmParams {
+  int M, N, K;
+  int k_blocks_per_split;   // 64-wide k blocks each split handles
+  int splits;
+  const bf16* bias;
+  void* out;
+  int out_f32;
+  float* scratch;           // [tiles][splits][BN][128] partial tiles (splits > 1)
+  int* counters;            // one per output tile, zero between launches
+  int* error_word;
+};
+
+// SWAP = true:  A (128 rows) = weights, B (BN rows) = activations; tile row = output column n.
+// SWAP = false: A (128 rows) = activations, B (BN rows) = weights; tile row = output row m.
+template <int BN, bool SWAP, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+  constexpr uint32_t A_BYTES = TILE_ROWS * TILE_K * 2;
+  constexpr uint32_t B_BYTES = BN * TILE_K * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+  extern __shared__ uint8_t raw_shared[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)raw_shared + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accumulator_bar;
+  __shared__ uint32_t tmem_holder;
+  __shared__ int is_last_cta, epilogue_failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int a_row0 = blockIdx.x * TILE_ROWS;   // first row of the 128-row operand
+  const int b_row0 = blockIdx.y * BN;          // first row of the BN-row operand
+  const int split = blockIdx.z;
+  const int total_kb = (p.K + TILE_K - 1) / TILE_K;
+  const int kb_begin = split * p.k_blocks_per_split;
+  const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
+  const int num_kb = kb_end - kb_begin;        // >= 1 by construction of the grid
+
+  if (threadIdx.x == 0) {
+    epilogue_failed = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&accumulator_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_holder)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_holder;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- producer
+    for (int i = 0; i < num_kb; ++i) {
+      const int s = i % STAGES;
+      if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, p.error_word, 1)) break;
+      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+      const int k = (kb_begin + i) * TILE_K;
+      tma_load_2d(&map_a, &full_bar[s], stage, k, a_row0);
+      tma_load_2d(&map_b, &full_bar[s], stage + A_BYTES, k, b_row0);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    constexpr uint32_t idesc = instruction_descriptor(TILE_ROWS, BN);
+    bool ok = true;
+    for (int i = 0; i < num_kb && ok; ++i) {
+      const int s = i % STAGES;
+      ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, p.error_word, 2);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+      const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+      for (int k = 0; k < TILE_K / MMA_K; ++k)
+        umma(tmem_base, smem_descriptor(a_addr + k * MMA_K * 2), smem_descriptor(b_addr + k * MMA_K * 2), idesc,
+             (i > 0 || k > 0) ? 1u : 0u);
+      umma_commit(&empty_bar[s]);
+    }
+    umma_commit(&accumulator_bar);   // arrives once every MMA issued above has finished
+  } else if (warp >= 2) {
+    // ---------------- epilogue: thread <-> TMEM lane <-> tile row
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    if (!mbar_wait(&accumulator_bar, 0, p.error_word, 3)) atomicOr(&epilogue_failed, 1);
+    asm volatile("bar.sync 1, 128;" ::: "memory");     // all four epilogue warps always get here
+    const bool ok = epilogue_failed == 0;               // the same answer in all of them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    if (ok && p.splits > 1) {
+      float* mine = p.scratch + ((size_t)tile_id * p.splits + split) * BN * TILE_ROWS;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, r);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) mine[(size_t)(c0 + c) * TILE_ROWS + row] = __uint_as_float(r[c]);
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) is_last_cta = (atomicAdd(&p.counters[tile_id], 1) == p.splits - 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    const bool reduce = ok && p.splits > 1 && is_last_cta;
+    if (ok && (p.splits == 1 || reduce)) {
+      if (reduce) __threadfence();
+      const float* partials = p.scratch + (size_t)tile_id * p.splits * BN * TILE_ROWS;
+      bf16* out_bf16 = (bf16*)p.out;
+      float* out_f32 = (float*)p.out;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        if (reduce) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) v[c] = 0.f;
+          for (int s = 0; s < p.splits; ++s)
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              v[c] += __ldcg(&partials[((size_t)s * BN + c0 + c) * TILE_ROWS + row]);
+        } else {
+          uint32_t r[16];
+          tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, r);
+#pragma unroll
+          for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+        }
+        if (SWAP) {
+          const int n = a_row0 + row;
+          if (n < p.N) {
+            const float b = p.bias != nullptr ? to_float(p.bias[n]) : 0.f;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int m = b_row0 + c0 + c;
+              if (m < p.M) {
+                if (p.out_f32) out_f32[(size_t)m * p.N + n] = v[c] + b;
+                else out_bf16[(size_t)m * p.N + n] = __float2bfloat16_rn(v[c] + b);
+              }
+            }
+          }
+        } else {
+          const int m = a_row0 + row;
+          const int n0 = b_row0 + c0;
+          if (m < p.M && !p.out_f32 && (p.N & 7) == 0 && n0 + 16 <= p.N) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int c = 0; c < 16; c += 2) {
+              const float b0 = p.bias != nullptr ? to_float(p.bias[n0 + c]) : 0.f;
+              const float b1 = p.bias != nullptr ? to_float(p.bias[n0 + c + 1]) : 0.f;
+              __nv_bfloat162 pair = __floats2bfloat162_rn(v[c] + b0, v[c + 1] + b1);
+              packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(out_bf16 + (size_t)m * p.N + n0);
+            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else if (m < p.M) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int n = b_row0 + c0 + c;
+              if (n < p.N) {
+                const float b = p.bias != nullptr ? to_float(p.bias[n]) : 0.f;
+                if (p.out_f32) out_f32[(size_t)m * p.N + n] = v[c] + b;
+                else out_bf16[(size_t)m * p.N + n] = __float2bfloat16_rn(v[c] + b);
+              }
+            }
+          }
+        }
+      }
+      if (reduce && warp == 2 && lane == 0) p.counters[tile_id] = 0;   // ready for the next launch
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+static PFN_cuTensorMapEncodeTiled_v12000 encode_tiled() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)ptr;
+  }
+  return fn;
+}
+
+// rows x K bfloat16, row-major; box = [box_rows x 64], 128-byte swizzle, out-of-range reads give zero.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  auto encode = encode_tiled();
+  if (encode == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t element_strides[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool SWAP, int STAGES>
+static int launch(const void* x, const void* w, const GemmParams& p, int splits, cudaStream_t stream) {
+  constexpr size_t shared = (size_t)STAGES * (TILE_ROWS * TILE_K * 2 + BN * TILE_K * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, SWAP, STAGES>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  CUtensorMap map_a, map_b;
+  const void* a_base = SWAP ? w : x;
+  const void* b_base = SWAP ? x : w;
+  const int a_rows = SWAP ? p.N : p.M, b_rows = SWAP ? p.M : p.N;
+  if (!make_map(&map_a, a_base, a_rows, p.K, TILE_ROWS) || !make_map(&map_b, b_base, b_rows, p.K, BN))
+    return MLR_BAD_ALIGNMENT;
+  dim3 grid((a_rows + TILE_ROWS - 1) / TILE_ROWS, (b_rows + BN - 1) / BN, splits);
+  gemm_tcgen05_kernel<BN, SWAP, STAGES><<<grid, GEMM_THREADS, shared, stream>>>(map_a, map_b, p);
+  return launch_status();
+}
+
+}  // namespace mlr
+
+using namespace mlr;
+
+// Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
+// `splits_out` receives the split count the launcher will use.
+MLR_EXPORT long long mlr_gemm_tcgen05_plan(int M, int N, int K, int* splits_out, int* tiles_out) {
+  const int total_kb = (K + TILE_K - 1) / TILE_K;
+  int bn, tiles;
+  if (M <= 128) {
+    bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+    tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
+  } else {
+    bn = 128;
+    tiles = ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + bn - 1) / bn);
+  }
+  int splits = 1;
+  if (M <= 128) {
+    // Few tiles cannot keep 148 SMs streaming weights: cut K so that about two CTAs per SM exist,
+    // but leave every split at least two k blocks.
+    const int wanted = (2 * 148 + tiles - 1) / tiles;
+    splits = wanted < 1 ? 1 : wanted;
+    if (splits > total_kb / 2) splits = total_kb / 2;
+    if (splits < 1) splits = 1;
+    const int per = (total_kb + splits - 1) / splits;
+    splits = (total_kb + per - 1) / per;   // no empty split
+  }
+  if (splits_out) *splits_out = splits;
+  if (tiles_out) *tiles_out = tiles;
+  return splits > 1 ? (long long)tiles * splits * bn * TILE_ROWS * 4 : 0;
+}
+
+// x [M,K], w [N,K], bias [N] or null, all bfloat16; out [M,N] bfloat16 (out_f32 = 0) or float32.
+// scratch: at least mlr_gemm_tcgen05_plan(...) bytes; counters: one zeroed int per tile;
+// error_word: host-visible int that receives a non-zero code if a wait inside the kernel runs out.
+MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                                int out_f32, void* scratch, int* counters, int* error_word,
+                                cudaStream_t stream) {
+  if (M == 0) return MLR_OK;
+  if (M < 0 || N <= 0 || K <= 0) return MLR_BAD_SIZE;
+  if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MLR_BAD_ALIGNMENT;
+  int splits = 1, tiles = 0;
+  mlr_gemm_tcgen05_plan(M, N, K, &splits, &tiles);
+  const int total_kb = (K + TILE_K - 1) / TILE_K;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+  p.splits = splits;
+  p.bias = (const bf16*)bias;
+  p.out = out;
+  p.out_f32 = out_f32;
+  p.scratch = (float*)scratch;
+  p.counters = counters;
+  p.error_word = error_word;
+  if (splits > 1 && (scratch == nullptr || counters == nullptr)) return MLR_BAD_SIZE;
+  if (M <= 16) return launch<16, true, 8>(x, w, p, splits, stream);
+  if (M <= 32) return launch<32, true, 8>(x, w, p, splits, stream);
+  if (M <= 64) return launch<64, true, 6>(x, w, p, splits, stream);
+  if (M <= 128) return launch<128, true, 5>(x, w, p, splits, stream);
+  return launch<128, false, 5>(x, w, p, splits, stream);
+}

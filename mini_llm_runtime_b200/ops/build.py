@@ -37,6 +37,7 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "linear_simt": (),
     "attention_generic": (),
     "sampling": (),
+    "gemm_tcgen05": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -93,9 +93,39 @@ class AttentionBatch:
 
 
 class CudaOps:
-    """The kernels, as methods.  One instance per process is enough."""
+    """The kernels, as methods.  One instance per process is enough.
+
+    Kernels that need scratch memory (split-K partial tiles, split-KV partial softmax states) share
+    per-device buffers owned by this object; calls are ordered by the CUDA stream they run on, so
+    one stream at a time may use an instance.
+    """
 
     name = "cuda"
+    GEMM_SCRATCH_BYTES = 32 << 20
+    GEMM_COUNTERS = 1 << 15
+
+    def __init__(self) -> None:
+        self._workspaces: dict[int, dict[str, torch.Tensor]] = {}
+        self.use_tensor_cores = True
+
+    def _workspace(self, device: torch.device) -> dict[str, torch.Tensor]:
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        if index not in self._workspaces:
+            self._workspaces[index] = {
+                "gemm_scratch": torch.empty(self.GEMM_SCRATCH_BYTES, dtype=torch.uint8, device=device),
+                "gemm_counters": torch.zeros(self.GEMM_COUNTERS, dtype=torch.int32, device=device),
+                # written by a kernel whose bounded wait ran out; read by the host without a copy
+                "error_word": torch.zeros(1, dtype=torch.int32).pin_memory(),
+            }
+        return self._workspaces[index]
+
+    def raise_if_device_error(self) -> None:
+        """Call after a synchronisation point: raises if a kernel gave up on a bounded wait."""
+        for space in self._workspaces.values():
+            code = int(space["error_word"][0])
+            if code != 0:
+                space["error_word"][0] = 0
+                raise KernelError(f"a kernel's bounded wait ran out (code {code}); its results are invalid")
 
     # ------------------------------------------------------------------ elementwise
     def embedding(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
@@ -197,7 +227,27 @@ class CudaOps:
         if x.shape[1] != weight.shape[1]:
             raise KernelError(f"x has {x.shape[1]} columns, weight expects {weight.shape[1]}")
         out_dtype = out_dtype or x.dtype
+        if (self.use_tensor_cores and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+                and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.shape[0] > 0):
+            return self._linear_tcgen05(x, weight, bias, out_dtype)
         return self._linear_simt(x, weight, bias, out_dtype)
+
+    def _linear_tcgen05(self, x, weight, bias, out_dtype):
+        M, K = x.shape
+        N = weight.shape[0]
+        lib = build.load_library("gemm_tcgen05")
+        lib.mlr_gemm_tcgen05_plan.restype = ctypes.c_longlong
+        splits, tiles = ctypes.c_int(0), ctypes.c_int(0)
+        need = lib.mlr_gemm_tcgen05_plan(M, N, K, ctypes.byref(splits), ctypes.byref(tiles))
+        space = self._workspace(x.device)
+        if need > space["gemm_scratch"].numel() or (splits.value > 1 and tiles.value > space["gemm_counters"].numel()):
+            return self._linear_simt(x, weight, bias, out_dtype)
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        _check(lib.mlr_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
+                                    int(out_dtype == torch.float32), _ptr(space["gemm_scratch"]),
+                                    _ptr(space["gemm_counters"]), _ptr(space["error_word"]), _stream()),
+               "linear (tcgen05)")
+        return out
 
     def _linear_simt(self, x, weight, bias, out_dtype):
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)

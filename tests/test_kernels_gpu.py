@@ -87,10 +87,42 @@ def test_linear(dtype, m, n, k):
     assert_close(got32, x.double() @ w.double().T, torch.float32 if dtype == torch.float32 else dtype, "linear f32 out")
 
 
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 33, 64, 100, 128, 129, 300])
+@pytest.mark.parametrize("n,k", [(896, 896), (1152, 896), (200, 72), (896, 4864), (130, 64), (4000, 136)])
+def test_tensor_core_linear(m, n, k):
+    """The tcgen05 product in both orientations, with and without split-K, K tails and N tails."""
+    x = rnd((m, k), torch.bfloat16, 40 + m)
+    w = rnd((n, k), torch.bfloat16, 41, 0.1)
+    b = rnd((n,), torch.bfloat16, 42)
+    want = x.double() @ w.double().T + b.double()
+    got = cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE))
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    assert_close(got, want, torch.bfloat16, f"tcgen05 linear {m}x{n}x{k}")
+    # float32 output keeps the accumulator's precision: far tighter than bfloat16 rounding
+    got32 = cuda().linear(x.to(DEVICE), w.to(DEVICE), None, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    want32 = x.double() @ w.double().T
+    assert float((got32.double().cpu() - want32).abs().max()) <= 1e-4 * float(want32.abs().max()) + 1e-5
+    # and it is the same bits when called again (split-K partials are added in a fixed order)
+    assert torch.equal(got32, cuda().linear(x.to(DEVICE), w.to(DEVICE), None, out_dtype=torch.float32))
+
+
+def test_tensor_core_linear_large_vocabulary():
+    x = rnd((8, 896), torch.bfloat16, 50)
+    w = rnd((151936, 896), torch.bfloat16, 51, 0.02)
+    got = cuda().linear(x.to(DEVICE), w.to(DEVICE), None, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    want = x.double() @ w.double().T
+    assert float((got.double().cpu() - want).abs().max()) <= 1e-4 * float(want.abs().max()) + 1e-5
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_rows_do_not_depend_on_the_batch(dtype):
-    x = rnd((70, 150), dtype, 12).to(DEVICE)
-    w = rnd((90, 150), dtype, 13, 0.2).to(DEVICE)
+    x = rnd((70, 152), dtype, 12).to(DEVICE)
+    w = rnd((90, 152), dtype, 13, 0.2).to(DEVICE)
     whole = cuda().linear(x, w)
     for start, stop in [(0, 1), (5, 22), (69, 70), (16, 70)]:
         assert torch.equal(cuda().linear(x[start:stop].contiguous(), w), whole[start:stop])
