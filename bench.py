@@ -47,6 +47,9 @@ def parse_args():
     parser.add_argument("--skip-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profiling)")
+    parser.add_argument("--context-mean", type=int, default=CONTEXT_MEAN,
+                        help="context length the timed steps are centred on (default 3072)")
     return parser.parse_args()
 
 
@@ -172,19 +175,27 @@ def time_decode(runner, request_ids, vocab, steps, warmup):
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = cuda_ops.launches
+    replays_before = runner.graph_replays
+    host_started = time.perf_counter()
     start.record()
     for _ in range(steps):
         one_step()
     end.record()
+    host_ms = (time.perf_counter() - host_started) * 1e3
     torch.cuda.synchronize()
-    return start.elapsed_time(end), cuda_ops.launches - launches_before
+    launched = cuda_ops.launches - launches_before
+    launched += (runner.graph_replays - replays_before) * runner.launches_per_replay(batch, True)
+    print(f"[bench] batch {batch}: device {start.elapsed_time(end) / steps:.3f} ms/step, host issue "
+          f"{host_ms / steps:.3f} ms/step, graph replays {runner.graph_replays - replays_before}", file=sys.stderr)
+    return start.elapsed_time(end), launched
 
 
-def decode_point(layers, batch, steps, warmup):
+def decode_point(layers, batch, steps, warmup, context_mean=CONTEXT_MEAN, graphs=True):
     import torch
 
-    prefix = CONTEXT_MEAN - (steps + warmup) // 2
+    prefix = max(1, context_mean - (steps + warmup) // 2)
     config, model, runner = build_runner(layers, batch, CONTEXT)
+    runner.use_graphs = runner.use_graphs and graphs
     ids = [f"d{i}" for i in range(batch)]
     fill(runner, ids, prefix, config.vocab_size)
     torch.cuda.synchronize()
@@ -274,10 +285,11 @@ def run_ours(args):
     numbers = model_numbers(config, layers)
 
     with ClockSampler() as clocks:
-        ms, launches, prefix = decode_point(layers, args.batch, args.steps, args.warmup)
+        ms, launches, prefix = decode_point(layers, args.batch, args.steps, args.warmup, args.context_mean,
+                                            not args.no_graphs)
     ms_per_step = ms / args.steps
     value = args.batch * args.steps / (ms / 1e3)
-    step_bytes = numbers["weight_bytes"] + args.batch * CONTEXT_MEAN * numbers["kv_bytes_per_token"]
+    step_bytes = numbers["weight_bytes"] + args.batch * args.context_mean * numbers["kv_bytes_per_token"]
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
 
     record = {
@@ -289,7 +301,7 @@ def run_ours(args):
                    "hidden": config.hidden_size, "q_heads": config.num_attention_heads,
                    "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
                    "intermediate": config.intermediate_size, "vocab": config.vocab_size, "tied_head": True,
-                   "global_batch": args.batch, "seq_len": CONTEXT, "context_mean": CONTEXT_MEAN,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "context_mean": args.context_mean,
                    "prefix": prefix, "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights + KV > 1 GB)",
                    "peaks": peak["source"]},

@@ -146,7 +146,7 @@ class ContinuousBatchEngine:
                     indices.append(len(request.generated_token_ids))
                     emitting.append(item.request_id)
             with _nvtx_range(self.enable_nvtx, f"model.step:tokens={batch.token_count}"):
-                _, tokens = self.runner.step(entries, SamplingRows(temperatures, seeds, indices))
+                _, tokens = self.runner.step(entries, SamplingRows(temperatures, seeds, indices), borrow=True)
         except Exception:
             with _nvtx_range(self.enable_nvtx, "engine.rollback"):
                 admitted = tuple(rid for rid in batch.admitted_request_ids

@@ -137,6 +137,17 @@ class _Packer:
         self.size += (array.nbytes + 15) // 16 * 16
 
 
+@dataclass
+class _CapturedStep:
+    """A decode step of one batch size as a CUDA graph with its fixed metadata buffer."""
+
+    metadata: torch.Tensor
+    graph: "torch.cuda.CUDAGraph | None" = None
+    logits: torch.Tensor | None = None
+    tokens: torch.Tensor | None = None
+    launches: int = 0      # kernels in the graph
+
+
 _TORCH_OF = {np.dtype(np.int32): torch.int32, np.dtype(np.int64): torch.int64,
              np.dtype(np.float32): torch.float32}
 
@@ -154,19 +165,33 @@ class ModelRunner:
         self.max_positions = model.spec.max_positions
         self._ring = _PinnedRing(self.device)
         self._device_meta: torch.Tensor | None = None
+        self._last_layout_bytes = 0
         self.steps_run = 0
+        # Decode-only steps (one token per request, its logits wanted) are captured into CUDA
+        # graphs, one per batch size, and replayed: a decode step is some two hundred small
+        # kernels, and launching them one by one from the host costs more than running them.
+        self.use_graphs = (self.device.type == "cuda"
+                           and all(getattr(part, "graph_safe", False) for part in model.parts()))
+        self.graph_max_batch = 256
+        self._graphs: dict[tuple[int, bool], _CapturedStep] = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ metadata
-    def _upload(self, packer: _Packer) -> dict[str, torch.Tensor]:
+    def _upload(self, packer: _Packer, device_buffer: torch.Tensor | None = None) -> dict[str, torch.Tensor]:
+        """Copy the packed arrays to the device in one transfer and return views of them.  With
+        ``device_buffer`` (a captured graph's own metadata buffer) the views have fixed addresses."""
         nbytes = max(packer.size, 16)
         staging, index = self._ring.stage(nbytes)
         host = staging.numpy()
         for _, array, offset in packer.items:
             host[offset:offset + array.nbytes] = array.view(np.uint8).reshape(-1)
-        if self._device_meta is None or self._device_meta.numel() < nbytes:
-            size = max(1 << 16, 1 << (nbytes - 1).bit_length())
-            self._device_meta = torch.empty(size, dtype=torch.uint8, device=self.device)
-        device_buffer = self._device_meta
+        if device_buffer is None:
+            if self._device_meta is None or self._device_meta.numel() < nbytes:
+                size = max(1 << 16, 1 << (nbytes - 1).bit_length())
+                self._device_meta = torch.empty(size, dtype=torch.uint8, device=self.device)
+            device_buffer = self._device_meta
+        elif device_buffer.numel() < nbytes:
+            raise RuntimeError("a captured step's metadata outgrew its buffer")
         device_buffer[:nbytes].copy_(staging[:nbytes], non_blocking=True)
         self._ring.sent(index)
         out = {}
@@ -176,7 +201,11 @@ class ModelRunner:
         return out
 
     def _build_context(self, entries: Sequence[StepEntry], requests: list[RequestCache],
-                       sampling: SamplingRows | None = None) -> StepContext:
+                       sampling: SamplingRows | None = None, *, fixed_width: int | None = None,
+                       device_buffer: torch.Tensor | None = None) -> StepContext:
+        """Host-side description of the step, sent to the device.  ``fixed_width`` pins the block
+        tables' width (and with it the whole buffer layout for a given batch shape), which a
+        captured graph needs; ``device_buffer`` is that graph's own metadata buffer."""
         cache = self.cache
         lengths = np.array([len(e.tokens) for e in entries], dtype=np.int32)
         row_start = np.zeros(len(entries), dtype=np.int32)
@@ -191,15 +220,20 @@ class ModelRunner:
         wanted = [row_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
         wanted_rows = np.concatenate(wanted).astype(np.int32) if wanted else np.zeros(0, dtype=np.int32)
 
-        tiles_per_segment = (lengths + ROWS_PER_TILE - 1) // ROWS_PER_TILE
-        tile_seg = np.repeat(np.arange(len(entries), dtype=np.int32), tiles_per_segment)
+        # Attention tiles of at most 16 rows: segments longer than one row first, then the
+        # single-row (decode) segments, which a split-KV kernel may take instead.
+        decode_seg = np.flatnonzero(lengths == 1).astype(np.int32)
+        order = np.concatenate([np.flatnonzero(lengths != 1), decode_seg]).astype(np.int32)
+        tiles_per_segment = ((lengths + ROWS_PER_TILE - 1) // ROWS_PER_TILE)[order]
+        tile_seg = np.repeat(order, tiles_per_segment)
         tile_first = np.zeros(len(entries), dtype=np.int32)
         np.cumsum(tiles_per_segment[:-1], out=tile_first[1:])
-        tile_row0 = ((np.arange(len(tile_seg), dtype=np.int32) - tile_first[tile_seg]) * ROWS_PER_TILE).astype(np.int32)
+        tile_row0 = ((np.arange(len(tile_seg), dtype=np.int32) - np.repeat(tile_first, tiles_per_segment))
+                     * ROWS_PER_TILE).astype(np.int32)
 
         slots = np.array([r.slot for r in requests], dtype=np.int32)
         kv_end = position_start + lengths
-        table_width = max(1, int(-(-int(kv_end.max()) // cache.page_size)))
+        table_width = fixed_width or max(1, int(-(-int(kv_end.max()) // cache.page_size)))
 
         packer = _Packer()
         packer.add("token_ids", token_ids)
@@ -211,6 +245,7 @@ class ModelRunner:
         packer.add("seg_slots", slots)
         packer.add("tile_seg", tile_seg)
         packer.add("tile_row0", tile_row0)
+        packer.add("decode_seg", decode_seg)
         for group in cache.groups:
             rows_slots = np.concatenate([
                 cache.slot_mapping(group, request, int(position_start[i]), int(lengths[i]))
@@ -224,7 +259,8 @@ class ModelRunner:
             packer.add("temperatures", np.asarray(sampling.temperatures, dtype=np.float32))
             packer.add("seeds", np.asarray(sampling.seeds, dtype=np.int64))
             packer.add("token_indices", np.asarray(sampling.token_indices, dtype=np.int64))
-        dev = self._upload(packer)
+        dev = self._upload(packer, device_buffer)
+        self._last_layout_bytes = packer.size
 
         segments = [Segment(e.request_id, int(slots[i]), int(row_start[i]), int(lengths[i]),
                             int(position_start[i])) for i, e in enumerate(entries)]
@@ -239,7 +275,9 @@ class ModelRunner:
                 seg_q_start=dev["seg_q_start"], seg_q_len=dev["seg_q_len"], seg_pos0=dev["seg_pos0"],
                 block_table=dev[f"table{group.index}"], tile_seg=dev["tile_seg"], tile_row0=dev["tile_row0"],
                 num_segments=len(entries), num_tiles=int(tile_seg.shape[0]),
-                max_q_len=int(lengths.max()), max_kv_len=int(kv_end.max()))
+                max_q_len=int(lengths.max()),
+                max_kv_len=int(kv_end.max()) if fixed_width is None else fixed_width * cache.page_size,
+                decode_seg=dev["decode_seg"], num_decode=int(decode_seg.shape[0]))
         for entry, need in enumerate(cache.needs):
             if entry in cache.entry_group:
                 k_pool, v_pool, group = cache.entry_pools(entry)
@@ -270,19 +308,78 @@ class ModelRunner:
                 raise ValueError(f"request {entry.request_id!r} would reach {held + count} positions, "
                                  f"the model allows {self.max_positions}")
 
+    def _forward(self, ctx: StepContext, sampling: SamplingRows | None):
+        logits = self.model.forward(ctx)
+        tokens = ctx.ops.sample(logits, *ctx.sampling) if sampling is not None else None
+        return logits, tokens
+
+    def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
+        return (self.use_graphs and len(entries) <= self.graph_max_batch
+                and isinstance(ops.current(), ops.CudaOps)
+                and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
+
+    def _graph_step(self, entries, requests, sampling):
+        """A decode-only step through the captured graph of its batch size.  The first step of a
+        size runs eagerly on the graph's fixed buffers and is then captured; later steps only
+        refresh the metadata buffer and replay."""
+        key = (len(entries), sampling is not None)
+        kernels = ops.current()
+        captured = self._graphs.get(key)
+        width = self.cache.max_pages_per_request
+        longest = width * self.cache.page_size
+        kv_heads = max((g.need.num_kv_heads for g in self.cache.groups), default=1)
+        chunk, splits = kernels.plan_decode(len(entries), kv_heads, longest)
+        if captured is None:
+            # learn the layout's size with a throw-away packing, then give the graph its own buffer
+            probe = self._build_context(entries, requests, sampling, fixed_width=width)
+            del probe
+            captured = _CapturedStep(torch.empty(self._last_layout_bytes + 64, dtype=torch.uint8, device=self.device))
+            self._graphs[key] = captured
+        ctx = self._build_context(entries, requests, sampling, fixed_width=width,
+                                  device_buffer=captured.metadata)
+        if captured.graph is not None:
+            captured.graph.replay()
+            self.graph_replays += 1
+            return captured.logits, captured.tokens
+        previous = (kernels.decode_chunk, kernels.decode_max_splits)
+        kernels.decode_chunk, kernels.decode_max_splits = chunk, splits
+        try:
+            logits, tokens = self._forward(ctx, sampling)          # this step's real result, eagerly
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            from ..ops import cuda_ops
+            before = cuda_ops.launches
+            with torch.cuda.graph(graph):
+                captured.logits, captured.tokens = self._forward(ctx, sampling)
+            captured.launches = cuda_ops.launches - before
+            captured.graph = graph
+        finally:
+            kernels.decode_chunk, kernels.decode_max_splits = previous
+        return logits, tokens
+
+    def launches_per_replay(self, batch: int, sampling: bool) -> int:
+        """Kernels one replay of the captured step of this batch size launches (0 if not captured)."""
+        captured = self._graphs.get((batch, sampling))
+        return captured.launches if captured is not None and captured.graph is not None else 0
+
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry], sampling: SamplingRows | None = None):
+    def step(self, entries: Sequence[StepEntry], sampling: SamplingRows | None = None, *,
+             borrow: bool = False):
         """Run the entries as one batch.  Returns float32 logits [wanted places, vocab] on the
         device, in the order of the entries and of each entry's ``want``.  With ``sampling`` it
-        returns ``(logits, tokens)``: one int32 token per wanted place, chosen on the device."""
+        returns ``(logits, tokens)``: one int32 token per wanted place, chosen on the device.
+        ``borrow=True`` may return buffers that the next step overwrites (no copy is made)."""
         self._validate(entries)
         requests = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
         try:
-            ctx = self._build_context(entries, requests, sampling)
-            logits = self.model.forward(ctx)
-            tokens = None
-            if sampling is not None:
-                tokens = ctx.ops.sample(logits, *ctx.sampling)
+            if self._graph_eligible(entries):
+                logits, tokens = self._graph_step(entries, requests, sampling)
+                if not borrow:
+                    logits = logits.clone()
+                    tokens = tokens.clone() if tokens is not None else None
+            else:
+                ctx = self._build_context(entries, requests, sampling)
+                logits, tokens = self._forward(ctx, sampling)
         except BaseException:
             self.cache.abort_step()
             raise

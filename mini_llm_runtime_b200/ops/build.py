@@ -38,6 +38,7 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "attention_generic": (),
     "sampling": (),
     "gemm_tcgen05": (),
+    "attention_decode": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -76,8 +76,10 @@ class AttentionBatch:
     """Device-side description of one step's ragged batch for one cache group.
 
     ``seg_*`` have one entry per request in the step; ``tile_*`` cut every segment into tiles
-    of at most 16 rows (the unit one CTA of the generic kernel works on).  ``block_table`` is
-    int32 [segments, table_width] with -1 where the request holds no page.
+    of at most 16 rows (the unit one CTA of the generic kernel works on), the tiles of segments
+    longer than one row first.  ``decode_seg`` lists the segments of exactly one row (decoded
+    tokens), which a split-KV kernel may take instead of the last ``num_decode`` tiles.
+    ``block_table`` is int32 [segments, table_width] with -1 where the request holds no page.
     """
 
     seg_q_start: torch.Tensor
@@ -90,6 +92,8 @@ class AttentionBatch:
     num_tiles: int
     max_q_len: int
     max_kv_len: int
+    decode_seg: torch.Tensor | None = None
+    num_decode: int = 0
 
 
 class CudaOps:
@@ -103,10 +107,14 @@ class CudaOps:
     name = "cuda"
     GEMM_SCRATCH_BYTES = 32 << 20
     GEMM_COUNTERS = 1 << 15
+    ATTENTION_COUNTERS = 1 << 16
 
     def __init__(self) -> None:
         self._workspaces: dict[int, dict[str, torch.Tensor]] = {}
         self.use_tensor_cores = True
+        self.use_decode_kernel = True
+        self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
+        self.decode_max_splits: int | None = None  # None: just enough for the longest context
 
     def _workspace(self, device: torch.device) -> dict[str, torch.Tensor]:
         index = device.index if device.index is not None else torch.cuda.current_device()
@@ -114,6 +122,8 @@ class CudaOps:
             self._workspaces[index] = {
                 "gemm_scratch": torch.empty(self.GEMM_SCRATCH_BYTES, dtype=torch.uint8, device=device),
                 "gemm_counters": torch.zeros(self.GEMM_COUNTERS, dtype=torch.int32, device=device),
+                "attention_counters": torch.zeros(self.ATTENTION_COUNTERS, dtype=torch.int32, device=device),
+                "attention_scratch": torch.empty(8 << 20, dtype=torch.uint8, device=device),
                 # written by a kernel whose bounded wait ran out; read by the host without a copy
                 "error_word": torch.zeros(1, dtype=torch.int32).pin_memory(),
             }
@@ -271,14 +281,50 @@ class CudaOps:
             raise KernelError(f"page pools have shape {tuple(k_pool.shape)}, expected "
                               f"[pages, {num_kv_heads}, page_size, {head_dim}]")
         out = torch.empty_like(q)
-        lib = build.load_library("attention_generic")
-        _check(lib.mlr_attention_generic(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.tile_seg), _ptr(batch.tile_row0),
-            _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
-            batch.block_table.shape[1], batch.num_tiles, num_heads, num_kv_heads, head_dim,
-            k_pool.shape[2], int(window or 0), ctypes.c_float(scale), _code(q.dtype), _stream()),
-            "paged_attention")
+        generic_tiles = batch.num_tiles
+        group = num_heads // num_kv_heads
+        if (self.use_decode_kernel and batch.num_decode > 0 and batch.decode_seg is not None
+                and q.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 8
+                and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS):
+            self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window)
+            generic_tiles -= batch.num_decode
+        if generic_tiles > 0:
+            lib = build.load_library("attention_generic")
+            _check(lib.mlr_attention_generic(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.tile_seg), _ptr(batch.tile_row0),
+                _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
+                batch.block_table.shape[1], generic_tiles, num_heads, num_kv_heads, head_dim,
+                k_pool.shape[2], int(window or 0), ctypes.c_float(scale), _code(q.dtype), _stream()),
+                "paged_attention")
         return out
+
+    @staticmethod
+    def plan_decode(num_decode: int, num_kv_heads: int, longest: int) -> tuple[int, int]:
+        """(chunk, splits): keys per CTA so that the grid has about two CTAs per SM."""
+        chunk = 512
+        while chunk > 128 and num_decode * num_kv_heads * -(-longest // chunk) < 2 * 148:
+            chunk //= 2
+        return chunk, max(1, -(-longest // chunk))
+
+    def _decode_attention(self, q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window):
+        lib = build.load_library("attention_decode")
+        chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len)
+        if self.decode_chunk is not None:
+            chunk = self.decode_chunk
+            splits = max(1, -(-batch.max_kv_len // chunk))
+        if self.decode_max_splits is not None:
+            splits = max(splits, self.decode_max_splits)
+        lib.mlr_attention_decode_scratch.restype = ctypes.c_longlong
+        need = lib.mlr_attention_decode_scratch(batch.num_decode, num_heads, head_dim, splits)
+        space = self._workspace(q.device)
+        if need > space["attention_scratch"].numel():
+            space["attention_scratch"] = torch.empty(int(need * 1.5), dtype=torch.uint8, device=q.device)
+        _check(lib.mlr_attention_decode(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.decode_seg), _ptr(batch.seg_q_start),
+            _ptr(batch.seg_pos0), _ptr(batch.block_table), batch.block_table.shape[1], batch.num_decode,
+            num_heads, num_kv_heads, head_dim, k_pool.shape[2], int(window or 0), ctypes.c_float(scale), chunk,
+            splits, _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _stream()),
+            "decode attention")
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,

@@ -17,6 +17,8 @@ from .base import KVCacheNeed, Mixer, TensorSpec, build_part, register_part
 
 
 class GQAAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
         a = self.args

@@ -64,6 +64,10 @@ class Part:
     """Base of all parts.  ``compute_dtype`` is float32 or bfloat16 for the whole model."""
 
     category = ""
+    # True if forward() only launches kernels whose arguments are device buffers of the step
+    # context (no host-side dependence on the batch's contents): such a part can be captured
+    # into a CUDA graph and replayed for other batches of the same shape.
+    graph_safe = False
 
     def __init__(self, spec: PartSpec, compute_dtype: torch.dtype) -> None:
         self.spec = spec

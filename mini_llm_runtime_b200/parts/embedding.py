@@ -15,6 +15,8 @@ from .base import Embedding, Head, TensorSpec, register_part
 
 
 class TokenEmbedding(Embedding):
+    graph_safe = True
+
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
         self.vocab_size = int(self.args["vocab_size"])
@@ -34,6 +36,8 @@ class TokenEmbedding(Embedding):
 class TiedHead(Head):
     """logits = x E^T.  A checkpoint may still carry ``lm_head.weight``; it must then equal the
     embedding (reference rule: src/mini_llm_runtime/qwen_weights.py:113-119)."""
+
+    graph_safe = True
 
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
@@ -59,6 +63,8 @@ class TiedHead(Head):
 
 
 class LinearHead(Head):
+    graph_safe = True
+
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
         self.vocab_size = int(self.args["vocab_size"])

@@ -11,6 +11,8 @@ from .base import FeedForward, TensorSpec, register_part
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
         self.hidden_size = int(self.args["hidden_size"])

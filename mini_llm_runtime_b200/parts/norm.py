@@ -12,6 +12,8 @@ from .base import Norm, TensorSpec, register_part
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
         self.size = int(self.args["size"])

@@ -16,6 +16,8 @@ from .base import PositionEncoding, register_part
 
 
 class RotateHalfRope(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
         self.head_dim = int(self.args["head_dim"])

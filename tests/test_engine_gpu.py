@@ -148,3 +148,22 @@ def test_failed_step_leaves_no_trace(setup):
     want = small.plain_logits(tokens)
     assert_close(first, want[2 * page - 1:2 * page], dtype, "before the failed step")
     assert_close(rest, want[2 * page:], dtype, "after the failed step")
+
+
+def test_decode_steps_replay_a_captured_graph(setup):
+    """Decode-only steps of one batch size run through a CUDA graph after the first; the logits
+    must not change because of it, whatever the requests' lengths and slots."""
+    name, dtype, engine, requests = setup
+    config, page = TINY[name]
+    fresh = TinyEngine(config, page, dtype, DEVICE, num_pages=64, max_requests=4, max_tokens=256,
+                       tensors=engine.tensors)
+    assert fresh.runner.use_graphs
+    prompts = {rid: random_prompt(config.vocab_size, n, 90 + n) for rid, n in (("u", 40), ("v", 27), ("w", 23))}
+    steps = [{"entries": [(rid, 0, len(t) - 20) for rid, t in prompts.items()], "end": []}]
+    for k in range(20):
+        order = ["u", "v", "w"] if k % 2 == 0 else ["w", "u", "v"]
+        steps.append({"entries": [(rid, len(prompts[rid]) - 20 + k, len(prompts[rid]) - 19 + k) for rid in order],
+                      "end": list(prompts) if k == 19 else []})
+    results = replay(fresh, prompts, steps)
+    assert fresh.runner.graph_replays >= 18
+    check_all(fresh, prompts, results, dtype, "graph replay")

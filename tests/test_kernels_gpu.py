@@ -177,11 +177,16 @@ def make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, seed, 
             v_pool[pg, :, off] = torch.randn(kv_heads, head_dim, generator=generator)
     rows = sum(q for _, q in segments)
     q = torch.randn(rows, heads * head_dim, generator=generator)
-    q_start, tile_seg, tile_row0, row = [], [], [], 0
-    for s, (pos0, q_len) in enumerate(segments):
+    q_start, row = [], 0
+    for _, q_len in segments:
         q_start.append(row)
         row += q_len
-        for r0 in range(0, q_len, 16):
+    # tiles of segments longer than one row first, single-row (decode) segments last
+    decode = [s for s, (_, q_len) in enumerate(segments) if q_len == 1]
+    order = [s for s, (_, q_len) in enumerate(segments) if q_len != 1] + decode
+    tile_seg, tile_row0 = [], []
+    for s in order:
+        for r0 in range(0, segments[s][1], 16):
             tile_seg.append(s)
             tile_row0.append(r0)
 
@@ -194,7 +199,8 @@ def make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, seed, 
             seg_pos0=ints([p for p, _ in segments], device), block_table=table.to(device),
             tile_seg=ints(tile_seg, device), tile_row0=ints(tile_row0, device),
             num_segments=len(segments), num_tiles=len(tile_seg),
-            max_q_len=max(q for _, q in segments), max_kv_len=max(p + q for p, q in segments))
+            max_q_len=max(q for _, q in segments), max_kv_len=max(p + q for p, q in segments),
+            decode_seg=ints(decode, device), num_decode=len(decode))
 
     return q.to(dtype), k_pool.to(dtype), v_pool.to(dtype), batch, table
 
@@ -217,6 +223,32 @@ def test_attention_ragged_batch(dtype, heads, kv_heads, head_dim, page):
     q, k_pool, v_pool, batch, _ = make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, 21)
     got, want = run_attention_both(dtype, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
     assert_close(got, want, dtype, "attention")
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (3, 1, 128, 8), (8, 8, 64, 16), (8, 1, 128, 32), (5, 1, 64, 3)])
+@pytest.mark.parametrize("chunk", [None, 128, 512])
+def test_decode_attention_split_kv(heads, kv_heads, head_dim, page, chunk):
+    """Single-row segments go through the split-KV kernel: contexts around the warp (32), CTA (128)
+    and chunk boundaries, beside a prompt portion that takes the other kernel."""
+    contexts = [0, 1, 30, 31, 32, 33, 126, 127, 128, 129, 255, 256, 511, 512, 513, 700, 1500]
+    segments = [(c, 1) for c in contexts[:9]] + [(40, 21)] + [(c, 1) for c in contexts[9:]]
+    q, k_pool, v_pool, batch, _ = make_attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, segments, 25)
+    cuda().decode_chunk = chunk
+    try:
+        for window in (None, 100):
+            got, want = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+            assert_close(got, want, torch.bfloat16, f"decode attention chunk={chunk} window={window}")
+            again, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+            assert torch.equal(got, again), "chunks are merged in a fixed order: same bits every time"
+    finally:
+        cuda().decode_chunk = None
+    cuda().use_decode_kernel = False
+    try:
+        generic, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+    finally:
+        cuda().use_decode_kernel = True
+    both, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+    assert_close(both, generic, torch.bfloat16, "split-KV kernel against the generic kernel")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
