@@ -254,3 +254,56 @@ MLR_EXPORT int mlr_attention_decode(const void* q, const void* k_pool, const voi
         max_splits);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate (declared in attention_decode_static.h).
+// Same kernel as above; the partial states and the per-(request, kv head) counters live in a
+// fixed array inside this library instead of a buffer the caller allocates.
+// ---------------------------------------------------------------------------------------------
+namespace mlr {
+
+constexpr size_t STATIC_STATE_BYTES = 4u << 20;       // partial softmax states
+constexpr size_t STATIC_COUNTER_BYTES = 64u << 10;    // 16384 counters
+static __device__ __align__(256) unsigned char static_scratch[STATIC_STATE_BYTES + STATIC_COUNTER_BYTES];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+static void* static_scratch_address[STATIC_MAX_DEVICES];   // device address of the array, per device
+
+}  // namespace mlr
+
+MLR_EXPORT long long mlr_attention_decode_static_capacity(void) { return (long long)STATIC_STATE_BYTES; }
+
+MLR_EXPORT int mlr_attention_decode_static(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                           const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
+                                           const int* block_table, int table_width, int rows, int heads,
+                                           int kv_heads, int head_dim, int page_size, int window, float scale,
+                                           int chunk, int max_splits, cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || heads <= 0 || kv_heads <= 0 || max_splits <= 0 || (head_dim != 64 && head_dim != 128))
+    return MLR_BAD_SIZE;
+  // Refuse what does not fit the fixed array: the caller cannot be given more, and must not be
+  // given less than the kernel will write.
+  if (mlr_attention_decode_scratch(rows, heads, head_dim, max_splits) > (long long)STATIC_STATE_BYTES ||
+      (size_t)rows * kv_heads * sizeof(int) > STATIC_COUNTER_BYTES)
+    return MLR_TOO_LARGE;
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return (int)err;
+  if (device < 0 || device >= STATIC_MAX_DEVICES) return MLR_TOO_LARGE;
+  if (static_scratch_address[device] == nullptr) {
+    // In host code `static_scratch` is only a handle; the kernel needs the array's address on the
+    // current device, which the runtime reports here.  Done once per device.
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, static_scratch);
+    if (err != cudaSuccess) return (int)err;
+    static_scratch_address[device] = address;
+  }
+  unsigned char* base = (unsigned char*)static_scratch_address[device];
+  int* counters = (int*)(base + STATIC_STATE_BYTES);
+  // The array keeps whatever the previous call left; the counters must start at zero.
+  err = cudaMemsetAsync(counters, 0, (size_t)rows * kv_heads * sizeof(int), stream);
+  if (err != cudaSuccess) return (int)err;
+  return mlr_attention_decode(q, k_pool, v_pool, out, decode_seg, seg_q_start, seg_pos0, block_table,
+                              table_width, rows, heads, kv_heads, head_dim, page_size, window, scale, chunk,
+                              max_splits, base, counters, stream);
+}
