@@ -1,0 +1,520 @@
+// Tensor-core attention over the paged bfloat16 K/V cache (head_dim 64 or 128), two kernels that
+// share their tile loader and fragment code:
+//
+//   prefill_attention_kernel  rows = the query positions of a prompt portion.  One CTA owns 64
+//       rows of one query head; its 4 warps own 16 rows each and walk the request's keys in tiles
+//       of 64, K and V fetched page by page with cp.async into swizzled shared memory (double
+//       buffered), S = Q K^T and O += P V on mma.sync m16n8k16 (bfloat16 in, float32 out), the
+//       online softmax kept in registers.  Causal limit, window and the portion's start position
+//       are applied per element, so a portion in the middle of a request reads earlier keys from
+//       the cache exactly like a whole prompt.
+//   decode_attention_mma_kernel  rows = the query heads that share one kv head (one decoded token).
+//       One CTA owns (request, kv head, chunk of keys); its 4 warps take 16 keys each of every
+//       64-key tile, all tiles of the chunk are requested up front (4 cp.async stages in flight),
+//       the warps' states are merged in shared memory, and the chunks' states are merged by the CTA
+//       that finishes last for that (request, kv head), in chunk order.
+//
+// Semantics as in the reference (scores = q.k * head_dim^-0.5, float32 softmax with running max and
+// sum, csrc/paged_attention_cuda.cu:50-105; GQA head mapping :44-46; causal mask
+// src/mini_llm_runtime/qwen_model_runner.py:157-177).  Keys beyond a row's limit, and slots of pages
+// the request does not hold, are loaded as zeros and their scores set to -inf before the softmax.
+//
+// mma.sync is the legacy tensor path on sm_100a; attention here is far from the bound of either
+// path for the model sizes served (the projections dominate), and tcgen05 serves those.
+#include "common.cuh"
+
+namespace mlr {
+
+constexpr int ATTN_WARPS = 4;
+constexpr int ATTN_THREADS = ATTN_WARPS * 32;
+constexpr int TILE_Q = 64;
+constexpr int TILE_KV = 64;
+constexpr int DECODE_STAGES = 4;
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // 0: the 16 destination bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(shared_address(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(shared_address(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(shared_address(p)));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&pair);
+}
+
+// A tile in shared memory: rows of D bfloat16, the 16-byte chunks of a row XOR-swizzled by the row
+// index so that ldmatrix (8 rows x 16 bytes) is free of bank conflicts.
+template <int D>
+__device__ __forceinline__ bf16* tile_at(bf16* tile, int row, int chunk) {
+  return tile + row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+// Fetch `rows` rows starting at key `key0` of one kv head into a swizzled tile.  Keys outside
+// [key_lo, key_hi] and keys on pages the request does not hold become zeros.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ pool, const int* __restrict__ table,
+                                             int key0, int rows, int key_lo, int key_hi, int kv_heads, int kv_head,
+                                             int page_size) {
+  constexpr int CHUNKS = D / 8;
+  for (int item = threadIdx.x; item < rows * CHUNKS; item += ATTN_THREADS) {
+    const int r = item / CHUNKS, c = item - r * CHUNKS;
+    const int key = key0 + r;
+    bool valid = key >= key_lo && key <= key_hi;
+    const bf16* src = pool;
+    if (valid) {
+      const int page = table[key / page_size];
+      valid = page >= 0;
+      if (valid) src = pool + (((size_t)page * kv_heads + kv_head) * page_size + key % page_size) * D + c * 8;
+    }
+    cp_async_16(tile_at<D>(tile, r, c), src, valid);
+  }
+}
+
+// One warp: S[16 x (8*NT)] = Q[16 x D] K^T for keys key_row0.. of a K tile.
+template <int D, int NT>
+__device__ __forceinline__ void warp_qk(float (*s)[4], const uint32_t (*q_frag)[4], bf16* k_tile, int key_row0, int lane) {
+#pragma unroll
+  for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int jp = 0; jp < NT / 2; ++jp) {
+      uint32_t b[4];
+      const int key = key_row0 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int chunk = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(b, tile_at<D>(k_tile, key, chunk));
+      mma_bf16(s[2 * jp], q_frag[ks], b[0], b[1]);
+      mma_bf16(s[2 * jp + 1], q_frag[ks], b[2], b[3]);
+    }
+  }
+}
+
+// One warp: O[16 x D] += P[16 x (8*NT)] V for keys key_row0.. of a V tile; P comes from the score
+// registers, rounded to bfloat16.
+template <int D, int NT>
+__device__ __forceinline__ void warp_pv(float (*o)[4], const float (*p)[4], bf16* v_tile, int key_row0, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+    a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+    a[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+    a[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+      uint32_t b[4];
+      const int key = key_row0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      const int chunk = dp * 2 + (lane >> 4);
+      ldmatrix_x4_trans(b, tile_at<D>(v_tile, key, chunk));
+      mma_bf16(o[2 * dp], a, b[0], b[1]);
+      mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Online softmax step on one warp's score fragment.  Thread owns rows r0 = lane/4 and r0 + 8;
+// limit_lo[i] <= key <= limit_hi[i] are visible for row i.  Scores arrive unscaled; `scale_log2`
+// = head_dim^-0.5 * log2(e).  Leaves probabilities in s and rescales o.
+template <int NT, int OT>
+__device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, int key_base,
+                                             const int* limit_lo, const int* limit_hi, float scale_log2, int lane) {
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key_base + j * 8 + (lane & 3) * 2 + (e & 1);
+      const int i = e >> 1;
+      const bool visible = key >= limit_lo[i] && key <= limit_hi[i];
+      s[j][e] = visible ? s[j][e] * scale_log2 : -INFINITY;
+      tile_max[i] = fmaxf(tile_max[i], s[j][e]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 1));
+    tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 2));
+  }
+  float alpha[2], row_sum[2] = {0.f, 0.f}, base[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float m_new = fmaxf(m[i], tile_max[i]);
+    base[i] = m_new == -INFINITY ? 0.f : m_new;       // nothing visible yet: keep everything at zero
+    alpha[i] = exp2f(m[i] - base[i]);                  // m = -inf gives 0
+    m[i] = m_new;
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float prob = exp2f(s[j][e] - base[e >> 1]);   // -inf gives 0
+      s[j][e] = prob;
+      row_sum[e >> 1] += prob;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    row_sum[i] += __shfl_xor_sync(0xffffffffu, row_sum[i], 1);
+    row_sum[i] += __shfl_xor_sync(0xffffffffu, row_sum[i], 2);
+    l[i] = l[i] * alpha[i] + row_sum[i];
+  }
+#pragma unroll
+  for (int t = 0; t < OT; ++t) {
+    o[t][0] *= alpha[0]; o[t][1] *= alpha[0];
+    o[t][2] *= alpha[1]; o[t][3] *= alpha[1];
+  }
+}
+
+// ------------------------------------------------------------------------------------------ prefill
+template <int D>
+__global__ void __launch_bounds__(ATTN_THREADS)
+prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                         bf16* __restrict__ out, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
+                         const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
+                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int table_width,
+                         int heads, int kv_heads, int page_size, int window, float scale_log2) {
+  extern __shared__ __align__(128) uint8_t attn_shared[];
+  bf16* q_tile = reinterpret_cast<bf16*>(attn_shared);         // [64][D]
+  bf16* k_tiles = q_tile + TILE_Q * D;                          // 2 x [64][D]
+  bf16* v_tiles = k_tiles + 2 * TILE_KV * D;                    // 2 x [64][D]
+
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int kv_head = head / (heads / kv_heads);
+  const int seg = tile_seg[tile], row0 = tile_row0[tile];
+  const int q_start = seg_q_start[seg], q_len = seg_q_len[seg], pos0 = seg_pos0[seg];
+  const int rows = min(TILE_Q, q_len - row0);
+  const int* table = block_table + (size_t)seg * table_width;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int first_pos = pos0 + row0, last_pos = first_pos + rows - 1;
+  const int lowest = window > 0 ? max(0, first_pos - window + 1) : 0;
+  const int tile_begin = lowest / TILE_KV, tile_end = last_pos / TILE_KV;   // inclusive
+
+  // Q tile (rows beyond the segment are zeros) and the first K/V tile
+  constexpr int CHUNKS = D / 8;
+  for (int item = threadIdx.x; item < TILE_Q * CHUNKS; item += ATTN_THREADS) {
+    const int r = item / CHUNKS, c = item - r * CHUNKS;
+    const bool valid = r < rows;
+    const bf16* src = valid ? q + ((size_t)(q_start + row0 + r) * heads + head) * D + c * 8 : q;
+    cp_async_16(tile_at<D>(q_tile, r, c), src, valid);
+  }
+  load_kv_tile<D>(k_tiles, k_pool, table, tile_begin * TILE_KV, TILE_KV, lowest, last_pos, kv_heads, kv_head, page_size);
+  load_kv_tile<D>(v_tiles, v_pool, table, tile_begin * TILE_KV, TILE_KV, lowest, last_pos, kv_heads, kv_head, page_size);
+  cp_async_commit();
+
+  // per-thread rows and their visibility limits
+  int limit_lo[2], limit_hi[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + (lane >> 2) + 8 * i;
+    const int position = first_pos + r;
+    limit_hi[i] = r < rows ? position : -1;                       // rows past the segment see nothing
+    limit_lo[i] = window > 0 ? max(0, position - window + 1) : 0;
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  uint32_t q_frag[D / 16][4];
+
+  for (int t = tile_begin; t <= tile_end; ++t) {
+    const int buffer = (t - tile_begin) & 1;
+    if (t < tile_end) {
+      const int next = buffer ^ 1;
+      load_kv_tile<D>(k_tiles + next * TILE_KV * D, k_pool, table, (t + 1) * TILE_KV, TILE_KV, lowest, last_pos,
+                      kv_heads, kv_head, page_size);
+      load_kv_tile<D>(v_tiles + next * TILE_KV * D, v_pool, table, (t + 1) * TILE_KV, TILE_KV, lowest, last_pos,
+                      kv_heads, kv_head, page_size);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (t == tile_begin) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int r = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        ldmatrix_x4(q_frag[ks], tile_at<D>(q_tile, r, ks * 2 + (lane >> 4)));
+      }
+    }
+    // a warp whose rows all end before this tile has nothing left to do in it
+    const int warp_last = first_pos + min(rows - 1, warp * 16 + 15);
+    if (warp * 16 < rows && t * TILE_KV <= warp_last) {
+      float s[TILE_KV / 8][4];
+      warp_qk<D, TILE_KV / 8>(s, q_frag, k_tiles + buffer * TILE_KV * D, 0, lane);
+      softmax_step<TILE_KV / 8, D / 8>(s, o, m, l, t * TILE_KV, limit_lo, limit_hi, scale_log2, lane);
+      warp_pv<D, TILE_KV / 8>(o, s, v_tiles + buffer * TILE_KV * D, 0, lane);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + (lane >> 2) + 8 * i;
+    if (r >= rows) continue;
+    const float inv = 1.f / l[i];
+    bf16* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * D + (lane & 3) * 2;
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t)
+      *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16(o[t][2 * i] * inv, o[t][2 * i + 1] * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ decode
+template <int D>
+__global__ void __launch_bounds__(ATTN_THREADS)
+decode_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                            bf16* __restrict__ out, const int* __restrict__ decode_seg,
+                            const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
+                            const int* __restrict__ block_table, int table_width, int heads, int kv_heads,
+                            int page_size, int window, float scale_log2, int chunk, float* __restrict__ scratch,
+                            int* __restrict__ counters, int max_splits) {
+  constexpr int STATE = D + 2;
+  extern __shared__ __align__(128) uint8_t attn_shared[];
+  bf16* q_tile = reinterpret_cast<bf16*>(attn_shared);            // [16][D], rows >= group are zeros
+  bf16* k_tiles = q_tile + 16 * D;                                 // STAGES x [64][D]
+  bf16* v_tiles = k_tiles + DECODE_STAGES * TILE_KV * D;           // STAGES x [64][D]
+  float* merge = reinterpret_cast<float*>(v_tiles + DECODE_STAGES * TILE_KV * D);   // [4 warps][16][D + 2]
+  __shared__ int last_flag;
+
+  const int group = heads / kv_heads;
+  const int split = blockIdx.x, kv_head = blockIdx.y, index = blockIdx.z;
+  const int seg = decode_seg[index];
+  const int row = seg_q_start[seg];
+  const int position = seg_pos0[seg];
+  const int lowest = window > 0 ? max(0, position - window + 1) : 0;
+  const int first_chunk = lowest / chunk;
+  const int splits = position / chunk - first_chunk + 1;
+  if (split >= splits) return;
+  const int k_begin = max(lowest, (first_chunk + split) * chunk);
+  const int k_end = min(position + 1, (first_chunk + split + 1) * chunk);   // exclusive
+  const int* table = block_table + (size_t)seg * table_width;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_begin = k_begin / TILE_KV, tile_end = (k_end - 1) / TILE_KV;   // inclusive
+  const int tiles = tile_end - tile_begin + 1;
+
+  constexpr int CHUNKS = D / 8;
+  for (int item = threadIdx.x; item < 16 * CHUNKS; item += ATTN_THREADS) {
+    const int g = item / CHUNKS, c = item - g * CHUNKS;
+    const bool valid = g < group;
+    const bf16* src = valid ? q + ((size_t)row * heads + kv_head * group + g) * D + c * 8 : q;
+    cp_async_16(tile_at<D>(q_tile, g, c), src, valid);
+  }
+  // request the first tiles of the chunk at once: their latencies overlap
+#pragma unroll
+  for (int s = 0; s < DECODE_STAGES; ++s) {
+    if (s < tiles) {
+      load_kv_tile<D>(k_tiles + s * TILE_KV * D, k_pool, table, (tile_begin + s) * TILE_KV, TILE_KV, k_begin, k_end - 1,
+                      kv_heads, kv_head, page_size);
+      load_kv_tile<D>(v_tiles + s * TILE_KV * D, v_pool, table, (tile_begin + s) * TILE_KV, TILE_KV, k_begin, k_end - 1,
+                      kv_heads, kv_head, page_size);
+    }
+    cp_async_commit();     // one group per stage, empty or not, so that the wait counts line up
+  }
+
+  int limit_lo[2] = {k_begin, k_begin}, limit_hi[2];
+  limit_hi[0] = (lane >> 2) < group ? k_end - 1 : -1;          // rows that are no real head see nothing
+  limit_hi[1] = (lane >> 2) + 8 < group ? k_end - 1 : -1;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  uint32_t q_frag[D / 16][4];
+
+  for (int t = 0; t < tiles; ++t) {
+    const int stage = t % DECODE_STAGES;
+    cp_async_wait<DECODE_STAGES - 1>();
+    __syncthreads();
+    if (t == 0) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int r = (lane & 7) + (((lane >> 3) & 1) << 3);
+        ldmatrix_x4(q_frag[ks], tile_at<D>(q_tile, r, ks * 2 + (lane >> 4)));
+      }
+    }
+    const int key0 = (tile_begin + t) * TILE_KV + warp * 16;     // this warp's 16 keys of the tile
+    if (key0 < k_end && key0 + 16 > k_begin) {
+      float s[2][4];
+      warp_qk<D, 2>(s, q_frag, k_tiles + stage * TILE_KV * D, warp * 16, lane);
+      softmax_step<2, D / 8>(s, o, m, l, key0, limit_lo, limit_hi, scale_log2, lane);
+      warp_pv<D, 2>(o, s, v_tiles + stage * TILE_KV * D, warp * 16, lane);
+    }
+    __syncthreads();
+    if (t + DECODE_STAGES < tiles) {
+      load_kv_tile<D>(k_tiles + stage * TILE_KV * D, k_pool, table, (tile_begin + t + DECODE_STAGES) * TILE_KV, TILE_KV,
+                      k_begin, k_end - 1, kv_heads, kv_head, page_size);
+      load_kv_tile<D>(v_tiles + stage * TILE_KV * D, v_pool, table, (tile_begin + t + DECODE_STAGES) * TILE_KV, TILE_KV,
+                      k_begin, k_end - 1, kv_heads, kv_head, page_size);
+    }
+    cp_async_commit();
+  }
+
+  // ---- merge the four warps (each saw a quarter of the keys)
+  float* mine = merge + (size_t)warp * 16 * STATE;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int g = (lane >> 2) + 8 * i;
+    if ((lane & 3) == 0) { mine[g * STATE] = m[i]; mine[g * STATE + 1] = l[i]; }
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t) {
+      mine[g * STATE + 2 + t * 8 + (lane & 3) * 2] = o[t][2 * i];
+      mine[g * STATE + 2 + t * 8 + (lane & 3) * 2 + 1] = o[t][2 * i + 1];
+    }
+  }
+  __syncthreads();
+  const size_t state_base = ((size_t)index * heads + kv_head * group) * max_splits;
+  for (int item = threadIdx.x; item < group * D; item += ATTN_THREADS) {
+    const int g = item / D, d = item - g * D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATTN_WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + g) * STATE]);
+    float l_all = 0.f, a_all = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATTN_WARPS; ++w) {
+      const float* state = merge + ((size_t)w * 16 + g) * STATE;
+      const float factor = exp2f(state[0] - m_all);      // a warp without keys has m = -inf: factor 0
+      l_all += state[1] * factor;
+      a_all += state[2 + d] * factor;
+    }
+    if (splits == 1) {
+      out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(a_all / l_all);
+    } else {
+      float* state = scratch + (state_base + (size_t)g * max_splits + split) * STATE;
+      state[2 + d] = a_all;
+      if (d == 0) { state[0] = m_all; state[1] = l_all; }
+    }
+  }
+  if (splits == 1) return;
+
+  // ---- the CTA that arrives last for this (request, kv head) merges all chunks, in chunk order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_flag = (atomicAdd(&counters[index * kv_heads + kv_head], 1) == splits - 1);
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  for (int item = threadIdx.x; item < group * D; item += ATTN_THREADS) {
+    const int g = item / D, d = item - g * D;
+    const float* states = scratch + (state_base + (size_t)g * max_splits) * STATE;
+    // Loads of eight chunks' states are issued together so that their latencies overlap; the
+    // sums still run in chunk order.
+    float m_all = -INFINITY;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float part[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) part[j] = s0 + j < splits ? __ldcg(&states[(size_t)(s0 + j) * STATE]) : -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m_all = fmaxf(m_all, part[j]);
+    }
+    float l_all = 0.f, a_all = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float pm[8], pl[8], pa[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool live = s0 + j < splits;
+        pm[j] = live ? __ldcg(&states[(size_t)(s0 + j) * STATE]) : -INFINITY;
+        pl[j] = live ? __ldcg(&states[(size_t)(s0 + j) * STATE + 1]) : 0.f;
+        pa[j] = live ? __ldcg(&states[(size_t)(s0 + j) * STATE + 2 + d]) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float factor = exp2f(pm[j] - m_all);
+        l_all += pl[j] * factor;
+        a_all += pa[j] * factor;
+      }
+    }
+    out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(a_all / l_all);
+  }
+  if (threadIdx.x == 0) counters[index * kv_heads + kv_head] = 0;
+}
+
+template <typename Kernel>
+static int set_shared(Kernel kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return MLR_OK;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  return err == cudaSuccess ? MLR_OK : (int)err;
+}
+
+}  // namespace mlr
+
+using namespace mlr;
+
+constexpr float LOG2_E = 1.4426950408889634f;
+
+// Prompt portions: tiles of up to 64 rows of one segment (tile_seg, tile_row0).
+MLR_EXPORT int mlr_attention_prefill_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                         const int* tile_seg, const int* tile_row0, const int* seg_q_start,
+                                         const int* seg_q_len, const int* seg_pos0, const int* block_table,
+                                         int table_width, int tiles, int heads, int kv_heads, int head_dim,
+                                         int page_size, int window, float scale, cudaStream_t stream) {
+  if (tiles == 0) return MLR_OK;
+  if (tiles < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 || table_width <= 0)
+    return MLR_BAD_SIZE;
+  if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
+  if (heads > 65535) return MLR_TOO_LARGE;
+  const size_t shared = (size_t)(TILE_Q + 4 * TILE_KV) * head_dim * 2;
+  dim3 grid(tiles, heads);
+  int status;
+  if (head_dim == 64) {
+    if ((status = set_shared(prefill_attention_kernel<64>, shared)) != MLR_OK) return status;
+    prefill_attention_kernel<64><<<grid, ATTN_THREADS, shared, stream>>>(
+        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, tile_seg, tile_row0, seg_q_start,
+        seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, page_size, window, scale * LOG2_E);
+  } else {
+    if ((status = set_shared(prefill_attention_kernel<128>, shared)) != MLR_OK) return status;
+    prefill_attention_kernel<128><<<grid, ATTN_THREADS, shared, stream>>>(
+        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, tile_seg, tile_row0, seg_q_start,
+        seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, page_size, window, scale * LOG2_E);
+  }
+  return launch_status();
+}
+
+// Decoded tokens: same contract as mlr_attention_decode (same scratch layout and counters).
+MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                        const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
+                                        const int* block_table, int table_width, int rows, int heads, int kv_heads,
+                                        int head_dim, int page_size, int window, float scale, int chunk,
+                                        int max_splits, void* scratch, int* counters, cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 || chunk <= 0 ||
+      chunk % TILE_KV != 0 || max_splits <= 0 || table_width <= 0)
+    return MLR_BAD_SIZE;
+  if (heads / kv_heads > 16 || rows > 65535 || kv_heads > 65535) return MLR_TOO_LARGE;
+  if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
+  const size_t shared = (size_t)(16 + 2 * DECODE_STAGES * TILE_KV) * head_dim * 2 +
+                        (size_t)ATTN_WARPS * 16 * (head_dim + 2) * sizeof(float);
+  dim3 grid(max_splits, kv_heads, rows);
+  int status;
+  if (head_dim == 64) {
+    if ((status = set_shared(decode_attention_mma_kernel<64>, shared)) != MLR_OK) return status;
+    decode_attention_mma_kernel<64><<<grid, ATTN_THREADS, shared, stream>>>(
+        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
+        block_table, table_width, heads, kv_heads, page_size, window, scale * LOG2_E, chunk, (float*)scratch,
+        counters, max_splits);
+  } else {
+    if ((status = set_shared(decode_attention_mma_kernel<128>, shared)) != MLR_OK) return status;
+    decode_attention_mma_kernel<128><<<grid, ATTN_THREADS, shared, stream>>>(
+        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
+        block_table, table_width, heads, kv_heads, page_size, window, scale * LOG2_E, chunk, (float*)scratch,
+        counters, max_splits);
+  }
+  return launch_status();
+}

@@ -61,16 +61,18 @@ __global__ void rms_norm_kernel(T* __restrict__ residual, const T* __restrict__ 
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// in: [rows, 2*inner] holding gate in the first half of each row and up in the second.
+// in: [rows, 2*inner].  Each row holds blocks of `block` gate values followed by the `block` up
+// values of the same outputs; block == inner is the plain "all gates, then all ups" layout.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner,
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner, int block,
                               size_t total) {
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / inner;
     const int col = (int)(idx - row * inner);
-    const float g = to_float(gate_up[row * 2 * inner + col]);
-    const float u = to_float(gate_up[row * 2 * inner + inner + col]);
+    const size_t at = row * 2 * inner + (size_t)(col / block) * 2 * block + col % block;
+    const float g = to_float(gate_up[at]);
+    const float u = to_float(gate_up[at + block]);
     out[idx] = from_float<T>((g / (1.f + expf(-g))) * u);
   }
 }
@@ -209,18 +211,18 @@ MLR_EXPORT int mlr_rms_norm(void* residual, const void* delta, const void* weigh
   return MLR_BAD_DTYPE;
 }
 
-MLR_EXPORT int mlr_swiglu(const void* gate_up, void* out, long long rows, int inner, int dtype,
+MLR_EXPORT int mlr_swiglu(const void* gate_up, void* out, long long rows, int inner, int block, int dtype,
                           cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
-  if (rows < 0 || inner <= 0) return MLR_BAD_SIZE;
+  if (rows < 0 || inner <= 0 || block <= 0 || inner % block != 0) return MLR_BAD_SIZE;
   const size_t total = (size_t)rows * inner;
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (dtype == MLR_F32)
-    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inner, total);
+    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inner, block, total);
   else if (dtype == MLR_BF16)
-    swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inner, total);
+    swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inner, block, total);
   else
     return MLR_BAD_DTYPE;
   return launch_status();

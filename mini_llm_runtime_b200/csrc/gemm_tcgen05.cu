@@ -115,6 +115,7 @@ struct GemmParams {
   int M, N, K;
   int k_blocks_per_split;   // 64-wide k blocks each split handles
   int splits;
+  int stages;               // shared-memory stages in the ring (2..8)
   const bf16* bias;
   void* out;
   int out_f32;
@@ -123,9 +124,35 @@ struct GemmParams {
   int* error_word;
 };
 
+constexpr int MAX_STAGES = 8;
+
+__device__ __forceinline__ float silu_times(float gate, float up) { return gate / (1.f + __expf(-gate)) * up; }
+
+// Sum of the splits' partial values of 16 columns of one tile row, in split order.  Loads of four
+// splits are issued together so that their latencies overlap; a missing split adds zeros.
+template <int BN>
+__device__ __forceinline__ void reduce_partials(const float* partials, int splits, int c0, int row, float* v) {
+#pragma unroll
+  for (int c = 0; c < 16; ++c) v[c] = 0.f;
+  for (int s0 = 0; s0 < splits; s0 += 4) {
+    float t[4][16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        t[j][c] = s0 + j < splits ? __ldcg(&partials[((size_t)(s0 + j) * BN + c0 + c) * TILE_ROWS + row]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 16; ++c) v[c] += t[j][c];
+  }
+}
+
 // SWAP = true:  A (128 rows) = weights, B (BN rows) = activations; tile row = output column n.
 // SWAP = false: A (128 rows) = activations, B (BN rows) = weights; tile row = output row m.
-template <int BN, bool SWAP, int STAGES>
+// SWIGLU: the weight rows come in blocks of 128 = 64 gate rows followed by the 64 up rows of the
+// same outputs; the epilogue writes silu(gate) * up, [M, N/2].
+template <int BN, bool SWAP, bool SWIGLU>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
@@ -133,14 +160,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr uint32_t B_BYTES = BN * TILE_K * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  static_assert(!SWIGLU || SWAP || BN == 128, "fused SwiGLU needs gate and up columns in one tile");
 
   extern __shared__ uint8_t raw_shared[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)raw_shared + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accumulator_bar;
+  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], accumulator_bar;
   __shared__ uint32_t tmem_holder;
   __shared__ int is_last_cta, epilogue_failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
   const int a_row0 = blockIdx.x * TILE_ROWS;   // first row of the 128-row operand
   const int b_row0 = blockIdx.y * BN;          // first row of the BN-row operand
   const int split = blockIdx.z;
@@ -151,7 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     epilogue_failed = 0;
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(&accumulator_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -168,23 +197,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (warp == 0 && lane == 0) {
     // ---------------- producer
+    int s = 0, round = 0;
     for (int i = 0; i < num_kb; ++i) {
-      const int s = i % STAGES;
-      if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, p.error_word, 1)) break;
+      if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, p.error_word, 1)) break;
       mbar_expect_tx(&full_bar[s], STAGE_BYTES);
       uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
       const int k = (kb_begin + i) * TILE_K;
       tma_load_2d(&map_a, &full_bar[s], stage, k, a_row0);
       tma_load_2d(&map_b, &full_bar[s], stage + A_BYTES, k, b_row0);
+      if (++s == stages) { s = 0; ++round; }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
     constexpr uint32_t idesc = instruction_descriptor(TILE_ROWS, BN);
-    bool ok = true;
-    for (int i = 0; i < num_kb && ok; ++i) {
-      const int s = i % STAGES;
-      ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, p.error_word, 2);
-      if (!ok) break;
+    int s = 0, round = 0;
+    for (int i = 0; i < num_kb; ++i) {
+      if (!mbar_wait(&full_bar[s], round & 1, p.error_word, 2)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
       const uint32_t b_addr = a_addr + A_BYTES;
@@ -193,6 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         umma(tmem_base, smem_descriptor(a_addr + k * MMA_K * 2), smem_descriptor(b_addr + k * MMA_K * 2), idesc,
              (i > 0 || k > 0) ? 1u : 0u);
       umma_commit(&empty_bar[s]);
+      if (++s == stages) { s = 0; ++round; }
     }
     umma_commit(&accumulator_bar);   // arrives once every MMA issued above has finished
   } else if (warp >= 2) {
@@ -204,12 +233,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const bool ok = epilogue_failed == 0;               // the same answer in all of them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     if (ok && p.splits > 1) {
       float* mine = p.scratch + ((size_t)tile_id * p.splits + split) * BN * TILE_ROWS;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t r[16];
-        tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, r);
+        tmem_load16(lane_base + c0, r);
 #pragma unroll
         for (int c = 0; c < 16; ++c) mine[(size_t)(c0 + c) * TILE_ROWS + row] = __uint_as_float(r[c]);
       }
@@ -219,24 +249,92 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     const bool reduce = ok && p.splits > 1 && is_last_cta;
-    if (ok && (p.splits == 1 || reduce)) {
-      if (reduce) __threadfence();
-      const float* partials = p.scratch + (size_t)tile_id * p.splits * BN * TILE_ROWS;
-      bf16* out_bf16 = (bf16*)p.out;
-      float* out_f32 = (float*)p.out;
+    const bool finish = ok && (p.splits == 1 || reduce);
+    if (reduce) __threadfence();
+    const float* partials = p.scratch + (size_t)tile_id * p.splits * BN * TILE_ROWS;
+    bf16* out_bf16 = (bf16*)p.out;
+    float* out_f32 = (float*)p.out;
+
+    if (SWIGLU && SWAP) {
+      // rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same 64 outputs.
+      // Without split-K the halves meet through shared memory (the stage ring is idle by now).
+      float* exchange = reinterpret_cast<float*>(tiles);            // [BN][128]
+      if (finish && !reduce) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_load16(lane_base + c0, r);
+#pragma unroll
+          for (int c = 0; c < 16; ++c) exchange[(c0 + c) * TILE_ROWS + row] = __uint_as_float(r[c]);
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (finish && row < 64) {
+        const int n = blockIdx.x * 64 + row;        // output column
+        const int half = p.N >> 1;
+        if (n < half) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            float g[16], u[16];
+            if (reduce) {
+              reduce_partials<BN>(partials, p.splits, c0, row, g);
+              reduce_partials<BN>(partials, p.splits, c0, row + 64, u);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                g[c] = exchange[(c0 + c) * TILE_ROWS + row];
+                u[c] = exchange[(c0 + c) * TILE_ROWS + row + 64];
+              }
+            }
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int m = b_row0 + c0 + c;
+              if (m < p.M) out_bf16[(size_t)m * half + n] = __float2bfloat16_rn(silu_times(g[c], u[c]));
+            }
+          }
+        }
+      }
+    } else if (SWIGLU) {
+      // not swapped, BN = 128: columns 0..63 are gate, 64..127 up, all in this thread's TMEM lane
+      // tcgen05.ld is warp-collective: every lane runs the loads, only the stores depend on m.
+      const int m = a_row0 + row;
+      const int half = p.N >> 1;
+      if (finish) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 16) {
+          uint32_t g[16], u[16];
+          tmem_load16(lane_base + c0, g);
+          tmem_load16(lane_base + 64 + c0, u);
+          if (m >= p.M) continue;
+          const int n0 = blockIdx.y * 64 + c0;
+          uint32_t packed[8];
+#pragma unroll
+          for (int c = 0; c < 16; c += 2)
+            packed[c >> 1] = [&] {
+              __nv_bfloat162 pair = __floats2bfloat162_rn(silu_times(__uint_as_float(g[c]), __uint_as_float(u[c])),
+                                                          silu_times(__uint_as_float(g[c + 1]), __uint_as_float(u[c + 1])));
+              return *reinterpret_cast<uint32_t*>(&pair);
+            }();
+          if ((half & 7) == 0 && n0 + 16 <= half) {
+            uint4* dst = reinterpret_cast<uint4*>(out_bf16 + (size_t)m * half + n0);
+            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+            const bf16* values = reinterpret_cast<const bf16*>(packed);
+            for (int c = 0; c < 16; ++c)
+              if (n0 + c < half) out_bf16[(size_t)m * half + n0 + c] = values[c];
+          }
+        }
+      }
+    } else if (finish) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         float v[16];
         if (reduce) {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) v[c] = 0.f;
-          for (int s = 0; s < p.splits; ++s)
-#pragma unroll
-            for (int c = 0; c < 16; ++c)
-              v[c] += __ldcg(&partials[((size_t)s * BN + c0 + c) * TILE_ROWS + row]);
+          reduce_partials<BN>(partials, p.splits, c0, row, v);
         } else {
           uint32_t r[16];
-          tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, r);
+          tmem_load16(lane_base + c0, r);
 #pragma unroll
           for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
         }
@@ -271,7 +369,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           } else if (m < p.M) {
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-              const int n = b_row0 + c0 + c;
+              const int n = n0 + c;
               if (n < p.N) {
                 const float b = p.bias != nullptr ? to_float(p.bias[n]) : 0.f;
                 if (p.out_f32) out_f32[(size_t)m * p.N + n] = v[c] + b;
@@ -281,8 +379,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
-      if (reduce && warp == 2 && lane == 0) p.counters[tile_id] = 0;   // ready for the next launch
     }
+    if (reduce && warp == 2 && lane == 0) p.counters[tile_id] = 0;   // ready for the next launch
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -318,15 +416,15 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int bo
                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, bool SWAP, int STAGES>
+template <int BN, bool SWAP, bool SWIGLU>
 static int launch(const void* x, const void* w, const GemmParams& p, int splits, cudaStream_t stream) {
-  constexpr size_t shared = (size_t)STAGES * (TILE_ROWS * TILE_K * 2 + BN * TILE_K * 2) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, SWAP, STAGES>,
+  const size_t shared = (size_t)p.stages * (TILE_ROWS * TILE_K * 2 + BN * TILE_K * 2) + 1024;
+  static size_t configured = 0;
+  if (shared > configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, SWAP, SWIGLU>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;
-    configured = true;
+    configured = shared;
   }
   CUtensorMap map_a, map_b;
   const void* a_base = SWAP ? w : x;
@@ -335,8 +433,41 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
   if (!make_map(&map_a, a_base, a_rows, p.K, TILE_ROWS) || !make_map(&map_b, b_base, b_rows, p.K, BN))
     return MLR_BAD_ALIGNMENT;
   dim3 grid((a_rows + TILE_ROWS - 1) / TILE_ROWS, (b_rows + BN - 1) / BN, splits);
-  gemm_tcgen05_kernel<BN, SWAP, STAGES><<<grid, GEMM_THREADS, shared, stream>>>(map_a, map_b, p);
+  gemm_tcgen05_kernel<BN, SWAP, SWIGLU><<<grid, GEMM_THREADS, shared, stream>>>(map_a, map_b, p);
   return launch_status();
+}
+
+// Tile shape, split count and ring depth for a product of this shape.
+struct GemmPlan { int bn, tiles, splits, stages, kb_per_split; };
+
+static GemmPlan plan_gemm(int M, int N, int K) {
+  GemmPlan plan;
+  const int total_kb = (K + TILE_K - 1) / TILE_K;
+  if (M <= 128) {
+    plan.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+    plan.tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
+  } else {
+    plan.bn = 128;
+    plan.tiles = ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + 127) / 128);
+  }
+  int splits = 1;
+  if (M <= 128) {
+    // Few tiles cannot keep 148 SMs streaming weights: cut K until about one CTA per SM exists,
+    // but leave every split at least two k blocks and the final reduction at most 16 partials.
+    splits = (148 + plan.tiles - 1) / plan.tiles;
+    if (splits > total_kb / 2) splits = total_kb / 2;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+  }
+  plan.kb_per_split = (total_kb + splits - 1) / splits;
+  plan.splits = (total_kb + plan.kb_per_split - 1) / plan.kb_per_split;   // no empty split
+  // A ring as deep as the split is long (at most 6 stages) leaves room for several CTAs per SM,
+  // so that one CTA's prologue and epilogue overlap another's streaming.
+  int stages = plan.kb_per_split < 2 ? 2 : (plan.kb_per_split > 6 ? 6 : plan.kb_per_split);
+  const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
+  while (stages > 2 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
+  plan.stages = stages;
+  return plan;
 }
 
 }  // namespace mlr
@@ -344,59 +475,49 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
 using namespace mlr;
 
 // Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
-// `splits_out` receives the split count the launcher will use.
+// `splits_out` receives the split count the launcher will use, `tiles_out` the number of tiles.
 MLR_EXPORT long long mlr_gemm_tcgen05_plan(int M, int N, int K, int* splits_out, int* tiles_out) {
-  const int total_kb = (K + TILE_K - 1) / TILE_K;
-  int bn, tiles;
-  if (M <= 128) {
-    bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-    tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
-  } else {
-    bn = 128;
-    tiles = ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + bn - 1) / bn);
-  }
-  int splits = 1;
-  if (M <= 128) {
-    // Few tiles cannot keep 148 SMs streaming weights: cut K so that about two CTAs per SM exist,
-    // but leave every split at least two k blocks.
-    const int wanted = (2 * 148 + tiles - 1) / tiles;
-    splits = wanted < 1 ? 1 : wanted;
-    if (splits > total_kb / 2) splits = total_kb / 2;
-    if (splits < 1) splits = 1;
-    const int per = (total_kb + splits - 1) / splits;
-    splits = (total_kb + per - 1) / per;   // no empty split
-  }
-  if (splits_out) *splits_out = splits;
-  if (tiles_out) *tiles_out = tiles;
-  return splits > 1 ? (long long)tiles * splits * bn * TILE_ROWS * 4 : 0;
+  const GemmPlan plan = plan_gemm(M, N, K);
+  if (splits_out) *splits_out = plan.splits;
+  if (tiles_out) *tiles_out = plan.tiles;
+  return plan.splits > 1 ? (long long)plan.tiles * plan.splits * plan.bn * TILE_ROWS * 4 : 0;
 }
 
 // x [M,K], w [N,K], bias [N] or null, all bfloat16; out [M,N] bfloat16 (out_f32 = 0) or float32.
+// swiglu != 0: w holds blocks of 64 gate rows followed by the 64 up rows of the same outputs
+// (N % 128 == 0, no bias) and out is silu(gate) * up, [M, N/2] bfloat16.
 // scratch: at least mlr_gemm_tcgen05_plan(...) bytes; counters: one zeroed int per tile;
 // error_word: host-visible int that receives a non-zero code if a wait inside the kernel runs out.
 MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                                int out_f32, void* scratch, int* counters, int* error_word,
+                                int out_f32, int swiglu, void* scratch, int* counters, int* error_word,
                                 cudaStream_t stream) {
   if (M == 0) return MLR_OK;
   if (M < 0 || N <= 0 || K <= 0) return MLR_BAD_SIZE;
   if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MLR_BAD_ALIGNMENT;
-  int splits = 1, tiles = 0;
-  mlr_gemm_tcgen05_plan(M, N, K, &splits, &tiles);
-  const int total_kb = (K + TILE_K - 1) / TILE_K;
+  if (swiglu && (N % 128 != 0 || bias != nullptr || out_f32)) return MLR_BAD_SIZE;
+  const GemmPlan plan = plan_gemm(M, N, K);
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  p.k_blocks_per_split = (total_kb + splits - 1) / splits;
-  p.splits = splits;
+  p.k_blocks_per_split = plan.kb_per_split;
+  p.splits = plan.splits;
+  p.stages = plan.stages;
   p.bias = (const bf16*)bias;
   p.out = out;
   p.out_f32 = out_f32;
   p.scratch = (float*)scratch;
   p.counters = counters;
   p.error_word = error_word;
-  if (splits > 1 && (scratch == nullptr || counters == nullptr)) return MLR_BAD_SIZE;
-  if (M <= 16) return launch<16, true, 8>(x, w, p, splits, stream);
-  if (M <= 32) return launch<32, true, 8>(x, w, p, splits, stream);
-  if (M <= 64) return launch<64, true, 6>(x, w, p, splits, stream);
-  if (M <= 128) return launch<128, true, 5>(x, w, p, splits, stream);
-  return launch<128, false, 5>(x, w, p, splits, stream);
+  if (plan.splits > 1 && (scratch == nullptr || counters == nullptr)) return MLR_BAD_SIZE;
+  if (swiglu) {
+    if (M <= 16) return launch<16, true, true>(x, w, p, plan.splits, stream);
+    if (M <= 32) return launch<32, true, true>(x, w, p, plan.splits, stream);
+    if (M <= 64) return launch<64, true, true>(x, w, p, plan.splits, stream);
+    if (M <= 128) return launch<128, true, true>(x, w, p, plan.splits, stream);
+    return launch<128, false, true>(x, w, p, plan.splits, stream);
+  }
+  if (M <= 16) return launch<16, true, false>(x, w, p, plan.splits, stream);
+  if (M <= 32) return launch<32, true, false>(x, w, p, plan.splits, stream);
+  if (M <= 64) return launch<64, true, false>(x, w, p, plan.splits, stream);
+  if (M <= 128) return launch<128, true, false>(x, w, p, plan.splits, stream);
+  return launch<128, false, false>(x, w, p, plan.splits, stream);
 }

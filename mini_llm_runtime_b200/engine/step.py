@@ -29,7 +29,8 @@ from ..cache.manager import CacheGroup, CacheManager, RequestCache
 from ..models.decoder import DecoderModel
 from ..ops.cuda_ops import AttentionBatch
 
-ROWS_PER_TILE = 16  # rows one CTA of the generic attention kernel handles
+ROWS_PER_TILE = 16    # rows one CTA of the generic attention kernel handles
+WIDE_TILE_ROWS = 64   # rows one CTA of the tensor-core prefill kernel handles
 
 
 @dataclass
@@ -231,6 +232,15 @@ class ModelRunner:
         tile_row0 = ((np.arange(len(tile_seg), dtype=np.int32) - np.repeat(tile_first, tiles_per_segment))
                      * ROWS_PER_TILE).astype(np.int32)
 
+        # tiles of at most 64 rows over the longer segments, for the tensor-core prefill kernel
+        longer = np.flatnonzero(lengths != 1).astype(np.int32)
+        wide_per_segment = (lengths[longer] + WIDE_TILE_ROWS - 1) // WIDE_TILE_ROWS
+        wide_tile_seg = np.repeat(longer, wide_per_segment)
+        wide_first = np.zeros(len(longer), dtype=np.int32)
+        np.cumsum(wide_per_segment[:-1], out=wide_first[1:])
+        wide_tile_row0 = ((np.arange(len(wide_tile_seg), dtype=np.int32) - np.repeat(wide_first, wide_per_segment))
+                          * WIDE_TILE_ROWS).astype(np.int32)
+
         slots = np.array([r.slot for r in requests], dtype=np.int32)
         kv_end = position_start + lengths
         table_width = fixed_width or max(1, int(-(-int(kv_end.max()) // cache.page_size)))
@@ -246,6 +256,8 @@ class ModelRunner:
         packer.add("tile_seg", tile_seg)
         packer.add("tile_row0", tile_row0)
         packer.add("decode_seg", decode_seg)
+        packer.add("wide_tile_seg", wide_tile_seg)
+        packer.add("wide_tile_row0", wide_tile_row0)
         for group in cache.groups:
             rows_slots = np.concatenate([
                 cache.slot_mapping(group, request, int(position_start[i]), int(lengths[i]))
@@ -277,7 +289,9 @@ class ModelRunner:
                 num_segments=len(entries), num_tiles=int(tile_seg.shape[0]),
                 max_q_len=int(lengths.max()),
                 max_kv_len=int(kv_end.max()) if fixed_width is None else fixed_width * cache.page_size,
-                decode_seg=dev["decode_seg"], num_decode=int(decode_seg.shape[0]))
+                decode_seg=dev["decode_seg"], num_decode=int(decode_seg.shape[0]),
+                wide_tile_seg=dev["wide_tile_seg"], wide_tile_row0=dev["wide_tile_row0"],
+                num_wide_tiles=int(wide_tile_seg.shape[0]))
         for entry, need in enumerate(cache.needs):
             if entry in cache.entry_group:
                 k_pool, v_pool, group = cache.entry_pools(entry)

@@ -39,6 +39,7 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "sampling": (),
     "gemm_tcgen05": (),
     "attention_decode": (),
+    "attention_mma": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

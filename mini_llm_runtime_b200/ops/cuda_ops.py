@@ -94,6 +94,10 @@ class AttentionBatch:
     max_kv_len: int
     decode_seg: torch.Tensor | None = None
     num_decode: int = 0
+    # tiles of at most 64 rows over the segments longer than one row (tensor-core prefill kernel)
+    wide_tile_seg: torch.Tensor | None = None
+    wide_tile_row0: torch.Tensor | None = None
+    num_wide_tiles: int = 0
 
 
 class CudaOps:
@@ -113,6 +117,8 @@ class CudaOps:
         self._workspaces: dict[int, dict[str, torch.Tensor]] = {}
         self.use_tensor_cores = True
         self.use_decode_kernel = True
+        self.use_mma_attention = True
+        self.use_fused_swiglu = True
         self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
         self.decode_max_splits: int | None = None  # None: just enough for the longest context
 
@@ -181,17 +187,39 @@ class CudaOps:
                                 ctypes.c_float(eps), _code(x.dtype), _code(weight.dtype), _stream()), "rms_norm")
         return out
 
-    def swiglu(self, gate_up: torch.Tensor) -> torch.Tensor:
-        """silu(gate) * up for rows laid out as [gate | up]."""
+    def swiglu(self, gate_up: torch.Tensor, block: int | None = None) -> torch.Tensor:
+        """silu(gate) * up.  Rows hold blocks of ``block`` gate values followed by the ``block`` up
+        values of the same outputs; by default one block: [all gates | all ups]."""
         _need(gate_up, "gate_up", dims=2)
         if gate_up.shape[1] % 2 != 0:
             raise KernelError("gate_up rows must hold gate and up halves of equal width")
         inner = gate_up.shape[1] // 2
+        block = inner if block is None else int(block)
+        if block <= 0 or inner % block:
+            raise KernelError(f"the block size {block} does not divide the inner width {inner}")
         out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
         lib = build.load_library("elementwise")
-        _check(lib.mlr_swiglu(_ptr(gate_up), _ptr(out), ctypes.c_longlong(gate_up.shape[0]), inner,
+        _check(lib.mlr_swiglu(_ptr(gate_up), _ptr(out), ctypes.c_longlong(gate_up.shape[0]), inner, block,
                               _code(gate_up.dtype), _stream()), "swiglu")
         return out
+
+    SWIGLU_BLOCK = 64   # rows of gate, then rows of up, per 128-row weight tile of the fused kernel
+
+    def linear_swiglu(self, x: torch.Tensor, weight: torch.Tensor, block: int) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) where ``weight`` [2*inner, K] interleaves ``block`` gate rows
+        with the ``block`` up rows of the same outputs.  One tensor-core kernel when the shapes
+        allow (block 64), else the product followed by the activation kernel."""
+        _need(x, "x", dims=2)
+        _need(weight, "weight", x.dtype, 2)
+        if x.shape[1] != weight.shape[1] or weight.shape[0] % (2 * block):
+            raise KernelError("linear_swiglu: shapes do not fit the interleaved gate/up layout")
+        if (self.use_tensor_cores and self.use_fused_swiglu and block == self.SWIGLU_BLOCK
+                and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[0] > 0
+                and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+            out = self._linear_tcgen05(x, weight, None, torch.bfloat16, swiglu=True)
+            if out is not None:
+                return out
+        return self.swiglu(self.linear(x, weight), block)
 
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                       slots: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, num_heads: int,
@@ -239,10 +267,12 @@ class CudaOps:
         out_dtype = out_dtype or x.dtype
         if (self.use_tensor_cores and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.shape[0] > 0):
-            return self._linear_tcgen05(x, weight, bias, out_dtype)
+            out = self._linear_tcgen05(x, weight, bias, out_dtype)
+            if out is not None:
+                return out
         return self._linear_simt(x, weight, bias, out_dtype)
 
-    def _linear_tcgen05(self, x, weight, bias, out_dtype):
+    def _linear_tcgen05(self, x, weight, bias, out_dtype, swiglu=False):
         M, K = x.shape
         N = weight.shape[0]
         lib = build.load_library("gemm_tcgen05")
@@ -251,10 +281,10 @@ class CudaOps:
         need = lib.mlr_gemm_tcgen05_plan(M, N, K, ctypes.byref(splits), ctypes.byref(tiles))
         space = self._workspace(x.device)
         if need > space["gemm_scratch"].numel() or (splits.value > 1 and tiles.value > space["gemm_counters"].numel()):
-            return self._linear_simt(x, weight, bias, out_dtype)
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+            return None
+        out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
         _check(lib.mlr_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
-                                    int(out_dtype == torch.float32), _ptr(space["gemm_scratch"]),
+                                    int(out_dtype == torch.float32), int(swiglu), _ptr(space["gemm_scratch"]),
                                     _ptr(space["gemm_counters"]), _ptr(space["error_word"]), _stream()),
                "linear (tcgen05)")
         return out
@@ -283,6 +313,21 @@ class CudaOps:
         out = torch.empty_like(q)
         generic_tiles = batch.num_tiles
         group = num_heads // num_kv_heads
+        if (self.use_mma_attention and q.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 16
+                and batch.decode_seg is not None and batch.wide_tile_seg is not None
+                and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS):
+            if batch.num_decode > 0:
+                self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale,
+                                       window, mma=True)
+            if batch.num_wide_tiles > 0:
+                lib = build.load_library("attention_mma")
+                _check(lib.mlr_attention_prefill_mma(
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.wide_tile_seg),
+                    _ptr(batch.wide_tile_row0), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
+                    _ptr(batch.block_table), batch.block_table.shape[1], batch.num_wide_tiles, num_heads,
+                    num_kv_heads, head_dim, k_pool.shape[2], int(window or 0), ctypes.c_float(scale), _stream()),
+                    "prefill attention")
+            return out
         if (self.use_decode_kernel and batch.num_decode > 0 and batch.decode_seg is not None
                 and q.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 8
                 and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS):
@@ -306,7 +351,8 @@ class CudaOps:
             chunk //= 2
         return chunk, max(1, -(-longest // chunk))
 
-    def _decode_attention(self, q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window):
+    def _decode_attention(self, q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window,
+                          mma=False):
         lib = build.load_library("attention_decode")
         chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len)
         if self.decode_chunk is not None:
@@ -319,7 +365,8 @@ class CudaOps:
         space = self._workspace(q.device)
         if need > space["attention_scratch"].numel():
             space["attention_scratch"] = torch.empty(int(need * 1.5), dtype=torch.uint8, device=q.device)
-        _check(lib.mlr_attention_decode(
+        entry = build.load_library("attention_mma").mlr_attention_decode_mma if mma else lib.mlr_attention_decode
+        _check(entry(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.decode_seg), _ptr(batch.seg_q_start),
             _ptr(batch.seg_pos0), _ptr(batch.block_table), batch.block_table.shape[1], batch.num_decode,
             num_heads, num_kv_heads, head_dim, k_pool.shape[2], int(window or 0), ctypes.c_float(scale), chunk,

@@ -1,6 +1,9 @@
 """Dense SwiGLU feed-forward: down(silu(gate(x)) * up(x)), no biases
 (reference: src/mini_llm_runtime/qwen_model_runner.py:215-217).  gate and up are stacked into one
-[2*intermediate, hidden] matrix at load time so that one product feeds the activation kernel."""
+[2*intermediate, hidden] matrix at load time so that one product feeds the activation.  When the
+intermediate width is a multiple of 64 the rows are interleaved in blocks (64 gate rows, then the
+64 up rows of the same outputs), which lets the tensor-core kernel apply the activation in its
+epilogue; otherwise all gate rows come first."""
 
 from __future__ import annotations
 
@@ -18,6 +21,7 @@ class SwiGLU(FeedForward):
         self.hidden_size = int(self.args["hidden_size"])
         self.intermediate_size = int(self.args["intermediate_size"])
         self.w_gate_up = self.w_down = None
+        self.block = self.intermediate_size   # gate/up interleaving of w_gate_up
 
     def tensors(self):
         p = self.prefix
@@ -29,13 +33,19 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors, device):
         p = self.prefix
-        self.w_gate_up = self._to_compute(
-            torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]], dim=0), device)
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        if self.intermediate_size % 64 == 0:
+            self.block = 64
+            stacked = torch.cat([gate.view(-1, 64, self.hidden_size), up.view(-1, 64, self.hidden_size)], dim=1)
+            stacked = stacked.reshape(2 * self.intermediate_size, self.hidden_size)
+        else:
+            stacked = torch.cat([gate, up], dim=0)
+        self.w_gate_up = self._to_compute(stacked, device)
         self.w_down = self._to_compute(tensors[p + "down_proj.weight"], device)
 
     def forward(self, x, ctx):
         k = ops.current()
-        return k.linear(k.swiglu(k.linear(x, self.w_gate_up)), self.w_down)
+        return k.linear(k.linear_swiglu(x, self.w_gate_up, self.block), self.w_down)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

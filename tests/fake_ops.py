@@ -29,10 +29,15 @@ class FakeOps:
         residual.copy_((residual.float() + delta.float()).to(residual.dtype))
         return self.rms_norm(residual, weight, eps)
 
-    def swiglu(self, gate_up):
+    def swiglu(self, gate_up, block=None):
         inner = gate_up.shape[1] // 2
-        gate, up = gate_up[:, :inner].float(), gate_up[:, inner:].float()
+        block = block or inner
+        blocks = gate_up.float().view(gate_up.shape[0], inner // block, 2, block)
+        gate, up = blocks[:, :, 0].reshape(-1, inner), blocks[:, :, 1].reshape(-1, inner)
         return (torch.nn.functional.silu(gate) * up).to(gate_up.dtype)
+
+    def linear_swiglu(self, x, weight, block):
+        return self.swiglu(self.linear(x, weight), block)
 
     def linear(self, x, weight, bias=None, out_dtype=None):
         out = x.float() @ weight.float().T

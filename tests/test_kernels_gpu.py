@@ -71,6 +71,32 @@ def test_swiglu(dtype):
     gate_up = rnd((13, 2 * 203), dtype, 8, 3.0)
     got = cuda().swiglu(gate_up.to(DEVICE))
     assert_close(got, FAKE.swiglu(gate_up.float()), dtype, "swiglu")
+    blocked = rnd((5, 2 * 192), dtype, 9, 3.0)
+    got = cuda().swiglu(blocked.to(DEVICE), 64)
+    assert_close(got, FAKE.swiglu(blocked.float(), 64), dtype, "swiglu, interleaved blocks")
+
+
+@pytest.mark.parametrize("m", [1, 8, 20, 40, 100, 128, 200, 700])
+@pytest.mark.parametrize("inner,k", [(4864, 896), (128, 64), (320, 200), (1216, 4864)])
+def test_fused_linear_swiglu(m, inner, k):
+    """The gate/up product with the activation in the tensor-core kernel's epilogue, in both
+    orientations and with split-K, against the unfused float32 computation."""
+    x = rnd((m, k), torch.bfloat16, 60 + m)
+    gate = rnd((inner, k), torch.bfloat16, 61, 0.1)
+    up = rnd((inner, k), torch.bfloat16, 62, 0.1)
+    weight = torch.cat([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k)
+    want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
+    got = cuda().linear_swiglu(x.to(DEVICE), weight.to(DEVICE), 64)
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    assert got.shape == (m, inner)
+    assert_close(got, want, torch.bfloat16, f"fused linear+swiglu {m}x{inner}x{k}")
+    cuda().use_fused_swiglu = False
+    try:
+        unfused = cuda().linear_swiglu(x.to(DEVICE), weight.to(DEVICE), 64)
+    finally:
+        cuda().use_fused_swiglu = True
+    assert_close(unfused, want, torch.bfloat16, "unfused path on the interleaved layout")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -190,6 +216,13 @@ def make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, seed, 
             tile_seg.append(s)
             tile_row0.append(r0)
 
+    wide_seg, wide_row0 = [], []
+    for s, (_, q_len) in enumerate(segments):
+        if q_len != 1:
+            for r0 in range(0, q_len, 64):
+                wide_seg.append(s)
+                wide_row0.append(r0)
+
     def ints(values, device):
         return torch.tensor(values, dtype=torch.int32, device=device)
 
@@ -200,7 +233,9 @@ def make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, seed, 
             tile_seg=ints(tile_seg, device), tile_row0=ints(tile_row0, device),
             num_segments=len(segments), num_tiles=len(tile_seg),
             max_q_len=max(q for _, q in segments), max_kv_len=max(p + q for p, q in segments),
-            decode_seg=ints(decode, device), num_decode=len(decode))
+            decode_seg=ints(decode, device), num_decode=len(decode),
+            wide_tile_seg=ints(wide_seg, device), wide_tile_row0=ints(wide_row0, device),
+            num_wide_tiles=len(wide_seg))
 
     return q.to(dtype), k_pool.to(dtype), v_pool.to(dtype), batch, table
 
@@ -243,12 +278,30 @@ def test_decode_attention_split_kv(heads, kv_heads, head_dim, page, chunk):
     finally:
         cuda().decode_chunk = None
     cuda().use_decode_kernel = False
+    cuda().use_mma_attention = False
     try:
-        generic, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+        generic, want = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+        cuda().use_decode_kernel = True
+        simt, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
     finally:
         cuda().use_decode_kernel = True
+        cuda().use_mma_attention = True
+    assert_close(generic, want, torch.bfloat16, "generic kernel")
+    assert_close(simt, want, torch.bfloat16, "split-KV kernel on the CUDA cores")
     both, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
-    assert_close(both, generic, torch.bfloat16, "split-KV kernel against the generic kernel")
+    assert_close(both, generic, torch.bfloat16, "tensor-core kernels against the generic kernel")
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (4, 1, 128, 8), (6, 6, 64, 32), (16, 1, 128, 16)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_prefill_attention_tensor_cores(heads, kv_heads, head_dim, page, window):
+    """Prompt portions through the tensor-core kernel: a whole prompt longer than several tiles,
+    portions that start in the middle of a request (at and off tile and page edges), very short
+    portions, beside decoded tokens."""
+    segments = [(0, 300), (64, 64), (100, 130), (63, 2), (500, 1), (0, 1), (127, 65), (5, 3)]
+    q, k_pool, v_pool, batch, _ = make_attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, segments, 26)
+    got, want = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+    assert_close(got, want, torch.bfloat16, f"prefill attention window={window}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -283,12 +336,17 @@ def test_attention_finds_one_far_key(dtype, far_key):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_rows_do_not_depend_on_the_cut(dtype):
-    """The same request as one portion, as two portions and as single rows: identical bits."""
+    """The same request as one portion, as two portions and as single rows: identical bits from
+    the generic kernel (the float32 path's attention, whatever the storage type)."""
     heads, kv_heads, head_dim, page = 6, 2, 64, 16
     q, k_pool, v_pool, batch, table = make_attention_case(dtype, heads, kv_heads, head_dim, page, [(0, 45)], 24)
     scale = head_dim ** -0.5
     qd, kd, vd = q.to(DEVICE), k_pool.to(DEVICE), v_pool.to(DEVICE)
-    whole = cuda().paged_attention(qd, kd, vd, batch(DEVICE), heads, kv_heads, head_dim, scale, None)
+    cuda().use_mma_attention = cuda().use_decode_kernel = False
+    try:
+        whole = cuda().paged_attention(qd, kd, vd, batch(DEVICE), heads, kv_heads, head_dim, scale, None)
+    finally:
+        cuda().use_mma_attention = cuda().use_decode_kernel = True
 
     def piece(pos0, count):
         tiles = list(range(0, count, 16))
