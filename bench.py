@@ -333,7 +333,101 @@ def run_ours(args):
 
 
 def run_reference(args):
-    print(json.dumps({"impl": "reference", "unavailable": "reference arm not wired up yet"}))
+    """The unmodified reference (installed into baseline/_ref) on the same workload: its
+    ContinuousBatchEngine with its paged CUDA decode kernel, float16 (the only dtype that kernel
+    takes), random weights of the same sizes, 8 requests decoding from the same prefix.  Its
+    extension loader looks for csrc/ two levels above the installed package, i.e. baseline/csrc,
+    which holds an untouched copy of the reference's csrc/ (the wheel does not ship it)."""
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "mini_llm_runtime")):
+        return unavailable("baseline/_ref holds no installed reference (pip install --no-deps --target baseline/_ref)")
+    if not os.path.isfile(os.path.join(ROOT, "baseline", "csrc", "paged_attention_cuda.cu")):
+        return unavailable("baseline/csrc (the reference's kernel sources) is missing, its CUDA extension cannot be built")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+        sys.path.insert(0, ref_root)
+        from mini_llm_runtime.block_admission import PagedBlockAdmissionController
+        from mini_llm_runtime.engine import ContinuousBatchEngine
+        from mini_llm_runtime.paged_kv_manager import PagedKVCacheManager
+        from mini_llm_runtime.qwen_config import QwenConfig
+        from mini_llm_runtime.qwen_model_runner import QwenPrefillRunner
+        from mini_llm_runtime.qwen_weights import QwenWeights
+        from mini_llm_runtime.scheduler import RequestScheduler
+    except Exception as error:  # noqa: BLE001
+        return unavailable(f"the installed reference cannot be imported: {type(error).__name__}: {error}"[:300])
+
+    try:
+        device = torch.device("cuda:0")
+        layers = args.layers
+        config = QwenConfig(**dict(SIZES, num_hidden_layers=layers))
+        generator = torch.Generator(device=device).manual_seed(0)
+
+        def rand(*shape, mean=0.0):
+            return (torch.randn(*shape, generator=generator, device=device) * 0.02 + mean).half()
+
+        h, i, kv = config.hidden_size, config.intermediate_size, config.num_key_value_heads * config.head_dim
+        state = {"model.embed_tokens.weight": rand(config.vocab_size, h), "model.norm.weight": rand(h, mean=1.0)}
+        for index in range(layers):
+            p = f"model.layers.{index}."
+            state.update({
+                p + "input_layernorm.weight": rand(h, mean=1.0), p + "post_attention_layernorm.weight": rand(h, mean=1.0),
+                p + "self_attn.q_proj.weight": rand(h, h), p + "self_attn.q_proj.bias": rand(h),
+                p + "self_attn.k_proj.weight": rand(kv, h), p + "self_attn.k_proj.bias": rand(kv),
+                p + "self_attn.v_proj.weight": rand(kv, h), p + "self_attn.v_proj.bias": rand(kv),
+                p + "self_attn.o_proj.weight": rand(h, h), p + "mlp.gate_proj.weight": rand(i, h),
+                p + "mlp.up_proj.weight": rand(i, h), p + "mlp.down_proj.weight": rand(h, i)})
+        runner = QwenPrefillRunner(config, QwenWeights.from_state_dict(config, state), decode_attention_backend="paged_cuda")
+        batch, steps, warmup = args.batch, args.steps, args.warmup
+        prefix = max(1, args.context_mean - (steps + warmup) // 2)
+        blocks = batch * -(-(prefix + steps + warmup + 2) // BLOCK_SIZE)
+        manager = PagedKVCacheManager(total_blocks=blocks, block_size=BLOCK_SIZE, num_layers=layers,
+                                      num_kv_heads=config.num_key_value_heads, head_dim=config.head_dim,
+                                      dtype=torch.float16, device=device)
+        admission = PagedBlockAdmissionController(manager)
+        scheduler = RequestScheduler(max_running_requests=batch, max_batch_tokens=batch * prefix + batch,
+                                     admission_callback=admission.try_admit)
+        engine = ContinuousBatchEngine(scheduler=scheduler, runner=runner, admission=admission)
+        for index in range(batch):
+            engine.submit(f"r{index}", random_tokens(prefix, config.vocab_size, 2000 + index),
+                          max_new_tokens=steps + warmup + 1)
+        engine.step()                                    # packed prefill of all prompts
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler() as clocks:
+            wall = time.perf_counter()
+            start.record()
+            for _ in range(steps):
+                result = engine.step()
+                assert len(result.update.emitted_tokens) == batch
+            end.record()
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - wall
+        ms = start.elapsed_time(end)
+    except Exception as error:  # noqa: BLE001
+        return unavailable(f"the reference failed on this workload: {type(error).__name__}: {error}"[:300])
+
+    value = batch * steps / (ms / 1e3)
+    print(json.dumps({
+        "metric": "decode tokens/s (batch 8, context 4096)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (the reference kernel's only dtype)",
+        "data": "synthetic (random weights and token ids)", "impl": "reference",
+        "config": {"model": "Qwen2.5-0.5B sizes", "layers": layers, "layers_of_model": SIZES["num_hidden_layers"],
+                   "global_batch": batch, "seq_len": CONTEXT, "context_mean": args.context_mean, "prefix": prefix,
+                   "block_size": BLOCK_SIZE, "parallelism": "single GPU",
+                   "path": "ContinuousBatchEngine + paged_cuda decode kernel"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(batch * steps / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": 8 * batch * 2,
+                "d2h_bytes_per_step": 8 * batch},
+    }))
     return 0
 
 

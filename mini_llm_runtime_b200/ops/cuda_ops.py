@@ -353,19 +353,18 @@ class CudaOps:
 
     def _decode_attention(self, q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window,
                           mma=False):
-        lib = build.load_library("attention_decode")
         chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len)
         if self.decode_chunk is not None:
             chunk = self.decode_chunk
             splits = max(1, -(-batch.max_kv_len // chunk))
         if self.decode_max_splits is not None:
             splits = max(splits, self.decode_max_splits)
-        lib.mlr_attention_decode_scratch.restype = ctypes.c_longlong
-        need = lib.mlr_attention_decode_scratch(batch.num_decode, num_heads, head_dim, splits)
+        need = batch.num_decode * num_heads * splits * (head_dim + 2) * 4    # float32 partial states
         space = self._workspace(q.device)
         if need > space["attention_scratch"].numel():
             space["attention_scratch"] = torch.empty(int(need * 1.5), dtype=torch.uint8, device=q.device)
-        entry = build.load_library("attention_mma").mlr_attention_decode_mma if mma else lib.mlr_attention_decode
+        entry = (build.load_library("attention_mma").mlr_attention_decode_mma if mma
+                 else build.load_library("attention_decode").mlr_attention_decode)
         _check(entry(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.decode_seg), _ptr(batch.seg_q_start),
             _ptr(batch.seg_pos0), _ptr(batch.block_table), batch.block_table.shape[1], batch.num_decode,
