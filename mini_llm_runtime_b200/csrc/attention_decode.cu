@@ -40,6 +40,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
                         int table_width, int heads, int kv_heads, int page_size, int window, float scale,
                         int chunk, float* __restrict__ scratch, int* __restrict__ counters, int max_splits) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int PER_LANE = D / 32;            // output dimensions each lane owns
   constexpr int STATE = D + 2;                // floats per partial state: max, sum, accumulator
   __shared__ float q_s[GROUP_MAX][D];
@@ -222,6 +224,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 
 using namespace mlr;
 
+MLR_DEFINE_PDL_SWITCH
+
 // Bytes of scratch for `rows` decode rows (float32 partial states).
 MLR_EXPORT long long mlr_attention_decode_scratch(int rows, int heads, int head_dim, int max_splits) {
   return (long long)rows * heads * max_splits * (head_dim + 2) * 4;
@@ -243,12 +247,12 @@ MLR_EXPORT int mlr_attention_decode(const void* q, const void* k_pool, const voi
   if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
   dim3 grid(max_splits, kv_heads, rows);
   if (head_dim == 64)
-    decode_attention_kernel<64><<<grid, DECODE_WARPS * 32, 0, stream>>>(
+    launch_kernel(decode_attention_kernel<64>, dim3(grid), dim3(DECODE_WARPS * 32), 0, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
         block_table, table_width, heads, kv_heads, page_size, window, scale, chunk, (float*)scratch, counters,
         max_splits);
   else
-    decode_attention_kernel<128><<<grid, DECODE_WARPS * 32, 0, stream>>>(
+    launch_kernel(decode_attention_kernel<128>, dim3(grid), dim3(DECODE_WARPS * 32), 0, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
         block_table, table_width, heads, kv_heads, page_size, window, scale, chunk, (float*)scratch, counters,
         max_splits);

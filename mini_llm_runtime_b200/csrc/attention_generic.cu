@@ -33,6 +33,8 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool,
                          const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
                          int table_width, int heads, int kv_heads, int head_dim, int page_size,
                          int window, float scale) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float shared[];
   const int D = head_dim;
   float* q_rows = shared;                                   // [16][D]
@@ -145,7 +147,7 @@ int attention_generic_launch(const void* q, const void* k_pool, const void* v_po
     if (err != cudaSuccess) return (int)err;
   }
   dim3 grid(tiles, heads);
-  attention_generic_kernel<T><<<grid, 128, shared, stream>>>(
+  launch_kernel(attention_generic_kernel<T>, dim3(grid), dim3(128), shared, stream, 
       (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, tile_seg, tile_row0, seg_q_start,
       seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, head_dim, page_size, window, scale);
   return launch_status();
@@ -154,6 +156,8 @@ int attention_generic_launch(const void* q, const void* k_pool, const void* v_po
 }  // namespace mlr
 
 using namespace mlr;
+
+MLR_DEFINE_PDL_SWITCH
 
 // q, out: [rows, heads, head_dim]; pools: [pages, kv_heads, page_size, head_dim].
 // tile_seg/tile_row0: one entry per CTA tile of up to 16 rows of one segment.

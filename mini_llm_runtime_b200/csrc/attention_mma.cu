@@ -68,10 +68,12 @@ __device__ __forceinline__ bf16* tile_at(bf16* tile, int row, int chunk) {
 
 // Fetch `rows` rows starting at key `key0` of one kv head into a swizzled tile.  Keys outside
 // [key_lo, key_hi] and keys on pages the request does not hold become zeros.
+// `page_shift` is log2(page_size) when the page size is a power of two (the usual case: address
+// arithmetic by shifts), else -1 (division).
 template <int D>
 __device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ pool, const int* __restrict__ table,
                                              int key0, int rows, int key_lo, int key_hi, int kv_heads, int kv_head,
-                                             int page_size) {
+                                             int page_size, int page_shift) {
   constexpr int CHUNKS = D / 8;
   for (int item = threadIdx.x; item < rows * CHUNKS; item += ATTN_THREADS) {
     const int r = item / CHUNKS, c = item - r * CHUNKS;
@@ -79,9 +81,11 @@ __device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict_
     bool valid = key >= key_lo && key <= key_hi;
     const bf16* src = pool;
     if (valid) {
-      const int page = table[key / page_size];
+      const int logical = page_shift >= 0 ? key >> page_shift : key / page_size;
+      const int offset = page_shift >= 0 ? key & (page_size - 1) : key - logical * page_size;
+      const int page = table[logical];
       valid = page >= 0;
-      if (valid) src = pool + (((size_t)page * kv_heads + kv_head) * page_size + key % page_size) * D + c * 8;
+      if (valid) src = pool + (((size_t)page * kv_heads + kv_head) * page_size + offset) * D + c * 8;
     }
     cp_async_16(tile_at<D>(tile, r, c), src, valid);
   }
@@ -189,13 +193,16 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          bf16* __restrict__ out, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                          const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
                          const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int table_width,
-                         int heads, int kv_heads, int page_size, int window, float scale_log2) {
+                         int heads, int kv_heads, int page_size, int page_shift, int window, float scale_log2) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(128) uint8_t attn_shared[];
   bf16* q_tile = reinterpret_cast<bf16*>(attn_shared);         // [64][D]
   bf16* k_tiles = q_tile + TILE_Q * D;                          // 2 x [64][D]
   bf16* v_tiles = k_tiles + 2 * TILE_KV * D;                    // 2 x [64][D]
 
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // Tiles are listed in order of position; the last ones see the most keys, so they go first.
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
   const int kv_head = head / (heads / kv_heads);
   const int seg = tile_seg[tile], row0 = tile_row0[tile];
   const int q_start = seg_q_start[seg], q_len = seg_q_len[seg], pos0 = seg_pos0[seg];
@@ -215,8 +222,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     const bf16* src = valid ? q + ((size_t)(q_start + row0 + r) * heads + head) * D + c * 8 : q;
     cp_async_16(tile_at<D>(q_tile, r, c), src, valid);
   }
-  load_kv_tile<D>(k_tiles, k_pool, table, tile_begin * TILE_KV, TILE_KV, lowest, last_pos, kv_heads, kv_head, page_size);
-  load_kv_tile<D>(v_tiles, v_pool, table, tile_begin * TILE_KV, TILE_KV, lowest, last_pos, kv_heads, kv_head, page_size);
+  load_kv_tile<D>(k_tiles, k_pool, table, tile_begin * TILE_KV, TILE_KV, lowest, last_pos, kv_heads, kv_head, page_size, page_shift);
+  load_kv_tile<D>(v_tiles, v_pool, table, tile_begin * TILE_KV, TILE_KV, lowest, last_pos, kv_heads, kv_head, page_size, page_shift);
   cp_async_commit();
 
   // per-thread rows and their visibility limits
@@ -239,9 +246,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     if (t < tile_end) {
       const int next = buffer ^ 1;
       load_kv_tile<D>(k_tiles + next * TILE_KV * D, k_pool, table, (t + 1) * TILE_KV, TILE_KV, lowest, last_pos,
-                      kv_heads, kv_head, page_size);
+                      kv_heads, kv_head, page_size, page_shift);
       load_kv_tile<D>(v_tiles + next * TILE_KV * D, v_pool, table, (t + 1) * TILE_KV, TILE_KV, lowest, last_pos,
-                      kv_heads, kv_head, page_size);
+                      kv_heads, kv_head, page_size, page_shift);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -285,8 +292,11 @@ decode_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             bf16* __restrict__ out, const int* __restrict__ decode_seg,
                             const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
                             const int* __restrict__ block_table, int table_width, int heads, int kv_heads,
-                            int page_size, int window, float scale_log2, int chunk, float* __restrict__ scratch,
+                            int page_size, int page_shift, int window, float scale_log2, int chunk,
+                            float* __restrict__ scratch,
                             int* __restrict__ counters, int max_splits) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int STATE = D + 2;
   extern __shared__ __align__(128) uint8_t attn_shared[];
   bf16* q_tile = reinterpret_cast<bf16*>(attn_shared);            // [16][D], rows >= group are zeros
@@ -323,9 +333,9 @@ decode_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
   for (int s = 0; s < DECODE_STAGES; ++s) {
     if (s < tiles) {
       load_kv_tile<D>(k_tiles + s * TILE_KV * D, k_pool, table, (tile_begin + s) * TILE_KV, TILE_KV, k_begin, k_end - 1,
-                      kv_heads, kv_head, page_size);
+                      kv_heads, kv_head, page_size, page_shift);
       load_kv_tile<D>(v_tiles + s * TILE_KV * D, v_pool, table, (tile_begin + s) * TILE_KV, TILE_KV, k_begin, k_end - 1,
-                      kv_heads, kv_head, page_size);
+                      kv_heads, kv_head, page_size, page_shift);
     }
     cp_async_commit();     // one group per stage, empty or not, so that the wait counts line up
   }
@@ -360,9 +370,9 @@ decode_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     __syncthreads();
     if (t + DECODE_STAGES < tiles) {
       load_kv_tile<D>(k_tiles + stage * TILE_KV * D, k_pool, table, (tile_begin + t + DECODE_STAGES) * TILE_KV, TILE_KV,
-                      k_begin, k_end - 1, kv_heads, kv_head, page_size);
+                      k_begin, k_end - 1, kv_heads, kv_head, page_size, page_shift);
       load_kv_tile<D>(v_tiles + stage * TILE_KV * D, v_pool, table, (tile_begin + t + DECODE_STAGES) * TILE_KV, TILE_KV,
-                      k_begin, k_end - 1, kv_heads, kv_head, page_size);
+                      k_begin, k_end - 1, kv_heads, kv_head, page_size, page_shift);
     }
     cp_async_commit();
   }
@@ -411,37 +421,66 @@ decode_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
   __syncthreads();
   if (!last_flag) return;
   __threadfence();
-  for (int item = threadIdx.x; item < group * D; item += ATTN_THREADS) {
-    const int g = item / D, d = item - g * D;
-    const float* states = scratch + (state_base + (size_t)g * max_splits) * STATE;
-    // Loads of eight chunks' states are issued together so that their latencies overlap; the
-    // sums still run in chunk order.
+  // (1) every chunk's (max, sum) into shared memory with one round of loads
+  float* max_s = merge;                         // [group][splits], later the chunks' weights
+  float* sum_s = merge + 16 * max_splits;       // [group][splits]
+  float* inv_s = sum_s + 16 * max_splits;       // [group]
+  for (int item = threadIdx.x; item < group * splits; item += ATTN_THREADS) {
+    const int g = item / splits, s = item - g * splits;
+    const float2 pair = __ldcg(reinterpret_cast<const float2*>(
+        scratch + (state_base + (size_t)g * max_splits + s) * STATE));
+    max_s[g * max_splits + s] = pair.x;
+    sum_s[g * max_splits + s] = pair.y;
+  }
+  __syncthreads();
+  // (2) per head: overall max, each chunk's weight exp2(m_s - max), overall sum (chunk order)
+  if (threadIdx.x < group) {
+    const int g = threadIdx.x;
     float m_all = -INFINITY;
-    for (int s0 = 0; s0 < splits; s0 += 8) {
-      float part[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) part[j] = s0 + j < splits ? __ldcg(&states[(size_t)(s0 + j) * STATE]) : -INFINITY;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) m_all = fmaxf(m_all, part[j]);
+    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, max_s[g * max_splits + s]);
+    float l_all = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float factor = exp2f(max_s[g * max_splits + s] - m_all);
+      max_s[g * max_splits + s] = factor;
+      l_all += sum_s[g * max_splits + s] * factor;
     }
-    float l_all = 0.f, a_all = 0.f;
-    for (int s0 = 0; s0 < splits; s0 += 8) {
-      float pm[8], pl[8], pa[8];
+    inv_s[g] = 1.f / l_all;
+  }
+  __syncthreads();
+  // (3) weighted sum of the chunks' accumulators; the loads of four outputs and eight chunks are
+  // issued together so that their latencies overlap, the additions run in chunk order
+  constexpr int PER_PASS = 4;
+  for (int item0 = threadIdx.x; item0 < group * D; item0 += ATTN_THREADS * PER_PASS) {
+    float total[PER_PASS];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const bool live = s0 + j < splits;
-        pm[j] = live ? __ldcg(&states[(size_t)(s0 + j) * STATE]) : -INFINITY;
-        pl[j] = live ? __ldcg(&states[(size_t)(s0 + j) * STATE + 1]) : 0.f;
-        pa[j] = live ? __ldcg(&states[(size_t)(s0 + j) * STATE + 2 + d]) : 0.f;
+    for (int i = 0; i < PER_PASS; ++i) total[i] = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float part[PER_PASS][8];
+#pragma unroll
+      for (int i = 0; i < PER_PASS; ++i) {
+        const int item = item0 + i * ATTN_THREADS;
+        const int g = min(item / D, group - 1), d = item % D;
+        const float* states = scratch + (state_base + (size_t)g * max_splits) * STATE + 2 + d;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          part[i][j] = (item < group * D && s0 + j < splits) ? __ldcg(&states[(size_t)(s0 + j) * STATE]) : 0.f;
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float factor = exp2f(pm[j] - m_all);
-        l_all += pl[j] * factor;
-        a_all += pa[j] * factor;
+      for (int i = 0; i < PER_PASS; ++i) {
+        const int g = min((item0 + i * ATTN_THREADS) / D, group - 1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (s0 + j < splits) total[i] += part[i][j] * max_s[g * max_splits + s0 + j];
       }
     }
-    out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(a_all / l_all);
+#pragma unroll
+    for (int i = 0; i < PER_PASS; ++i) {
+      const int item = item0 + i * ATTN_THREADS;
+      if (item < group * D) {
+        const int g = item / D, d = item % D;
+        out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(total[i] * inv_s[g]);
+      }
+    }
   }
   if (threadIdx.x == 0) counters[index * kv_heads + kv_head] = 0;
 }
@@ -457,7 +496,15 @@ static int set_shared(Kernel kernel, size_t bytes) {
 
 using namespace mlr;
 
+MLR_DEFINE_PDL_SWITCH
+
 constexpr float LOG2_E = 1.4426950408889634f;
+
+static int shift_of(int page_size) {
+  for (int shift = 0; shift < 31; ++shift)
+    if ((1 << shift) == page_size) return shift;
+  return -1;
+}
 
 // Prompt portions: tiles of up to 64 rows of one segment (tile_seg, tile_row0).
 MLR_EXPORT int mlr_attention_prefill_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
@@ -471,18 +518,19 @@ MLR_EXPORT int mlr_attention_prefill_mma(const void* q, const void* k_pool, cons
   if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
   if (heads > 65535) return MLR_TOO_LARGE;
   const size_t shared = (size_t)(TILE_Q + 4 * TILE_KV) * head_dim * 2;
+  const int page_shift = shift_of(page_size);
   dim3 grid(tiles, heads);
   int status;
   if (head_dim == 64) {
     if ((status = set_shared(prefill_attention_kernel<64>, shared)) != MLR_OK) return status;
-    prefill_attention_kernel<64><<<grid, ATTN_THREADS, shared, stream>>>(
+    launch_kernel(prefill_attention_kernel<64>, dim3(grid), dim3(ATTN_THREADS), shared, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, tile_seg, tile_row0, seg_q_start,
-        seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, page_size, window, scale * LOG2_E);
+        seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E);
   } else {
     if ((status = set_shared(prefill_attention_kernel<128>, shared)) != MLR_OK) return status;
-    prefill_attention_kernel<128><<<grid, ATTN_THREADS, shared, stream>>>(
+    launch_kernel(prefill_attention_kernel<128>, dim3(grid), dim3(ATTN_THREADS), shared, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, tile_seg, tile_row0, seg_q_start,
-        seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, page_size, window, scale * LOG2_E);
+        seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E);
   }
   return launch_status();
 }
@@ -499,21 +547,24 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
     return MLR_BAD_SIZE;
   if (heads / kv_heads > 16 || rows > 65535 || kv_heads > 65535) return MLR_TOO_LARGE;
   if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
+  // the final merge keeps 2 * 16 * max_splits + 16 floats in the warps' merge area
+  if ((size_t)(2 * 16 * max_splits + 16) > (size_t)ATTN_WARPS * 16 * (head_dim + 2)) return MLR_TOO_LARGE;
   const size_t shared = (size_t)(16 + 2 * DECODE_STAGES * TILE_KV) * head_dim * 2 +
                         (size_t)ATTN_WARPS * 16 * (head_dim + 2) * sizeof(float);
   dim3 grid(max_splits, kv_heads, rows);
+  const int page_shift = shift_of(page_size);
   int status;
   if (head_dim == 64) {
     if ((status = set_shared(decode_attention_mma_kernel<64>, shared)) != MLR_OK) return status;
-    decode_attention_mma_kernel<64><<<grid, ATTN_THREADS, shared, stream>>>(
+    launch_kernel(decode_attention_mma_kernel<64>, dim3(grid), dim3(ATTN_THREADS), shared, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
-        block_table, table_width, heads, kv_heads, page_size, window, scale * LOG2_E, chunk, (float*)scratch,
+        block_table, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk, (float*)scratch,
         counters, max_splits);
   } else {
     if ((status = set_shared(decode_attention_mma_kernel<128>, shared)) != MLR_OK) return status;
-    decode_attention_mma_kernel<128><<<grid, ATTN_THREADS, shared, stream>>>(
+    launch_kernel(decode_attention_mma_kernel<128>, dim3(grid), dim3(ATTN_THREADS), shared, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
-        block_table, table_width, heads, kv_heads, page_size, window, scale * LOG2_E, chunk, (float*)scratch,
+        block_table, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk, (float*)scratch,
         counters, max_splits);
   }
   return launch_status();

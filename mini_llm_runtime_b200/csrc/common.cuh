@@ -72,6 +72,42 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return total;
 }
 
+// Programmatic dependent launch.  Every kernel of this package is launched with the attribute that
+// lets it start while the kernel before it on the stream is still running; it then does whatever
+// does not depend on that kernel (barrier set-up, tensor-memory allocation, weight loads) and calls
+// pdl_wait() before its first access to memory an earlier kernel wrote and before its own first
+// write.  pdl_wait() returns once the preceding kernel has completed and its writes are visible;
+// since every kernel waits before it finishes, completion is transitive along the stream.
+// pdl_trigger() tells the scheduler that the next kernel may be brought in.  Launched without the
+// attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool& pdl_enabled() {
+  static bool enabled = true;
+  return enabled;
+}
+
+template <typename... KernelArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
+// One switch per library (each .cu is its own shared object).
+#define MLR_DEFINE_PDL_SWITCH \
+  MLR_EXPORT void mlr_set_pdl(int enabled) { mlr::pdl_enabled() = enabled != 0; }
+
 inline int launch_status() {
   cudaError_t err = cudaGetLastError();
   return err == cudaSuccess ? MLR_OK : (int)err;

@@ -13,6 +13,8 @@ namespace mlr {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  T* __restrict__ out, int width, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   // Host code validates ids; clamp so a bad id can never read outside the table.
@@ -26,6 +28,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows,
                                    T* __restrict__ out, int width) {
+  pdl_trigger();
+  pdl_wait();
   const T* src = x + (size_t)rows[blockIdx.x] * width;
   T* dst = out + (size_t)blockIdx.x * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
@@ -40,6 +44,8 @@ template <typename T, typename W>
 __global__ void rms_norm_kernel(T* __restrict__ residual, const T* __restrict__ delta,
                                 const W* __restrict__ weight, T* __restrict__ out, int width,
                                 float eps) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float row_cache[];
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * width;
@@ -66,6 +72,8 @@ __global__ void rms_norm_kernel(T* __restrict__ residual, const T* __restrict__ 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner, int block,
                               size_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / inner;
@@ -89,6 +97,8 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const int* __res
                                      const long long* __restrict__ slots, T* __restrict__ q_out,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, int heads,
                                      int kv_heads, int head_dim, int page_size, int write_kv) {
+  pdl_trigger();
+  pdl_wait();
   const int token = blockIdx.x;
   const int half = head_dim >> 1;
   const int row_width = (heads + 2 * kv_heads) * head_dim;
@@ -135,7 +145,7 @@ int rope_kv_write_launch(const void* qkv, const int* positions, const float* inv
                          int write_kv, cudaStream_t stream) {
   int work = (heads + kv_heads) * (head_dim / 2);
   int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
-  rope_kv_write_kernel<T><<<tokens, threads, 0, stream>>>(
+  launch_kernel(rope_kv_write_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 
       (const T*)qkv, positions, inv_freq, slots, (T*)q_out, (T*)k_pool, (T*)v_pool, heads,
       kv_heads, head_dim, page_size, write_kv);
   return launch_status();
@@ -152,15 +162,17 @@ static int row_threads(int width) {
 
 using namespace mlr;
 
+MLR_DEFINE_PDL_SWITCH
+
 MLR_EXPORT int mlr_embedding(const int* ids, const void* table, void* out, int rows, int width,
                              int vocab, int dtype, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || width <= 0 || vocab <= 0) return MLR_BAD_SIZE;
   const int threads = row_threads(width);
   if (dtype == MLR_F32)
-    embedding_kernel<float><<<rows, threads, 0, stream>>>(ids, (const float*)table, (float*)out, width, vocab);
+    launch_kernel(embedding_kernel<float>, dim3(rows), dim3(threads), 0, stream, ids, (const float*)table, (float*)out, width, vocab);
   else if (dtype == MLR_BF16)
-    embedding_kernel<bf16><<<rows, threads, 0, stream>>>(ids, (const bf16*)table, (bf16*)out, width, vocab);
+    launch_kernel(embedding_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, ids, (const bf16*)table, (bf16*)out, width, vocab);
   else
     return MLR_BAD_DTYPE;
   return launch_status();
@@ -172,9 +184,9 @@ MLR_EXPORT int mlr_gather_rows(const void* x, const int* rows, void* out, int co
   if (count < 0 || width <= 0) return MLR_BAD_SIZE;
   const int threads = row_threads(width);
   if (dtype == MLR_F32)
-    gather_rows_kernel<float><<<count, threads, 0, stream>>>((const float*)x, rows, (float*)out, width);
+    launch_kernel(gather_rows_kernel<float>, dim3(count), dim3(threads), 0, stream, (const float*)x, rows, (float*)out, width);
   else if (dtype == MLR_BF16)
-    gather_rows_kernel<bf16><<<count, threads, 0, stream>>>((const bf16*)x, rows, (bf16*)out, width);
+    launch_kernel(gather_rows_kernel<bf16>, dim3(count), dim3(threads), 0, stream, (const bf16*)x, rows, (bf16*)out, width);
   else
     return MLR_BAD_DTYPE;
   return launch_status();
@@ -189,7 +201,7 @@ static int rms_norm_launch(void* residual, const void* delta, const void* weight
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;
   }
-  rms_norm_kernel<T, W><<<rows, row_threads(width), shared, stream>>>(
+  launch_kernel(rms_norm_kernel<T, W>, dim3(rows), dim3(row_threads(width)), shared, stream, 
       (T*)residual, (const T*)delta, (const W*)weight, (T*)out, width, eps);
   return launch_status();
 }
@@ -220,9 +232,9 @@ MLR_EXPORT int mlr_swiglu(const void* gate_up, void* out, long long rows, int in
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (dtype == MLR_F32)
-    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inner, block, total);
+    launch_kernel(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inner, block, total);
   else if (dtype == MLR_BF16)
-    swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inner, block, total);
+    launch_kernel(swiglu_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inner, block, total);
   else
     return MLR_BAD_DTYPE;
   return launch_status();

@@ -195,10 +195,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_holder;
 
+  pdl_trigger();
   if (warp == 0 && lane == 0) {
     // ---------------- producer
-    int s = 0, round = 0;
-    for (int i = 0; i < num_kb; ++i) {
+    // The weight tiles of the first ring-full of k blocks do not depend on the kernel before this
+    // one: request them at once, then wait for that kernel and request the activation tiles.
+    const int ahead = min(stages, num_kb);
+    for (int i = 0; i < ahead; ++i) {
+      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+      uint8_t* stage = tiles + (size_t)i * STAGE_BYTES;
+      const int k = (kb_begin + i) * TILE_K;
+      if (SWAP) tma_load_2d(&map_a, &full_bar[i], stage, k, a_row0);
+      else tma_load_2d(&map_b, &full_bar[i], stage + A_BYTES, k, b_row0);
+    }
+    pdl_wait();
+    for (int i = 0; i < ahead; ++i) {
+      uint8_t* stage = tiles + (size_t)i * STAGE_BYTES;
+      const int k = (kb_begin + i) * TILE_K;
+      if (SWAP) tma_load_2d(&map_b, &full_bar[i], stage + A_BYTES, k, b_row0);
+      else tma_load_2d(&map_a, &full_bar[i], stage, k, a_row0);
+    }
+    int s = ahead == stages ? 0 : ahead, round = ahead == stages ? 1 : 0;
+    for (int i = ahead; i < num_kb; ++i) {
       if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, p.error_word, 1)) break;
       mbar_expect_tx(&full_bar[s], STAGE_BYTES);
       uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
@@ -228,6 +246,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ---------------- epilogue: thread <-> TMEM lane <-> tile row
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
+    pdl_wait();                                         // before any write of this kernel
     if (!mbar_wait(&accumulator_bar, 0, p.error_word, 3)) atomicOr(&epilogue_failed, 1);
     asm volatile("bar.sync 1, 128;" ::: "memory");     // all four epilogue warps always get here
     const bool ok = epilogue_failed == 0;               // the same answer in all of them
@@ -433,7 +452,7 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
   if (!make_map(&map_a, a_base, a_rows, p.K, TILE_ROWS) || !make_map(&map_b, b_base, b_rows, p.K, BN))
     return MLR_BAD_ALIGNMENT;
   dim3 grid((a_rows + TILE_ROWS - 1) / TILE_ROWS, (b_rows + BN - 1) / BN, splits);
-  gemm_tcgen05_kernel<BN, SWAP, SWIGLU><<<grid, GEMM_THREADS, shared, stream>>>(map_a, map_b, p);
+  launch_kernel(gemm_tcgen05_kernel<BN, SWAP, SWIGLU>, dim3(grid), dim3(GEMM_THREADS), shared, stream, map_a, map_b, p);
   return launch_status();
 }
 
@@ -464,6 +483,9 @@ static GemmPlan plan_gemm(int M, int N, int K) {
   // A ring as deep as the split is long (at most 6 stages) leaves room for several CTAs per SM,
   // so that one CTA's prologue and epilogue overlap another's streaming.
   int stages = plan.kb_per_split < 2 ? 2 : (plan.kb_per_split > 6 ? 6 : plan.kb_per_split);
+  // Many-row products are compute bound and their operands come from L2: three stages are enough
+  // and leave room for two CTAs per SM, one's epilogue under the other's main loop.
+  if (M > 128 && stages > 3) stages = 3;
   const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
   while (stages > 2 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
   plan.stages = stages;
@@ -473,6 +495,8 @@ static GemmPlan plan_gemm(int M, int N, int K) {
 }  // namespace mlr
 
 using namespace mlr;
+
+MLR_DEFINE_PDL_SWITCH
 
 // Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
 // `splits_out` receives the split count the launcher will use, `tiles_out` the number of tiles.

@@ -18,6 +18,8 @@ template <typename TIn, typename TOut, int BM>
 __global__ void __launch_bounds__(256)
 linear_simt_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w, const TIn* __restrict__ bias,
                    TOut* __restrict__ y, int M, int N, int K) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int TM = BM / 16;  // rows per thread
   constexpr int TN = BN / 16;  // columns per thread
   __shared__ float a_tile[BK][BM + 1];
@@ -77,11 +79,11 @@ int linear_simt_launch(const void* x, const void* w, const void* bias, void* y, 
                        cudaStream_t stream) {
   if (M <= 16) {
     dim3 grid((N + BN - 1) / BN, (M + 15) / 16);
-    linear_simt_kernel<TIn, TOut, 16><<<grid, 256, 0, stream>>>((const TIn*)x, (const TIn*)w,
+    launch_kernel(linear_simt_kernel<TIn, TOut, 16>, dim3(grid), dim3(256), 0, stream, (const TIn*)x, (const TIn*)w,
                                                                  (const TIn*)bias, (TOut*)y, M, N, K);
   } else {
     dim3 grid((N + BN - 1) / BN, (M + 63) / 64);
-    linear_simt_kernel<TIn, TOut, 64><<<grid, 256, 0, stream>>>((const TIn*)x, (const TIn*)w,
+    launch_kernel(linear_simt_kernel<TIn, TOut, 64>, dim3(grid), dim3(256), 0, stream, (const TIn*)x, (const TIn*)w,
                                                                  (const TIn*)bias, (TOut*)y, M, N, K);
   }
   return launch_status();
@@ -90,6 +92,8 @@ int linear_simt_launch(const void* x, const void* w, const void* bias, void* y, 
 }  // namespace mlr
 
 using namespace mlr;
+
+MLR_DEFINE_PDL_SWITCH
 
 // in_dtype: storage of x, w and bias.  out_dtype: storage of y (float32 output from bfloat16
 // inputs is used for logits).

@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperatures,
               const long long* __restrict__ seeds, const long long* __restrict__ counters,
               int* __restrict__ tokens, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float scratch[32];
   __shared__ int scratch_index[32];
   __shared__ float warp_totals[SAMPLE_WARPS];
@@ -119,12 +121,14 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
 using namespace mlr;
 
+MLR_DEFINE_PDL_SWITCH
+
 // temperatures[r] <= 0 selects greedy for row r.  tokens: int32 [rows].
 MLR_EXPORT int mlr_sample(const float* logits, const float* temperatures, const long long* seeds,
                           const long long* counters, int* tokens, int rows, int vocab,
                           cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || vocab <= 0) return MLR_BAD_SIZE;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperatures, seeds, counters, tokens, vocab);
+  launch_kernel(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, temperatures, seeds, counters, tokens, vocab);
   return launch_status();
 }

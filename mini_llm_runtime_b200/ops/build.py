@@ -184,7 +184,23 @@ def load_library(name: str) -> ctypes.CDLL:
                 _loaded[name] = ctypes.CDLL(str(path))
             except OSError as error:
                 raise BuildError(f"cannot load {path}: {error}") from error
+            if hasattr(_loaded[name], "mlr_set_pdl"):
+                _loaded[name].mlr_set_pdl(int(_pdl))
         return _loaded[name]
+
+
+_pdl = os.environ.get("MLR_PDL", "1") != "0"
+
+
+def set_programmatic_launch(enabled: bool) -> None:
+    """Launch kernels so that each may start while its predecessor on the stream still runs
+    (programmatic dependent launch).  On by default; MLR_PDL=0 in the environment turns it off."""
+    global _pdl
+    _pdl = bool(enabled)
+    with _lock:
+        for library in _loaded.values():
+            if hasattr(library, "mlr_set_pdl"):
+                library.mlr_set_pdl(int(_pdl))
 
 
 def build_all() -> dict[str, Path]:

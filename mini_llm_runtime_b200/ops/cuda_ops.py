@@ -349,6 +349,8 @@ class CudaOps:
         chunk = 512
         while chunk > 128 and num_decode * num_kv_heads * -(-longest // chunk) < 2 * 148:
             chunk //= 2
+        while -(-longest // chunk) > 64:      # the final merge handles at most 64 chunks per request
+            chunk *= 2
         return chunk, max(1, -(-longest // chunk))
 
     def _decode_attention(self, q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window,
