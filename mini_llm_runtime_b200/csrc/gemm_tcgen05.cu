@@ -160,7 +160,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr uint32_t B_BYTES = BN * TILE_K * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-  static_assert(!SWIGLU || SWAP || BN == 128, "fused SwiGLU needs gate and up columns in one tile");
+  static_assert(!SWIGLU || SWAP || BN % 128 == 0, "fused SwiGLU needs gate and up columns in one tile");
 
   extern __shared__ uint8_t raw_shared[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)raw_shared + 1023) & ~(uintptr_t)1023);
@@ -314,18 +314,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
     } else if (SWIGLU) {
-      // not swapped, BN = 128: columns 0..63 are gate, 64..127 up, all in this thread's TMEM lane
+      // not swapped: each group of 128 columns holds 64 gate columns, then the 64 up columns of
+      // the same outputs, all in this thread's TMEM lane.
       // tcgen05.ld is warp-collective: every lane runs the loads, only the stores depend on m.
       const int m = a_row0 + row;
       const int half = p.N >> 1;
       if (finish) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < 64; c0 += 16) {
+        for (int cc = 0; cc < BN / 2; cc += 16) {
+          const int block = cc >> 6, c0 = cc & 63;           // which 128-column group, offset in it
           uint32_t g[16], u[16];
-          tmem_load16(lane_base + c0, g);
-          tmem_load16(lane_base + 64 + c0, u);
+          tmem_load16(lane_base + block * 128 + c0, g);
+          tmem_load16(lane_base + block * 128 + 64 + c0, u);
           if (m >= p.M) continue;
-          const int n0 = blockIdx.y * 64 + c0;
+          const int n0 = (blockIdx.y * (BN / 128) + block) * 64 + c0;
           uint32_t packed[8];
 #pragma unroll
           for (int c = 0; c < 16; c += 2)
@@ -466,8 +468,9 @@ static GemmPlan plan_gemm(int M, int N, int K) {
     plan.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     plan.tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
   } else {
-    plan.bn = 128;
-    plan.tiles = ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + 127) / 128);
+    // Wide tiles halve the activation traffic per flop; worth it once they still fill the SMs.
+    plan.bn = (N >= 256 && ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + 255) / 256) >= 148) ? 256 : 128;
+    plan.tiles = ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + plan.bn - 1) / plan.bn);
   }
   int splits = 1;
   if (M <= 128) {
@@ -485,7 +488,7 @@ static GemmPlan plan_gemm(int M, int N, int K) {
   int stages = plan.kb_per_split < 2 ? 2 : (plan.kb_per_split > 6 ? 6 : plan.kb_per_split);
   // Many-row products are compute bound and their operands come from L2: three stages are enough
   // and leave room for two CTAs per SM, one's epilogue under the other's main loop.
-  if (M > 128 && stages > 3) stages = 3;
+  if (M > 128 && stages > 3) stages = plan.bn == 256 ? 4 : 3;
   const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
   while (stages > 2 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
   plan.stages = stages;
@@ -537,11 +540,13 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
     if (M <= 32) return launch<32, true, true>(x, w, p, plan.splits, stream);
     if (M <= 64) return launch<64, true, true>(x, w, p, plan.splits, stream);
     if (M <= 128) return launch<128, true, true>(x, w, p, plan.splits, stream);
+    if (plan.bn == 256) return launch<256, false, true>(x, w, p, plan.splits, stream);
     return launch<128, false, true>(x, w, p, plan.splits, stream);
   }
   if (M <= 16) return launch<16, true, false>(x, w, p, plan.splits, stream);
   if (M <= 32) return launch<32, true, false>(x, w, p, plan.splits, stream);
   if (M <= 64) return launch<64, true, false>(x, w, p, plan.splits, stream);
   if (M <= 128) return launch<128, true, false>(x, w, p, plan.splits, stream);
+  if (plan.bn == 256) return launch<256, false, false>(x, w, p, plan.splits, stream);
   return launch<128, false, false>(x, w, p, plan.splits, stream);
 }

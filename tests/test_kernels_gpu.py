@@ -135,6 +135,19 @@ def test_tensor_core_linear(m, n, k):
     assert torch.equal(got32, cuda().linear(x.to(DEVICE), w.to(DEVICE), None, out_dtype=torch.float32))
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 4864, 896), (1000, 896, 4864), (2048, 1152, 896), (517, 5000, 264)])
+def test_tensor_core_linear_many_rows(m, n, k):
+    """Prefill-sized products: 128x128 and 128x256 tiles, ragged edges in every dimension."""
+    x = rnd((m, k), torch.bfloat16, 70)
+    w = rnd((n, k), torch.bfloat16, 71, 0.05)
+    b = rnd((n,), torch.bfloat16, 72)
+    got = cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE))
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    want = (x.to(DEVICE).double() @ w.to(DEVICE).double().T + b.to(DEVICE).double()).cpu()
+    assert_close(got, want, torch.bfloat16, f"tcgen05 linear {m}x{n}x{k}")
+
+
 def test_tensor_core_linear_large_vocabulary():
     x = rnd((8, 896), torch.bfloat16, 50)
     w = rnd((151936, 896), torch.bfloat16, 51, 0.02)
