@@ -25,9 +25,19 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-SIZES = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
-             num_attention_heads=14, num_key_value_heads=2, max_position_embeddings=32768,
-             rms_norm_eps=1e-6, rope_theta=1000000.0, hidden_act="silu", tie_word_embeddings=True)
+MODEL_SIZES = {
+    "0.5b": dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
+                 num_attention_heads=14, num_key_value_heads=2, max_position_embeddings=32768,
+                 rms_norm_eps=1e-6, rope_theta=1000000.0, hidden_act="silu", tie_word_embeddings=True),
+    "7b": dict(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+               num_attention_heads=28, num_key_value_heads=4, max_position_embeddings=32768,
+               rms_norm_eps=1e-6, rope_theta=1000000.0, hidden_act="silu", tie_word_embeddings=False),
+    "14b": dict(vocab_size=152064, hidden_size=5120, intermediate_size=13824, num_hidden_layers=48,
+                num_attention_heads=40, num_key_value_heads=8, max_position_embeddings=32768,
+                rms_norm_eps=1e-5, rope_theta=1000000.0, hidden_act="silu", tie_word_embeddings=False),
+}
+MODEL_NAMES = {"0.5b": "Qwen2.5-0.5B sizes", "7b": "Qwen2.5-7B sizes", "14b": "Qwen2.5-14B sizes"}
+SIZES = MODEL_SIZES["0.5b"]      # the default workload (BASELINE.json configs[2]); --size replaces it
 CONTEXT = 4096
 CONTEXT_MEAN = 3072
 PREFILL_TOKENS = 2048
@@ -42,7 +52,9 @@ def parse_args():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"],
+    parser.add_argument("--size", choices=sorted(MODEL_SIZES), default="0.5b",
+                        help="layer sizes: Qwen2.5-0.5B (default, the headline workload), 7B or 14B")
+    parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the model has (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--skip-prefill", action="store_true")
@@ -112,7 +124,7 @@ def model_numbers(config, layers):
     h, i, v = config.hidden_size, config.intermediate_size, config.vocab_size
     hq, hkv, d = config.num_attention_heads, config.num_key_value_heads, config.head_dim
     per_layer = (hq + 2 * hkv) * d * h + (hq + 2 * hkv) * d + h * hq * d + 3 * h * i + 2 * h
-    head = v * h
+    head = v * h          # the head's matrix is read once per step, tied to the embedding or not
     weight_bytes = 2 * (layers * per_layer + head + h)
     kv_bytes_per_token = 2 * layers * hkv * d * 2
     linear_flops_per_token = 2 * layers * ((hq + 2 * hkv) * d * h + h * hq * d + 3 * h * i)
@@ -156,7 +168,7 @@ def fill(runner, request_ids, prefix, vocab):
             runner.step([StepEntry(rid, tokens[start:start + PREFILL_TOKENS], [])])
 
 
-def time_decode(runner, request_ids, vocab, steps, warmup):
+def time_decode(runner, request_ids, vocab, steps, warmup, clocks=None):
     """Device time of ``steps`` decode steps of the whole batch (CUDA events), after ``warmup``."""
     import torch
 
@@ -176,6 +188,8 @@ def time_decode(runner, request_ids, vocab, steps, warmup):
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = cuda_ops.launches
     replays_before = runner.graph_replays
+    if clocks is not None:
+        clocks.__enter__()            # sample clocks during the timed steps only
     host_started = time.perf_counter()
     start.record()
     for _ in range(steps):
@@ -183,6 +197,8 @@ def time_decode(runner, request_ids, vocab, steps, warmup):
     end.record()
     host_ms = (time.perf_counter() - host_started) * 1e3
     torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.__exit__(None, None, None)
     launched = cuda_ops.launches - launches_before
     launched += (runner.graph_replays - replays_before) * runner.launches_per_replay(batch, True)
     print(f"[bench] batch {batch}: device {start.elapsed_time(end) / steps:.3f} ms/step, host issue "
@@ -190,7 +206,7 @@ def time_decode(runner, request_ids, vocab, steps, warmup):
     return start.elapsed_time(end), launched
 
 
-def decode_point(layers, batch, steps, warmup, context_mean=CONTEXT_MEAN, graphs=True):
+def decode_point(layers, batch, steps, warmup, context_mean=CONTEXT_MEAN, graphs=True, clocks=None):
     import torch
 
     prefix = max(1, context_mean - (steps + warmup) // 2)
@@ -199,7 +215,7 @@ def decode_point(layers, batch, steps, warmup, context_mean=CONTEXT_MEAN, graphs
     ids = [f"d{i}" for i in range(batch)]
     fill(runner, ids, prefix, config.vocab_size)
     torch.cuda.synchronize()
-    ms, launches = time_decode(runner, ids, config.vocab_size, steps, warmup)
+    ms, launches = time_decode(runner, ids, config.vocab_size, steps, warmup, clocks)
     for rid in ids:
         runner.cache.release(rid)
     del runner, model
@@ -284,23 +300,23 @@ def run_ours(args):
     config = Qwen2Config(**dict(SIZES, num_hidden_layers=layers))
     numbers = model_numbers(config, layers)
 
-    with ClockSampler() as clocks:
-        ms, launches, prefix = decode_point(layers, args.batch, args.steps, args.warmup, args.context_mean,
-                                            not args.no_graphs)
+    clocks = ClockSampler()
+    ms, launches, prefix = decode_point(layers, args.batch, args.steps, args.warmup, args.context_mean,
+                                        not args.no_graphs, clocks)
     ms_per_step = ms / args.steps
     value = args.batch * args.steps / (ms / 1e3)
     step_bytes = numbers["weight_bytes"] + args.batch * args.context_mean * numbers["kv_bytes_per_token"]
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
 
     record = {
-        "metric": "decode tokens/s (batch 8, context 4096)", "value": round(value, 1), "unit": "tokens/s",
+        "metric": f"decode tokens/s (batch {args.batch}, context 4096)", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (seeded random weights and token ids)", "impl": "ours",
-        "config": {"model": "Qwen2.5-0.5B sizes", "layers": layers, "layers_of_model": SIZES["num_hidden_layers"],
+        "config": {"model": MODEL_NAMES[args.size], "layers": layers, "layers_of_model": SIZES["num_hidden_layers"],
                    "hidden": config.hidden_size, "q_heads": config.num_attention_heads,
                    "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
-                   "intermediate": config.intermediate_size, "vocab": config.vocab_size, "tied_head": True,
+                   "intermediate": config.intermediate_size, "vocab": config.vocab_size, "tied_head": config.tie_word_embeddings,
                    "global_batch": args.batch, "seq_len": CONTEXT, "context_mean": args.context_mean,
                    "prefix": prefix, "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights + KV > 1 GB)",
@@ -420,7 +436,7 @@ def run_reference(args):
         "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (the reference kernel's only dtype)",
         "data": "synthetic (random weights and token ids)", "impl": "reference",
-        "config": {"model": "Qwen2.5-0.5B sizes", "layers": layers, "layers_of_model": SIZES["num_hidden_layers"],
+        "config": {"model": MODEL_NAMES[args.size], "layers": layers, "layers_of_model": SIZES["num_hidden_layers"],
                    "global_batch": batch, "seq_len": CONTEXT, "context_mean": args.context_mean, "prefix": prefix,
                    "block_size": BLOCK_SIZE, "parallelism": "single GPU",
                    "path": "ContinuousBatchEngine + paged_cuda decode kernel"},
@@ -432,7 +448,11 @@ def run_reference(args):
 
 
 def main():
+    global SIZES
     args = parse_args()
+    SIZES = MODEL_SIZES[args.size]
+    if args.layers is None:
+        args.layers = SIZES["num_hidden_layers"]
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2

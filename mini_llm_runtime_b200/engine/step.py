@@ -147,6 +147,10 @@ class _CapturedStep:
     logits: torch.Tensor | None = None
     tokens: torch.Tensor | None = None
     launches: int = 0      # kernels in the graph
+    nbytes: int = 0
+    # pinned staging buffers with numpy views of every array at its fixed offset, used in turn
+    stagings: list = field(default_factory=list)
+    cursor: int = 0
 
 
 _TORCH_OF = {np.dtype(np.int32): torch.int32, np.dtype(np.int64): torch.int64,
@@ -167,6 +171,7 @@ class ModelRunner:
         self._ring = _PinnedRing(self.device)
         self._device_meta: torch.Tensor | None = None
         self._last_layout_bytes = 0
+        self._last_layout: list = []
         self.steps_run = 0
         # Decode-only steps (one token per request, its logits wanted) are captured into CUDA
         # graphs, one per batch size, and replayed: a decode step is some two hundred small
@@ -273,6 +278,7 @@ class ModelRunner:
             packer.add("token_indices", np.asarray(sampling.token_indices, dtype=np.int64))
         dev = self._upload(packer, device_buffer)
         self._last_layout_bytes = packer.size
+        self._last_layout = [(name, array.dtype, array.shape, offset, array) for name, array, offset in packer.items]
 
         segments = [Segment(e.request_id, int(slots[i]), int(row_start[i]), int(lengths[i]),
                             int(position_start[i])) for i, e in enumerate(entries)]
@@ -309,6 +315,12 @@ class ModelRunner:
             count = len(entry.tokens)
             if count == 0:
                 raise ValueError(f"request {entry.request_id!r}: a step must bring at least one token")
+            if count == 1 and type(entry.tokens[0]) is int and 0 <= entry.tokens[0] < self.vocab_size \
+                    and len(entry.want) <= 1 and (not entry.want or entry.want[0] == 0):
+                if self.cache.get(entry.request_id).committed + 1 > self.max_positions:
+                    raise ValueError(f"request {entry.request_id!r} would exceed the model's "
+                                     f"{self.max_positions} positions")
+                continue                      # the common decode entry: nothing more to check
             tokens = np.asarray(entry.tokens)
             if tokens.dtype.kind not in "iu" or tokens.min() < 0 or tokens.max() >= self.vocab_size:
                 raise ValueError(f"request {entry.request_id!r}: token ids must be integers in "
@@ -349,12 +361,14 @@ class ModelRunner:
             del probe
             captured = _CapturedStep(torch.empty(self._last_layout_bytes + 64, dtype=torch.uint8, device=self.device))
             self._graphs[key] = captured
-        ctx = self._build_context(entries, requests, sampling, fixed_width=width,
-                                  device_buffer=captured.metadata)
         if captured.graph is not None:
+            self._refresh_captured(captured, entries, requests, sampling)
             captured.graph.replay()
             self.graph_replays += 1
             return captured.logits, captured.tokens
+        ctx = self._build_context(entries, requests, sampling, fixed_width=width,
+                                  device_buffer=captured.metadata)
+        self._prepare_stagings(captured)
         previous = (kernels.decode_chunk, kernels.decode_max_splits)
         kernels.decode_chunk, kernels.decode_max_splits = chunk, splits
         try:
@@ -370,6 +384,54 @@ class ModelRunner:
         finally:
             kernels.decode_chunk, kernels.decode_max_splits = previous
         return logits, tokens
+
+    def _prepare_stagings(self, captured: "_CapturedStep") -> None:
+        """Pinned copies of the step's metadata layout, each with numpy views of its arrays.  What
+        depends only on the batch size (segment table, tiles, wanted rows) is written once."""
+        captured.nbytes = max(self._last_layout_bytes, 16)
+        captured.stagings = []
+        for _ in range(3):
+            buffer = torch.empty(captured.nbytes, dtype=torch.uint8, pin_memory=True)
+            host = buffer.numpy()
+            views = {}
+            for name, dtype, shape, offset, array in self._last_layout:
+                view = host[offset:offset + array.nbytes].view(dtype).reshape(shape)
+                view[...] = array
+                views[name] = view
+            captured.stagings.append([buffer, views, None])
+
+    def _refresh_captured(self, captured: "_CapturedStep", entries, requests, sampling) -> None:
+        """Write what changes from one decode step to the next (tokens, positions, slots, block
+        tables, sampling rows) into the next pinned copy and send it in one transfer."""
+        staging = captured.stagings[captured.cursor]
+        captured.cursor = (captured.cursor + 1) % len(captured.stagings)
+        buffer, views, event = staging
+        if event is not None:
+            event.synchronize()
+        count = len(entries)
+        cache = self.cache
+        views["token_ids"][:] = np.fromiter((e.tokens[0] for e in entries), np.int32, count)
+        positions = np.fromiter((r.pending[0] for r in requests), np.int32, count)
+        slots = np.fromiter((r.slot for r in requests), np.int32, count)
+        views["positions"][:] = positions
+        views["seg_pos0"][:] = positions
+        views["seg_slots"][:] = slots
+        logical = positions // cache.page_size
+        offsets = positions - logical * cache.page_size
+        for group in cache.groups:
+            pages = group.table[slots, logical].astype(np.int64)
+            if (pages < 0).any():
+                raise RuntimeError("a request has no page for the token it is writing")
+            views[f"slots{group.index}"][:] = pages * cache.page_size + offsets
+            np.take(group.table, slots, axis=0, out=views[f"table{group.index}"])
+        if sampling is not None:
+            views["temperatures"][:] = sampling.temperatures
+            views["seeds"][:] = sampling.seeds
+            views["token_indices"][:] = sampling.token_indices
+        captured.metadata[:captured.nbytes].copy_(buffer, non_blocking=True)
+        if staging[2] is None:
+            staging[2] = torch.cuda.Event()
+        staging[2].record()
 
     def launches_per_replay(self, batch: int, sampling: bool) -> int:
         """Kernels one replay of the captured step of this batch size launches (0 if not captured)."""
