@@ -1,0 +1,203 @@
+// y[M,N] = x[M,K] * W[N,K]^T (+ bias) for very few rows (M <= 16, a decode step of a small batch),
+// bfloat16 in, float32 accumulate, for the layer products whose weight matrix is too small to
+// give every SM a 128-row tcgen05 tile: there the cost is a chain of latencies, not bandwidth, and
+// this kernel keeps the chain short.
+//
+// One CTA owns 16 weight rows (output columns).  Its warps split K between them in blocks of 32;
+// every lane fetches its pieces of W and x with plain 16-byte loads - all loads of a batch of
+// k blocks are issued before any is used - and feeds them to mma.sync.m16n8k16 with the 16 weight
+// rows on the M side and up to 8 tokens on the N side.  The 16 bytes a lane loads from a row are 8
+// consecutive k values; A and B fragments take them in the same (permuted) k order, which leaves
+// the dot products unchanged and needs no shared-memory staging.  The warps' partial tiles are
+// added in warp order through shared memory (deterministic), bias is added, and for the fused
+// gate/up product (weight rows in blocks of 64 gate rows followed by the 64 up rows of the same
+// outputs, as the tensor-core kernel takes them) silu(gate) * up is applied before the store.
+//
+// Weight loads of the first batch are issued before the programmatic dependency wait: they do
+// not depend on the previous kernel.  Requires K % 8 == 0 and 16-byte aligned rows.
+#include "common.cuh"
+
+namespace mlr {
+
+constexpr int SKINNY_BATCH = 8;       // k blocks (of 32) whose loads are in flight together
+
+__device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// GROUPS: 16-row groups per CTA (2 for the fused gate/up product: the gate rows and their up rows).
+// TOKENS8: token blocks of 8 (1 for M <= 8, 2 for M <= 16).
+template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU>
+__global__ void __launch_bounds__(WARPS * 32)
+skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ bias,
+                   void* __restrict__ out, int M, int N, int K, int out_f32) {
+  __shared__ float partial[WARPS][GROUPS * TOKENS8 * 4][32];
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int k_blocks = (K + 31) / 32;
+
+  // first weight row of each group of 16
+  int row0[GROUPS];
+  if (SWIGLU) {
+    const int o0 = blockIdx.x * 16;                       // first output column of this CTA
+    row0[0] = (o0 / 64) * 128 + (o0 % 64);                // its gate rows
+    row0[GROUPS - 1] = row0[0] + 64;                      // and the up rows of the same outputs
+  } else {
+    row0[0] = blockIdx.x * 16;
+  }
+  const uint4* w_row[GROUPS][2];
+  bool w_valid[GROUPS][2];
+#pragma unroll
+  for (int r = 0; r < GROUPS; ++r)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = row0[r] + g + 8 * h;
+      w_valid[r][h] = row < N;
+      w_row[r][h] = reinterpret_cast<const uint4*>(w + (size_t)(w_valid[r][h] ? row : 0) * K);
+    }
+  const uint4* x_row[TOKENS8];
+  bool x_valid[TOKENS8];
+#pragma unroll
+  for (int n = 0; n < TOKENS8; ++n) {
+    const int token = n * 8 + g;
+    x_valid[n] = token < M;
+    x_row[n] = reinterpret_cast<const uint4*>(x + (size_t)(x_valid[n] ? token : 0) * K);
+  }
+
+  float acc[GROUPS][TOKENS8][4];
+#pragma unroll
+  for (int r = 0; r < GROUPS; ++r)
+#pragma unroll
+    for (int n = 0; n < TOKENS8; ++n) acc[r][n][0] = acc[r][n][1] = acc[r][n][2] = acc[r][n][3] = 0.f;
+
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  bool waited = false;
+  for (int first = warp; first < k_blocks; first += WARPS * SKINNY_BATCH) {
+    uint4 wv[SKINNY_BATCH][GROUPS][2], xv[SKINNY_BATCH][TOKENS8];
+#pragma unroll
+    for (int i = 0; i < SKINNY_BATCH; ++i) {
+      const int piece = (first + i * WARPS) * 4 + t;          // index of this lane's 16 bytes in the row
+      const bool in_range = first + i * WARPS < k_blocks && piece * 8 < K;
+#pragma unroll
+      for (int r = 0; r < GROUPS; ++r)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) wv[i][r][h] = (in_range && w_valid[r][h]) ? __ldg(w_row[r][h] + piece) : zero;
+    }
+    if (!waited) {
+      pdl_wait();                                             // x comes from the kernel before this one
+      waited = true;
+    }
+#pragma unroll
+    for (int i = 0; i < SKINNY_BATCH; ++i) {
+      const int piece = (first + i * WARPS) * 4 + t;
+      const bool in_range = first + i * WARPS < k_blocks && piece * 8 < K;
+#pragma unroll
+      for (int n = 0; n < TOKENS8; ++n) xv[i][n] = (in_range && x_valid[n]) ? __ldg(x_row[n] + piece) : zero;
+    }
+#pragma unroll
+    for (int i = 0; i < SKINNY_BATCH; ++i)
+#pragma unroll
+      for (int r = 0; r < GROUPS; ++r)
+#pragma unroll
+        for (int n = 0; n < TOKENS8; ++n) {
+          // the lane's 8 k values: (x, y) feed one MMA, (z, w) the next, same order in A and B
+          mma_16x8x16(acc[r][n], wv[i][r][0].x, wv[i][r][1].x, wv[i][r][0].y, wv[i][r][1].y, xv[i][n].x, xv[i][n].y);
+          mma_16x8x16(acc[r][n], wv[i][r][0].z, wv[i][r][1].z, wv[i][r][0].w, wv[i][r][1].w, xv[i][n].z, xv[i][n].w);
+        }
+  }
+  if (!waited) pdl_wait();
+
+  // ---- add the warps' partial tiles in warp order
+#pragma unroll
+  for (int r = 0; r < GROUPS; ++r)
+#pragma unroll
+    for (int n = 0; n < TOKENS8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) partial[warp][(r * TOKENS8 + n) * 4 + e][lane] = acc[r][n][e];
+  __syncthreads();
+  if (warp != 0) return;
+#pragma unroll
+  for (int r = 0; r < GROUPS; ++r)
+#pragma unroll
+    for (int n = 0; n < TOKENS8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float sum = 0.f;
+#pragma unroll
+        for (int v = 0; v < WARPS; ++v) sum += partial[v][(r * TOKENS8 + n) * 4 + e][lane];
+        acc[r][n][e] = sum;
+      }
+
+  // ---- epilogue: element e of a tile is (row g + 8*(e/2), token n*8 + 2t + e%2)
+  bf16* out_bf16 = (bf16*)out;
+  float* out_f32p = (float*)out;
+#pragma unroll
+  for (int n = 0; n < TOKENS8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int token = n * 8 + 2 * t + (e & 1);
+      if (token >= M) continue;
+      if (SWIGLU) {
+        const int column = blockIdx.x * 16 + g + 8 * (e >> 1);
+        const int half = N >> 1;
+        if (column < half) {
+          const float gate = acc[0][n][e], up = acc[GROUPS - 1][n][e];
+          out_bf16[(size_t)token * half + column] = __float2bfloat16_rn(gate / (1.f + __expf(-gate)) * up);
+        }
+      } else {
+        const int row = row0[0] + g + 8 * (e >> 1);
+        if (row < N) {
+          const float value = acc[0][n][e] + (bias != nullptr ? to_float(bias[row]) : 0.f);
+          if (out_f32) out_f32p[(size_t)token * N + row] = value;
+          else out_bf16[(size_t)token * N + row] = __float2bfloat16_rn(value);
+        }
+      }
+    }
+}
+
+template <int WARPS, int TOKENS8>
+static int skinny_launch(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                         int out_f32, int swiglu, cudaStream_t stream) {
+  if (swiglu) {
+    dim3 grid((N / 2 + 15) / 16);
+    launch_kernel(skinny_gemm_kernel<WARPS, 2, TOKENS8, true>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x,
+                  (const bf16*)w, (const bf16*)bias, out, M, N, K, out_f32);
+  } else {
+    dim3 grid((N + 15) / 16);
+    launch_kernel(skinny_gemm_kernel<WARPS, 1, TOKENS8, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x,
+                  (const bf16*)w, (const bf16*)bias, out, M, N, K, out_f32);
+  }
+  return launch_status();
+}
+
+}  // namespace mlr
+
+using namespace mlr;
+
+MLR_DEFINE_PDL_SWITCH
+
+// x [M,K], w [N,K], bias [N] or null (bfloat16); out [M,N] bfloat16 or float32 (out_f32).
+// swiglu != 0: w interleaves blocks of 64 gate rows with the 64 up rows of the same outputs
+// (N % 128 == 0, no bias); out is silu(gate) * up, [M, N/2] bfloat16.  M <= 16, K % 8 == 0.
+MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                               int out_f32, int swiglu, cudaStream_t stream) {
+  if (M == 0) return MLR_OK;
+  if (M < 0 || N <= 0 || K <= 0) return MLR_BAD_SIZE;
+  if (M > 16) return MLR_TOO_LARGE;
+  if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MLR_BAD_ALIGNMENT;
+  if (swiglu && (N % 128 != 0 || bias != nullptr || out_f32)) return MLR_BAD_SIZE;
+  // Short rows: 4 warps share K; long rows (the down projection): 16 warps, so that a warp's
+  // share is again one or two batches of loads.
+  const bool many_warps = K > 2048;
+  if (M <= 8) {
+    if (many_warps) return skinny_launch<16, 1>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+    return skinny_launch<4, 1>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+  }
+  if (many_warps) return skinny_launch<16, 2>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+  return skinny_launch<4, 2>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+}

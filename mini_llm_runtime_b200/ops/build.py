@@ -40,6 +40,7 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "gemm_tcgen05": (),
     "attention_decode": (),
     "attention_mma": (),
+    "gemm_skinny": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -119,6 +119,7 @@ class CudaOps:
         self.use_decode_kernel = True
         self.use_mma_attention = True
         self.use_fused_swiglu = True
+        self.use_skinny = True
         self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
         self.decode_max_splits: int | None = None  # None: just enough for the longest context
 
@@ -216,6 +217,8 @@ class CudaOps:
         if (self.use_tensor_cores and self.use_fused_swiglu and block == self.SWIGLU_BLOCK
                 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[0] > 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+            if self._skinny_fits(x, weight, swiglu=True):
+                return self._linear_skinny(x, weight, None, torch.bfloat16, swiglu=True)
             out = self._linear_tcgen05(x, weight, None, torch.bfloat16, swiglu=True)
             if out is not None:
                 return out
@@ -267,10 +270,29 @@ class CudaOps:
         out_dtype = out_dtype or x.dtype
         if (self.use_tensor_cores and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.shape[0] > 0):
+            if self._skinny_fits(x, weight):
+                return self._linear_skinny(x, weight, bias, out_dtype, swiglu=False)
             out = self._linear_tcgen05(x, weight, bias, out_dtype)
             if out is not None:
                 return out
         return self._linear_simt(x, weight, bias, out_dtype)
+
+    SKINNY_ROWS = 16            # most rows the few-rows kernel takes
+    SKINNY_WEIGHT_ROWS = 148 * 128   # beyond this the 128-row tensor-memory tiles fill every SM
+
+    def _skinny_fits(self, x, weight, swiglu=False) -> bool:
+        """Few rows and a weight too small for one 128-row tile per SM: the latency-lean kernel."""
+        return (self.use_skinny and x.shape[0] <= self.SKINNY_ROWS and weight.shape[0] < self.SKINNY_WEIGHT_ROWS
+                and (not swiglu or x.shape[1] <= 2048))
+
+    def _linear_skinny(self, x, weight, bias, out_dtype, swiglu):
+        M, K = x.shape
+        N = weight.shape[0]
+        out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+        lib = build.load_library("gemm_skinny")
+        _check(lib.mlr_gemm_skinny(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
+                                   int(out_dtype == torch.float32), int(swiglu), _stream()), "linear (few rows)")
+        return out
 
     def _linear_tcgen05(self, x, weight, bias, out_dtype, swiglu=False):
         M, K = x.shape

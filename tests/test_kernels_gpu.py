@@ -28,6 +28,14 @@ def cuda():
     return ops.current()
 
 
+@pytest.fixture
+def tcgen05_only():
+    """Route few-row products to the tcgen05 kernel too (they default to the few-rows kernel)."""
+    ops.current().use_skinny = False
+    yield
+    ops.current().use_skinny = True
+
+
 def rnd(shape, dtype, seed, scale=1.0):
     generator = torch.Generator().manual_seed(seed)
     return (torch.randn(shape, generator=generator) * scale).to(dtype)
@@ -78,7 +86,7 @@ def test_swiglu(dtype):
 
 @pytest.mark.parametrize("m", [1, 8, 20, 40, 100, 128, 200, 700])
 @pytest.mark.parametrize("inner,k", [(4864, 896), (128, 64), (320, 200), (1216, 4864)])
-def test_fused_linear_swiglu(m, inner, k):
+def test_fused_linear_swiglu(m, inner, k, tcgen05_only):
     """The gate/up product with the activation in the tensor-core kernel's epilogue, in both
     orientations and with split-K, against the unfused float32 computation."""
     x = rnd((m, k), torch.bfloat16, 60 + m)
@@ -115,7 +123,7 @@ def test_linear(dtype, m, n, k):
 
 @pytest.mark.parametrize("m", [1, 8, 16, 17, 33, 64, 100, 128, 129, 300])
 @pytest.mark.parametrize("n,k", [(896, 896), (1152, 896), (200, 72), (896, 4864), (130, 64), (4000, 136)])
-def test_tensor_core_linear(m, n, k):
+def test_tensor_core_linear(m, n, k, tcgen05_only):
     """The tcgen05 product in both orientations, with and without split-K, K tails and N tails."""
     x = rnd((m, k), torch.bfloat16, 40 + m)
     w = rnd((n, k), torch.bfloat16, 41, 0.1)
@@ -146,6 +154,44 @@ def test_tensor_core_linear_many_rows(m, n, k):
     cuda().raise_if_device_error()
     want = (x.to(DEVICE).double() @ w.to(DEVICE).double().T + b.to(DEVICE).double()).cpu()
     assert_close(got, want, torch.bfloat16, f"tcgen05 linear {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(896, 896), (1152, 896), (896, 4864), (200, 72), (130, 64), (4000, 136), (5120, 5120)])
+def test_few_rows_linear(m, n, k):
+    """The few-rows kernel (mma.sync on 16-row weight groups, K shared by the CTA's warps) against
+    float64, and against the tcgen05 kernel on the same inputs."""
+    x = rnd((m, k), torch.bfloat16, 90 + m)
+    w = rnd((n, k), torch.bfloat16, 91, 0.1)
+    b = rnd((n,), torch.bfloat16, 92)
+    want = x.double() @ w.double().T + b.double()
+    assert cuda()._skinny_fits(x, w)
+    got = cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE))
+    assert_close(got, want, torch.bfloat16, f"few-rows linear {m}x{n}x{k}")
+    got32 = cuda().linear(x.to(DEVICE), w.to(DEVICE), None, out_dtype=torch.float32)
+    want32 = x.double() @ w.double().T
+    assert float((got32.double().cpu() - want32).abs().max()) <= 1e-4 * float(want32.abs().max()) + 1e-5
+    assert torch.equal(got32, cuda().linear(x.to(DEVICE), w.to(DEVICE), None, out_dtype=torch.float32))
+    cuda().use_skinny = False
+    try:
+        other = cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE))
+    finally:
+        cuda().use_skinny = True
+    assert_close(got, other, torch.bfloat16, "few-rows kernel against the tcgen05 kernel")
+
+
+@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("inner,k", [(4864, 896), (128, 64), (320, 200)])
+def test_few_rows_linear_swiglu(m, inner, k):
+    x = rnd((m, k), torch.bfloat16, 95 + m)
+    gate = rnd((inner, k), torch.bfloat16, 96, 0.1)
+    up = rnd((inner, k), torch.bfloat16, 97, 0.1)
+    weight = torch.cat([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k)
+    want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
+    assert cuda()._skinny_fits(x, weight, swiglu=True)
+    got = cuda().linear_swiglu(x.to(DEVICE), weight.to(DEVICE), 64)
+    assert got.shape == (m, inner)
+    assert_close(got, want, torch.bfloat16, f"few-rows fused gate/up {m}x{inner}x{k}")
 
 
 def test_tensor_core_linear_large_vocabulary():
