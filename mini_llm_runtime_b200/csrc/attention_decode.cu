@@ -34,8 +34,8 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
 
 template <int D>
 __global__ void __launch_bounds__(DECODE_WARPS * 32)
-decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool,
-                        const bf16* __restrict__ v_pool, bf16* __restrict__ out,
+decode_attention_kernel(const bf16* q, const bf16* k_pool,
+                        const bf16* v_pool, bf16* __restrict__ out,
                         const int* __restrict__ decode_seg, const int* __restrict__ seg_q_start,
                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
                         int table_width, int heads, int kv_heads, int page_size, int window, float scale,
@@ -96,7 +96,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
       for (int c = 0; c < D / 8; ++c) {
         float kf[8];
-        unpack8(__ldg(k_row + c), kf);
+        unpack8(__ldcg(k_row + c), kf);
 #pragma unroll
         for (int g = 0; g < GROUP_MAX; ++g) {
           if (g < group) {

@@ -26,8 +26,8 @@ constexpr int MAX_HEAD_DIM = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool,
-                         const T* __restrict__ v_pool, T* __restrict__ out,
+attention_generic_kernel(const T* q, const T* k_pool,
+                         const T* v_pool, T* __restrict__ out,
                          const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                          const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
                          const int* __restrict__ seg_pos0, const int* __restrict__ block_table,

@@ -71,7 +71,7 @@ __device__ __forceinline__ bf16* tile_at(bf16* tile, int row, int chunk) {
 // `page_shift` is log2(page_size) when the page size is a power of two (the usual case: address
 // arithmetic by shifts), else -1 (division).
 template <int D>
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ pool, const int* __restrict__ table,
+__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* pool, const int* __restrict__ table,
                                              int key0, int rows, int key_lo, int key_hi, int kv_heads, int kv_head,
                                              int page_size, int page_shift) {
   constexpr int CHUNKS = D / 8;
@@ -189,7 +189,7 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
 // ------------------------------------------------------------------------------------------ prefill
 template <int D>
 __global__ void __launch_bounds__(ATTN_THREADS)
-prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+prefill_attention_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
                          bf16* __restrict__ out, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                          const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
                          const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int table_width,
@@ -288,7 +288,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 // ------------------------------------------------------------------------------------------ decode
 template <int D>
 __global__ void __launch_bounds__(ATTN_THREADS)
-decode_attention_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
                             bf16* __restrict__ out, const int* __restrict__ decode_seg,
                             const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
                             const int* __restrict__ block_table, int table_width, int heads, int kv_heads,

@@ -80,6 +80,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // since every kernel waits before it finishes, completion is transitive along the stream.
 // pdl_trigger() tells the scheduler that the next kernel may be brought in.  Launched without the
 // attribute both are no-ops.
+// Because a kernel may begin before its input exists, inputs written by earlier kernels are never
+// read through the read-only (non-coherent) path: their pointers carry no __restrict__, and
+// explicit loads use __ldcg, not __ldg.  Weights and the step's metadata may.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -26,7 +26,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 
 // ---------------------------------------------------------------- gather rows
 template <typename T>
-__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows,
+__global__ void gather_rows_kernel(const T* x, const int* __restrict__ rows,
                                    T* __restrict__ out, int width) {
   pdl_trigger();
   pdl_wait();
@@ -41,7 +41,7 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restric
 // so the fused kernel equals "add, then norm" exactly.  The row is staged in shared memory as
 // float32 so that global memory is read once.
 template <typename T, typename W>
-__global__ void rms_norm_kernel(T* __restrict__ residual, const T* __restrict__ delta,
+__global__ void rms_norm_kernel(T* residual, const T* delta,
                                 const W* __restrict__ weight, T* __restrict__ out, int width,
                                 float eps) {
   pdl_trigger();
@@ -70,7 +70,7 @@ __global__ void rms_norm_kernel(T* __restrict__ residual, const T* __restrict__ 
 // in: [rows, 2*inner].  Each row holds blocks of `block` gate values followed by the `block` up
 // values of the same outputs; block == inner is the plain "all gates, then all ups" layout.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner, int block,
+__global__ void swiglu_kernel(const T* gate_up, T* __restrict__ out, int inner, int block,
                               size_t total) {
   pdl_trigger();
   pdl_wait();
@@ -92,7 +92,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // token is padding, nothing is stored).  angle = position * inv_freq[i] in float32; element i
 // pairs with element i + head_dim/2.
 template <typename T>
-__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_kv_write_kernel(const T* qkv, const int* __restrict__ positions,
                                      const float* __restrict__ inv_freq,
                                      const long long* __restrict__ slots, T* __restrict__ q_out,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, int heads,

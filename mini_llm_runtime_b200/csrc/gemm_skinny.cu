@@ -33,7 +33,7 @@ __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, 
 // TOKENS8: token blocks of 8 (1 for M <= 8, 2 for M <= 16).
 template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU>
 __global__ void __launch_bounds__(WARPS * 32)
-skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ bias,
+skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __restrict__ bias,
                    void* __restrict__ out, int M, int N, int K, int out_f32) {
   __shared__ float partial[WARPS][GROUPS * TOKENS8 * 4][32];
   pdl_trigger();
@@ -97,7 +97,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       const int piece = (first + i * WARPS) * 4 + t;
       const bool in_range = first + i * WARPS < k_blocks && piece * 8 < K;
 #pragma unroll
-      for (int n = 0; n < TOKENS8; ++n) xv[i][n] = (in_range && x_valid[n]) ? __ldg(x_row[n] + piece) : zero;
+      for (int n = 0; n < TOKENS8; ++n) xv[i][n] = (in_range && x_valid[n]) ? __ldcg(x_row[n] + piece) : zero;
     }
 #pragma unroll
     for (int i = 0; i < SKINNY_BATCH; ++i)

@@ -16,7 +16,7 @@ constexpr int BK = 16;
 
 template <typename TIn, typename TOut, int BM>
 __global__ void __launch_bounds__(256)
-linear_simt_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w, const TIn* __restrict__ bias,
+linear_simt_kernel(const TIn* x, const TIn* __restrict__ w, const TIn* __restrict__ bias,
                    TOut* __restrict__ y, int M, int N, int K) {
   pdl_trigger();
   pdl_wait();

@@ -24,7 +24,7 @@ __device__ __forceinline__ float uniform_from_seed(unsigned long long seed, long
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperatures,
+sample_kernel(const float* logits, const float* __restrict__ temperatures,
               const long long* __restrict__ seeds, const long long* __restrict__ counters,
               int* __restrict__ tokens, int vocab) {
   pdl_trigger();
