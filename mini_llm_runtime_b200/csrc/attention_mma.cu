@@ -29,7 +29,6 @@ constexpr int ATTN_WARPS = 4;
 constexpr int ATTN_THREADS = ATTN_WARPS * 32;
 constexpr int TILE_Q = 64;
 constexpr int TILE_KV = 64;
-constexpr int DECODE_STAGES = 4;
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -286,7 +285,10 @@ prefill_attention_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
 }
 
 // ------------------------------------------------------------------------------------------ decode
-template <int D>
+// STAGES: 64-key tiles in flight per CTA.  Four when a chunk is short and CTAs are few (every load
+// of the chunk is requested at once); two when chunks are long and CTAs many (four CTAs then
+// fit on an SM and hide one another's waits).
+template <int D, int DECODE_STAGES>
 __global__ void __launch_bounds__(ATTN_THREADS)
 decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
                             bf16* __restrict__ out, const int* __restrict__ decode_seg,
@@ -549,23 +551,27 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
   if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
   // the final merge keeps 2 * 16 * max_splits + 16 floats in the warps' merge area
   if ((size_t)(2 * 16 * max_splits + 16) > (size_t)ATTN_WARPS * 16 * (head_dim + 2)) return MLR_TOO_LARGE;
-  const size_t shared = (size_t)(16 + 2 * DECODE_STAGES * TILE_KV) * head_dim * 2 +
+  // long chunks on a grid of several waves: fewer stages, more CTAs per SM
+  const bool deep = chunk <= 4 * TILE_KV || (long long)max_splits * kv_heads * rows <= 2 * 148;
+  const int stages = deep ? 4 : 2;
+  const size_t shared = (size_t)(16 + 2 * stages * TILE_KV) * head_dim * 2 +
                         (size_t)ATTN_WARPS * 16 * (head_dim + 2) * sizeof(float);
   dim3 grid(max_splits, kv_heads, rows);
   const int page_shift = shift_of(page_size);
   int status;
+#define MLR_LAUNCH_DECODE(D_, S_)                                                                          \
+  do {                                                                                                     \
+    if ((status = set_shared(decode_attention_mma_kernel<D_, S_>, shared)) != MLR_OK) return status;       \
+    launch_kernel(decode_attention_mma_kernel<D_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream,     \
+                  (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg,        \
+                  seg_q_start, seg_pos0, block_table, table_width, heads, kv_heads, page_size, page_shift, \
+                  window, scale * LOG2_E, chunk, (float*)scratch, counters, max_splits);                   \
+  } while (0)
   if (head_dim == 64) {
-    if ((status = set_shared(decode_attention_mma_kernel<64>, shared)) != MLR_OK) return status;
-    launch_kernel(decode_attention_mma_kernel<64>, dim3(grid), dim3(ATTN_THREADS), shared, stream, 
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
-        block_table, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk, (float*)scratch,
-        counters, max_splits);
+    if (deep) MLR_LAUNCH_DECODE(64, 4); else MLR_LAUNCH_DECODE(64, 2);
   } else {
-    if ((status = set_shared(decode_attention_mma_kernel<128>, shared)) != MLR_OK) return status;
-    launch_kernel(decode_attention_mma_kernel<128>, dim3(grid), dim3(ATTN_THREADS), shared, stream, 
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
-        block_table, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk, (float*)scratch,
-        counters, max_splits);
+    if (deep) MLR_LAUNCH_DECODE(128, 4); else MLR_LAUNCH_DECODE(128, 2);
   }
+#undef MLR_LAUNCH_DECODE
   return launch_status();
 }

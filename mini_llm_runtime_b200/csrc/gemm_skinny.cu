@@ -1,4 +1,4 @@
-// y[M,N] = x[M,K] * W[N,K]^T (+ bias) for very few rows (M <= 16, a decode step of a small batch),
+// y[M,N] = x[M,K] * W[N,K]^T (+ bias) for few rows (M <= 64, a decode step of a small batch),
 // bfloat16 in, float32 accumulate, for the layer products whose weight matrix is too small to
 // give every SM a 128-row tcgen05 tile: there the cost is a chain of latencies, not bandwidth, and
 // this kernel keeps the chain short.
@@ -19,7 +19,8 @@
 
 namespace mlr {
 
-constexpr int SKINNY_BATCH = 8;       // k blocks (of 32) whose loads are in flight together
+// k blocks (of 32) whose loads are in flight together: fewer when more tokens need registers
+__host__ __device__ constexpr int skinny_batch(int tokens8) { return tokens8 <= 2 ? 8 : (tokens8 == 4 ? 4 : 2); }
 
 __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                             uint32_t b0, uint32_t b1) {
@@ -30,12 +31,14 @@ __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, 
 }
 
 // GROUPS: 16-row groups per CTA (2 for the fused gate/up product: the gate rows and their up rows).
-// TOKENS8: token blocks of 8 (1 for M <= 8, 2 for M <= 16).
+// TOKENS8: token blocks of 8 (1 for M <= 8, 2 for M <= 16, 4 for M <= 32, 8 for M <= 64).
 template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __restrict__ bias,
                    void* __restrict__ out, int M, int N, int K, int out_f32) {
-  __shared__ float partial[WARPS][GROUPS * TOKENS8 * 4][32];
+  constexpr int SKINNY_BATCH = skinny_batch(TOKENS8);
+  extern __shared__ float partial_raw[];
+  float (*partial)[GROUPS * TOKENS8 * 4][32] = reinterpret_cast<float (*)[GROUPS * TOKENS8 * 4][32]>(partial_raw);
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -160,19 +163,30 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
     }
 }
 
+template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU>
+static int skinny_launch_one(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                             int out_f32, int groups_of_rows, cudaStream_t stream) {
+  const size_t shared = (size_t)WARPS * GROUPS * TOKENS8 * 4 * 32 * sizeof(float);
+  if (shared > 48 * 1024) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t err = cudaFuncSetAttribute(skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+      if (err != cudaSuccess) return (int)err;
+      configured = true;
+    }
+  }
+  launch_kernel(skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU>, dim3(groups_of_rows), dim3(WARPS * 32), shared,
+                stream, (const bf16*)x, (const bf16*)w, (const bf16*)bias, out, M, N, K, out_f32);
+  return launch_status();
+}
+
 template <int WARPS, int TOKENS8>
 static int skinny_launch(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
                          int out_f32, int swiglu, cudaStream_t stream) {
-  if (swiglu) {
-    dim3 grid((N / 2 + 15) / 16);
-    launch_kernel(skinny_gemm_kernel<WARPS, 2, TOKENS8, true>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x,
-                  (const bf16*)w, (const bf16*)bias, out, M, N, K, out_f32);
-  } else {
-    dim3 grid((N + 15) / 16);
-    launch_kernel(skinny_gemm_kernel<WARPS, 1, TOKENS8, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x,
-                  (const bf16*)w, (const bf16*)bias, out, M, N, K, out_f32);
-  }
-  return launch_status();
+  if (swiglu)
+    return skinny_launch_one<WARPS, 2, TOKENS8, true>(x, w, bias, out, M, N, K, out_f32, (N / 2 + 15) / 16, stream);
+  return skinny_launch_one<WARPS, 1, TOKENS8, false>(x, w, bias, out, M, N, K, out_f32, (N + 15) / 16, stream);
 }
 
 }  // namespace mlr
@@ -183,21 +197,25 @@ MLR_DEFINE_PDL_SWITCH
 
 // x [M,K], w [N,K], bias [N] or null (bfloat16); out [M,N] bfloat16 or float32 (out_f32).
 // swiglu != 0: w interleaves blocks of 64 gate rows with the 64 up rows of the same outputs
-// (N % 128 == 0, no bias); out is silu(gate) * up, [M, N/2] bfloat16.  M <= 16, K % 8 == 0.
+// (N % 128 == 0, no bias); out is silu(gate) * up, [M, N/2] bfloat16.  M <= 64, K % 8 == 0.
 MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
                                int out_f32, int swiglu, cudaStream_t stream) {
   if (M == 0) return MLR_OK;
   if (M < 0 || N <= 0 || K <= 0) return MLR_BAD_SIZE;
-  if (M > 16) return MLR_TOO_LARGE;
+  if (M > 64) return MLR_TOO_LARGE;
   if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MLR_BAD_ALIGNMENT;
   if (swiglu && (N % 128 != 0 || bias != nullptr || out_f32)) return MLR_BAD_SIZE;
-  // Short rows: 4 warps share K; long rows (the down projection): 16 warps, so that a warp's
-  // share is again one or two batches of loads.
-  const bool many_warps = K > 2048;
+  // The CTA's warps share K.  Short rows: 4 warps (8 once many tokens shrink the load batches);
+  // long rows (the down projection): 16 warps, or 8 where 16 would run out of registers.
+  const bool long_rows = K > 2048;
   if (M <= 8) {
-    if (many_warps) return skinny_launch<16, 1>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+    if (long_rows) return skinny_launch<16, 1>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
     return skinny_launch<4, 1>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
   }
-  if (many_warps) return skinny_launch<16, 2>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
-  return skinny_launch<4, 2>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+  if (M <= 16) {
+    if (long_rows) return skinny_launch<16, 2>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+    return skinny_launch<4, 2>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+  }
+  if (M <= 32) return skinny_launch<8, 4>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+  return skinny_launch<8, 8>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
 }

@@ -156,7 +156,7 @@ def test_tensor_core_linear_many_rows(m, n, k):
     assert_close(got, want, torch.bfloat16, f"tcgen05 linear {m}x{n}x{k}")
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32, 33, 64])
 @pytest.mark.parametrize("n,k", [(896, 896), (1152, 896), (896, 4864), (200, 72), (130, 64), (4000, 136), (5120, 5120)])
 def test_few_rows_linear(m, n, k):
     """The few-rows kernel (mma.sync on 16-row weight groups, K shared by the CTA's warps) against
@@ -165,6 +165,14 @@ def test_few_rows_linear(m, n, k):
     w = rnd((n, k), torch.bfloat16, 91, 0.1)
     b = rnd((n,), torch.bfloat16, 92)
     want = x.double() @ w.double().T + b.double()
+    cuda().SKINNY_ROWS = 64          # the kernel takes up to 64 rows; the dispatcher stops at 16
+    try:
+        _check_few_rows(m, n, k, x, w, b, want)
+    finally:
+        del cuda().SKINNY_ROWS
+
+
+def _check_few_rows(m, n, k, x, w, b, want):
     assert cuda()._skinny_fits(x, w)
     got = cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE))
     assert_close(got, want, torch.bfloat16, f"few-rows linear {m}x{n}x{k}")
@@ -180,7 +188,7 @@ def test_few_rows_linear(m, n, k):
     assert_close(got, other, torch.bfloat16, "few-rows kernel against the tcgen05 kernel")
 
 
-@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("m", [1, 8, 13, 30, 64])
 @pytest.mark.parametrize("inner,k", [(4864, 896), (128, 64), (320, 200)])
 def test_few_rows_linear_swiglu(m, inner, k):
     x = rnd((m, k), torch.bfloat16, 95 + m)
@@ -188,8 +196,12 @@ def test_few_rows_linear_swiglu(m, inner, k):
     up = rnd((inner, k), torch.bfloat16, 97, 0.1)
     weight = torch.cat([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k)
     want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
-    assert cuda()._skinny_fits(x, weight, swiglu=True)
-    got = cuda().linear_swiglu(x.to(DEVICE), weight.to(DEVICE), 64)
+    cuda().SKINNY_ROWS = 64
+    try:
+        assert cuda()._skinny_fits(x, weight, swiglu=True)
+        got = cuda().linear_swiglu(x.to(DEVICE), weight.to(DEVICE), 64)
+    finally:
+        del cuda().SKINNY_ROWS
     assert got.shape == (m, inner)
     assert_close(got, want, torch.bfloat16, f"few-rows fused gate/up {m}x{inner}x{k}")
 
