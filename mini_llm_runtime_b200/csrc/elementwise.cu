@@ -62,8 +62,20 @@ __global__ void rms_norm_kernel(T* residual, const T* delta,
   }
   const float total = block_sum(partial, scratch);
   const float scale = rsqrtf(total / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += blockDim.x)
-    out[base + i] = from_float<T>(to_float(weight[i]) * (row_cache[i] * scale));
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float w = weight != nullptr ? to_float(weight[i]) : 1.f;   // no weight: normalise only
+    out[base + i] = from_float<T>(w * (row_cache[i] * scale));
+  }
+}
+
+// ---------------------------------------------------------------- in-place add
+template <typename T>
+__global__ void add_inplace_kernel(T* target, const T* delta, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x)
+    target[idx] = from_float<T>(to_float(target[idx]) + to_float(delta[idx]));
 }
 
 // ---------------------------------------------------------------- SwiGLU
@@ -221,6 +233,20 @@ MLR_EXPORT int mlr_rms_norm(void* residual, const void* delta, const void* weigh
   if (dtype == MLR_BF16 && weight_dtype == MLR_F32)
     return rms_norm_launch<bf16, float>(residual, delta, weight, out, rows, width, eps, stream);
   return MLR_BAD_DTYPE;
+}
+
+MLR_EXPORT int mlr_add_inplace(void* target, const void* delta, long long total, int dtype, cudaStream_t stream) {
+  if (total == 0) return MLR_OK;
+  if (total < 0) return MLR_BAD_SIZE;
+  size_t blocks = ((size_t)total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == MLR_F32)
+    launch_kernel(add_inplace_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)target, (const float*)delta, (size_t)total);
+  else if (dtype == MLR_BF16)
+    launch_kernel(add_inplace_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, (bf16*)target, (const bf16*)delta, (size_t)total);
+  else
+    return MLR_BAD_DTYPE;
+  return launch_status();
 }
 
 MLR_EXPORT int mlr_swiglu(const void* gate_up, void* out, long long rows, int inner, int block, int dtype,

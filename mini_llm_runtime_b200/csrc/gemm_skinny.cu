@@ -13,6 +13,12 @@
 // gate/up product (weight rows in blocks of 64 gate rows followed by the 64 up rows of the same
 // outputs, as the tensor-core kernel takes them) silu(gate) * up is applied before the store.
 //
+// Two fusions ride along for free.  (1) RMS norm: with rms_eps >= 0 the product is taken of the
+// normalised rows x * rsqrt(mean(x^2) + eps); the sums of squares come from the x pieces the lanes
+// hold anyway, and the row scale is applied to the finished tile (the norm's weight is expected
+// folded into w).  (2) Residual: with a residual pointer the result is added to it (it may be the
+// output itself: every element is read and written by the same thread).
+//
 // Weight loads of the first batch are issued before the programmatic dependency wait: they do
 // not depend on the previous kernel.  Requires K % 8 == 0 and 16-byte aligned rows.
 #include "common.cuh"
@@ -34,11 +40,13 @@ __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, 
 // TOKENS8: token blocks of 8 (1 for M <= 8, 2 for M <= 16, 4 for M <= 32, 8 for M <= 64).
 template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU>
 __global__ void __launch_bounds__(WARPS * 32)
-skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __restrict__ bias,
-                   void* __restrict__ out, int M, int N, int K, int out_f32) {
+skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __restrict__ bias, void* out,
+                   const bf16* residual, int M, int N, int K, int out_f32, float rms_eps) {
   constexpr int SKINNY_BATCH = skinny_batch(TOKENS8);
   extern __shared__ float partial_raw[];
   float (*partial)[GROUPS * TOKENS8 * 4][32] = reinterpret_cast<float (*)[GROUPS * TOKENS8 * 4][32]>(partial_raw);
+  __shared__ float squares[WARPS][TOKENS8 * 8];     // per warp: sum of x^2 over its share of K, per token
+  __shared__ float row_scale[TOKENS8 * 8];
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -78,6 +86,9 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
 #pragma unroll
     for (int n = 0; n < TOKENS8; ++n) acc[r][n][0] = acc[r][n][1] = acc[r][n][2] = acc[r][n][3] = 0.f;
 
+  float square_sum[TOKENS8];
+#pragma unroll
+  for (int n = 0; n < TOKENS8; ++n) square_sum[n] = 0.f;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   bool waited = false;
   for (int first = warp; first < k_blocks; first += WARPS * SKINNY_BATCH) {
@@ -102,6 +113,19 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
 #pragma unroll
       for (int n = 0; n < TOKENS8; ++n) xv[i][n] = (in_range && x_valid[n]) ? __ldcg(x_row[n] + piece) : zero;
     }
+    if (rms_eps >= 0.f) {
+#pragma unroll
+      for (int i = 0; i < SKINNY_BATCH; ++i)
+#pragma unroll
+        for (int n = 0; n < TOKENS8; ++n) {
+          const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&xv[i][n]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 two = __bfloat1622float2(pairs[j]);
+            square_sum[n] += two.x * two.x + two.y * two.y;
+          }
+        }
+    }
 #pragma unroll
     for (int i = 0; i < SKINNY_BATCH; ++i)
 #pragma unroll
@@ -122,8 +146,29 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
     for (int n = 0; n < TOKENS8; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) partial[warp][(r * TOKENS8 + n) * 4 + e][lane] = acc[r][n][e];
+  // the four lanes of a token (t = 0..3) hold disjoint pieces of its row
+#pragma unroll
+  for (int n = 0; n < TOKENS8; ++n) {
+    float sum = square_sum[n];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (t == 0) squares[warp][n * 8 + g] = sum;
+  }
   __syncthreads();
   if (warp != 0) return;
+  if (lane < TOKENS8 * 8) {
+    float sum = 0.f;
+#pragma unroll
+    for (int v = 0; v < WARPS; ++v) sum += squares[v][lane];
+    row_scale[lane] = rms_eps >= 0.f ? rsqrtf(sum / (float)K + rms_eps) : 1.f;
+  }
+  if (TOKENS8 * 8 > 32 && lane + 32 < TOKENS8 * 8) {
+    float sum = 0.f;
+#pragma unroll
+    for (int v = 0; v < WARPS; ++v) sum += squares[v][lane + 32];
+    row_scale[lane + 32] = rms_eps >= 0.f ? rsqrtf(sum / (float)K + rms_eps) : 1.f;
+  }
+  __syncwarp();
 #pragma unroll
   for (int r = 0; r < GROUPS; ++r)
 #pragma unroll
@@ -145,17 +190,19 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
     for (int e = 0; e < 4; ++e) {
       const int token = n * 8 + 2 * t + (e & 1);
       if (token >= M) continue;
+      const float scale = row_scale[token];
       if (SWIGLU) {
         const int column = blockIdx.x * 16 + g + 8 * (e >> 1);
         const int half = N >> 1;
         if (column < half) {
-          const float gate = acc[0][n][e], up = acc[GROUPS - 1][n][e];
+          const float gate = acc[0][n][e] * scale, up = acc[GROUPS - 1][n][e] * scale;
           out_bf16[(size_t)token * half + column] = __float2bfloat16_rn(gate / (1.f + __expf(-gate)) * up);
         }
       } else {
         const int row = row0[0] + g + 8 * (e >> 1);
         if (row < N) {
-          const float value = acc[0][n][e] + (bias != nullptr ? to_float(bias[row]) : 0.f);
+          float value = acc[0][n][e] * scale + (bias != nullptr ? to_float(bias[row]) : 0.f);
+          if (residual != nullptr) value += to_float(residual[(size_t)token * N + row]);
           if (out_f32) out_f32p[(size_t)token * N + row] = value;
           else out_bf16[(size_t)token * N + row] = __float2bfloat16_rn(value);
         }
@@ -164,8 +211,8 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
 }
 
 template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU>
-static int skinny_launch_one(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                             int out_f32, int groups_of_rows, cudaStream_t stream) {
+static int skinny_launch_one(const void* x, const void* w, const void* bias, void* out, const void* residual, int M,
+                             int N, int K, int out_f32, float rms_eps, int groups_of_rows, cudaStream_t stream) {
   const size_t shared = (size_t)WARPS * GROUPS * TOKENS8 * 4 * 32 * sizeof(float);
   if (shared > 48 * 1024) {
     static bool configured = false;
@@ -177,16 +224,21 @@ static int skinny_launch_one(const void* x, const void* w, const void* bias, voi
     }
   }
   launch_kernel(skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU>, dim3(groups_of_rows), dim3(WARPS * 32), shared,
-                stream, (const bf16*)x, (const bf16*)w, (const bf16*)bias, out, M, N, K, out_f32);
+                stream, (const bf16*)x, (const bf16*)w, (const bf16*)bias, out, (const bf16*)residual, M, N, K, out_f32,
+                rms_eps);
   return launch_status();
 }
 
 template <int WARPS, int TOKENS8>
-static int skinny_launch(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                         int out_f32, int swiglu, cudaStream_t stream) {
-  if (swiglu)
-    return skinny_launch_one<WARPS, 2, TOKENS8, true>(x, w, bias, out, M, N, K, out_f32, (N / 2 + 15) / 16, stream);
-  return skinny_launch_one<WARPS, 1, TOKENS8, false>(x, w, bias, out, M, N, K, out_f32, (N + 15) / 16, stream);
+static int skinny_launch(const void* x, const void* w, const void* bias, void* out, const void* residual, int M, int N,
+                         int K, int out_f32, int swiglu, float rms_eps, cudaStream_t stream) {
+  if constexpr (WARPS <= 8) {
+    if (swiglu)
+      return skinny_launch_one<WARPS, 2, TOKENS8, true>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
+                                                        (N / 2 + 15) / 16, stream);
+  }
+  return skinny_launch_one<WARPS, 1, TOKENS8, false>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
+                                                     (N + 15) / 16, stream);
 }
 
 }  // namespace mlr
@@ -198,24 +250,27 @@ MLR_DEFINE_PDL_SWITCH
 // x [M,K], w [N,K], bias [N] or null (bfloat16); out [M,N] bfloat16 or float32 (out_f32).
 // swiglu != 0: w interleaves blocks of 64 gate rows with the 64 up rows of the same outputs
 // (N % 128 == 0, no bias); out is silu(gate) * up, [M, N/2] bfloat16.  M <= 64, K % 8 == 0.
-MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                               int out_f32, int swiglu, cudaStream_t stream) {
+// rms_eps >= 0: the product acts on the RMS-normalised rows of x.  residual: [M,N] bfloat16 added
+// to the result (it may be `out`), or null; not with swiglu.
+MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, void* out, const void* residual,
+                               int M, int N, int K, int out_f32, int swiglu, float rms_eps, cudaStream_t stream) {
   if (M == 0) return MLR_OK;
   if (M < 0 || N <= 0 || K <= 0) return MLR_BAD_SIZE;
   if (M > 64) return MLR_TOO_LARGE;
   if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MLR_BAD_ALIGNMENT;
-  if (swiglu && (N % 128 != 0 || bias != nullptr || out_f32)) return MLR_BAD_SIZE;
+  if (swiglu && (N % 128 != 0 || bias != nullptr || out_f32 || residual != nullptr)) return MLR_BAD_SIZE;
+  if (swiglu && K > 2048) return MLR_TOO_LARGE;      // two row groups and a long K do not fit the registers
   // The CTA's warps share K.  Short rows: 4 warps (8 once many tokens shrink the load batches);
   // long rows (the down projection): 16 warps, or 8 where 16 would run out of registers.
   const bool long_rows = K > 2048;
   if (M <= 8) {
-    if (long_rows) return skinny_launch<16, 1>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
-    return skinny_launch<4, 1>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+    if (long_rows) return skinny_launch<16, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+    return skinny_launch<4, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
   }
   if (M <= 16) {
-    if (long_rows) return skinny_launch<16, 2>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
-    return skinny_launch<4, 2>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+    if (long_rows) return skinny_launch<8, 2>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+    return skinny_launch<4, 2>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
   }
-  if (M <= 32) return skinny_launch<8, 4>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
-  return skinny_launch<8, 8>(x, w, bias, out, M, N, K, out_f32, swiglu, stream);
+  if (M <= 32) return skinny_launch<8, 4>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+  return skinny_launch<8, 8>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
 }

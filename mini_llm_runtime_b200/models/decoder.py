@@ -60,6 +60,8 @@ class DecoderModel:
         self.device = torch.device(device)
         for part in self.parts():
             part.load(tensors, self.device)
+        for block in self.blocks:
+            block.finish_load(self.compute_dtype)
         return self
 
     # ------------------------------------------------------------------ cache

@@ -120,6 +120,7 @@ class CudaOps:
         self.use_mma_attention = True
         self.use_fused_swiglu = True
         self.use_skinny = True
+        self.use_fused_norm = True
         self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
         self.decode_max_splits: int | None = None  # None: just enough for the longest context
 
@@ -163,11 +164,28 @@ class CudaOps:
                                    _code(x.dtype), _stream()), "gather_rows")
         return out
 
-    def rms_norm(self, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-        """weight * x * rsqrt(mean(x^2) + eps), row by row."""
+    def rms_norm(self, x: torch.Tensor, weight: torch.Tensor | None, eps: float) -> torch.Tensor:
+        """weight * x * rsqrt(mean(x^2) + eps), row by row; without a weight, the normalised row."""
         return self._rms_norm(x, None, weight, eps)
 
-    def add_rms_norm(self, residual: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor,
+    def add_inplace(self, target: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+        """target += delta (float32 add, rounded once)."""
+        _need(target, "target")
+        _need(delta, "delta", target.dtype)
+        if target.shape != delta.shape:
+            raise KernelError("add_inplace needs equal shapes")
+        lib = build.load_library("elementwise")
+        _check(lib.mlr_add_inplace(_ptr(target), _ptr(delta), ctypes.c_longlong(target.numel()),
+                                   _code(target.dtype), _stream()), "add_inplace")
+        return target
+
+    def fuses_norm(self, rows: int) -> bool:
+        """True if products of ``rows`` rows can take an RMS norm (``rms_eps``) and a residual add
+        in their own kernel: the few-rows kernel computes the row scale from the fragments it
+        holds anyway.  Callers then skip the norm kernel; otherwise they run it first."""
+        return self.use_skinny and self.use_fused_norm and 0 < rows <= self.SKINNY_ROWS
+
+    def add_rms_norm(self, residual: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor | None,
                      eps: float) -> torch.Tensor:
         """residual += delta (in place), then the norm of the new residual."""
         _need(delta, "delta", residual.dtype, 2)
@@ -177,15 +195,17 @@ class CudaOps:
 
     def _rms_norm(self, x, delta, weight, eps):
         _need(x, "x", dims=2)
-        _need(weight, "weight", None, 1)
-        if weight.dtype != x.dtype and weight.dtype != torch.float32:
-            raise KernelError(f"norm weight must be {x.dtype} or float32, got {weight.dtype}")
-        if weight.shape[0] != x.shape[1]:
-            raise KernelError(f"norm weight has {weight.shape[0]} entries, rows have {x.shape[1]}")
+        if weight is not None:
+            _need(weight, "weight", None, 1)
+            if weight.dtype != x.dtype and weight.dtype != torch.float32:
+                raise KernelError(f"norm weight must be {x.dtype} or float32, got {weight.dtype}")
+            if weight.shape[0] != x.shape[1]:
+                raise KernelError(f"norm weight has {weight.shape[0]} entries, rows have {x.shape[1]}")
         out = torch.empty_like(x)
         lib = build.load_library("elementwise")
         _check(lib.mlr_rms_norm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), x.shape[0], x.shape[1],
-                                ctypes.c_float(eps), _code(x.dtype), _code(weight.dtype), _stream()), "rms_norm")
+                                ctypes.c_float(eps), _code(x.dtype),
+                                _code(x.dtype if weight is None else weight.dtype), _stream()), "rms_norm")
         return out
 
     def swiglu(self, gate_up: torch.Tensor, block: int | None = None) -> torch.Tensor:
@@ -206,10 +226,12 @@ class CudaOps:
 
     SWIGLU_BLOCK = 64   # rows of gate, then rows of up, per 128-row weight tile of the fused kernel
 
-    def linear_swiglu(self, x: torch.Tensor, weight: torch.Tensor, block: int) -> torch.Tensor:
+    def linear_swiglu(self, x: torch.Tensor, weight: torch.Tensor, block: int,
+                      rms_eps: float | None = None) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) where ``weight`` [2*inner, K] interleaves ``block`` gate rows
         with the ``block`` up rows of the same outputs.  One tensor-core kernel when the shapes
-        allow (block 64), else the product followed by the activation kernel."""
+        allow (block 64), else the product followed by the activation kernel.  ``rms_eps`` as in
+        ``linear``."""
         _need(x, "x", dims=2)
         _need(weight, "weight", x.dtype, 2)
         if x.shape[1] != weight.shape[1] or weight.shape[0] % (2 * block):
@@ -218,11 +240,14 @@ class CudaOps:
                 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[0] > 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
             if self._skinny_fits(x, weight, swiglu=True):
-                return self._linear_skinny(x, weight, None, torch.bfloat16, swiglu=True)
+                return self._linear_skinny(x, weight, None, torch.bfloat16, swiglu=True, rms_eps=rms_eps)
+            if rms_eps is not None:
+                x = self.rms_norm(x, None, rms_eps)
+                rms_eps = None
             out = self._linear_tcgen05(x, weight, None, torch.bfloat16, swiglu=True)
             if out is not None:
                 return out
-        return self.swiglu(self.linear(x, weight), block)
+        return self.swiglu(self.linear(x, weight, rms_eps=rms_eps), block)
 
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                       slots: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, num_heads: int,
@@ -257,8 +282,14 @@ class CudaOps:
 
     # ------------------------------------------------------------------ matrix product
     def linear(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-               out_dtype: torch.dtype | None = None) -> torch.Tensor:
-        """x [M,K] times weight [N,K] transposed, plus bias [N]."""
+               out_dtype: torch.dtype | None = None, rms_eps: float | None = None,
+               residual: torch.Tensor | None = None) -> torch.Tensor:
+        """x [M,K] times weight [N,K] transposed, plus bias [N].
+
+        ``rms_eps``: the product is taken of the RMS-normalised rows x * rsqrt(mean(x^2) + eps)
+        (a norm whose weight has been folded into ``weight``).  ``residual`` [M,N]: the result is
+        added into it in place and it is returned.  The few-rows kernel does both itself; for
+        other shapes a normalising kernel runs first and an add kernel last."""
         _need(x, "x", dims=2)
         _need(weight, "weight", x.dtype, 2)
         if bias is not None:
@@ -268,14 +299,20 @@ class CudaOps:
         if x.shape[1] != weight.shape[1]:
             raise KernelError(f"x has {x.shape[1]} columns, weight expects {weight.shape[1]}")
         out_dtype = out_dtype or x.dtype
-        if (self.use_tensor_cores and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
-                and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.shape[0] > 0):
-            if self._skinny_fits(x, weight):
-                return self._linear_skinny(x, weight, bias, out_dtype, swiglu=False)
-            out = self._linear_tcgen05(x, weight, bias, out_dtype)
-            if out is not None:
-                return out
-        return self._linear_simt(x, weight, bias, out_dtype)
+        if residual is not None:
+            _need(residual, "residual", out_dtype, 2)
+            if residual.shape != (x.shape[0], weight.shape[0]):
+                raise KernelError("residual must have the shape of the result")
+        tensor_cores = (self.use_tensor_cores and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+                        and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.shape[0] > 0)
+        if tensor_cores and self._skinny_fits(x, weight) and (residual is None or out_dtype == torch.bfloat16):
+            return self._linear_skinny(x, weight, bias, out_dtype, swiglu=False, rms_eps=rms_eps, residual=residual)
+        if rms_eps is not None:
+            x = self.rms_norm(x, None, rms_eps)
+        out = self._linear_tcgen05(x, weight, bias, out_dtype) if tensor_cores else None
+        if out is None:
+            out = self._linear_simt(x, weight, bias, out_dtype)
+        return self.add_inplace(residual, out) if residual is not None else out
 
     # Rows up to which the few-rows kernel is chosen.  It accepts up to 64, but measured on the
     # 0.5B layer sizes it loses to the tcgen05 kernel at 64 rows (3.72 against 3.23 ms per step).
@@ -287,13 +324,18 @@ class CudaOps:
         return (self.use_skinny and x.shape[0] <= self.SKINNY_ROWS and weight.shape[0] < self.SKINNY_WEIGHT_ROWS
                 and (not swiglu or x.shape[1] <= 2048))
 
-    def _linear_skinny(self, x, weight, bias, out_dtype, swiglu):
+    def _linear_skinny(self, x, weight, bias, out_dtype, swiglu, rms_eps=None, residual=None):
         M, K = x.shape
         N = weight.shape[0]
-        out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+        if residual is not None:
+            out = residual      # the kernel adds the product into it
+        else:
+            out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
         lib = build.load_library("gemm_skinny")
-        _check(lib.mlr_gemm_skinny(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
-                                   int(out_dtype == torch.float32), int(swiglu), _stream()), "linear (few rows)")
+        _check(lib.mlr_gemm_skinny(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual), M, N, K,
+                                   int(out_dtype == torch.float32), int(swiglu),
+                                   ctypes.c_float(-1.0 if rms_eps is None else rms_eps), _stream()),
+               "linear (few rows)")
         return out
 
     def _linear_tcgen05(self, x, weight, bias, out_dtype, swiglu=False):

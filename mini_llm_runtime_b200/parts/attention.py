@@ -18,6 +18,7 @@ from .base import KVCacheNeed, Mixer, TensorSpec, build_part, register_part
 
 class GQAAttention(Mixer):
     graph_safe = True
+    supports_norm_fusion = True
 
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
@@ -36,6 +37,7 @@ class GQAAttention(Mixer):
         self.scale = float(self.head_dim) ** -0.5
         self.position = build_part("position", a["position"], compute_dtype)
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+        self.input_norm_eps: float | None = None     # set once the preceding norm's weight is folded in
 
     def cache_need(self):
         return KVCacheNeed(self.num_kv_heads, self.head_dim, None if self.window is None else int(self.window))
@@ -71,14 +73,21 @@ class GQAAttention(Mixer):
             self.b_o = self._to_compute(tensors[p + "o_proj.bias"], device)
         self.position.load({}, device)
 
-    def forward(self, x, ctx, view, writes_cache):
+    def absorb_input_norm(self, weight, eps):
+        folded = self.w_qkv.float() * weight.to(self.w_qkv.device).float()[None, :]
+        self.w_qkv = folded.to(self.compute_dtype).contiguous()
+        self.input_norm_eps = float(eps)
+
+    def forward(self, x, ctx, view, writes_cache, raw_input=False, residual=None):
+        """``raw_input``: x is the un-normalised stream and the q/k/v product applies the row scale
+        of the folded norm.  ``residual``: the output product adds into it in place."""
         k = ops.current()
-        qkv = k.linear(x, self.w_qkv, self.b_qkv)
+        qkv = k.linear(x, self.w_qkv, self.b_qkv, rms_eps=self.input_norm_eps if raw_input else None)
         q = self.position.rotate_and_store(qkv, ctx, view, self.num_heads, self.num_kv_heads,
                                            self.head_dim, writes_cache)
         mixed = k.paged_attention(q, view.k_pool, view.v_pool, view.batch, self.num_heads,
                                   self.num_kv_heads, self.head_dim, self.scale, self.window)
-        return k.linear(mixed, self.w_o, self.b_o)
+        return k.linear(mixed, self.w_o, self.b_o, residual=residual)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

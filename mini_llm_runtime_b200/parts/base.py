@@ -101,6 +101,12 @@ class Norm(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    def fold(self) -> tuple[torch.Tensor, float] | None:
+        """If this norm is "scale each row by rsqrt(mean(x^2) + eps), then multiply by a weight":
+        hand out (weight, eps) and from now on apply the row scale only - the caller multiplies
+        the weight into the matrix that follows.  None if the norm cannot be expressed so."""
+        return None
+
     def add_forward(self, residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         """residual += delta in place; returns norm(residual)."""
         raise NotImplementedError
@@ -118,6 +124,10 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     category = "mixer"
+    # A part that sets this implements ``absorb_input_norm`` and accepts ``raw_input=`` and
+    # ``residual=`` in forward: the block may hand it the un-normalised stream (the part applies the
+    # row scale inside its first product) and let it add its output into the stream in place.
+    supports_norm_fusion = False
 
     def cache_need(self) -> KVCacheNeed | StateNeed | None:
         return None
@@ -126,11 +136,19 @@ class Mixer(Part):
         """x: [rows, hidden] of this step; ``view`` is this run step's cache entry."""
         raise NotImplementedError
 
+    def absorb_input_norm(self, weight: torch.Tensor, eps: float) -> None:
+        """Multiply the preceding norm's weight into the input projection."""
+        raise NotImplementedError
+
 
 class FeedForward(Part):
     category = "feed_forward"
+    supports_norm_fusion = False
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+    def absorb_input_norm(self, weight: torch.Tensor, eps: float) -> None:
         raise NotImplementedError
 
 
@@ -162,6 +180,9 @@ class Block:
 
     def parts(self) -> tuple[Part, ...]:
         return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+
+    def finish_load(self, compute_dtype: torch.dtype) -> None:
+        """Called once all four parts hold their tensors; an arrangement may fuse across them."""
 
     def forward(self, residual: torch.Tensor, pending: torch.Tensor | None, ctx, view,
                 writes_cache: bool) -> tuple[torch.Tensor, torch.Tensor | None]:

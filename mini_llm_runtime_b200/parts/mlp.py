@@ -15,6 +15,7 @@ from .base import FeedForward, TensorSpec, register_part
 
 class SwiGLU(FeedForward):
     graph_safe = True
+    supports_norm_fusion = True
 
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
@@ -22,6 +23,7 @@ class SwiGLU(FeedForward):
         self.intermediate_size = int(self.args["intermediate_size"])
         self.w_gate_up = self.w_down = None
         self.block = self.intermediate_size   # gate/up interleaving of w_gate_up
+        self.input_norm_eps: float | None = None
 
     def tensors(self):
         p = self.prefix
@@ -43,9 +45,16 @@ class SwiGLU(FeedForward):
         self.w_gate_up = self._to_compute(stacked, device)
         self.w_down = self._to_compute(tensors[p + "down_proj.weight"], device)
 
-    def forward(self, x, ctx):
+    def absorb_input_norm(self, weight, eps):
+        folded = self.w_gate_up.float() * weight.to(self.w_gate_up.device).float()[None, :]
+        self.w_gate_up = folded.to(self.compute_dtype).contiguous()
+        self.input_norm_eps = float(eps)
+
+    def forward(self, x, ctx, raw_input=False, residual=None):
         k = ops.current()
-        return k.linear(k.linear_swiglu(x, self.w_gate_up, self.block), self.w_down)
+        hidden = k.linear_swiglu(x, self.w_gate_up, self.block,
+                                 rms_eps=self.input_norm_eps if raw_input else None)
+        return k.linear(hidden, self.w_down, residual=residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

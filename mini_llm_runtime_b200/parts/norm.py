@@ -19,6 +19,7 @@ class RMSNorm(Norm):
         self.size = int(self.args["size"])
         self.eps = float(self.args["eps"])
         self.weight: torch.Tensor | None = None
+        self.folded = False       # True once the weight lives in the matrix that follows
 
     def tensors(self):
         return {self.prefix + "weight": TensorSpec((self.size,), init="norm")}
@@ -26,11 +27,15 @@ class RMSNorm(Norm):
     def load(self, tensors, device):
         self.weight = self._keep_precision(tensors[self.prefix + "weight"], device)
 
+    def fold(self):
+        self.folded = True
+        return self.weight, self.eps
+
     def forward(self, x):
-        return ops.current().rms_norm(x, self.weight, self.eps)
+        return ops.current().rms_norm(x, None if self.folded else self.weight, self.eps)
 
     def add_forward(self, residual, delta):
-        return ops.current().add_rms_norm(residual, delta, self.weight, self.eps)
+        return ops.current().add_rms_norm(residual, delta, None if self.folded else self.weight, self.eps)
 
 
 register_part("norm", "rms_norm", RMSNorm)

@@ -22,8 +22,17 @@ class FakeOps:
 
     def rms_norm(self, x, weight, eps):
         x32 = x.float()
-        out = weight.float() * (x32 * torch.rsqrt((x32 * x32).mean(-1, keepdim=True) + eps))
+        out = x32 * torch.rsqrt((x32 * x32).mean(-1, keepdim=True) + eps)
+        if weight is not None:
+            out = weight.float() * out
         return out.to(x.dtype)
+
+    def add_inplace(self, target, delta):
+        target.copy_((target.float() + delta.float()).to(target.dtype))
+        return target
+
+    def fuses_norm(self, rows):
+        return 0 < rows <= 16
 
     def add_rms_norm(self, residual, delta, weight, eps):
         residual.copy_((residual.float() + delta.float()).to(residual.dtype))
@@ -36,13 +45,19 @@ class FakeOps:
         gate, up = blocks[:, :, 0].reshape(-1, inner), blocks[:, :, 1].reshape(-1, inner)
         return (torch.nn.functional.silu(gate) * up).to(gate_up.dtype)
 
-    def linear_swiglu(self, x, weight, block):
-        return self.swiglu(self.linear(x, weight), block)
+    def linear_swiglu(self, x, weight, block, rms_eps=None):
+        return self.swiglu(self.linear(x, weight, rms_eps=rms_eps), block)
 
-    def linear(self, x, weight, bias=None, out_dtype=None):
-        out = x.float() @ weight.float().T
+    def linear(self, x, weight, bias=None, out_dtype=None, rms_eps=None, residual=None):
+        x32 = x.float()
+        if rms_eps is not None:
+            x32 = x32 * torch.rsqrt((x32 * x32).mean(-1, keepdim=True) + rms_eps)
+        out = x32 @ weight.float().T
         if bias is not None:
             out = out + bias.float()
+        if residual is not None:
+            residual.copy_((residual.float() + out).to(residual.dtype))
+            return residual
         return out.to(out_dtype or x.dtype)
 
     def rope_kv_write(self, qkv, positions, inv_freq, slots, k_pool, v_pool, num_heads, num_kv_heads,

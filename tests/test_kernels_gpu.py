@@ -188,6 +188,74 @@ def _check_few_rows(m, n, k, x, w, b, want):
     assert_close(got, other, torch.bfloat16, "few-rows kernel against the tcgen05 kernel")
 
 
+@pytest.mark.parametrize("m", [1, 7, 16, 30, 64])
+@pytest.mark.parametrize("n,k,eps", [(896, 4864, 1e-6), (1152, 896, 1e-5), (100, 72, 1e-3), (24, 4104, 1e-6)])
+def test_few_rows_linear_with_norm_and_residual(m, n, k, eps):
+    """The row scale of an RMS norm taken inside the product, and the result added into a residual
+    in place; alone and together, against the same operations done separately in float64.  The
+    same calls through the many-rows kernels (norm kernel, product, add kernel) must agree."""
+    x = rnd((m, k), torch.bfloat16, 300 + m, 3.0)
+    x[m // 2] *= 40.0                               # rows of very different size: each needs its own scale
+    w = rnd((n, k), torch.bfloat16, 301, 0.1)
+    b = rnd((n,), torch.bfloat16, 302)
+    base = rnd((m, n), torch.bfloat16, 303, 2.0)
+    xd = x.double()
+    normed = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + eps)
+    cuda().SKINNY_ROWS = 64
+    try:
+        assert cuda()._skinny_fits(x, w) and cuda().fuses_norm(m)
+        for skinny in (True, False):
+            cuda().use_skinny = skinny
+            got = cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE), rms_eps=eps)
+            assert_close(got, normed @ w.double().T + b.double(), torch.bfloat16, f"norm inside the product, few-rows={skinny}")
+            stream = base.clone().to(DEVICE)
+            got = cuda().linear(x.to(DEVICE), w.to(DEVICE), None, residual=stream)
+            assert got.data_ptr() == stream.data_ptr()
+            assert_close(got, base.double() + xd @ w.double().T, torch.bfloat16, f"residual add, few-rows={skinny}")
+            stream = base.clone().to(DEVICE)
+            cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE), rms_eps=eps, residual=stream)
+            assert_close(stream, base.double() + normed @ w.double().T + b.double(), torch.bfloat16,
+                         f"norm and residual, few-rows={skinny}")
+    finally:
+        cuda().use_skinny = True
+        del cuda().SKINNY_ROWS
+
+
+@pytest.mark.parametrize("m", [2, 16, 40])
+def test_few_rows_linear_swiglu_with_norm(m):
+    inner, k, eps = 320, 200, 1e-6
+    x = rnd((m, k), torch.bfloat16, 310 + m, 5.0)
+    gate = rnd((inner, k), torch.bfloat16, 311, 0.1)
+    up = rnd((inner, k), torch.bfloat16, 312, 0.1)
+    weight = torch.cat([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k)
+    xd = x.double()
+    normed = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + eps)
+    want = torch.nn.functional.silu(normed @ gate.double().T) * (normed @ up.double().T)
+    cuda().SKINNY_ROWS = 64
+    try:
+        for skinny in (True, False):
+            cuda().use_skinny = skinny
+            got = cuda().linear_swiglu(x.to(DEVICE), weight.to(DEVICE), 64, rms_eps=eps)
+            assert_close(got, want, torch.bfloat16, f"norm inside the fused gate/up product, few-rows={skinny}")
+    finally:
+        cuda().use_skinny = True
+        del cuda().SKINNY_ROWS
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_weightless_norm_and_add_inplace(dtype):
+    x = rnd((9, 200), dtype, 320, 2.0)
+    delta = rnd((9, 200), dtype, 321)
+    got = cuda().rms_norm(x.to(DEVICE), None, 1e-5)
+    assert_close(got, plain.rms_norm(x, torch.ones(200), 1e-5), dtype, "norm without a weight")
+    target = x.clone().to(DEVICE)
+    assert cuda().add_inplace(target, delta.to(DEVICE)).data_ptr() == target.data_ptr()
+    assert torch.equal(target.cpu(), (x.float() + delta.float()).to(dtype))
+    target = x.clone().to(DEVICE)
+    got = cuda().add_rms_norm(target, delta.to(DEVICE), None, 1e-5)
+    assert_close(got, plain.rms_norm((x.float() + delta.float()).to(dtype), torch.ones(200), 1e-5), dtype, "add + weightless norm")
+
+
 @pytest.mark.parametrize("m", [1, 8, 13, 30, 64])
 @pytest.mark.parametrize("inner,k", [(4864, 896), (128, 64), (320, 200)])
 def test_few_rows_linear_swiglu(m, inner, k):

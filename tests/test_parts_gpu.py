@@ -154,7 +154,10 @@ def test_embedding_and_heads(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_pre_norm_block(dtype):
+@pytest.mark.parametrize("rows", [21, 6])
+def test_pre_norm_block(dtype, rows):
+    """21 rows take the arrangement with norm kernels, 6 rows (in bfloat16, after the norms'
+    weights were folded into the projections) the one where the products normalise and add."""
     hidden, heads, kv_heads, head_dim, inner, eps = 48, 3, 3, 16, 80, 1e-5
     mixer = build_part("mixer", PartSpec("gqa_attention", {
         "hidden_size": hidden, "num_heads": heads, "num_kv_heads": kv_heads, "head_dim": head_dim, "qkv_bias": True,
@@ -174,12 +177,17 @@ def test_pre_norm_block(dtype):
     tensors = stored(tensors)
     for part in block.parts():
         part.load(tensors, torch.device(DEVICE))
-    cache, open_step = context_for(mixer.cache_need(), dtype, 21)
-    x = rnd((21, hidden), 40).to(dtype)
-    ctx = open_step(21)
+    block.finish_load(dtype)
+    assert block.folded == (dtype == torch.bfloat16)
+    cache, open_step = context_for(mixer.cache_need(), dtype, rows)
+    x = rnd((rows, hidden), 40).to(dtype)
+    ctx = open_step(rows)
     residual, pending = block.forward(x.clone().to(DEVICE), None, ctx, ctx.cache_view(0), True)
     cache.commit_step()
+    if pending is None:
+        assert block.folded and rows <= 16
+        pending = torch.zeros_like(residual)
     cfg = {"num_attention_heads": heads, "num_key_value_heads": kv_heads, "hidden_size": hidden, "head_dim": head_dim,
            "rope_theta": 1e6, "rms_norm_eps": eps, "num_hidden_layers": 1}
-    want = plain.decoder_layer(x.float(), torch.arange(21), tensors, 0, cfg)
+    want = plain.decoder_layer(x.float(), torch.arange(rows), tensors, 0, cfg)
     assert_close(residual.float() + pending.float(), want, dtype, "pre-norm block")
