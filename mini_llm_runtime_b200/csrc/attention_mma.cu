@@ -21,7 +21,7 @@
 //
 // mma.sync is the legacy tensor path on sm_100a; attention here is far from the bound of either
 // path for the model sizes served (the projections dominate), and tcgen05 serves those.
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace mlr {
 
@@ -60,8 +60,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // A tile in shared memory: rows of D bfloat16, the 16-byte chunks of a row XOR-swizzled by the row
 // index so that ldmatrix (8 rows x 16 bytes) is free of bank conflicts.
-template <int D>
+// HALVES (head_dim 128 as the tensor memory accelerator delivers it): two sub-tiles of 64 columns,
+// each with rows of 128 bytes and the same swizzle; for head_dim 64 both layouts coincide.
+template <int D, bool HALVES = false>
 __device__ __forceinline__ bf16* tile_at(bf16* tile, int row, int chunk) {
+  if (HALVES && D > 64) return tile + (chunk >> 3) * (TILE_KV * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
   return tile + row * D + ((chunk ^ (row & 7)) << 3);
 }
 
@@ -91,7 +94,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* pool, const
 }
 
 // One warp: S[16 x (8*NT)] = Q[16 x D] K^T for keys key_row0.. of a K tile.
-template <int D, int NT>
+template <int D, int NT, bool HALVES = false>
 __device__ __forceinline__ void warp_qk(float (*s)[4], const uint32_t (*q_frag)[4], bf16* k_tile, int key_row0, int lane) {
 #pragma unroll
   for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -102,7 +105,7 @@ __device__ __forceinline__ void warp_qk(float (*s)[4], const uint32_t (*q_frag)[
       uint32_t b[4];
       const int key = key_row0 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
       const int chunk = ks * 2 + ((lane >> 3) & 1);
-      ldmatrix_x4(b, tile_at<D>(k_tile, key, chunk));
+      ldmatrix_x4(b, tile_at<D, HALVES>(k_tile, key, chunk));
       mma_bf16(s[2 * jp], q_frag[ks], b[0], b[1]);
       mma_bf16(s[2 * jp + 1], q_frag[ks], b[2], b[3]);
     }
@@ -111,7 +114,7 @@ __device__ __forceinline__ void warp_qk(float (*s)[4], const uint32_t (*q_frag)[
 
 // One warp: O[16 x D] += P[16 x (8*NT)] V for keys key_row0.. of a V tile; P comes from the score
 // registers, rounded to bfloat16.
-template <int D, int NT>
+template <int D, int NT, bool HALVES = false>
 __device__ __forceinline__ void warp_pv(float (*o)[4], const float (*p)[4], bf16* v_tile, int key_row0, int lane) {
 #pragma unroll
   for (int kk = 0; kk < NT / 2; ++kk) {
@@ -125,7 +128,7 @@ __device__ __forceinline__ void warp_pv(float (*o)[4], const float (*p)[4], bf16
       uint32_t b[4];
       const int key = key_row0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
       const int chunk = dp * 2 + (lane >> 4);
-      ldmatrix_x4_trans(b, tile_at<D>(v_tile, key, chunk));
+      ldmatrix_x4_trans(b, tile_at<D, HALVES>(v_tile, key, chunk));
       mma_bf16(o[2 * dp], a, b[0], b[1]);
       mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
     }
@@ -284,6 +287,124 @@ prefill_attention_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
   }
 }
 
+// The end of both decode kernels: merge the four warps' states (each saw a quarter of the keys) in
+// shared memory, write the output if the request has one chunk, else store the chunk's state and
+// let the CTA that arrives last for this (request, kv head) merge all chunks in chunk order.
+template <int D>
+__device__ __forceinline__ void decode_finish(float* merge, int* last_flag_ptr, const float* m, const float* l,
+                                              const float (*o)[4], bf16* out, float* scratch, int* counters,
+                                              int index, int row, int heads, int kv_heads, int kv_head, int group,
+                                              int split, int splits, int max_splits) {
+  constexpr int STATE = D + 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // ---- merge the four warps (each saw a quarter of the keys)
+  float* mine = merge + (size_t)warp * 16 * STATE;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int g = (lane >> 2) + 8 * i;
+    if ((lane & 3) == 0) { mine[g * STATE] = m[i]; mine[g * STATE + 1] = l[i]; }
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t) {
+      mine[g * STATE + 2 + t * 8 + (lane & 3) * 2] = o[t][2 * i];
+      mine[g * STATE + 2 + t * 8 + (lane & 3) * 2 + 1] = o[t][2 * i + 1];
+    }
+  }
+  __syncthreads();
+  const size_t state_base = ((size_t)index * heads + kv_head * group) * max_splits;
+  for (int item = threadIdx.x; item < group * D; item += ATTN_THREADS) {
+    const int g = item / D, d = item - g * D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATTN_WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + g) * STATE]);
+    float l_all = 0.f, a_all = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATTN_WARPS; ++w) {
+      const float* state = merge + ((size_t)w * 16 + g) * STATE;
+      const float factor = exp2f(state[0] - m_all);      // a warp without keys has m = -inf: factor 0
+      l_all += state[1] * factor;
+      a_all += state[2 + d] * factor;
+    }
+    if (splits == 1) {
+      out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(a_all / l_all);
+    } else {
+      float* state = scratch + (state_base + (size_t)g * max_splits + split) * STATE;
+      state[2 + d] = a_all;
+      if (d == 0) { state[0] = m_all; state[1] = l_all; }
+    }
+  }
+  if (splits == 1) return;
+
+  // ---- the CTA that arrives last for this (request, kv head) merges all chunks, in chunk order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) (*last_flag_ptr) = (atomicAdd(&counters[index * kv_heads + kv_head], 1) == splits - 1);
+  __syncthreads();
+  if (!(*last_flag_ptr)) return;
+  __threadfence();
+  // (1) every chunk's (max, sum) into shared memory with one round of loads
+  float* max_s = merge;                         // [group][splits], later the chunks' weights
+  float* sum_s = merge + 16 * max_splits;       // [group][splits]
+  float* inv_s = sum_s + 16 * max_splits;       // [group]
+  for (int item = threadIdx.x; item < group * splits; item += ATTN_THREADS) {
+    const int g = item / splits, s = item - g * splits;
+    const float2 pair = __ldcg(reinterpret_cast<const float2*>(
+        scratch + (state_base + (size_t)g * max_splits + s) * STATE));
+    max_s[g * max_splits + s] = pair.x;
+    sum_s[g * max_splits + s] = pair.y;
+  }
+  __syncthreads();
+  // (2) per head: overall max, each chunk's weight exp2(m_s - max), overall sum (chunk order)
+  if (threadIdx.x < group) {
+    const int g = threadIdx.x;
+    float m_all = -INFINITY;
+    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, max_s[g * max_splits + s]);
+    float l_all = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float factor = exp2f(max_s[g * max_splits + s] - m_all);
+      max_s[g * max_splits + s] = factor;
+      l_all += sum_s[g * max_splits + s] * factor;
+    }
+    inv_s[g] = 1.f / l_all;
+  }
+  __syncthreads();
+  // (3) weighted sum of the chunks' accumulators; the loads of four outputs and eight chunks are
+  // issued together so that their latencies overlap, the additions run in chunk order
+  constexpr int PER_PASS = 4;
+  for (int item0 = threadIdx.x; item0 < group * D; item0 += ATTN_THREADS * PER_PASS) {
+    float total[PER_PASS];
+#pragma unroll
+    for (int i = 0; i < PER_PASS; ++i) total[i] = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float part[PER_PASS][8];
+#pragma unroll
+      for (int i = 0; i < PER_PASS; ++i) {
+        const int item = item0 + i * ATTN_THREADS;
+        const int g = min(item / D, group - 1), d = item % D;
+        const float* states = scratch + (state_base + (size_t)g * max_splits) * STATE + 2 + d;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          part[i][j] = (item < group * D && s0 + j < splits) ? __ldcg(&states[(size_t)(s0 + j) * STATE]) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < PER_PASS; ++i) {
+        const int g = min((item0 + i * ATTN_THREADS) / D, group - 1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (s0 + j < splits) total[i] += part[i][j] * max_s[g * max_splits + s0 + j];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < PER_PASS; ++i) {
+      const int item = item0 + i * ATTN_THREADS;
+      if (item < group * D) {
+        const int g = item / D, d = item % D;
+        out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(total[i] * inv_s[g]);
+      }
+    }
+  }
+  if (threadIdx.x == 0) counters[index * kv_heads + kv_head] = 0;
+}
+
 // ------------------------------------------------------------------------------------------ decode
 // STAGES: 64-key tiles in flight per CTA.  Four when a chunk is short and CTAs are few (every load
 // of the chunk is requested at once); two when chunks are long and CTAs many (four CTAs then
@@ -379,112 +500,158 @@ decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_poo
     cp_async_commit();
   }
 
-  // ---- merge the four warps (each saw a quarter of the keys)
-  float* mine = merge + (size_t)warp * 16 * STATE;
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int g = (lane >> 2) + 8 * i;
-    if ((lane & 3) == 0) { mine[g * STATE] = m[i]; mine[g * STATE + 1] = l[i]; }
-#pragma unroll
-    for (int t = 0; t < D / 8; ++t) {
-      mine[g * STATE + 2 + t * 8 + (lane & 3) * 2] = o[t][2 * i];
-      mine[g * STATE + 2 + t * 8 + (lane & 3) * 2 + 1] = o[t][2 * i + 1];
-    }
-  }
-  __syncthreads();
-  const size_t state_base = ((size_t)index * heads + kv_head * group) * max_splits;
-  for (int item = threadIdx.x; item < group * D; item += ATTN_THREADS) {
-    const int g = item / D, d = item - g * D;
-    float m_all = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < ATTN_WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + g) * STATE]);
-    float l_all = 0.f, a_all = 0.f;
-#pragma unroll
-    for (int w = 0; w < ATTN_WARPS; ++w) {
-      const float* state = merge + ((size_t)w * 16 + g) * STATE;
-      const float factor = exp2f(state[0] - m_all);      // a warp without keys has m = -inf: factor 0
-      l_all += state[1] * factor;
-      a_all += state[2 + d] * factor;
-    }
-    if (splits == 1) {
-      out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(a_all / l_all);
-    } else {
-      float* state = scratch + (state_base + (size_t)g * max_splits + split) * STATE;
-      state[2 + d] = a_all;
-      if (d == 0) { state[0] = m_all; state[1] = l_all; }
-    }
-  }
-  if (splits == 1) return;
+  decode_finish<D>(merge, &last_flag, m, l, o, out, scratch, counters, index, row, heads, kv_heads, kv_head, group,
+                   split, splits, max_splits);
+}
 
-  // ---- the CTA that arrives last for this (request, kv head) merges all chunks, in chunk order
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) last_flag = (atomicAdd(&counters[index * kv_heads + kv_head], 1) == splits - 1);
-  __syncthreads();
-  if (!last_flag) return;
-  __threadfence();
-  // (1) every chunk's (max, sum) into shared memory with one round of loads
-  float* max_s = merge;                         // [group][splits], later the chunks' weights
-  float* sum_s = merge + 16 * max_splits;       // [group][splits]
-  float* inv_s = sum_s + 16 * max_splits;       // [group]
-  for (int item = threadIdx.x; item < group * splits; item += ATTN_THREADS) {
-    const int g = item / splits, s = item - g * splits;
-    const float2 pair = __ldcg(reinterpret_cast<const float2*>(
-        scratch + (state_base + (size_t)g * max_splits + s) * STATE));
-    max_s[g * max_splits + s] = pair.x;
-    sum_s[g * max_splits + s] = pair.y;
+// ------------------------------------------------------------------------------------- decode, TMA
+// The same work as decode_attention_mma_kernel with K and V brought in by the tensor memory
+// accelerator: the pools are described as [pages * kv_heads * page_size, D] matrices, one
+// cp.async.bulk.tensor per page (and per 64-column half) lands a page's keys of one kv head in the
+// 128-byte-swizzled tile that ldmatrix reads, and an mbarrier per stage counts the bytes.  No thread
+// computes an address per 16 bytes; warp 0's lanes issue one page each.  For page sizes that are a
+// power of two >= 8 (pages of 64 keys or more are read in boxes of 64 keys).
+//
+// Slots of pages the request does not hold (beyond its last page, or released by the window) are
+// filled from page 0 of the pool.  Keys outside the chunk's range - those slots, the rest of the
+// last page, keys the window has passed - get the score -inf whatever was loaded, and their V rows
+// are overwritten with zeros in shared memory before use (only a chunk's first and last tile can
+// hold such keys), so that nothing a request does not own reaches its result.
+//
+// Chunks other than a request's last hold no key of this step, so their first loads are issued
+// before the wait on the previous kernel (which writes this step's keys).
+// The stages are reused as the merge area once the last tile has been consumed.
+template <int D, int STAGES>
+__global__ void __launch_bounds__(ATTN_THREADS)
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                            const bf16* q, bf16* __restrict__ out, const int* __restrict__ decode_seg,
+                            const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
+                            const int* __restrict__ block_table, int table_width, int heads, int kv_heads,
+                            int page_size, int page_shift, int window, float scale_log2, int chunk,
+                            float* __restrict__ scratch, int* __restrict__ counters, int max_splits,
+                            int* error_word) {
+  constexpr int HALVES = D / 64;
+  constexpr int TILE_ELEMS = TILE_KV * D;
+  extern __shared__ uint8_t attn_shared_raw[];
+  uint8_t* aligned = (uint8_t*)(((uintptr_t)attn_shared_raw + 1023) & ~(uintptr_t)1023);
+  bf16* kv_tiles = reinterpret_cast<bf16*>(aligned);                 // STAGES x (K [64][D], V [64][D])
+  bf16* q_tile = kv_tiles + (size_t)STAGES * 2 * TILE_ELEMS;         // [16][D], rows >= group are zeros
+  float* merge = reinterpret_cast<float*>(aligned);                  // after the loop: [4 warps][16][D + 2]
+  __shared__ uint64_t full_bar[STAGES];
+  __shared__ int last_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
   }
+  pdl_trigger();
   __syncthreads();
-  // (2) per head: overall max, each chunk's weight exp2(m_s - max), overall sum (chunk order)
-  if (threadIdx.x < group) {
-    const int g = threadIdx.x;
-    float m_all = -INFINITY;
-    for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, max_s[g * max_splits + s]);
-    float l_all = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float factor = exp2f(max_s[g * max_splits + s] - m_all);
-      max_s[g * max_splits + s] = factor;
-      l_all += sum_s[g * max_splits + s] * factor;
+
+  // Step metadata was copied to the device before the first kernel of the step: safe to read now.
+  const int group = heads / kv_heads;
+  const int split = blockIdx.x, kv_head = blockIdx.y, index = blockIdx.z;
+  const int seg = decode_seg[index];
+  const int row = seg_q_start[seg];
+  const int position = seg_pos0[seg];
+  const int lowest = window > 0 ? max(0, position - window + 1) : 0;
+  const int first_chunk = lowest / chunk;
+  const int splits = position / chunk - first_chunk + 1;
+  if (split >= splits) return;
+  const int k_begin = max(lowest, (first_chunk + split) * chunk);
+  const int k_end = min(position + 1, (first_chunk + split + 1) * chunk);   // exclusive
+  const int* table = block_table + (size_t)seg * table_width;
+  const int tile_begin = k_begin / TILE_KV, tile_end = (k_end - 1) / TILE_KV;   // inclusive
+  const int tiles = tile_end - tile_begin + 1;
+
+  // warp 0: lane j fetches the j-th page (or the one 64-key box) of a tile, K and V
+  const int boxes = page_size >= TILE_KV ? 1 : TILE_KV >> page_shift;
+  const int box_rows = page_size >= TILE_KV ? TILE_KV : page_size;
+  auto issue = [&](int t) {
+    const int stage = t % STAGES;
+    uint64_t* bar = &full_bar[stage];
+    if (lane == 0) mbar_expect_tx(bar, 2u * TILE_ELEMS * 2u);
+    __syncwarp();
+    if (lane < boxes) {
+      const int key0 = (tile_begin + t) * TILE_KV + lane * box_rows;
+      const int logical = key0 >> page_shift;
+      int page = logical < table_width ? table[logical] : -1;
+      int offset = key0 & (page_size - 1);
+      if (page < 0) { page = 0; offset = 0; }
+      const int y = (page * kv_heads + kv_head) * page_size + offset;
+      bf16* k_dst = kv_tiles + (size_t)stage * 2 * TILE_ELEMS + lane * box_rows * 64;
+      bf16* v_dst = k_dst + TILE_ELEMS;
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        tma_load_2d(&k_map, bar, k_dst + h * (TILE_KV * 64), h * 64, y);
+        tma_load_2d(&v_map, bar, v_dst + h * (TILE_KV * 64), h * 64, y);
+      }
     }
-    inv_s[g] = 1.f / l_all;
+  };
+  const bool holds_new_key = split == splits - 1;
+  if (warp == 0 && !holds_new_key)
+    for (int t = 0; t < STAGES && t < tiles; ++t) issue(t);
+  pdl_wait();
+  if (warp == 0 && holds_new_key)
+    for (int t = 0; t < STAGES && t < tiles; ++t) issue(t);
+
+  constexpr int CHUNKS = D / 8;
+  for (int item = threadIdx.x; item < 16 * CHUNKS; item += ATTN_THREADS) {
+    const int g = item / CHUNKS, c = item - g * CHUNKS;
+    const bool valid = g < group;
+    const bf16* src = valid ? q + ((size_t)row * heads + kv_head * group + g) * D + c * 8 : q;
+    cp_async_16(tile_at<D>(q_tile, g, c), src, valid);
   }
+  cp_async_commit();
+
+  int limit_lo[2] = {k_begin, k_begin}, limit_hi[2];
+  limit_hi[0] = (lane >> 2) < group ? k_end - 1 : -1;          // rows that are no real head see nothing
+  limit_hi[1] = (lane >> 2) + 8 < group ? k_end - 1 : -1;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  uint32_t q_frag[D / 16][4];
+  cp_async_wait<0>();
   __syncthreads();
-  // (3) weighted sum of the chunks' accumulators; the loads of four outputs and eight chunks are
-  // issued together so that their latencies overlap, the additions run in chunk order
-  constexpr int PER_PASS = 4;
-  for (int item0 = threadIdx.x; item0 < group * D; item0 += ATTN_THREADS * PER_PASS) {
-    float total[PER_PASS];
 #pragma unroll
-    for (int i = 0; i < PER_PASS; ++i) total[i] = 0.f;
-    for (int s0 = 0; s0 < splits; s0 += 8) {
-      float part[PER_PASS][8];
-#pragma unroll
-      for (int i = 0; i < PER_PASS; ++i) {
-        const int item = item0 + i * ATTN_THREADS;
-        const int g = min(item / D, group - 1), d = item % D;
-        const float* states = scratch + (state_base + (size_t)g * max_splits) * STATE + 2 + d;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          part[i][j] = (item < group * D && s0 + j < splits) ? __ldcg(&states[(size_t)(s0 + j) * STATE]) : 0.f;
-      }
-#pragma unroll
-      for (int i = 0; i < PER_PASS; ++i) {
-        const int g = min((item0 + i * ATTN_THREADS) / D, group - 1);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (s0 + j < splits) total[i] += part[i][j] * max_s[g * max_splits + s0 + j];
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < PER_PASS; ++i) {
-      const int item = item0 + i * ATTN_THREADS;
-      if (item < group * D) {
-        const int g = item / D, d = item % D;
-        out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(total[i] * inv_s[g]);
-      }
-    }
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const int r = (lane & 7) + (((lane >> 3) & 1) << 3);
+    ldmatrix_x4(q_frag[ks], tile_at<D>(q_tile, r, ks * 2 + (lane >> 4)));
   }
-  if (threadIdx.x == 0) counters[index * kv_heads + kv_head] = 0;
+
+  bool gave_up = false;       // after one wait ran out, later waits are skipped: the kernel ends, the host raises
+  for (int t = 0; t < tiles; ++t) {
+    const int stage = t % STAGES;
+    if (!gave_up) gave_up = !mbar_wait(&full_bar[stage], (uint32_t)(t / STAGES) & 1u, error_word, 0x41);
+    gave_up = __any_sync(0xffffffffu, gave_up);                  // warp-uniform: warp 0 issues as one
+    bf16* k_tile = kv_tiles + (size_t)stage * 2 * TILE_ELEMS;
+    const int tile_key0 = (tile_begin + t) * TILE_KV;
+    if (tile_key0 < k_begin || tile_key0 + TILE_KV > k_end) {    // same for the whole CTA
+      for (int item = threadIdx.x; item < TILE_KV * CHUNKS; item += ATTN_THREADS) {
+        const int r = item / CHUNKS, c = item - r * CHUNKS;
+        if (tile_key0 + r < k_begin || tile_key0 + r >= k_end)
+          *reinterpret_cast<uint4*>(tile_at<D, true>(k_tile + TILE_ELEMS, r, c)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // a later bulk copy reuses the stage
+      __syncthreads();
+    }
+    const int key0 = tile_key0 + warp * 16;                      // this warp's 16 keys of the tile
+    if (key0 < k_end && key0 + 16 > k_begin) {
+      float s[2][4];
+      warp_qk<D, 2, true>(s, q_frag, k_tile, warp * 16, lane);
+      softmax_step<2, D / 8>(s, o, m, l, key0, limit_lo, limit_hi, scale_log2, lane);
+      warp_pv<D, 2, true>(o, s, k_tile + TILE_ELEMS, warp * 16, lane);
+    }
+    __syncthreads();                                             // every warp is done with this stage
+    if (warp == 0 && t + STAGES < tiles && !gave_up) issue(t + STAGES);
+  }
+  // No load is in flight here: every issued tile was waited for (or its wait ran out after a second).
+  decode_finish<D>(merge, &last_flag, m, l, o, out, scratch, counters, index, row, heads, kv_heads, kv_head, group,
+                   split, splits, max_splits);
 }
 
 template <typename Kernel>
@@ -573,5 +740,48 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
     if (deep) MLR_LAUNCH_DECODE(128, 4); else MLR_LAUNCH_DECODE(128, 2);
   }
 #undef MLR_LAUNCH_DECODE
+  return launch_status();
+}
+
+// Decoded tokens with K/V fetched by the tensor memory accelerator.  Same contract as
+// mlr_attention_decode_mma plus: pool_pages = pages in each pool (for the tensor maps), page_size a
+// power of two >= 8, error_word = host-visible int that receives a code if a wait runs out.
+MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                        const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
+                                        const int* block_table, int table_width, int rows, int heads, int kv_heads,
+                                        int head_dim, int page_size, int pool_pages, int window, float scale,
+                                        int chunk, int max_splits, void* scratch, int* counters, int* error_word,
+                                        cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 || chunk <= 0 ||
+      chunk % TILE_KV != 0 || max_splits <= 0 || table_width <= 0 || pool_pages <= 0 || error_word == nullptr)
+    return MLR_BAD_SIZE;
+  if (heads / kv_heads > 16 || rows > 65535 || kv_heads > 65535) return MLR_TOO_LARGE;
+  if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
+  const int page_shift = shift_of(page_size);
+  if (page_shift < 3) return MLR_BAD_SIZE;
+  if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15)) return MLR_BAD_ALIGNMENT;
+  const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
+  if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;           // tile coordinates are 32-bit
+  if ((size_t)(2 * 16 * max_splits + 16) > (size_t)ATTN_WARPS * 16 * (head_dim + 2)) return MLR_TOO_LARGE;
+  CUtensorMap k_map, v_map;
+  const int box_rows = page_size >= TILE_KV ? TILE_KV : page_size;
+  if (!make_tile_map(&k_map, k_pool, pool_rows, head_dim, box_rows) ||
+      !make_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
+    return MLR_BAD_SIZE;
+  dim3 grid(max_splits, kv_heads, rows);
+  int status;
+#define MLR_LAUNCH_DECODE_TMA(D_, S_)                                                                      \
+  do {                                                                                                     \
+    const size_t shared = 1024 + (size_t)(16 + 2 * S_ * TILE_KV) * D_ * 2;                                 \
+    static_assert((size_t)ATTN_WARPS * 16 * (D_ + 2) * 4 <= (size_t)2 * S_ * TILE_KV * D_ * 2, "merge area"); \
+    if ((status = set_shared(decode_attention_tma_kernel<D_, S_>, shared)) != MLR_OK) return status;       \
+    launch_kernel(decode_attention_tma_kernel<D_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream,     \
+                  k_map, v_map, (const bf16*)q, (bf16*)out, decode_seg, seg_q_start, seg_pos0, block_table, \
+                  table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk,      \
+                  (float*)scratch, counters, max_splits, error_word);                                      \
+  } while (0)
+  if (head_dim == 64) MLR_LAUNCH_DECODE_TMA(64, 4); else MLR_LAUNCH_DECODE_TMA(128, 3);
+#undef MLR_LAUNCH_DECODE_TMA
   return launch_status();
 }

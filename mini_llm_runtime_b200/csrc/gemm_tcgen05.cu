@@ -21,10 +21,7 @@
 // (host-visible memory), the CTA stops issuing work, frees its tensor memory and returns.
 // TMA loads use no cluster multicast.  Requirements: K % 8 == 0 (16-byte row pitch for TMA) and
 // 16-byte aligned base pointers; the caller falls back to the SIMT kernel otherwise.
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace mlr {
 
@@ -32,49 +29,6 @@ constexpr int TILE_ROWS = 128;      // MMA M
 constexpr int TILE_K = 64;          // one 128-byte swizzle atom of bfloat16
 constexpr int MMA_K = 16;
 constexpr int GEMM_THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;   // a wait gives up after one second
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false (and an error code in *error_word) if the phase does not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error_word, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = global_timer_ns();
-  do {
-    for (int i = 0; i < 128; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-  } while (global_timer_ns() - start < WAIT_LIMIT_NS);
-  *((volatile int*)error_word) = code;
-  __threadfence_system();
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups of
 // 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
 __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
@@ -412,31 +366,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------- host side
-static PFN_cuTensorMapEncodeTiled_v12000 encode_tiled() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = (PFN_cuTensorMapEncodeTiled_v12000)ptr;
-  }
-  return fn;
-}
-
-// rows x K bfloat16, row-major; box = [box_rows x 64], 128-byte swizzle, out-of-range reads give zero.
-static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  auto encode = encode_tiled();
-  if (encode == nullptr) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
-  cuuint32_t element_strides[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int BN, bool SWAP, bool SWIGLU>
 static int launch(const void* x, const void* w, const GemmParams& p, int splits, cudaStream_t stream) {
   const size_t shared = (size_t)p.stages * (TILE_ROWS * TILE_K * 2 + BN * TILE_K * 2) + 1024;
@@ -451,7 +380,7 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
   const void* a_base = SWAP ? w : x;
   const void* b_base = SWAP ? x : w;
   const int a_rows = SWAP ? p.N : p.M, b_rows = SWAP ? p.M : p.N;
-  if (!make_map(&map_a, a_base, a_rows, p.K, TILE_ROWS) || !make_map(&map_b, b_base, b_rows, p.K, BN))
+  if (!make_tile_map(&map_a, a_base, a_rows, p.K, TILE_ROWS) || !make_tile_map(&map_b, b_base, b_rows, p.K, BN))
     return MLR_BAD_ALIGNMENT;
   dim3 grid((a_rows + TILE_ROWS - 1) / TILE_ROWS, (b_rows + BN - 1) / BN, splits);
   launch_kernel(gemm_tcgen05_kernel<BN, SWAP, SWIGLU>, dim3(grid), dim3(GEMM_THREADS), shared, stream, map_a, map_b, p);

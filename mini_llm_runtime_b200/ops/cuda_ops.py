@@ -121,6 +121,7 @@ class CudaOps:
         self.use_fused_swiglu = True
         self.use_skinny = True
         self.use_fused_norm = True
+        self.use_tma_attention = True
         self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
         self.decode_max_splits: int | None = None  # None: just enough for the longest context
 
@@ -431,6 +432,17 @@ class CudaOps:
         space = self._workspace(q.device)
         if need > space["attention_scratch"].numel():
             space["attention_scratch"] = torch.empty(int(need * 1.5), dtype=torch.uint8, device=q.device)
+        page_size = k_pool.shape[2]
+        if mma and self.use_tma_attention and page_size >= 8 and page_size & (page_size - 1) == 0:
+            # pages arrive by the tensor memory accelerator, one bulk copy per page and kv head
+            _check(build.load_library("attention_mma").mlr_attention_decode_tma(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.decode_seg), _ptr(batch.seg_q_start),
+                _ptr(batch.seg_pos0), _ptr(batch.block_table), batch.block_table.shape[1], batch.num_decode,
+                num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
+                ctypes.c_float(scale), chunk, splits, _ptr(space["attention_scratch"]),
+                _ptr(space["attention_counters"]), _ptr(space["error_word"]), _stream()),
+                "decode attention (TMA)")
+            return
         entry = (build.load_library("attention_mma").mlr_attention_decode_mma if mma
                  else build.load_library("attention_decode").mlr_attention_decode)
         _check(entry(

@@ -399,7 +399,8 @@ def test_attention_ragged_batch(dtype, heads, kv_heads, head_dim, page):
     assert_close(got, want, dtype, "attention")
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (3, 1, 128, 8), (8, 8, 64, 16), (8, 1, 128, 32), (5, 1, 64, 3)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (3, 1, 128, 8), (8, 8, 64, 16), (8, 1, 128, 32), (5, 1, 64, 3),
+                                                          (4, 2, 64, 64), (7, 1, 128, 128), (2, 2, 64, 256), (6, 2, 64, 4)])
 @pytest.mark.parametrize("chunk", [None, 128, 512])
 def test_decode_attention_split_kv(heads, kv_heads, head_dim, page, chunk):
     """Single-row segments go through the split-KV kernel: contexts around the warp (32), CTA (128)
@@ -414,6 +415,14 @@ def test_decode_attention_split_kv(heads, kv_heads, head_dim, page, chunk):
             assert_close(got, want, torch.bfloat16, f"decode attention chunk={chunk} window={window}")
             again, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
             assert torch.equal(got, again), "chunks are merged in a fixed order: same bits every time"
+            # pages of 8 keys or more (a power of two) arrive by bulk tensor copies, others by cp.async;
+            # the arithmetic is the same, so the two loaders must agree to the bit
+            cuda().use_tma_attention = False
+            try:
+                other, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+            finally:
+                cuda().use_tma_attention = True
+            assert torch.equal(got, other), "bulk-copy loader against the cp.async loader"
     finally:
         cuda().decode_chunk = None
     cuda().use_decode_kernel = False
