@@ -62,9 +62,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // index so that ldmatrix (8 rows x 16 bytes) is free of bank conflicts.
 // HALVES (head_dim 128 as the tensor memory accelerator delivers it): two sub-tiles of 64 columns,
 // each with rows of 128 bytes and the same swizzle; for head_dim 64 both layouts coincide.
-template <int D, bool HALVES = false>
+template <int D, bool HALVES = false, int TKV = TILE_KV>
 __device__ __forceinline__ bf16* tile_at(bf16* tile, int row, int chunk) {
-  if (HALVES && D > 64) return tile + (chunk >> 3) * (TILE_KV * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+  if (HALVES && D > 64) return tile + (chunk >> 3) * (TKV * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
   return tile + row * D + ((chunk ^ (row & 7)) << 3);
 }
 
@@ -94,7 +94,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* pool, const
 }
 
 // One warp: S[16 x (8*NT)] = Q[16 x D] K^T for keys key_row0.. of a K tile.
-template <int D, int NT, bool HALVES = false>
+template <int D, int NT, bool HALVES = false, int TKV = TILE_KV>
 __device__ __forceinline__ void warp_qk(float (*s)[4], const uint32_t (*q_frag)[4], bf16* k_tile, int key_row0, int lane) {
 #pragma unroll
   for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -105,7 +105,7 @@ __device__ __forceinline__ void warp_qk(float (*s)[4], const uint32_t (*q_frag)[
       uint32_t b[4];
       const int key = key_row0 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
       const int chunk = ks * 2 + ((lane >> 3) & 1);
-      ldmatrix_x4(b, tile_at<D, HALVES>(k_tile, key, chunk));
+      ldmatrix_x4(b, tile_at<D, HALVES, TKV>(k_tile, key, chunk));
       mma_bf16(s[2 * jp], q_frag[ks], b[0], b[1]);
       mma_bf16(s[2 * jp + 1], q_frag[ks], b[2], b[3]);
     }
@@ -114,7 +114,7 @@ __device__ __forceinline__ void warp_qk(float (*s)[4], const uint32_t (*q_frag)[
 
 // One warp: O[16 x D] += P[16 x (8*NT)] V for keys key_row0.. of a V tile; P comes from the score
 // registers, rounded to bfloat16.
-template <int D, int NT, bool HALVES = false>
+template <int D, int NT, bool HALVES = false, int TKV = TILE_KV>
 __device__ __forceinline__ void warp_pv(float (*o)[4], const float (*p)[4], bf16* v_tile, int key_row0, int lane) {
 #pragma unroll
   for (int kk = 0; kk < NT / 2; ++kk) {
@@ -128,7 +128,7 @@ __device__ __forceinline__ void warp_pv(float (*o)[4], const float (*p)[4], bf16
       uint32_t b[4];
       const int key = key_row0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
       const int chunk = dp * 2 + (lane >> 4);
-      ldmatrix_x4_trans(b, tile_at<D, HALVES>(v_tile, key, chunk));
+      ldmatrix_x4_trans(b, tile_at<D, HALVES, TKV>(v_tile, key, chunk));
       mma_bf16(o[2 * dp], a, b[0], b[1]);
       mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
     }
@@ -138,7 +138,8 @@ __device__ __forceinline__ void warp_pv(float (*o)[4], const float (*p)[4], bf16
 // Online softmax step on one warp's score fragment.  Thread owns rows r0 = lane/4 and r0 + 8;
 // limit_lo[i] <= key <= limit_hi[i] are visible for row i.  Scores arrive unscaled; `scale_log2`
 // = head_dim^-0.5 * log2(e).  Leaves probabilities in s and rescales o.
-template <int NT, int OT>
+// MASKED = false: the caller knows that every key of the tile is visible to every row.
+template <int NT, int OT, bool MASKED = true>
 __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, int key_base,
                                              const int* limit_lo, const int* limit_hi, float scale_log2, int lane) {
   float tile_max[2] = {-INFINITY, -INFINITY};
@@ -148,7 +149,7 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
     for (int e = 0; e < 4; ++e) {
       const int key = key_base + j * 8 + (lane & 3) * 2 + (e & 1);
       const int i = e >> 1;
-      const bool visible = key >= limit_lo[i] && key <= limit_hi[i];
+      const bool visible = !MASKED || (key >= limit_lo[i] && key <= limit_hi[i]);
       s[j][e] = visible ? s[j][e] * scale_log2 : -INFINITY;
       tile_max[i] = fmaxf(tile_max[i], s[j][e]);
     }
@@ -505,12 +506,16 @@ decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_poo
 }
 
 // ------------------------------------------------------------------------------------- decode, TMA
-// The same work as decode_attention_mma_kernel with K and V brought in by the tensor memory
-// accelerator: the pools are described as [pages * kv_heads * page_size, D] matrices, one
-// cp.async.bulk.tensor per page (and per 64-column half) lands a page's keys of one kv head in the
-// 128-byte-swizzled tile that ldmatrix reads, and an mbarrier per stage counts the bytes.  No thread
-// computes an address per 16 bytes; warp 0's lanes issue one page each.  For page sizes that are a
-// power of two >= 8 (pages of 64 keys or more are read in boxes of 64 keys).
+// The decode kernel of choice: the same work as decode_attention_mma_kernel, with K and V brought in
+// by the tensor memory accelerator and no CTA-wide barrier in the loop.
+//
+// The pools are described as [pages * kv_heads * page_size, D] matrices; one cp.async.bulk.tensor
+// per page (and per 64-column half) lands a page's keys of one kv head in the 128-byte-swizzled
+// tile that ldmatrix reads, and an mbarrier per stage counts the bytes.  No thread computes an
+// address per 16 bytes.  Each warp owns whole tiles of TKV keys (tile t of the chunk belongs to
+// warp t % 4) and its own ring of STAGES stages: it waits for its tile, computes, and - being the
+// only reader - refills the stage itself.  The warps meet once, for the merge of their states.
+// For page sizes that are a power of two >= 8 (larger pages are read in boxes of TKV keys).
 //
 // Slots of pages the request does not hold (beyond its last page, or released by the window) are
 // filled from page 0 of the pool.  Keys outside the chunk's range - those slots, the rest of the
@@ -518,32 +523,36 @@ decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_poo
 // are overwritten with zeros in shared memory before use (only a chunk's first and last tile can
 // hold such keys), so that nothing a request does not own reaches its result.
 //
+// With even_split every request divides its own context evenly over the grid's max_splits chunks
+// (the host fixes only their number), so a launch captured in a CUDA graph adapts to the contexts
+// of each replay.
+//
 // Chunks other than a request's last hold no key of this step, so their first loads are issued
 // before the wait on the previous kernel (which writes this step's keys).
-// The stages are reused as the merge area once the last tile has been consumed.
-template <int D, int STAGES>
+// The stages are reused as the merge area once every warp has consumed its last tile.
+template <int D, int TKV, int STAGES>
 __global__ void __launch_bounds__(ATTN_THREADS)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                             const bf16* q, bf16* __restrict__ out, const int* __restrict__ decode_seg,
                             const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
                             const int* __restrict__ block_table, int table_width, int heads, int kv_heads,
-                            int page_size, int page_shift, int window, float scale_log2, int chunk,
-                            float* __restrict__ scratch, int* __restrict__ counters, int max_splits,
-                            int* error_word) {
+                            int page_size, int page_shift, int window, float scale_log2, int chunk_arg,
+                            int even_split, float* __restrict__ scratch, int* __restrict__ counters,
+                            int max_splits, int* error_word) {
   constexpr int HALVES = D / 64;
-  constexpr int TILE_ELEMS = TILE_KV * D;
+  constexpr int TILE_ELEMS = TKV * D;
+  constexpr int NT = TKV / 8;
   extern __shared__ uint8_t attn_shared_raw[];
   uint8_t* aligned = (uint8_t*)(((uintptr_t)attn_shared_raw + 1023) & ~(uintptr_t)1023);
-  bf16* kv_tiles = reinterpret_cast<bf16*>(aligned);                 // STAGES x (K [64][D], V [64][D])
-  bf16* q_tile = kv_tiles + (size_t)STAGES * 2 * TILE_ELEMS;         // [16][D], rows >= group are zeros
-  float* merge = reinterpret_cast<float*>(aligned);                  // after the loop: [4 warps][16][D + 2]
-  __shared__ uint64_t full_bar[STAGES];
+  bf16* kv_tiles = reinterpret_cast<bf16*>(aligned);      // [warp][stage] x (K [TKV][D], V [TKV][D])
+  bf16* q_tile = kv_tiles + (size_t)ATTN_WARPS * STAGES * 2 * TILE_ELEMS;   // [16][D], rows >= group are zeros
+  float* merge = reinterpret_cast<float*>(aligned);       // after the loop: [4 warps][16][D + 2]
+  __shared__ uint64_t full_bar[ATTN_WARPS][STAGES];
   __shared__ int last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    for (int i = 0; i < ATTN_WARPS * STAGES; ++i) mbar_init(&full_bar[0][0] + i, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
@@ -558,45 +567,51 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   const int row = seg_q_start[seg];
   const int position = seg_pos0[seg];
   const int lowest = window > 0 ? max(0, position - window + 1) : 0;
+  // even_split: the request's own context divided over the grid's chunks (at least chunk_arg keys
+  // each), so that one captured launch fits every context length; else chunks of chunk_arg keys
+  int chunk = chunk_arg;
+  if (even_split) chunk = max(chunk_arg, ((position + max_splits) / max_splits + TKV - 1) / TKV * TKV);
   const int first_chunk = lowest / chunk;
   const int splits = position / chunk - first_chunk + 1;
   if (split >= splits) return;
   const int k_begin = max(lowest, (first_chunk + split) * chunk);
   const int k_end = min(position + 1, (first_chunk + split + 1) * chunk);   // exclusive
   const int* table = block_table + (size_t)seg * table_width;
-  const int tile_begin = k_begin / TILE_KV, tile_end = (k_end - 1) / TILE_KV;   // inclusive
+  const int tile_begin = k_begin / TKV, tile_end = (k_end - 1) / TKV;       // inclusive
   const int tiles = tile_end - tile_begin + 1;
+  const int my_tiles = tiles > warp ? (tiles - warp + ATTN_WARPS - 1) / ATTN_WARPS : 0;   // tiles warp, warp + 4, ..
 
-  // warp 0: lane j fetches the j-th page (or the one 64-key box) of a tile, K and V
-  const int boxes = page_size >= TILE_KV ? 1 : TILE_KV >> page_shift;
-  const int box_rows = page_size >= TILE_KV ? TILE_KV : page_size;
-  auto issue = [&](int t) {
-    const int stage = t % STAGES;
-    uint64_t* bar = &full_bar[stage];
+  // lane j fetches the j-th page (or the one TKV-key box) of the warp's n-th tile, K and V
+  const int boxes = page_size >= TKV ? 1 : TKV >> page_shift;
+  const int box_rows = page_size >= TKV ? TKV : page_size;
+  bf16* my_stages = kv_tiles + (size_t)warp * STAGES * 2 * TILE_ELEMS;
+  auto issue = [&](int n) {
+    const int stage = n % STAGES;
+    uint64_t* bar = &full_bar[warp][stage];
     if (lane == 0) mbar_expect_tx(bar, 2u * TILE_ELEMS * 2u);
     __syncwarp();
     if (lane < boxes) {
-      const int key0 = (tile_begin + t) * TILE_KV + lane * box_rows;
+      const int key0 = (tile_begin + warp + n * ATTN_WARPS) * TKV + lane * box_rows;
       const int logical = key0 >> page_shift;
       int page = logical < table_width ? table[logical] : -1;
       int offset = key0 & (page_size - 1);
       if (page < 0) { page = 0; offset = 0; }
       const int y = (page * kv_heads + kv_head) * page_size + offset;
-      bf16* k_dst = kv_tiles + (size_t)stage * 2 * TILE_ELEMS + lane * box_rows * 64;
+      bf16* k_dst = my_stages + (size_t)stage * 2 * TILE_ELEMS + lane * box_rows * 64;
       bf16* v_dst = k_dst + TILE_ELEMS;
 #pragma unroll
       for (int h = 0; h < HALVES; ++h) {
-        tma_load_2d(&k_map, bar, k_dst + h * (TILE_KV * 64), h * 64, y);
-        tma_load_2d(&v_map, bar, v_dst + h * (TILE_KV * 64), h * 64, y);
+        tma_load_2d(&k_map, bar, k_dst + h * (TKV * 64), h * 64, y);
+        tma_load_2d(&v_map, bar, v_dst + h * (TKV * 64), h * 64, y);
       }
     }
   };
   const bool holds_new_key = split == splits - 1;
-  if (warp == 0 && !holds_new_key)
-    for (int t = 0; t < STAGES && t < tiles; ++t) issue(t);
+  if (!holds_new_key)
+    for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
   pdl_wait();
-  if (warp == 0 && holds_new_key)
-    for (int t = 0; t < STAGES && t < tiles; ++t) issue(t);
+  if (holds_new_key)
+    for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
 
   constexpr int CHUNKS = D / 8;
   for (int item = threadIdx.x; item < 16 * CHUNKS; item += ATTN_THREADS) {
@@ -607,9 +622,9 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   }
   cp_async_commit();
 
-  int limit_lo[2] = {k_begin, k_begin}, limit_hi[2];
-  limit_hi[0] = (lane >> 2) < group ? k_end - 1 : -1;          // rows that are no real head see nothing
-  limit_hi[1] = (lane >> 2) + 8 < group ? k_end - 1 : -1;
+  // Rows that are no real head (the group padded to the MMA's 16 rows) have zero queries; their
+  // states are computed like the others and never stored.
+  int limit_lo[2] = {k_begin, k_begin}, limit_hi[2] = {k_end - 1, k_end - 1};
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[D / 8][4];
 #pragma unroll
@@ -624,32 +639,35 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   }
 
   bool gave_up = false;       // after one wait ran out, later waits are skipped: the kernel ends, the host raises
-  for (int t = 0; t < tiles; ++t) {
-    const int stage = t % STAGES;
-    if (!gave_up) gave_up = !mbar_wait(&full_bar[stage], (uint32_t)(t / STAGES) & 1u, error_word, 0x41);
-    gave_up = __any_sync(0xffffffffu, gave_up);                  // warp-uniform: warp 0 issues as one
-    bf16* k_tile = kv_tiles + (size_t)stage * 2 * TILE_ELEMS;
-    const int tile_key0 = (tile_begin + t) * TILE_KV;
-    if (tile_key0 < k_begin || tile_key0 + TILE_KV > k_end) {    // same for the whole CTA
-      for (int item = threadIdx.x; item < TILE_KV * CHUNKS; item += ATTN_THREADS) {
+  for (int n = 0; n < my_tiles; ++n) {
+    const int stage = n % STAGES;
+    if (!gave_up) gave_up = !mbar_wait(&full_bar[warp][stage], (uint32_t)(n / STAGES) & 1u, error_word, 0x41);
+    gave_up = __any_sync(0xffffffffu, gave_up);                  // warp-uniform: the warp issues as one
+    bf16* k_tile = my_stages + (size_t)stage * 2 * TILE_ELEMS;
+    bf16* v_tile = k_tile + TILE_ELEMS;
+    const int key0 = (tile_begin + warp + n * ATTN_WARPS) * TKV;
+    float s[NT][4];
+    if (key0 < k_begin || key0 + TKV > k_end) {
+      // a ragged tile: zero the V rows outside the range, mask the scores
+      for (int item = lane; item < TKV * CHUNKS; item += 32) {
         const int r = item / CHUNKS, c = item - r * CHUNKS;
-        if (tile_key0 + r < k_begin || tile_key0 + r >= k_end)
-          *reinterpret_cast<uint4*>(tile_at<D, true>(k_tile + TILE_ELEMS, r, c)) = make_uint4(0u, 0u, 0u, 0u);
+        if (key0 + r < k_begin || key0 + r >= k_end)
+          *reinterpret_cast<uint4*>(tile_at<D, true, TKV>(v_tile, r, c)) = make_uint4(0u, 0u, 0u, 0u);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // a later bulk copy reuses the stage
-      __syncthreads();
+      __syncwarp();
+      warp_qk<D, NT, true, TKV>(s, q_frag, k_tile, 0, lane);
+      softmax_step<NT, D / 8, true>(s, o, m, l, key0, limit_lo, limit_hi, scale_log2, lane);
+    } else {
+      warp_qk<D, NT, true, TKV>(s, q_frag, k_tile, 0, lane);
+      softmax_step<NT, D / 8, false>(s, o, m, l, key0, limit_lo, limit_hi, scale_log2, lane);
     }
-    const int key0 = tile_key0 + warp * 16;                      // this warp's 16 keys of the tile
-    if (key0 < k_end && key0 + 16 > k_begin) {
-      float s[2][4];
-      warp_qk<D, 2, true>(s, q_frag, k_tile, warp * 16, lane);
-      softmax_step<2, D / 8>(s, o, m, l, key0, limit_lo, limit_hi, scale_log2, lane);
-      warp_pv<D, 2, true>(o, s, k_tile + TILE_ELEMS, warp * 16, lane);
-    }
-    __syncthreads();                                             // every warp is done with this stage
-    if (warp == 0 && t + STAGES < tiles && !gave_up) issue(t + STAGES);
+    warp_pv<D, NT, true, TKV>(o, s, v_tile, 0, lane);
+    __syncwarp();                                                // every lane is done with this stage
+    if (n + STAGES < my_tiles && !gave_up) issue(n + STAGES);
   }
   // No load is in flight here: every issued tile was waited for (or its wait ran out after a second).
+  __syncthreads();                                               // the merge area overlays the stages
   decode_finish<D>(merge, &last_flag, m, l, o, out, scratch, counters, index, row, heads, kv_heads, kv_head, group,
                    split, splits, max_splits);
 }
@@ -745,13 +763,15 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
 
 // Decoded tokens with K/V fetched by the tensor memory accelerator.  Same contract as
 // mlr_attention_decode_mma plus: pool_pages = pages in each pool (for the tensor maps), page_size a
-// power of two >= 8, error_word = host-visible int that receives a code if a wait runs out.
+// power of two >= 8, even_split (chunk is then the smallest chunk; each request divides its context
+// over max_splits chunks), stages = tiles per warp in flight or in use (0 = default), error_word =
+// host-visible int that receives a code if a wait runs out.
 MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                         const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
                                         const int* block_table, int table_width, int rows, int heads, int kv_heads,
                                         int head_dim, int page_size, int pool_pages, int window, float scale,
-                                        int chunk, int max_splits, void* scratch, int* counters, int* error_word,
-                                        cudaStream_t stream) {
+                                        int chunk, int even_split, int max_splits, int stages, void* scratch,
+                                        int* counters, int* error_word, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 || chunk <= 0 ||
       chunk % TILE_KV != 0 || max_splits <= 0 || table_width <= 0 || pool_pages <= 0 || error_word == nullptr)
@@ -765,23 +785,44 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
   if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;           // tile coordinates are 32-bit
   if ((size_t)(2 * 16 * max_splits + 16) > (size_t)ATTN_WARPS * 16 * (head_dim + 2)) return MLR_TOO_LARGE;
   CUtensorMap k_map, v_map;
-  const int box_rows = page_size >= TILE_KV ? TILE_KV : page_size;
+  const int tile_keys = head_dim == 64 && stages < 10 ? 64 : 32;
+  const int box_rows = page_size >= tile_keys ? tile_keys : page_size;
   if (!make_tile_map(&k_map, k_pool, pool_rows, head_dim, box_rows) ||
       !make_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
     return MLR_BAD_SIZE;
   dim3 grid(max_splits, kv_heads, rows);
   int status;
-#define MLR_LAUNCH_DECODE_TMA(D_, S_)                                                                      \
+#define MLR_LAUNCH_DECODE_TMA(D_, T_, S_)                                                                  \
   do {                                                                                                     \
-    const size_t shared = 1024 + (size_t)(16 + 2 * S_ * TILE_KV) * D_ * 2;                                 \
-    static_assert((size_t)ATTN_WARPS * 16 * (D_ + 2) * 4 <= (size_t)2 * S_ * TILE_KV * D_ * 2, "merge area"); \
-    if ((status = set_shared(decode_attention_tma_kernel<D_, S_>, shared)) != MLR_OK) return status;       \
-    launch_kernel(decode_attention_tma_kernel<D_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream,     \
+    const size_t shared = 1024 + (size_t)(16 + 2 * ATTN_WARPS * S_ * T_) * D_ * 2;                         \
+    static_assert((size_t)ATTN_WARPS * 16 * (D_ + 2) * 4 <= (size_t)2 * ATTN_WARPS * S_ * T_ * D_ * 2, "merge area"); \
+    if ((status = set_shared(decode_attention_tma_kernel<D_, T_, S_>, shared)) != MLR_OK) return status;   \
+    launch_kernel(decode_attention_tma_kernel<D_, T_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream, \
                   k_map, v_map, (const bf16*)q, (bf16*)out, decode_seg, seg_q_start, seg_pos0, block_table, \
                   table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk,      \
-                  (float*)scratch, counters, max_splits, error_word);                                      \
+                  even_split, (float*)scratch, counters, max_splits, error_word);                          \
   } while (0)
-  if (head_dim == 64) MLR_LAUNCH_DECODE_TMA(64, 4); else MLR_LAUNCH_DECODE_TMA(128, 3);
+  // stages: tiles each warp keeps in flight or in use; 0 = the default.  Tiles hold 64 keys
+  // (head_dim 64) or 32 keys (head_dim 128): 16 KB of K and V per stage either way.
+  if (stages == 0) stages = 1;       // three CTAs per SM, twelve tiles in flight: measured best at every batch size
+  if (head_dim == 64) {
+    switch (stages) {
+      case 1: MLR_LAUNCH_DECODE_TMA(64, 64, 1); break;
+      case 2: MLR_LAUNCH_DECODE_TMA(64, 64, 2); break;
+      case 3: MLR_LAUNCH_DECODE_TMA(64, 64, 3); break;
+      case 12: MLR_LAUNCH_DECODE_TMA(64, 32, 2); break;    // 32-key tiles, for measurements
+      case 13: MLR_LAUNCH_DECODE_TMA(64, 32, 3); break;
+      case 14: MLR_LAUNCH_DECODE_TMA(64, 32, 4); break;
+      default: return MLR_BAD_SIZE;
+    }
+  } else {
+    switch (stages) {
+      case 1: MLR_LAUNCH_DECODE_TMA(128, 32, 1); break;
+      case 2: MLR_LAUNCH_DECODE_TMA(128, 32, 2); break;
+      case 3: MLR_LAUNCH_DECODE_TMA(128, 32, 3); break;
+      default: return MLR_BAD_SIZE;
+    }
+  }
 #undef MLR_LAUNCH_DECODE_TMA
   return launch_status();
 }

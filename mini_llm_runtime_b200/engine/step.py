@@ -351,10 +351,9 @@ class ModelRunner:
         key = (len(entries), sampling is not None)
         kernels = ops.current()
         captured = self._graphs.get(key)
+        # The context is built at the block table's full width, so every kernel plans its grid
+        # against the cache's capacity, not against this step's contexts.
         width = self.cache.max_pages_per_request
-        longest = width * self.cache.page_size
-        kv_heads = max((g.need.num_kv_heads for g in self.cache.groups), default=1)
-        chunk, splits = kernels.plan_decode(len(entries), kv_heads, longest)
         if captured is None:
             # learn the layout's size with a throw-away packing, then give the graph its own buffer
             probe = self._build_context(entries, requests, sampling, fixed_width=width)
@@ -369,20 +368,15 @@ class ModelRunner:
         ctx = self._build_context(entries, requests, sampling, fixed_width=width,
                                   device_buffer=captured.metadata)
         self._prepare_stagings(captured)
-        previous = (kernels.decode_chunk, kernels.decode_max_splits)
-        kernels.decode_chunk, kernels.decode_max_splits = chunk, splits
-        try:
-            logits, tokens = self._forward(ctx, sampling)          # this step's real result, eagerly
-            torch.cuda.synchronize(self.device)
-            graph = torch.cuda.CUDAGraph()
-            from ..ops import cuda_ops
-            before = cuda_ops.launches
-            with torch.cuda.graph(graph):
-                captured.logits, captured.tokens = self._forward(ctx, sampling)
-            captured.launches = cuda_ops.launches - before
-            captured.graph = graph
-        finally:
-            kernels.decode_chunk, kernels.decode_max_splits = previous
+        logits, tokens = self._forward(ctx, sampling)          # this step's real result, eagerly
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        from ..ops import cuda_ops
+        before = cuda_ops.launches
+        with torch.cuda.graph(graph):
+            captured.logits, captured.tokens = self._forward(ctx, sampling)
+        captured.launches = cuda_ops.launches - before
+        captured.graph = graph
         return logits, tokens
 
     def _prepare_stagings(self, captured: "_CapturedStep") -> None:

@@ -122,6 +122,7 @@ class CudaOps:
         self.use_skinny = True
         self.use_fused_norm = True
         self.use_tma_attention = True
+        self.decode_stages = None      # tiles in flight per CTA of the bulk-copy decode kernel (None: its default)
         self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
         self.decode_max_splits: int | None = None  # None: just enough for the longest context
 
@@ -318,6 +319,8 @@ class CudaOps:
     # Rows up to which the few-rows kernel is chosen.  It accepts up to 64, but measured on the
     # 0.5B layer sizes it loses to the tcgen05 kernel at 64 rows (3.72 against 3.23 ms per step).
     SKINNY_ROWS = 16
+    TMA_MIN_CHUNK = 256               # keys per CTA of the bulk-copy decode attention, at least
+    TMA_RESIDENT_CTAS = 3 * 148       # its CTAs that are resident at once (three per SM)
     SKINNY_WEIGHT_ROWS = 148 * 128   # beyond this the 128-row tensor-memory tiles fill every SM
 
     def _skinny_fits(self, x, weight, swiglu=False) -> bool:
@@ -422,7 +425,16 @@ class CudaOps:
 
     def _decode_attention(self, q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window,
                           mma=False):
-        chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len)
+        page_size = k_pool.shape[2]
+        tma = mma and self.use_tma_attention and page_size >= 8 and page_size & (page_size - 1) == 0
+        even_split = tma and self.decode_chunk is None
+        if even_split:
+            # the kernel divides each request's context over `splits` chunks of at least `chunk` keys
+            chunk = self.TMA_MIN_CHUNK
+            splits = max(1, min(64, self.TMA_RESIDENT_CTAS // max(1, batch.num_decode * num_kv_heads),
+                                -(-batch.max_kv_len // chunk)))
+        else:
+            chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len)
         if self.decode_chunk is not None:
             chunk = self.decode_chunk
             splits = max(1, -(-batch.max_kv_len // chunk))
@@ -432,15 +444,15 @@ class CudaOps:
         space = self._workspace(q.device)
         if need > space["attention_scratch"].numel():
             space["attention_scratch"] = torch.empty(int(need * 1.5), dtype=torch.uint8, device=q.device)
-        page_size = k_pool.shape[2]
-        if mma and self.use_tma_attention and page_size >= 8 and page_size & (page_size - 1) == 0:
+        if tma:
             # pages arrive by the tensor memory accelerator, one bulk copy per page and kv head
             _check(build.load_library("attention_mma").mlr_attention_decode_tma(
                 _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.decode_seg), _ptr(batch.seg_q_start),
                 _ptr(batch.seg_pos0), _ptr(batch.block_table), batch.block_table.shape[1], batch.num_decode,
                 num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
-                ctypes.c_float(scale), chunk, splits, _ptr(space["attention_scratch"]),
-                _ptr(space["attention_counters"]), _ptr(space["error_word"]), _stream()),
+                ctypes.c_float(scale), chunk, int(even_split), splits, int(self.decode_stages or 0),
+                _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _ptr(space["error_word"]),
+                _stream()),
                 "decode attention (TMA)")
             return
         entry = (build.load_library("attention_mma").mlr_attention_decode_mma if mma
