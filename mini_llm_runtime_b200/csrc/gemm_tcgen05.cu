@@ -390,6 +390,9 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
 // Tile shape, split count and ring depth for a product of this shape.
 struct GemmPlan { int bn, tiles, splits, stages, kb_per_split; };
 
+// Overrides for measurements (0 = the planner decides): tile width and ring depth of many-row products.
+static int forced_bn = 0, forced_stages = 0;
+
 static GemmPlan plan_gemm(int M, int N, int K) {
   GemmPlan plan;
   const int total_kb = (K + TILE_K - 1) / TILE_K;
@@ -397,8 +400,10 @@ static GemmPlan plan_gemm(int M, int N, int K) {
     plan.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     plan.tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
   } else {
-    // Wide tiles halve the activation traffic per flop; worth it once they still fill the SMs.
-    plan.bn = (N >= 256 && ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + 255) / 256) >= 148) ? 256 : 128;
+    // Wide tiles cut the operand traffic per flop by a quarter; worth it once they still fill the
+    // SMs and K is long enough for the main loop, not the epilogue, to set the time.
+    plan.bn = (N >= 256 && total_kb > 16 && ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + 255) / 256) >= 148) ? 256 : 128;
+    if (forced_bn == 128 || (forced_bn == 256 && N >= 256)) plan.bn = forced_bn;
     plan.tiles = ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + plan.bn - 1) / plan.bn);
   }
   int splits = 1;
@@ -415,9 +420,13 @@ static GemmPlan plan_gemm(int M, int N, int K) {
   // A ring as deep as the split is long (at most 6 stages) leaves room for several CTAs per SM,
   // so that one CTA's prologue and epilogue overlap another's streaming.
   int stages = plan.kb_per_split < 2 ? 2 : (plan.kb_per_split > 6 ? 6 : plan.kb_per_split);
-  // Many-row products are compute bound and their operands come from L2: three stages are enough
-  // and leave room for two CTAs per SM, one's epilogue under the other's main loop.
-  if (M > 128 && stages > 3) stages = plan.bn == 256 ? 4 : 3;
+  // Many-row products: operands come from L2 and a CTA's epilogue (tensor memory -> registers ->
+  // global) is long, so what counts is that two or three CTAs share an SM and one's epilogue runs
+  // under another's main loop.  Two stages (96 KB at 256 columns, 64 KB at 128) allow that; only
+  // narrow tiles with a long K, which are too few to share SMs anyway, take a deeper ring.
+  // Measured at 2048 rows: 9728x896 with SwiGLU 75 -> 45 us, 37888x3584 628 -> 454 us, 8192^3 877 -> 791 us.
+  if (M > 128) stages = (plan.bn == 128 && total_kb > 16) ? 4 : 2;
+  if (M > 128 && forced_stages >= 2 && forced_stages <= MAX_STAGES) stages = forced_stages;
   const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
   while (stages > 2 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
   plan.stages = stages;
@@ -429,6 +438,8 @@ static GemmPlan plan_gemm(int M, int N, int K) {
 using namespace mlr;
 
 MLR_DEFINE_PDL_SWITCH
+
+MLR_EXPORT void mlr_gemm_tcgen05_tune(int bn, int stages) { forced_bn = bn; forced_stages = stages; }
 
 // Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
 // `splits_out` receives the split count the launcher will use, `tiles_out` the number of tiles.
