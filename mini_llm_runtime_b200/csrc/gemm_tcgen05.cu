@@ -102,6 +102,118 @@ __device__ __forceinline__ void reduce_partials(const float* partials, int split
   }
 }
 
+// The last CTA's reduction in the swapped orientation (tile row = output column n, tile column =
+// token m), for all 128 epilogue threads together: a thread owns four adjacent tile rows (one
+// 16-byte load per split and tile column) and every fourth (eighth with SwiGLU) tile column, so the
+// whole tile is fetched with a quarter of the loads and written in 8-byte pieces.  Splits are added
+// in split order.  `t` = 0..127.
+template <int BN>
+__device__ __forceinline__ void reduce_swapped(const float* partials, const GemmParams& p, int t, int a_row0,
+                                               int b_row0) {
+  const int rg = t & 31, cg = t >> 5;
+  const int n0 = a_row0 + 4 * rg;
+  if (n0 >= p.N) return;
+  float bias[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) bias[j] = (p.bias != nullptr && n0 + j < p.N) ? to_float(p.bias[n0 + j]) : 0.f;
+  const bool wide = (p.N & 3) == 0;                   // then n0 + 3 < N and the stores are aligned
+  constexpr int CB = 4;                                // tile columns in flight per thread
+  for (int c = cg; c < BN; c += 4 * CB) {
+    float4 acc[CB];
+#pragma unroll
+    for (int j = 0; j < CB; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < p.splits; s0 += 4) {
+      float4 part[4][CB];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+          const int col = c + 4 * j;
+          part[i][j] = (s0 + i < p.splits && col < BN && b_row0 + col < p.M)
+                           ? __ldcg(reinterpret_cast<const float4*>(partials + ((size_t)(s0 + i) * BN + col) * TILE_ROWS + 4 * rg))
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+          acc[j].x += part[i][j].x; acc[j].y += part[i][j].y; acc[j].z += part[i][j].z; acc[j].w += part[i][j].w;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CB; ++j) {
+      const int col = c + 4 * j, m = b_row0 + col;
+      if (col >= BN || m >= p.M) continue;
+      const float v[4] = {acc[j].x + bias[0], acc[j].y + bias[1], acc[j].z + bias[2], acc[j].w + bias[3]};
+      if (p.out_f32) {
+        float* dst = (float*)p.out + (size_t)m * p.N + n0;
+        if (wide) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        else for (int e = 0; e < 4; ++e) if (n0 + e < p.N) dst[e] = v[e];
+      } else {
+        bf16* dst = (bf16*)p.out + (size_t)m * p.N + n0;
+        if (wide) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+          *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        } else {
+          for (int e = 0; e < 4; ++e) if (n0 + e < p.N) dst[e] = __float2bfloat16_rn(v[e]);
+        }
+      }
+    }
+  }
+}
+
+// The same with the fused SwiGLU: tile rows 0..63 are gate rows, 64..127 the up rows of the same
+// 64 outputs; a thread owns four gate rows, their up rows, and every eighth tile column.
+template <int BN>
+__device__ __forceinline__ void reduce_swapped_swiglu(const float* partials, const GemmParams& p, int t, int tile_x,
+                                                      int b_row0) {
+  const int rg = t & 15, cg = t >> 4;
+  const int half = p.N >> 1;
+  const int n0 = tile_x * 64 + 4 * rg;
+  if (n0 >= half) return;
+  const bool wide = (half & 3) == 0;
+  constexpr int CB = 2;
+  for (int c = cg; c < BN; c += 8 * CB) {
+    float4 gate[CB], up[CB];
+#pragma unroll
+    for (int j = 0; j < CB; ++j) gate[j] = up[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < p.splits; s0 += 4) {
+      float4 pg[4][CB], pu[4][CB];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+          const int col = c + 8 * j;
+          const bool live = s0 + i < p.splits && col < BN && b_row0 + col < p.M;
+          const float* base = partials + ((size_t)(s0 + i) * BN + col) * TILE_ROWS + 4 * rg;
+          pg[i][j] = live ? __ldcg(reinterpret_cast<const float4*>(base)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          pu[i][j] = live ? __ldcg(reinterpret_cast<const float4*>(base + 64)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+          gate[j].x += pg[i][j].x; gate[j].y += pg[i][j].y; gate[j].z += pg[i][j].z; gate[j].w += pg[i][j].w;
+          up[j].x += pu[i][j].x; up[j].y += pu[i][j].y; up[j].z += pu[i][j].z; up[j].w += pu[i][j].w;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CB; ++j) {
+      const int col = c + 8 * j, m = b_row0 + col;
+      if (col >= BN || m >= p.M) continue;
+      const float v[4] = {silu_times(gate[j].x, up[j].x), silu_times(gate[j].y, up[j].y),
+                          silu_times(gate[j].z, up[j].z), silu_times(gate[j].w, up[j].w)};
+      bf16* dst = (bf16*)p.out + (size_t)m * half + n0;
+      if (wide) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      } else {
+        for (int e = 0; e < 4; ++e) if (n0 + e < half) dst[e] = __float2bfloat16_rn(v[e]);
+      }
+    }
+  }
+}
+
 // SWAP = true:  A (128 rows) = weights, B (BN rows) = activations; tile row = output column n.
 // SWAP = false: A (128 rows) = activations, B (BN rows) = weights; tile row = output row m.
 // SWIGLU: the weight rows come in blocks of 128 = 64 gate rows followed by the 64 up rows of the
@@ -228,7 +340,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bf16* out_bf16 = (bf16*)p.out;
     float* out_f32 = (float*)p.out;
 
-    if (SWIGLU && SWAP) {
+    if (SWAP && reduce) {
+      if (SWIGLU) reduce_swapped_swiglu<BN>(partials, p, row, blockIdx.x, b_row0);
+      else reduce_swapped<BN>(partials, p, row, a_row0, b_row0);
+    } else if (SWIGLU && SWAP) {
       // rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same 64 outputs.
       // Without split-K the halves meet through shared memory (the stage ring is idle by now).
       float* exchange = reinterpret_cast<float*>(tiles);            // [BN][128]
@@ -408,12 +523,25 @@ static GemmPlan plan_gemm(int M, int N, int K) {
   }
   int splits = 1;
   if (M <= 128) {
-    // Few tiles cannot keep 148 SMs streaming weights: cut K until about one CTA per SM exists,
-    // but leave every split at least two k blocks and the final reduction at most 16 partials.
-    splits = (148 + plan.tiles - 1) / plan.tiles;
-    if (splits > total_kb / 2) splits = total_kb / 2;
-    if (splits > 16) splits = 16;
-    if (splits < 1) splits = 1;
+    // Few tiles cannot keep 148 SMs streaming weights, so K is cut; but the CTA that arrives last
+    // for a tile re-reads every split's partial tile (splits x bn x 512 bytes), which soon costs
+    // more than the streaming saves when there are many token rows.  Estimate both and take the
+    // cheapest count (microseconds; an SM streams about 120 GB/s, all of them about 6 TB/s; two
+    // CTAs share an SM; a reduction costs 1.5 us of fences and round trips before its first byte).
+    const double sm_bytes_per_us = 120e3, all_bytes_per_us = 6.0e6;
+    const double tile_bytes = (double)(TILE_ROWS + plan.bn) * K * 2;
+    const int most = total_kb / 2 < 16 ? (total_kb / 2 < 1 ? 1 : total_kb / 2) : 16;
+    double best = 1e30;
+    for (int candidate = 1; candidate <= most; ++candidate) {
+      const double ctas = (double)plan.tiles * candidate;
+      const double resident = ctas < 296 ? ctas : 296;
+      const double waves = ctas <= 296 ? 1.0 : ctas / 296.0;
+      double rate = all_bytes_per_us / resident;
+      if (rate > sm_bytes_per_us) rate = sm_bytes_per_us;
+      double cost = waves * tile_bytes / candidate / rate;
+      if (candidate > 1) cost += 1.5 + (double)candidate * plan.bn * 512.0 / sm_bytes_per_us;
+      if (cost < best) { best = cost; splits = candidate; }
+    }
   }
   plan.kb_per_split = (total_kb + splits - 1) / splits;
   plan.splits = (total_kb + plan.kb_per_split - 1) / plan.kb_per_split;   // no empty split
