@@ -554,6 +554,13 @@ static GemmPlan plan_gemm(int M, int N, int K) {
   // narrow tiles with a long K, which are too few to share SMs anyway, take a deeper ring.
   // Measured at 2048 rows: 9728x896 with SwiGLU 75 -> 45 us, 37888x3584 628 -> 454 us, 8192^3 877 -> 791 us.
   if (M > 128) stages = (plan.bn == 128 && total_kb > 16) ? 4 : 2;
+  // Few rows but more CTAs than SMs (the head's matrix): keep the ring within 110 KB so that two
+  // CTAs share an SM and one's epilogue runs while the other streams (measured on 151936 x 896 at
+  // 64 rows: 86 us with one CTA per SM, 64 us with two).
+  const size_t few_rows_stage = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
+  if (M <= 128 && forced_stages >= 2) stages = forced_stages < stages ? forced_stages : stages;
+  else if (M <= 128 && plan.tiles * plan.splits > 148)
+    while (stages > 2 && stages * few_rows_stage > 110 * 1024) --stages;
   if (M > 128 && forced_stages >= 2 && forced_stages <= MAX_STAGES) stages = forced_stages;
   const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
   while (stages > 2 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
