@@ -523,6 +523,13 @@ decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_poo
 // are overwritten with zeros in shared memory before use (only a chunk's first and last tile can
 // hold such keys), so that nothing a request does not own reaches its result.
 //
+// Fused position encoding (qkv != null): the kernel takes the projection's raw output
+// [tokens, (heads + 2 kv_heads) * D] instead of rotated queries.  Every CTA rotates its group's
+// queries while it fills the Q tile (rotate-half pairs, angle = position * inv_freq[i], float32,
+// exactly as the stand-alone kernel does); the CTA that holds the request's newest position rotates
+// the new key, and puts it and the new value both into the cache pages (if write_kv) and into its
+// own tile in shared memory, over the stale row the bulk copy delivered.  No kernel in between.
+//
 // With even_split every request divides its own context evenly over the grid's max_splits chunks
 // (the host fixes only their number), so a launch captured in a CUDA graph adapts to the contexts
 // of each replay.
@@ -538,7 +545,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
                             const int* __restrict__ block_table, int table_width, int heads, int kv_heads,
                             int page_size, int page_shift, int window, float scale_log2, int chunk_arg,
                             int even_split, float* __restrict__ scratch, int* __restrict__ counters,
-                            int max_splits, int* error_word) {
+                            int max_splits, int* error_word, const bf16* qkv, const float* __restrict__ inv_freq,
+                            const long long* __restrict__ slots, bf16* k_pool_w, bf16* v_pool_w, int write_kv) {
   constexpr int HALVES = D / 64;
   constexpr int TILE_ELEMS = TKV * D;
   constexpr int NT = TKV / 8;
@@ -607,20 +615,44 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
   };
   const bool holds_new_key = split == splits - 1;
-  if (!holds_new_key)
+  const bool fused = qkv != nullptr;
+  const bool inject = fused && write_kv != 0 && holds_new_key;   // this CTA stores the step's key and value
+  // The newest key's row is stale in the pool until this step stores it: a CTA that reads it from
+  // the pool waits for the previous kernel first; one that overwrites it in shared memory need not.
+  const bool early = !holds_new_key || inject;
+  if (early)
     for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
   pdl_wait();
-  if (holds_new_key)
+  if (!early)
     for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
 
   constexpr int CHUNKS = D / 8;
-  for (int item = threadIdx.x; item < 16 * CHUNKS; item += ATTN_THREADS) {
-    const int g = item / CHUNKS, c = item - g * CHUNKS;
-    const bool valid = g < group;
-    const bf16* src = valid ? q + ((size_t)row * heads + kv_head * group + g) * D + c * 8 : q;
-    cp_async_16(tile_at<D>(q_tile, g, c), src, valid);
+  constexpr int HALF = D / 2;
+  const size_t qkv_width = (size_t)(heads + 2 * kv_heads) * D;
+  if (fused) {
+    // thread -> pair index i (the same for all its items, as 128 % HALF == 0) and rows g0, g0 + 128/HALF, ..
+    const int i = threadIdx.x % HALF;
+    float sine, cosine;
+    sincosf((float)position * inv_freq[i], &sine, &cosine);
+    const bf16* q_row = qkv + (size_t)row * qkv_width + (size_t)kv_head * group * D;
+    for (int g = threadIdx.x / HALF; g < 16; g += ATTN_THREADS / HALF) {
+      float y1 = 0.f, y2 = 0.f;
+      if (g < group) {
+        rotate_pair(__bfloat162float(q_row[g * D + i]), __bfloat162float(q_row[g * D + i + HALF]), sine, cosine, &y1, &y2);
+      }
+      tile_at<D>(q_tile, g, i >> 3)[i & 7] = __float2bfloat16_rn(y1);
+      tile_at<D>(q_tile, g, (i + HALF) >> 3)[(i + HALF) & 7] = __float2bfloat16_rn(y2);
+    }
+  } else {
+    for (int item = threadIdx.x; item < 16 * CHUNKS; item += ATTN_THREADS) {
+      const int g = item / CHUNKS, c = item - g * CHUNKS;
+      const bool valid = g < group;
+      const bf16* src = valid ? q + ((size_t)row * heads + kv_head * group + g) * D + c * 8 : q;
+      cp_async_16(tile_at<D>(q_tile, g, c), src, valid);
+    }
   }
   cp_async_commit();
+  const int newest_tile = position / TKV - tile_begin;          // among this chunk's tiles, if it holds it
 
   // Rows that are no real head (the group padded to the MMA's 16 rows) have zero queries; their
   // states are computed like the others and never stored.
@@ -646,6 +678,32 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     bf16* k_tile = my_stages + (size_t)stage * 2 * TILE_ELEMS;
     bf16* v_tile = k_tile + TILE_ELEMS;
     const int key0 = (tile_begin + warp + n * ATTN_WARPS) * TKV;
+    if (inject && warp + n * ATTN_WARPS == newest_tile) {
+      // the step's own key and value: into the pages and over the stale row of this tile
+      const int r = position - key0;
+      const long long slot = slots[row];
+      const long long page = slot / page_size;
+      const size_t at = (((size_t)page * kv_heads + kv_head) * page_size + (size_t)(slot - page * page_size)) * D;
+      const bf16* k_src = qkv + (size_t)row * qkv_width + (size_t)(heads + kv_head) * D;
+      const bf16* v_src = k_src + (size_t)kv_heads * D;
+      for (int i = lane; i < HALF; i += 32) {
+        float sine, cosine;
+        sincosf((float)position * inv_freq[i], &sine, &cosine);
+        float r1, r2;
+        rotate_pair(__bfloat162float(k_src[i]), __bfloat162float(k_src[i + HALF]), sine, cosine, &r1, &r2);
+        const bf16 y1 = __float2bfloat16_rn(r1), y2 = __float2bfloat16_rn(r2);
+        tile_at<D, true, TKV>(k_tile, r, i >> 3)[i & 7] = y1;
+        tile_at<D, true, TKV>(k_tile, r, (i + HALF) >> 3)[(i + HALF) & 7] = y2;
+        if (slot >= 0) { k_pool_w[at + i] = y1; k_pool_w[at + i + HALF] = y2; }
+      }
+      for (int i = lane; i < D; i += 32) {
+        const bf16 v = v_src[i];
+        tile_at<D, true, TKV>(v_tile, r, i >> 3)[i & 7] = v;
+        if (slot >= 0) v_pool_w[at + i] = v;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+    }
     float s[NT][4];
     if (key0 < k_begin || key0 + TKV > k_end) {
       // a ragged tile: zero the V rows outside the range, mask the scores
@@ -765,19 +823,23 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
 // mlr_attention_decode_mma plus: pool_pages = pages in each pool (for the tensor maps), page_size a
 // power of two >= 8, even_split (chunk is then the smallest chunk; each request divides its context
 // over max_splits chunks), stages = tiles per warp in flight or in use (0 = default), error_word =
-// host-visible int that receives a code if a wait runs out.
+// host-visible int that receives a code if a wait runs out.  qkv != null: the fused position
+// encoding described at the kernel (q is then unused; inv_freq [head_dim/2] float32; slots [tokens]
+// int64, page * page_size + offset of each token's cache slot; write_kv = 0 leaves the pages alone).
 MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                         const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
                                         const int* block_table, int table_width, int rows, int heads, int kv_heads,
                                         int head_dim, int page_size, int pool_pages, int window, float scale,
                                         int chunk, int even_split, int max_splits, int stages, void* scratch,
-                                        int* counters, int* error_word, cudaStream_t stream) {
+                                        int* counters, int* error_word, const void* qkv, const float* inv_freq,
+                                        const long long* slots, int write_kv, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 || chunk <= 0 ||
       chunk % TILE_KV != 0 || max_splits <= 0 || table_width <= 0 || pool_pages <= 0 || error_word == nullptr)
     return MLR_BAD_SIZE;
   if (heads / kv_heads > 16 || rows > 65535 || kv_heads > 65535) return MLR_TOO_LARGE;
   if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
+  if (qkv != nullptr && (inv_freq == nullptr || slots == nullptr)) return MLR_BAD_SIZE;
   const int page_shift = shift_of(page_size);
   if (page_shift < 3) return MLR_BAD_SIZE;
   if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15)) return MLR_BAD_ALIGNMENT;
@@ -800,7 +862,8 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
     launch_kernel(decode_attention_tma_kernel<D_, T_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream, \
                   k_map, v_map, (const bf16*)q, (bf16*)out, decode_seg, seg_q_start, seg_pos0, block_table, \
                   table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk,      \
-                  even_split, (float*)scratch, counters, max_splits, error_word);                          \
+                  even_split, (float*)scratch, counters, max_splits, error_word, (const bf16*)qkv, inv_freq, \
+                  slots, (bf16*)const_cast<void*>(k_pool), (bf16*)const_cast<void*>(v_pool), write_kv);    \
   } while (0)
   // stages: tiles each warp keeps in flight or in use; 0 = the default.  Tiles hold 64 keys
   // (head_dim 64) or 32 keys (head_dim 128): 16 KB of K and V per stage either way.

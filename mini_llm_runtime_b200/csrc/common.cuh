@@ -91,6 +91,13 @@ inline bool& pdl_enabled() {
   return enabled;
 }
 
+// One rotate-half pair: (x1, x2) turned by the angle whose sine and cosine are given.  Written with
+// explicit roundings so that every kernel that rotates gets the same bits.
+__device__ __forceinline__ void rotate_pair(float x1, float x2, float sine, float cosine, float* y1, float* y2) {
+  *y1 = __fsub_rn(__fmul_rn(x1, cosine), __fmul_rn(x2, sine));
+  *y2 = __fadd_rn(__fmul_rn(x2, cosine), __fmul_rn(x1, sine));
+}
+
 template <typename... KernelArgs, typename... Args>
 inline void launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
                           Args&&... args) {

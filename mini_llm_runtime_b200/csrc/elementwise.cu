@@ -128,8 +128,8 @@ __global__ void rope_kv_write_kernel(const T* qkv, const int* __restrict__ posit
     sincosf(position * inv_freq[i], &sine, &cosine);
     const float x1 = to_float(row[head * head_dim + i]);
     const float x2 = to_float(row[head * head_dim + i + half]);
-    const float y1 = x1 * cosine - x2 * sine;
-    const float y2 = x2 * cosine + x1 * sine;
+    float y1, y2;
+    rotate_pair(x1, x2, sine, cosine, &y1, &y2);
     if (head < heads) {
       T* dst = q_out + ((size_t)token * heads + head) * head_dim;
       dst[i] = from_float<T>(y1);

@@ -122,6 +122,7 @@ class CudaOps:
         self.use_skinny = True
         self.use_fused_norm = True
         self.use_tma_attention = True
+        self.use_fused_rope = True
         self.decode_stages = None      # tiles in flight per CTA of the bulk-copy decode kernel (None: its default)
         self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
         self.decode_max_splits: int | None = None  # None: just enough for the longest context
@@ -368,6 +369,42 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ attention
+    def rope_paged_attention(self, qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                             slots: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                             batch: "AttentionBatch", num_heads: int, num_kv_heads: int, head_dim: int,
+                             scale: float, window: int | None = None, write_kv: bool = True) -> torch.Tensor:
+        """``rope_kv_write`` followed by ``paged_attention``.  A step of decoded tokens only, in
+        bfloat16 with a head size and page size the bulk-copy decode kernel takes, runs as that one
+        kernel: it rotates q while loading it and stores the new key and value itself."""
+        page_size = k_pool.shape[2] if k_pool.dim() == 4 else 0
+        group = num_heads // max(1, num_kv_heads)
+        fused = (self.use_fused_rope and self.use_mma_attention and self.use_tma_attention
+                 and self.decode_chunk is None
+                 and qkv.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 16
+                 and batch.decode_seg is not None and 0 < batch.num_decode == batch.num_segments
+                 and page_size >= 8 and page_size & (page_size - 1) == 0
+                 and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS)
+        if not fused:
+            q = self.rope_kv_write(qkv, positions, inv_freq, slots, k_pool, v_pool, num_heads, num_kv_heads,
+                                   head_dim, write_kv)
+            return self.paged_attention(q, k_pool, v_pool, batch, num_heads, num_kv_heads, head_dim, scale, window)
+        _need(qkv, "qkv", dims=2)
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        _need(slots, "slots", torch.int64, 1)
+        _need(k_pool, "k_pool", qkv.dtype, 4)
+        _need(v_pool, "v_pool", qkv.dtype, 4)
+        tokens = qkv.shape[0]
+        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+            raise KernelError("qkv width does not match the head counts")
+        if slots.shape[0] != tokens or inv_freq.shape[0] != head_dim // 2 or batch.num_decode != tokens:
+            raise KernelError("one slot per token, head_dim/2 frequencies, one decoded token per segment")
+        if k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim or v_pool.shape != k_pool.shape:
+            raise KernelError("page pools do not match the head sizes")
+        out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        self._decode_attention(None, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window,
+                               mma=True, rope=(qkv, inv_freq, slots, write_kv))
+        return out
+
     def paged_attention(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                         batch: AttentionBatch, num_heads: int, num_kv_heads: int, head_dim: int,
                         scale: float, window: int | None) -> torch.Tensor:
@@ -424,7 +461,7 @@ class CudaOps:
         return chunk, max(1, -(-longest // chunk))
 
     def _decode_attention(self, q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window,
-                          mma=False):
+                          mma=False, rope=None):
         page_size = k_pool.shape[2]
         tma = mma and self.use_tma_attention and page_size >= 8 and page_size & (page_size - 1) == 0
         even_split = tma and self.decode_chunk is None
@@ -441,9 +478,12 @@ class CudaOps:
         if self.decode_max_splits is not None:
             splits = max(splits, self.decode_max_splits)
         need = batch.num_decode * num_heads * splits * (head_dim + 2) * 4    # float32 partial states
-        space = self._workspace(q.device)
+        space = self._workspace(out.device)
         if need > space["attention_scratch"].numel():
-            space["attention_scratch"] = torch.empty(int(need * 1.5), dtype=torch.uint8, device=q.device)
+            space["attention_scratch"] = torch.empty(int(need * 1.5), dtype=torch.uint8, device=out.device)
+        if rope is not None and not tma:
+            raise KernelError("the fused position encoding needs the bulk-copy decode kernel")
+        qkv, inv_freq, slots, write_kv = rope if rope is not None else (None, None, None, False)
         if tma:
             # pages arrive by the tensor memory accelerator, one bulk copy per page and kv head
             _check(build.load_library("attention_mma").mlr_attention_decode_tma(
@@ -452,7 +492,7 @@ class CudaOps:
                 num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
                 ctypes.c_float(scale), chunk, int(even_split), splits, int(self.decode_stages or 0),
                 _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _ptr(space["error_word"]),
-                _stream()),
+                _ptr(qkv), _ptr(inv_freq), _ptr(slots), int(bool(write_kv)), _stream()),
                 "decode attention (TMA)")
             return
         entry = (build.load_library("attention_mma").mlr_attention_decode_mma if mma

@@ -83,10 +83,8 @@ class GQAAttention(Mixer):
         of the folded norm.  ``residual``: the output product adds into it in place."""
         k = ops.current()
         qkv = k.linear(x, self.w_qkv, self.b_qkv, rms_eps=self.input_norm_eps if raw_input else None)
-        q = self.position.rotate_and_store(qkv, ctx, view, self.num_heads, self.num_kv_heads,
-                                           self.head_dim, writes_cache)
-        mixed = k.paged_attention(q, view.k_pool, view.v_pool, view.batch, self.num_heads,
-                                  self.num_kv_heads, self.head_dim, self.scale, self.window)
+        mixed = self.position.attend(qkv, ctx, view, self.num_heads, self.num_kv_heads, self.head_dim,
+                                     self.scale, self.window, writes_cache)
         return k.linear(mixed, self.w_o, self.b_o, residual=residual)
 
 

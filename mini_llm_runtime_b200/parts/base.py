@@ -121,6 +121,15 @@ class PositionEncoding(Part):
         store k and v into the cache view's pages, return q [rows, heads*head_dim]."""
         raise NotImplementedError
 
+    def attend(self, qkv: torch.Tensor, ctx, view, num_heads: int, num_kv_heads: int, head_dim: int,
+               scale: float, window: int | None, write_kv: bool) -> torch.Tensor:
+        """``rotate_and_store`` followed by attention over the cache, [rows, heads*head_dim].
+        An encoding whose kernels can do both at once overrides this; the default is the two steps."""
+        from .. import ops
+        q = self.rotate_and_store(qkv, ctx, view, num_heads, num_kv_heads, head_dim, write_kv)
+        return ops.current().paged_attention(q, view.k_pool, view.v_pool, view.batch, num_heads, num_kv_heads,
+                                             head_dim, scale, window)
+
 
 class Mixer(Part):
     category = "mixer"

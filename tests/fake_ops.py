@@ -86,6 +86,12 @@ class FakeOps:
                 v_pool[page, :, offset, :] = v[t].to(v_pool.dtype)
         return q.reshape(tokens, num_heads * head_dim).to(qkv.dtype)
 
+    def rope_paged_attention(self, qkv, positions, inv_freq, slots, k_pool, v_pool, batch, num_heads, num_kv_heads,
+                             head_dim, scale, window=None, write_kv=True):
+        q = self.rope_kv_write(qkv, positions, inv_freq, slots, k_pool, v_pool, num_heads, num_kv_heads, head_dim,
+                               write_kv)
+        return self.paged_attention(q, k_pool, v_pool, batch, num_heads, num_kv_heads, head_dim, scale, window)
+
     def paged_attention(self, q, k_pool, v_pool, batch, num_heads, num_kv_heads, head_dim, scale, window):
         page_size = k_pool.shape[2]
         group = num_heads // num_kv_heads

@@ -15,6 +15,7 @@ import plain_qwen2 as plain
 from fake_ops import FakeOps
 from harness import assert_close
 from mini_llm_runtime_b200 import ops
+from mini_llm_runtime_b200.ops import cuda_ops
 from mini_llm_runtime_b200.ops.cuda_ops import AttentionBatch
 
 pytestmark = pytest.mark.gpu
@@ -437,6 +438,48 @@ def test_decode_attention_split_kv(heads, kv_heads, head_dim, page, chunk):
     assert_close(simt, want, torch.bfloat16, "split-KV kernel on the CUDA cores")
     both, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
     assert_close(both, generic, torch.bfloat16, "tensor-core kernels against the generic kernel")
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (3, 1, 128, 8), (8, 8, 64, 64), (8, 2, 128, 32), (5, 1, 64, 256)])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_decode_attention_with_fused_position_encoding(heads, kv_heads, head_dim, page, write_kv):
+    """A step of decoded tokens only: rotation of q and k, the cache write and attention in one
+    kernel, against the two kernels it replaces.  Rotated values are rounded the same way in both,
+    so outputs and pages must agree to the bit.  Contexts sit on tile, page and chunk edges."""
+    contexts = [0, 1, 31, 32, 63, 64, 65, 127, 255, 256, 511, 512, 513, 700, 1500, 2047]
+    segments = [(c, 1) for c in contexts]
+    q, k_pool, v_pool, batch, table = make_attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, segments, 31)
+    k_pool, v_pool = torch.nan_to_num(k_pool, nan=3.0), torch.nan_to_num(v_pool, nan=-3.0)   # pages are compared whole
+    qkv = rnd((len(contexts), (heads + 2 * kv_heads) * head_dim), torch.bfloat16, 32)
+    positions = torch.tensor(contexts, dtype=torch.int32)
+    slots = torch.tensor([int(table[s, c // page]) * page + c % page for s, c in enumerate(contexts)], dtype=torch.int64)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    results = {}
+    for fused in (False, True):
+        k_dev, v_dev = k_pool.clone().to(DEVICE), v_pool.clone().to(DEVICE)
+        cuda().use_fused_rope = fused
+        try:
+            for window in (None, 100):
+                before = cuda_ops.launches
+                out = cuda().rope_paged_attention(qkv.to(DEVICE), positions.to(DEVICE), inv_freq.to(DEVICE),
+                                                  slots.to(DEVICE), k_dev, v_dev, batch(DEVICE), heads, kv_heads,
+                                                  head_dim, head_dim ** -0.5, window, write_kv)
+                assert cuda_ops.launches - before == (1 if fused else 2)
+                results[fused, window] = out
+        finally:
+            cuda().use_fused_rope = True
+        results[fused, "k"], results[fused, "v"] = k_dev, v_dev
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    for key in (None, 100, "k", "v"):
+        assert torch.equal(results[True, key], results[False, key]), f"fused and separate kernels differ in {key}"
+    if not write_kv:
+        assert torch.equal(results[True, "k"].cpu(), k_pool) and torch.equal(results[True, "v"].cpu(), v_pool)
+    # and against the plain stand-in, which rotates and attends in float32
+    k_ref, v_ref = k_pool.clone().float(), v_pool.clone().float()
+    want = FAKE.rope_paged_attention(qkv.float(), positions, inv_freq, slots, k_ref, v_ref, batch("cpu"), heads, kv_heads,
+                                     head_dim, head_dim ** -0.5, None, write_kv)
+    assert_close(results[True, None], want, torch.bfloat16, "fused position encoding and attention")
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (4, 1, 128, 8), (6, 6, 64, 32), (16, 1, 128, 16)])
