@@ -68,6 +68,69 @@ __global__ void rms_norm_kernel(T* residual, const T* delta,
   }
 }
 
+// bfloat16 rows whose width is a multiple of 8 (at most 256 * VECS): one warp per row, each lane
+// keeps its 16-byte pieces of the row in registers, so global memory is read once with wide loads
+// and no block-level reduction is needed.  Same arithmetic as above: float32 add rounded once and
+// stored back, float32 sum of squares, weight * (value * scale).
+template <typename W, int VECS>
+__global__ void __launch_bounds__(128)
+rms_norm_rows_kernel(bf16* residual, const bf16* delta, const W* __restrict__ weight, bf16* __restrict__ out,
+                     int rows, int width, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int pieces = width >> 3;
+  uint4* stream = reinterpret_cast<uint4*>(residual + (size_t)row * width);
+  const uint4* added = delta != nullptr ? reinterpret_cast<const uint4*>(delta + (size_t)row * width) : nullptr;
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * width);
+  uint4 raw[VECS], extra[VECS];
+#pragma unroll
+  for (int j = 0; j < VECS; ++j) {
+    const int piece = lane + 32 * j;
+    raw[j] = piece < pieces ? stream[piece] : make_uint4(0u, 0u, 0u, 0u);
+    if (added != nullptr) extra[j] = piece < pieces ? added[piece] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float partial = 0.f;
+#pragma unroll
+  for (int j = 0; j < VECS; ++j) {
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw[j]);
+    if (added != nullptr) {
+      const __nv_bfloat162* more = reinterpret_cast<const __nv_bfloat162*>(&extra[j]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(pairs[e]), b = __bfloat1622float2(more[e]);
+        pairs[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+      }
+      if (lane + 32 * j < pieces) stream[lane + 32 * j] = raw[j];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(pairs[e]);
+      partial += a.x * a.x + a.y * a.y;
+    }
+  }
+  const float scale = rsqrtf(warp_sum(partial) / (float)width + eps);
+#pragma unroll
+  for (int j = 0; j < VECS; ++j) {
+    const int piece = lane + 32 * j;
+    if (piece >= pieces) continue;
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+    float w[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[e] = weight != nullptr ? to_float(weight[piece * 8 + e]) : 1.f;
+    uint4 packed;
+    __nv_bfloat162* result = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(pairs[e]);
+      result[e] = __floats2bfloat162_rn(w[2 * e] * (a.x * scale), w[2 * e + 1] * (a.y * scale));
+    }
+    dst[piece] = packed;
+  }
+}
+
 // ---------------------------------------------------------------- in-place add
 template <typename T>
 __global__ void add_inplace_kernel(T* target, const T* delta, size_t total) {
@@ -122,23 +185,53 @@ __global__ void rope_kv_write_kernel(const T* qkv, const int* __restrict__ posit
   const bool store = write_kv != 0 && slot >= 0;
 
   const int rotated_heads = heads + kv_heads;
-  for (int item = threadIdx.x; item < rotated_heads * half; item += blockDim.x) {
-    const int head = item / half, i = item - head * half;
-    float sine, cosine;
-    sincosf(position * inv_freq[i], &sine, &cosine);
-    const float x1 = to_float(row[head * head_dim + i]);
-    const float x2 = to_float(row[head * head_dim + i + half]);
-    float y1, y2;
-    rotate_pair(x1, x2, sine, cosine, &y1, &y2);
-    if (head < heads) {
-      T* dst = q_out + ((size_t)token * heads + head) * head_dim;
-      dst[i] = from_float<T>(y1);
-      dst[i + half] = from_float<T>(y2);
-    } else if (store) {
-      const int kv_head = head - heads;
-      T* dst = k_pool + (((size_t)page * kv_heads + kv_head) * page_size + offset) * head_dim;
-      dst[i] = from_float<T>(y1);
-      dst[i + half] = from_float<T>(y2);
+  if ((half & 1) == 0) {
+    // two adjacent pair indices per item (4-byte accesses for 16-bit types); the angle depends on
+    // the index only, so a thread that keeps its index across items evaluates sine and cosine once
+    const int half_pairs = half >> 1;
+    int cached = -1;
+    float sine[2] = {0.f, 0.f}, cosine[2] = {1.f, 1.f};
+    for (int item = threadIdx.x; item < rotated_heads * half_pairs; item += blockDim.x) {
+      const int head = item / half_pairs, i = (item - head * half_pairs) * 2;
+      if (i != cached) {
+        sincosf(position * inv_freq[i], &sine[0], &cosine[0]);
+        sincosf(position * inv_freq[i + 1], &sine[1], &cosine[1]);
+        cached = i;
+      }
+      const T* src = row + head * head_dim + i;
+      float y1[2], y2[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) rotate_pair(to_float(src[e]), to_float(src[e + half]), sine[e], cosine[e], &y1[e], &y2[e]);
+      T* dst = nullptr;
+      if (head < heads) dst = q_out + ((size_t)token * heads + head) * head_dim;
+      else if (store) dst = k_pool + (((size_t)page * kv_heads + (head - heads)) * page_size + offset) * head_dim;
+      if (dst != nullptr) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          dst[i + e] = from_float<T>(y1[e]);
+          dst[i + e + half] = from_float<T>(y2[e]);
+        }
+      }
+    }
+  } else {
+    for (int item = threadIdx.x; item < rotated_heads * half; item += blockDim.x) {
+      const int head = item / half, i = item - head * half;
+      float sine, cosine;
+      sincosf(position * inv_freq[i], &sine, &cosine);
+      const float x1 = to_float(row[head * head_dim + i]);
+      const float x2 = to_float(row[head * head_dim + i + half]);
+      float y1, y2;
+      rotate_pair(x1, x2, sine, cosine, &y1, &y2);
+      if (head < heads) {
+        T* dst = q_out + ((size_t)token * heads + head) * head_dim;
+        dst[i] = from_float<T>(y1);
+        dst[i + half] = from_float<T>(y2);
+      } else if (store) {
+        const int kv_head = head - heads;
+        T* dst = k_pool + (((size_t)page * kv_heads + kv_head) * page_size + offset) * head_dim;
+        dst[i] = from_float<T>(y1);
+        dst[i + half] = from_float<T>(y2);
+      }
     }
   }
   if (store) {
@@ -155,8 +248,9 @@ int rope_kv_write_launch(const void* qkv, const int* positions, const float* inv
                          const long long* slots, void* q_out, void* k_pool, void* v_pool,
                          int tokens, int heads, int kv_heads, int head_dim, int page_size,
                          int write_kv, cudaStream_t stream) {
-  int work = (heads + kv_heads) * (head_dim / 2);
-  int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+  // items of two adjacent pairs; few enough threads that each keeps its pair index over its items
+  int work = (heads + kv_heads) * (head_dim / 4);
+  int threads = work >= 512 ? 256 : (work >= 256 ? 128 : 64);
   launch_kernel(rope_kv_write_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 
       (const T*)qkv, positions, inv_freq, slots, (T*)q_out, (T*)k_pool, (T*)v_pool, heads,
       kv_heads, head_dim, page_size, write_kv);
@@ -228,6 +322,24 @@ MLR_EXPORT int mlr_rms_norm(void* residual, const void* delta, const void* weigh
   if ((size_t)width * sizeof(float) > 200 * 1024) return MLR_TOO_LARGE;
   if (dtype == MLR_F32 && weight_dtype == MLR_F32)
     return rms_norm_launch<float, float>(residual, delta, weight, out, rows, width, eps, stream);
+  if (dtype == MLR_BF16 && width % 8 == 0 && width <= 8192 && (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)out) & 15) == 0) {
+    // warp-per-row kernel with the row in registers
+#define MLR_ROWS(W_, V_)                                                                                     \
+  launch_kernel(rms_norm_rows_kernel<W_, V_>, dim3((rows + 3) / 4), dim3(128), 0, stream, (bf16*)residual,   \
+                (const bf16*)delta, (const W_*)weight, (bf16*)out, rows, width, eps)
+#define MLR_ROWS_BY_WIDTH(W_)                                                                                \
+  do {                                                                                                       \
+    if (width <= 256) MLR_ROWS(W_, 1); else if (width <= 512) MLR_ROWS(W_, 2);                               \
+    else if (width <= 1024) MLR_ROWS(W_, 4); else if (width <= 2048) MLR_ROWS(W_, 8);                        \
+    else if (width <= 4096) MLR_ROWS(W_, 16); else MLR_ROWS(W_, 32);                                         \
+  } while (0)
+    if (weight_dtype == MLR_F32) MLR_ROWS_BY_WIDTH(float);
+    else if (weight_dtype == MLR_BF16) MLR_ROWS_BY_WIDTH(bf16);
+    else return MLR_BAD_DTYPE;
+#undef MLR_ROWS_BY_WIDTH
+#undef MLR_ROWS
+    return launch_status();
+  }
   if (dtype == MLR_BF16 && weight_dtype == MLR_BF16)
     return rms_norm_launch<bf16, bf16>(residual, delta, weight, out, rows, width, eps, stream);
   if (dtype == MLR_BF16 && weight_dtype == MLR_F32)
