@@ -288,6 +288,191 @@ prefill_attention_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
   }
 }
 
+// ------------------------------------------------------------------------------------ prefill, TMA
+// The prefill kernel of choice: the arithmetic of prefill_attention_kernel with three changes that
+// remove most of its instructions and its idle time.
+//   * K and V tiles arrive by bulk tensor copies (one per page and 64-column half, as in the decode
+//     kernel) into a ring of STAGES stages; a full/empty pair of mbarriers per stage replaces the
+//     two CTA-wide barriers per key tile.  The warps take turns issuing: at the start of iteration j
+//     warp (j + STAGES - 1) % 4 waits until all four have released the stage of tile j - 1 and
+//     refills it with tile j + STAGES - 1.
+//   * Work items (64 query rows of one head) are drawn from a counter in global memory, heaviest
+//     first (the host lists the tiles by falling number of keys), by as many CTAs as fit on the
+//     GPU at once: the causal triangle no longer leaves SMs idle while the last tiles finish.
+//   * Key tiles that every row of a warp sees completely skip the per-element mask.
+// Keys outside [lowest, last position of the tile] are masked to -inf; the V rows of such keys are
+// overwritten with zeros before use (first and last key tile of an item only), so that whatever
+// lies in slots the request does not own cannot reach the result.
+template <int D, int STAGES>
+__global__ void __launch_bounds__(ATTN_THREADS)
+prefill_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                             const bf16* q, bf16* __restrict__ out, const int* __restrict__ tile_seg,
+                             const int* __restrict__ tile_row0, const int* __restrict__ seg_q_start,
+                             const int* __restrict__ seg_q_len, const int* __restrict__ seg_pos0,
+                             const int* __restrict__ block_table, int table_width, int num_tiles, int heads,
+                             int kv_heads, int page_size, int page_shift, int window, float scale_log2,
+                             int* queue, int* error_word) {
+  constexpr int HALVES = D / 64;
+  constexpr int TILE_ELEMS = TILE_KV * D;
+  constexpr int NT = TILE_KV / 8;
+  constexpr int CHUNKS = D / 8;
+  extern __shared__ uint8_t attn_shared_raw[];
+  uint8_t* aligned = (uint8_t*)(((uintptr_t)attn_shared_raw + 1023) & ~(uintptr_t)1023);
+  bf16* kv_tiles = reinterpret_cast<bf16*>(aligned);                 // STAGES x (K [64][D], V [64][D])
+  bf16* q_tile = kv_tiles + (size_t)STAGES * 2 * TILE_ELEMS;         // [64][D]
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES];
+  __shared__ int item_shared;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ATTN_WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
+  }
+  pdl_trigger();
+  __syncthreads();
+  pdl_wait();                       // before the first draw from the queue and the first read of q
+
+  const int total_items = num_tiles * heads;
+  const int boxes = page_size >= TILE_KV ? 1 : TILE_KV >> page_shift;
+  const int box_rows = page_size >= TILE_KV ? TILE_KV : page_size;
+  unsigned loads_before = 0;        // tiles this CTA has loaded in earlier items (the ring runs on across items)
+  bool gave_up = false;             // a wait ran out: skip all later waits, finish, let the host raise
+
+  for (;;) {
+    if (threadIdx.x == 0) item_shared = atomicAdd(&queue[0], 1);
+    __syncthreads();
+    const int item = item_shared;
+    if (item >= total_items) break;
+    const int tile = item / heads, head = item - tile * heads;
+    const int kv_head = head / (heads / kv_heads);
+    const int seg = tile_seg[tile], row0 = tile_row0[tile];
+    const int q_start = seg_q_start[seg], q_len = seg_q_len[seg], pos0 = seg_pos0[seg];
+    const int rows = min(TILE_Q, q_len - row0);
+    const int* table = block_table + (size_t)seg * table_width;
+    const int first_pos = pos0 + row0, last_pos = first_pos + rows - 1;
+    const int lowest = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int tile_begin = lowest / TILE_KV, tile_end = last_pos / TILE_KV;   // inclusive
+    const int tiles = tile_end - tile_begin + 1;
+
+    for (int idx = threadIdx.x; idx < TILE_Q * CHUNKS; idx += ATTN_THREADS) {
+      const int r = idx / CHUNKS, c = idx - r * CHUNKS;
+      const bool valid = r < rows;
+      const bf16* src = valid ? q + ((size_t)(q_start + row0 + r) * heads + head) * D + c * 8 : q;
+      cp_async_16(tile_at<D>(q_tile, r, c), src, valid);
+    }
+    cp_async_commit();
+
+    // the whole warp calls this; lane b fetches the b-th page (or the one 64-key box) of key tile j
+    auto issue = [&](int j) {
+      const unsigned load = loads_before + (unsigned)j;
+      const int stage = load % STAGES;
+      const unsigned use = load / STAGES;
+      if (use > 0 && !gave_up) gave_up = !mbar_wait(&empty_bar[stage], (use - 1) & 1u, error_word, 0x51);
+      gave_up = __any_sync(0xffffffffu, gave_up);
+      if (gave_up) return;
+      uint64_t* bar = &full_bar[stage];
+      if (lane == 0) mbar_expect_tx(bar, 2u * TILE_ELEMS * 2u);
+      __syncwarp();
+      if (lane < boxes) {
+        const int key0 = (tile_begin + j) * TILE_KV + lane * box_rows;
+        const int logical = key0 >> page_shift;
+        int page = logical < table_width ? table[logical] : -1;
+        int offset = key0 & (page_size - 1);
+        if (page < 0) { page = 0; offset = 0; }
+        const int y = (page * kv_heads + kv_head) * page_size + offset;
+        bf16* k_dst = kv_tiles + (size_t)stage * 2 * TILE_ELEMS + lane * box_rows * 64;
+        bf16* v_dst = k_dst + TILE_ELEMS;
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+          tma_load_2d(&k_map, bar, k_dst + h * (TILE_KV * 64), h * 64, y);
+          tma_load_2d(&v_map, bar, v_dst + h * (TILE_KV * 64), h * 64, y);
+        }
+      }
+    };
+    for (int j = 0; j < STAGES - 1 && j < tiles; ++j)
+      if (warp == j % ATTN_WARPS) issue(j);
+
+    int limit_lo[2], limit_hi[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = warp * 16 + (lane >> 2) + 8 * i;
+      const int position = first_pos + r;
+      limit_hi[i] = r < rows ? position : -1;                       // rows past the segment see nothing
+      limit_lo[i] = window > 0 ? max(0, position - window + 1) : 0;
+    }
+    // every row of the warp sees all of a key tile [key0, key0 + 63] if it ends at or before the
+    // warp's first position and begins at or after the window start of the warp's last row
+    const bool warp_full = warp * 16 + 15 < rows;
+    const int warp_first = first_pos + warp * 16;
+    const int warp_last = first_pos + min(rows - 1, warp * 16 + 15);
+    const int warp_lo = window > 0 ? max(0, warp_last - window + 1) : 0;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+    uint32_t q_frag[D / 16][4];
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int r = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      ldmatrix_x4(q_frag[ks], tile_at<D>(q_tile, r, ks * 2 + (lane >> 4)));
+    }
+
+    for (int j = 0; j < tiles; ++j) {
+      if (j + STAGES - 1 < tiles && warp == (j + STAGES - 1) % ATTN_WARPS) issue(j + STAGES - 1);
+      const unsigned load = loads_before + (unsigned)j;
+      const int stage = load % STAGES;
+      if (!gave_up) gave_up = !mbar_wait(&full_bar[stage], (load / STAGES) & 1u, error_word, 0x52);
+      gave_up = __any_sync(0xffffffffu, gave_up);
+      bf16* k_tile = kv_tiles + (size_t)stage * 2 * TILE_ELEMS;
+      bf16* v_tile = k_tile + TILE_ELEMS;
+      const int key0 = (tile_begin + j) * TILE_KV;
+      if (key0 < lowest || key0 + TILE_KV - 1 > last_pos) {          // the same answer in every warp
+        for (int idx = lane; idx < 16 * CHUNKS; idx += 32) {
+          const int r = warp * 16 + idx / CHUNKS, c = idx % CHUNKS;
+          if (key0 + r < lowest || key0 + r > last_pos)
+            *reinterpret_cast<uint4*>(tile_at<D, true>(v_tile, r, c)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // a later bulk copy reuses the stage
+        __syncthreads();
+      }
+      // a warp whose rows all end before this tile has nothing to do in it
+      if (warp * 16 < rows && key0 <= warp_last) {
+        float s[NT][4];
+        warp_qk<D, NT, true>(s, q_frag, k_tile, 0, lane);
+        if (warp_full && key0 + TILE_KV - 1 <= warp_first && key0 >= warp_lo)
+          softmax_step<NT, D / 8, false>(s, o, m, l, key0, limit_lo, limit_hi, scale_log2, lane);
+        else
+          softmax_step<NT, D / 8, true>(s, o, m, l, key0, limit_lo, limit_hi, scale_log2, lane);
+        warp_pv<D, NT, true>(o, s, v_tile, 0, lane);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+    loads_before += (unsigned)tiles;
+
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = warp * 16 + (lane >> 2) + 8 * i;
+      if (r >= rows) continue;
+      const float inv = 1.f / l[i];
+      bf16* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * D + (lane & 3) * 2;
+#pragma unroll
+      for (int t = 0; t < D / 8; ++t)
+        *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16(o[t][2 * i] * inv, o[t][2 * i + 1] * inv);
+    }
+    __syncthreads();                // q_tile and item_shared are rewritten by the next item
+  }
+  // the CTA that leaves last puts the queue back for the next launch
+  if (threadIdx.x == 0) {
+    const int left = atomicAdd(&queue[1], 1);
+    if (left == (int)gridDim.x - 1) { queue[0] = 0; queue[1] = 0; }
+  }
+}
+
 // The end of both decode kernels: merge the four warps' states (each saw a quarter of the keys) in
 // shared memory, write the output if the request has one chunk, else store the chunk's state and
 // let the CTA that arrives last for this (request, kv head) merge all chunks in chunk order.
@@ -887,5 +1072,48 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
     }
   }
 #undef MLR_LAUNCH_DECODE_TMA
+  return launch_status();
+}
+
+// Prompt portions with K/V fetched by the tensor memory accelerator and work drawn from a queue.
+// Same contract as mlr_attention_prefill_mma plus: pool_pages = pages in each pool, page_size a power
+// of two >= 8, queue = two zeroed ints in device memory (left zeroed), error_word = host-visible
+// int that receives a code if a wait runs out.  The tile list is best ordered by falling key count.
+MLR_EXPORT int mlr_attention_prefill_tma(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                         const int* tile_seg, const int* tile_row0, const int* seg_q_start,
+                                         const int* seg_q_len, const int* seg_pos0, const int* block_table,
+                                         int table_width, int tiles, int heads, int kv_heads, int head_dim,
+                                         int page_size, int pool_pages, int window, float scale, int* queue,
+                                         int* error_word, cudaStream_t stream) {
+  if (tiles == 0) return MLR_OK;
+  if (tiles < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 || table_width <= 0 ||
+      pool_pages <= 0 || queue == nullptr || error_word == nullptr)
+    return MLR_BAD_SIZE;
+  if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
+  if ((long long)tiles * heads >= (1ll << 30)) return MLR_TOO_LARGE;
+  const int page_shift = shift_of(page_size);
+  if (page_shift < 3) return MLR_BAD_SIZE;
+  if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)q & 15)) return MLR_BAD_ALIGNMENT;
+  const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
+  if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;
+  CUtensorMap k_map, v_map;
+  const int box_rows = page_size >= TILE_KV ? TILE_KV : page_size;
+  if (!make_tile_map(&k_map, k_pool, pool_rows, head_dim, box_rows) ||
+      !make_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
+    return MLR_BAD_SIZE;
+  int status;
+#define MLR_LAUNCH_PREFILL_TMA(D_, S_, PER_SM_)                                                             \
+  do {                                                                                                      \
+    const size_t shared = 1024 + (size_t)(TILE_Q + 2 * S_ * TILE_KV) * D_ * 2;                              \
+    if ((status = set_shared(prefill_attention_tma_kernel<D_, S_>, shared)) != MLR_OK) return status;       \
+    const long long items = (long long)tiles * heads;                                                       \
+    const int ctas = (int)(items < 148 * PER_SM_ ? items : 148 * PER_SM_);                                  \
+    launch_kernel(prefill_attention_tma_kernel<D_, S_>, dim3(ctas), dim3(ATTN_THREADS), shared, stream,     \
+                  k_map, v_map, (const bf16*)q, (bf16*)out, tile_seg, tile_row0, seg_q_start, seg_q_len,    \
+                  seg_pos0, block_table, table_width, tiles, heads, kv_heads, page_size, page_shift, window, \
+                  scale * LOG2_E, queue, error_word);                                                       \
+  } while (0)
+  if (head_dim == 64) MLR_LAUNCH_PREFILL_TMA(64, 3, 3); else MLR_LAUNCH_PREFILL_TMA(128, 2, 2);
+#undef MLR_LAUNCH_PREFILL_TMA
   return launch_status();
 }

@@ -245,6 +245,12 @@ class ModelRunner:
         np.cumsum(wide_per_segment[:-1], out=wide_first[1:])
         wide_tile_row0 = ((np.arange(len(wide_tile_seg), dtype=np.int32) - np.repeat(wide_first, wide_per_segment))
                           * WIDE_TILE_ROWS).astype(np.int32)
+        # heaviest first (most keys to walk): the kernel that draws tiles from a queue ends evenly
+        if len(wide_tile_seg) > 1:
+            keys = position_start[wide_tile_seg] + np.minimum(wide_tile_row0 + WIDE_TILE_ROWS, lengths[wide_tile_seg])
+            heavy_first = np.argsort(-keys, kind="stable")
+            wide_tile_seg = np.ascontiguousarray(wide_tile_seg[heavy_first])
+            wide_tile_row0 = np.ascontiguousarray(wide_tile_row0[heavy_first])
 
         slots = np.array([r.slot for r in requests], dtype=np.int32)
         kv_end = position_start + lengths

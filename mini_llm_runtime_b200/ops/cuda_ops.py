@@ -137,6 +137,7 @@ class CudaOps:
                 "attention_scratch": torch.empty(8 << 20, dtype=torch.uint8, device=device),
                 # written by a kernel whose bounded wait ran out; read by the host without a copy
                 "error_word": torch.zeros(1, dtype=torch.int32).pin_memory(),
+                "prefill_queue": torch.zeros(2, dtype=torch.int32, device=device),
             }
         return self._workspaces[index]
 
@@ -426,7 +427,18 @@ class CudaOps:
             if batch.num_decode > 0:
                 self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale,
                                        window, mma=True)
-            if batch.num_wide_tiles > 0:
+            page_size = k_pool.shape[2]
+            if (batch.num_wide_tiles > 0 and self.use_tma_attention and page_size >= 8
+                    and page_size & (page_size - 1) == 0):
+                space = self._workspace(q.device)
+                _check(build.load_library("attention_mma").mlr_attention_prefill_tma(
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.wide_tile_seg),
+                    _ptr(batch.wide_tile_row0), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
+                    _ptr(batch.block_table), batch.block_table.shape[1], batch.num_wide_tiles, num_heads,
+                    num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0), ctypes.c_float(scale),
+                    _ptr(space["prefill_queue"]), _ptr(space["error_word"]), _stream()),
+                    "prefill attention (TMA)")
+            elif batch.num_wide_tiles > 0:
                 lib = build.load_library("attention_mma")
                 _check(lib.mlr_attention_prefill_mma(
                     _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.wide_tile_seg),

@@ -482,7 +482,8 @@ def test_decode_attention_with_fused_position_encoding(heads, kv_heads, head_dim
     assert_close(results[True, None], want, torch.bfloat16, "fused position encoding and attention")
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (4, 1, 128, 8), (6, 6, 64, 32), (16, 1, 128, 16)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (4, 1, 128, 8), (6, 6, 64, 32), (16, 1, 128, 16),
+                                                          (2, 1, 64, 64), (3, 3, 128, 128), (4, 2, 64, 4)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_prefill_attention_tensor_cores(heads, kv_heads, head_dim, page, window):
     """Prompt portions through the tensor-core kernel: a whole prompt longer than several tiles,
@@ -492,6 +493,16 @@ def test_prefill_attention_tensor_cores(heads, kv_heads, head_dim, page, window)
     q, k_pool, v_pool, batch, _ = make_attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, segments, 26)
     got, want = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
     assert_close(got, want, torch.bfloat16, f"prefill attention window={window}")
+    again, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+    assert torch.equal(got, again), "tiles drawn from the queue in any order give the same bits"
+    # tiles loaded by cp.async and one CTA per tile (the compiler contracts the unmasked softmax of
+    # interior tiles differently, so the two agree to rounding, not to the bit)
+    cuda().use_tma_attention = False
+    try:
+        other, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+    finally:
+        cuda().use_tma_attention = True
+    assert_close(got, other, torch.bfloat16, "bulk-copy prefill kernel against the cp.async prefill kernel")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
