@@ -526,9 +526,10 @@ static GemmPlan plan_gemm(int M, int N, int K) {
     // Few tiles cannot keep 148 SMs streaming weights, so K is cut; but the CTA that arrives last
     // for a tile re-reads every split's partial tile (splits x bn x 512 bytes), which soon costs
     // more than the streaming saves when there are many token rows.  Estimate both and take the
-    // cheapest count (microseconds; an SM streams about 120 GB/s, all of them about 6 TB/s; two
-    // CTAs share an SM; a reduction costs 1.5 us of fences and round trips before its first byte).
-    const double sm_bytes_per_us = 120e3, all_bytes_per_us = 6.0e6;
+    // cheapest count (microseconds; one CTA of this kernel streams about 50 GB/s - measured: 56 CTAs
+    // read a 136 MB matrix at 2.8 TB/s - all of them at most 6 TB/s; two CTAs share an SM; a
+    // reduction costs 1.5 us of fences and round trips before its first byte).
+    const double sm_bytes_per_us = 50e3, all_bytes_per_us = 6.0e6;
     const double tile_bytes = (double)(TILE_ROWS + plan.bn) * K * 2;
     const int most = total_kb / 2 < 16 ? (total_kb / 2 < 1 ? 1 : total_kb / 2) : 16;
     double best = 1e30;
