@@ -1,4 +1,4 @@
-"""The engine against the plain implementation, in float32 and bfloat16, for three tiny
+"""The engine against the plain implementation, in float32 and bfloat16, for the tiny
 configurations: each request alone and whole; most of it in one step and the last 32 tokens one by
 one; in portions of changing size down to two tokens; mixed with other requests in a pool so small
 that pages are used again; long decoding; the first tokens of a sequence.  Every position's logits
@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 
 DEVICE = "cuda:0"
 DTYPES = [torch.float32, torch.bfloat16]
-LENGTHS = {"A": (5, 17, 33, 150), "B": (1, 9, 24, 40, 131), "C": (3, 70, 45, 97, 160)}
+LENGTHS = {"A": (5, 17, 33, 150), "B": (1, 9, 24, 40, 131), "C": (3, 70, 45, 97, 160),
+           "D": (2, 64, 65, 130, 300), "E": (7, 33, 128, 200)}
 
 
 def make_requests(name, vocab):

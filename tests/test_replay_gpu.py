@@ -27,7 +27,8 @@ pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
 TRACE_RUN = ROOT / "bin" / "trace_run"
-LENGTHS = {"A": (5, 17, 33, 140), "B": (1, 9, 24, 40, 99), "C": (3, 70, 45, 97)}
+LENGTHS = {"A": (5, 17, 33, 140), "B": (1, 9, 24, 40, 99), "C": (3, 70, 45, 97),
+           "D": (2, 64, 65, 130, 300), "E": (7, 33, 128, 200)}
 
 
 def run_trace(model_dir, dtype_name, out_dir, max_tokens, page, requests, steps):
