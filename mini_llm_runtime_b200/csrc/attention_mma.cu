@@ -1032,7 +1032,7 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
   if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;           // tile coordinates are 32-bit
   if ((size_t)(2 * 16 * max_splits + 16) > (size_t)ATTN_WARPS * 16 * (head_dim + 2)) return MLR_TOO_LARGE;
   CUtensorMap k_map, v_map;
-  const int tile_keys = head_dim == 64 && stages < 10 ? 64 : 32;
+  const int tile_keys = (head_dim == 64 && stages < 10) || stages == 21 ? 64 : 32;
   const int box_rows = page_size >= tile_keys ? tile_keys : page_size;
   if (!make_tile_map(&k_map, k_pool, pool_rows, head_dim, box_rows) ||
       !make_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
@@ -1068,6 +1068,7 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
       case 1: MLR_LAUNCH_DECODE_TMA(128, 32, 1); break;
       case 2: MLR_LAUNCH_DECODE_TMA(128, 32, 2); break;
       case 3: MLR_LAUNCH_DECODE_TMA(128, 32, 3); break;
+      case 21: MLR_LAUNCH_DECODE_TMA(128, 64, 1); break;   // 64-key tiles, for measurements
       default: return MLR_BAD_SIZE;
     }
   }
