@@ -559,7 +559,7 @@ static GemmPlan plan_gemm(int M, int N, int K) {
   // CTAs share an SM and one's epilogue runs while the other streams (measured on 151936 x 896 at
   // 64 rows: 86 us with one CTA per SM, 64 us with two).
   const size_t few_rows_stage = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
-  if (M <= 128 && forced_stages >= 2) stages = forced_stages < stages ? forced_stages : stages;
+  if (M <= 128 && forced_stages >= 2) stages = forced_stages <= MAX_STAGES ? forced_stages : MAX_STAGES;
   else if (M <= 128 && plan.tiles * plan.splits > 148)
     while (stages > 2 && stages * few_rows_stage > 110 * 1024) --stages;
   if (M > 128 && forced_stages >= 2 && forced_stages <= MAX_STAGES) stages = forced_stages;
