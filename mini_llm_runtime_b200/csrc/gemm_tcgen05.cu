@@ -107,9 +107,11 @@ __device__ __forceinline__ void reduce_partials(const float* partials, int split
 // 16-byte load per split and tile column) and every fourth (eighth with SwiGLU) tile column, so the
 // whole tile is fetched with a quarter of the loads and written in 8-byte pieces.  Splits are added
 // in split order.  `t` = 0..127.
-template <int BN>
-__device__ __forceinline__ void reduce_swapped(const float* partials, const GemmParams& p, int t, int a_row0,
-                                               int b_row0) {
+// SHARED: `partials` is one tile in shared memory (the CTA's own accumulator, staged there so that
+// the same wide, row-major stores serve the product without split-K).
+template <int BN, bool SHARED>
+__device__ __forceinline__ void reduce_swapped(const float* partials, int splits, const GemmParams& p, int t,
+                                               int a_row0, int b_row0) {
   const int rg = t & 31, cg = t >> 5;
   const int n0 = a_row0 + 4 * rg;
   if (n0 >= p.N) return;
@@ -122,16 +124,16 @@ __device__ __forceinline__ void reduce_swapped(const float* partials, const Gemm
     float4 acc[CB];
 #pragma unroll
     for (int j = 0; j < CB; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < p.splits; s0 += 4) {
+    for (int s0 = 0; s0 < splits; s0 += 4) {
       float4 part[4][CB];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < CB; ++j) {
           const int col = c + 4 * j;
-          part[i][j] = (s0 + i < p.splits && col < BN && b_row0 + col < p.M)
-                           ? __ldcg(reinterpret_cast<const float4*>(partials + ((size_t)(s0 + i) * BN + col) * TILE_ROWS + 4 * rg))
-                           : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4* at = reinterpret_cast<const float4*>(partials + ((size_t)(s0 + i) * BN + col) * TILE_ROWS + 4 * rg);
+          part[i][j] = (s0 + i < splits && col < BN && b_row0 + col < p.M) ? (SHARED ? *at : __ldcg(at))
+                                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -164,9 +166,9 @@ __device__ __forceinline__ void reduce_swapped(const float* partials, const Gemm
 
 // The same with the fused SwiGLU: tile rows 0..63 are gate rows, 64..127 the up rows of the same
 // 64 outputs; a thread owns four gate rows, their up rows, and every eighth tile column.
-template <int BN>
-__device__ __forceinline__ void reduce_swapped_swiglu(const float* partials, const GemmParams& p, int t, int tile_x,
-                                                      int b_row0) {
+template <int BN, bool SHARED>
+__device__ __forceinline__ void reduce_swapped_swiglu(const float* partials, int splits, const GemmParams& p, int t,
+                                                      int tile_x, int b_row0) {
   const int rg = t & 15, cg = t >> 4;
   const int half = p.N >> 1;
   const int n0 = tile_x * 64 + 4 * rg;
@@ -177,17 +179,17 @@ __device__ __forceinline__ void reduce_swapped_swiglu(const float* partials, con
     float4 gate[CB], up[CB];
 #pragma unroll
     for (int j = 0; j < CB; ++j) gate[j] = up[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < p.splits; s0 += 4) {
+    for (int s0 = 0; s0 < splits; s0 += 4) {
       float4 pg[4][CB], pu[4][CB];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < CB; ++j) {
           const int col = c + 8 * j;
-          const bool live = s0 + i < p.splits && col < BN && b_row0 + col < p.M;
-          const float* base = partials + ((size_t)(s0 + i) * BN + col) * TILE_ROWS + 4 * rg;
-          pg[i][j] = live ? __ldcg(reinterpret_cast<const float4*>(base)) : make_float4(0.f, 0.f, 0.f, 0.f);
-          pu[i][j] = live ? __ldcg(reinterpret_cast<const float4*>(base + 64)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const bool live = s0 + i < splits && col < BN && b_row0 + col < p.M;
+          const float4* base = reinterpret_cast<const float4*>(partials + ((size_t)(s0 + i) * BN + col) * TILE_ROWS + 4 * rg);
+          pg[i][j] = live ? (SHARED ? base[0] : __ldcg(base)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          pu[i][j] = live ? (SHARED ? base[16] : __ldcg(base + 16)) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -340,14 +342,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bf16* out_bf16 = (bf16*)p.out;
     float* out_f32 = (float*)p.out;
 
-    if (SWAP && reduce) {
-      if (SWIGLU) reduce_swapped_swiglu<BN>(partials, p, row, blockIdx.x, b_row0);
-      else reduce_swapped<BN>(partials, p, row, a_row0, b_row0);
-    } else if (SWIGLU && SWAP) {
-      // rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same 64 outputs.
-      // Without split-K the halves meet through shared memory (the stage ring is idle by now).
-      float* exchange = reinterpret_cast<float*>(tiles);            // [BN][128]
-      if (finish && !reduce) {
+    if (SWAP) {
+      // Tile row = output column n, tile column = token m: the tile is written row-major in m by
+      // threads that own four adjacent n each, from the splits' partial tiles (split-K) or from the
+      // CTA's own accumulator staged in shared memory (the stage ring is idle by now).
+      if (reduce) {
+        if (SWIGLU) reduce_swapped_swiglu<BN, false>(partials, p.splits, p, row, blockIdx.x, b_row0);
+        else reduce_swapped<BN, false>(partials, p.splits, p, row, a_row0, b_row0);
+      } else if (finish) {                               // the same answer in all four epilogue warps
+        float* exchange = reinterpret_cast<float*>(tiles);            // [BN][128]
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           uint32_t r[16];
@@ -355,32 +358,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int c = 0; c < 16; ++c) exchange[(c0 + c) * TILE_ROWS + row] = __uint_as_float(r[c]);
         }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (finish && row < 64) {
-        const int n = blockIdx.x * 64 + row;        // output column
-        const int half = p.N >> 1;
-        if (n < half) {
-#pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
-            float g[16], u[16];
-            if (reduce) {
-              reduce_partials<BN>(partials, p.splits, c0, row, g);
-              reduce_partials<BN>(partials, p.splits, c0, row + 64, u);
-            } else {
-#pragma unroll
-              for (int c = 0; c < 16; ++c) {
-                g[c] = exchange[(c0 + c) * TILE_ROWS + row];
-                u[c] = exchange[(c0 + c) * TILE_ROWS + row + 64];
-              }
-            }
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const int m = b_row0 + c0 + c;
-              if (m < p.M) out_bf16[(size_t)m * half + n] = __float2bfloat16_rn(silu_times(g[c], u[c]));
-            }
-          }
-        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (SWIGLU) reduce_swapped_swiglu<BN, true>(exchange, 1, p, row, blockIdx.x, b_row0);
+        else reduce_swapped<BN, true>(exchange, 1, p, row, a_row0, b_row0);
       }
     } else if (SWIGLU) {
       // not swapped: each group of 128 columns holds 64 gate columns, then the 64 up columns of
@@ -428,20 +408,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
         }
-        if (SWAP) {
-          const int n = a_row0 + row;
-          if (n < p.N) {
-            const float b = p.bias != nullptr ? to_float(p.bias[n]) : 0.f;
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const int m = b_row0 + c0 + c;
-              if (m < p.M) {
-                if (p.out_f32) out_f32[(size_t)m * p.N + n] = v[c] + b;
-                else out_bf16[(size_t)m * p.N + n] = __float2bfloat16_rn(v[c] + b);
-              }
-            }
-          }
-        } else {
+        {
           const int m = a_row0 + row;
           const int n0 = b_row0 + c0;
           if (m < p.M && !p.out_f32 && (p.N & 7) == 0 && n0 + 16 <= p.N) {
