@@ -473,7 +473,7 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
 struct GemmPlan { int bn, tiles, splits, stages, kb_per_split; };
 
 // Overrides for measurements (0 = the planner decides): tile width and ring depth of many-row products.
-static int forced_bn = 0, forced_stages = 0;
+static int forced_bn = 0, forced_stages = 0, forced_splits = 0;
 
 static GemmPlan plan_gemm(int M, int N, int K) {
   GemmPlan plan;
@@ -495,7 +495,8 @@ static GemmPlan plan_gemm(int M, int N, int K) {
     // more than the streaming saves when there are many token rows.  Estimate both and take the
     // cheapest count (microseconds; one CTA of this kernel streams about 50 GB/s - measured: 56 CTAs
     // read a 136 MB matrix at 2.8 TB/s - all of them at most 6 TB/s; two CTAs share an SM; a
-    // reduction costs 1.5 us of fences and round trips before its first byte).
+    // reduction costs 3.5 us of fences and round trips before its first byte: fitted to 1152 x 896
+    // at 64 rows, 7.3 us unsplit against 8.6 / 8.2 / 8.2 / 9.4 us with 2 / 3 / 4 / 6 splits).
     const double sm_bytes_per_us = 50e3, all_bytes_per_us = 6.0e6;
     const double tile_bytes = (double)(TILE_ROWS + plan.bn) * K * 2;
     const int most = total_kb / 2 < 16 ? (total_kb / 2 < 1 ? 1 : total_kb / 2) : 16;
@@ -507,10 +508,11 @@ static GemmPlan plan_gemm(int M, int N, int K) {
       double rate = all_bytes_per_us / resident;
       if (rate > sm_bytes_per_us) rate = sm_bytes_per_us;
       double cost = waves * tile_bytes / candidate / rate;
-      if (candidate > 1) cost += 1.5 + (double)candidate * plan.bn * 512.0 / sm_bytes_per_us;
+      if (candidate > 1) cost += 3.5 + (double)candidate * plan.bn * 512.0 / sm_bytes_per_us;
       if (cost < best) { best = cost; splits = candidate; }
     }
   }
+  if (M <= 128 && forced_splits >= 1 && forced_splits <= 16 && forced_splits <= total_kb) splits = forced_splits;
   plan.kb_per_split = (total_kb + splits - 1) / splits;
   plan.splits = (total_kb + plan.kb_per_split - 1) / plan.kb_per_split;   // no empty split
   // A ring as deep as the split is long (at most 6 stages) leaves room for several CTAs per SM,
@@ -543,6 +545,7 @@ using namespace mlr;
 MLR_DEFINE_PDL_SWITCH
 
 MLR_EXPORT void mlr_gemm_tcgen05_tune(int bn, int stages) { forced_bn = bn; forced_stages = stages; }
+MLR_EXPORT void mlr_gemm_tcgen05_tune_splits(int splits) { forced_splits = splits; }
 
 // Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
 // `splits_out` receives the split count the launcher will use, `tiles_out` the number of tiles.
