@@ -31,6 +31,7 @@ from ..ops.cuda_ops import AttentionBatch
 
 ROWS_PER_TILE = 16    # rows one CTA of the generic attention kernel handles
 WIDE_TILE_ROWS = 64   # rows one CTA of the tensor-core prefill kernel handles
+BIG_TILE_ROWS = 128   # rows of one work item of the tcgen05 prefill kernel
 
 
 @dataclass
@@ -252,6 +253,19 @@ class ModelRunner:
             wide_tile_seg = np.ascontiguousarray(wide_tile_seg[heavy_first])
             wide_tile_row0 = np.ascontiguousarray(wide_tile_row0[heavy_first])
 
+        # and tiles of at most 128 rows, heaviest first, for the tcgen05 prefill kernel
+        big_per_segment = (lengths[longer] + BIG_TILE_ROWS - 1) // BIG_TILE_ROWS
+        big_tile_seg = np.repeat(longer, big_per_segment)
+        big_first = np.zeros(len(longer), dtype=np.int32)
+        np.cumsum(big_per_segment[:-1], out=big_first[1:])
+        big_tile_row0 = ((np.arange(len(big_tile_seg), dtype=np.int32) - np.repeat(big_first, big_per_segment))
+                         * BIG_TILE_ROWS).astype(np.int32)
+        if len(big_tile_seg) > 1:
+            keys = position_start[big_tile_seg] + np.minimum(big_tile_row0 + BIG_TILE_ROWS, lengths[big_tile_seg])
+            heavy_first = np.argsort(-keys, kind="stable")
+            big_tile_seg = np.ascontiguousarray(big_tile_seg[heavy_first])
+            big_tile_row0 = np.ascontiguousarray(big_tile_row0[heavy_first])
+
         slots = np.array([r.slot for r in requests], dtype=np.int32)
         kv_end = position_start + lengths
         table_width = fixed_width or max(1, int(-(-int(kv_end.max()) // cache.page_size)))
@@ -269,6 +283,8 @@ class ModelRunner:
         packer.add("decode_seg", decode_seg)
         packer.add("wide_tile_seg", wide_tile_seg)
         packer.add("wide_tile_row0", wide_tile_row0)
+        packer.add("big_tile_seg", big_tile_seg)
+        packer.add("big_tile_row0", big_tile_row0)
         for group in cache.groups:
             rows_slots = np.concatenate([
                 cache.slot_mapping(group, request, int(position_start[i]), int(lengths[i]))
@@ -303,7 +319,9 @@ class ModelRunner:
                 max_kv_len=int(kv_end.max()) if fixed_width is None else fixed_width * cache.page_size,
                 decode_seg=dev["decode_seg"], num_decode=int(decode_seg.shape[0]),
                 wide_tile_seg=dev["wide_tile_seg"], wide_tile_row0=dev["wide_tile_row0"],
-                num_wide_tiles=int(wide_tile_seg.shape[0]))
+                num_wide_tiles=int(wide_tile_seg.shape[0]),
+                big_tile_seg=dev["big_tile_seg"], big_tile_row0=dev["big_tile_row0"],
+                num_big_tiles=int(big_tile_seg.shape[0]))
         for entry, need in enumerate(cache.needs):
             if entry in cache.entry_group:
                 k_pool, v_pool, group = cache.entry_pools(entry)

@@ -41,6 +41,7 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "attention_decode": (),
     "attention_mma": (),
     "gemm_skinny": (),
+    "attention_tcgen05": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

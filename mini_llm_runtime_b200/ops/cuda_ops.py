@@ -98,6 +98,10 @@ class AttentionBatch:
     wide_tile_seg: torch.Tensor | None = None
     wide_tile_row0: torch.Tensor | None = None
     num_wide_tiles: int = 0
+    # the same in tiles of at most 128 rows (tcgen05 prefill kernel)
+    big_tile_seg: torch.Tensor | None = None
+    big_tile_row0: torch.Tensor | None = None
+    num_big_tiles: int = 0
 
 
 class CudaOps:
@@ -123,6 +127,7 @@ class CudaOps:
         self.use_fused_norm = True
         self.use_tma_attention = True
         self.use_fused_rope = True
+        self.use_tcgen05_attention = False
         self.decode_stages = None      # tiles in flight per CTA of the bulk-copy decode kernel (None: its default)
         self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
         self.decode_max_splits: int | None = None  # None: just enough for the longest context
@@ -438,7 +443,18 @@ class CudaOps:
                 self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale,
                                        window, mma=True)
             page_size = k_pool.shape[2]
-            if (batch.num_wide_tiles > 0 and self.use_tma_attention and page_size >= 8
+            if (batch.num_big_tiles > 0 and self.use_tcgen05_attention and head_dim == 64 and page_size >= 8
+                    and page_size & (page_size - 1) == 0 and batch.big_tile_seg is not None):
+                # S = Q K^T and P V on tcgen05 with tensor-memory accumulators
+                space = self._workspace(q.device)
+                _check(build.load_library("attention_tcgen05").mlr_attention_prefill_tcgen05(
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.big_tile_seg),
+                    _ptr(batch.big_tile_row0), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
+                    _ptr(batch.block_table), batch.block_table.shape[1], batch.num_big_tiles, q.shape[0], num_heads,
+                    num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0), ctypes.c_float(scale),
+                    _ptr(space["prefill_queue"]), _ptr(space["error_word"]), _stream()),
+                    "prefill attention (tcgen05)")
+            elif (batch.num_wide_tiles > 0 and self.use_tma_attention and page_size >= 8
                     and page_size & (page_size - 1) == 0):
                 space = self._workspace(q.device)
                 _check(build.load_library("attention_mma").mlr_attention_prefill_tma(

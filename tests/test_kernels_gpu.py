@@ -363,6 +363,13 @@ def make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, seed, 
                 wide_seg.append(s)
                 wide_row0.append(r0)
 
+    big_seg, big_row0 = [], []
+    for s, (_, q_len) in enumerate(segments):
+        if q_len != 1:
+            for r0 in range(0, q_len, 128):
+                big_seg.append(s)
+                big_row0.append(r0)
+
     def ints(values, device):
         return torch.tensor(values, dtype=torch.int32, device=device)
 
@@ -375,7 +382,8 @@ def make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, seed, 
             max_q_len=max(q for _, q in segments), max_kv_len=max(p + q for p, q in segments),
             decode_seg=ints(decode, device), num_decode=len(decode),
             wide_tile_seg=ints(wide_seg, device), wide_tile_row0=ints(wide_row0, device),
-            num_wide_tiles=len(wide_seg))
+            num_wide_tiles=len(wide_seg), big_tile_seg=ints(big_seg, device), big_tile_row0=ints(big_row0, device),
+            num_big_tiles=len(big_seg))
 
     return q.to(dtype), k_pool.to(dtype), v_pool.to(dtype), batch, table
 
@@ -503,6 +511,16 @@ def test_prefill_attention_tensor_cores(heads, kv_heads, head_dim, page, window)
     finally:
         cuda().use_tma_attention = True
     assert_close(got, other, torch.bfloat16, "bulk-copy prefill kernel against the cp.async prefill kernel")
+    if head_dim == 64 and page >= 8:
+        # S = Q K^T and P V on tcgen05, softmax with one thread per row
+        cuda().use_tcgen05_attention = True
+        try:
+            third, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+            torch.cuda.synchronize()
+            cuda().raise_if_device_error()
+        finally:
+            cuda().use_tcgen05_attention = False
+        assert_close(third, want, torch.bfloat16, f"tcgen05 prefill attention window={window}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
