@@ -6,9 +6,10 @@
 //   warps 0..3  softmax: thread r owns query row r (tensor-memory lane r).  Per 64-key tile it reads
 //               its row of S from tensor memory (64 values), masks (causal limit, window, rows past
 //               the portion), keeps the running max and sum, writes the probabilities as bfloat16
-//               into a 128-byte-swizzled tile in shared memory (the A operand of P V), reads the
-//               previous tile's P V from tensor memory and adds it to its output row in registers
-//               (rescaled by the change of the max).  No shuffles: a row lives in one thread.
+//               into a 128-byte-swizzled tile in shared memory (the A operand of P V; two buffers),
+//               and only then reads the previous tile's P V from tensor memory (two buffers) and adds
+//               it to its output row in registers, times the factor by which the max moved: the MMA
+//               runs under the next tile's exponentials.  No shuffles: a row lives in one thread.
 //   warp 4      loads and issues: Q by one bulk tensor copy per item, K and V page by page (one
 //               copy per page and kv head, as in the other attention kernels) into a ring of
 //               stages; one lane issues the MMAs: S_{j+1} = Q K_{j+1}^T goes out before the warp
@@ -33,7 +34,7 @@ constexpr int FA_D = 64;            // head_dim
 constexpr int FA_STAGES = 3;
 constexpr int FA_SOFTMAX_THREADS = 128;
 constexpr int FA_THREADS = FA_SOFTMAX_THREADS + 32;
-constexpr uint32_t FA_TMEM_COLS = 256;   // S0 | S1 | PV | unused
+constexpr uint32_t FA_TMEM_COLS = 256;   // S0 | S1 | PV0 | PV1
 constexpr int FA_KV_TILE_BYTES = FA_KEYS * FA_D * 2;       // one K or V tile
 constexpr int FA_Q_BYTES = FA_ROWS * FA_D * 2;
 
@@ -85,12 +86,19 @@ __device__ __forceinline__ void fa_tmem_wait_ld() { asm volatile("tcgen05.wait::
 __device__ __forceinline__ void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// 2^x with the hardware approximation (subnormal results flush to zero; -inf gives 0).
+__device__ __forceinline__ float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Bounded wait that remembers a failure: after the first wait that ran out, later waits return at once.
 __device__ __forceinline__ void fa_wait(uint64_t* bar, uint32_t parity, int* error_word, int code, bool& gave_up) {
   if (!gave_up) gave_up = !mbar_wait(bar, parity, error_word, code);
 }
 
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FA_THREADS, 2)      // two CTAs per SM: at most 204 registers
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                                  const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out,
                                  const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
@@ -101,8 +109,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   extern __shared__ uint8_t fa_shared_raw[];
   uint8_t* aligned = (uint8_t*)(((uintptr_t)fa_shared_raw + 1023) & ~(uintptr_t)1023);
   bf16* q_tile = reinterpret_cast<bf16*>(aligned);                                   // [128][64]
-  bf16* p_tile = reinterpret_cast<bf16*>(aligned + FA_Q_BYTES);                      // [128][64]
-  uint8_t* kv_ring = aligned + 2 * FA_Q_BYTES;                                       // STAGES x (K, V)
+  uint8_t* p_tiles = aligned + FA_Q_BYTES;                                           // 2 x [128][64]
+  uint8_t* kv_ring = aligned + 3 * FA_Q_BYTES;                                       // STAGES x (K, V)
   __shared__ uint64_t q_full, kv_full[FA_STAGES], kv_empty[FA_STAGES], s_ready[2], s_free[2], p_ready, pv_ready;
   __shared__ uint32_t tmem_holder;
   __shared__ int item_shared;
@@ -184,7 +192,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
 
       constexpr uint32_t idesc_qk = fa_idesc(FA_ROWS, FA_KEYS, false);
       constexpr uint32_t idesc_pv = fa_idesc(FA_ROWS, FA_D, true);
-      const uint32_t q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
+      const uint32_t q_addr = smem_u32(q_tile), p_addr0 = smem_u32(p_tiles);
       auto issue_qk = [&](int j) {
         const unsigned t = tiles_before + (unsigned)j;
         const int stage = t % FA_STAGES, buffer = t & 1;
@@ -215,9 +223,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         if (lane == 0 && !gave_up) {
           const uint32_t v_addr = smem_u32(kv_ring + (size_t)stage * 2 * FA_KV_TILE_BYTES + FA_KV_TILE_BYTES);
 #pragma unroll
+          const uint32_t p_addr = p_addr0 + (t & 1u) * FA_Q_BYTES;
           for (int k = 0; k < FA_KEYS / 16; ++k)
-            fa_mma(tmem_base + 2 * FA_KEYS, fa_desc_k_major(p_addr + k * 32), fa_desc_mn_major(v_addr + k * 2048),
-                   idesc_pv, k > 0 ? 1u : 0u);
+            fa_mma(tmem_base + (2 + (t & 1u)) * FA_KEYS, fa_desc_k_major(p_addr + k * 32),
+                   fa_desc_mn_major(v_addr + k * 2048), idesc_pv, k > 0 ? 1u : 0u);
           fa_commit(&pv_ready);
           fa_commit(&kv_empty[stage]);
         }
@@ -230,6 +239,11 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       const int limit_hi = r < rows ? position : -1;                // rows past the portion see nothing
       const int limit_lo = window > 0 ? max(0, position - window + 1) : 0;
       const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+      // every row of this warp sees all of a key tile that ends at or before the warp's first
+      // position and begins at or after the window start of the warp's last row
+      const bool warp_full = warp * 32 + 31 < rows;
+      const int warp_first = first_pos + warp * 32;
+      const int warp_lo = window > 0 ? max(0, first_pos + min(rows - 1, warp * 32 + 31) - window + 1) : 0;
       float m = -INFINITY, l = 0.f;
       float o[FA_D];
 #pragma unroll
@@ -239,17 +253,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         const unsigned t = tiles_before + (unsigned)j;
         const int buffer = t & 1, stage = t % FA_STAGES;
         const int key0 = (tile_begin + j) * FA_KEYS;
-        if (j > 0) {
-          // the previous tile's P V joins the output row (kept relative to the max so far)
-          fa_wait(&pv_ready, (t - 1) & 1u, error_word, 0x67, gave_up);
-          fa_fence_after();
-          float pv[FA_D];
-#pragma unroll
-          for (int c = 0; c < FA_D; c += 16) fa_tmem_load16(lane_base + 2 * FA_KEYS + c, reinterpret_cast<uint32_t*>(pv) + c);
-          fa_tmem_wait_ld();
-#pragma unroll
-          for (int d = 0; d < FA_D; ++d) o[d] += pv[d];
-        }
         fa_wait(&s_ready[buffer], (t >> 1) & 1u, error_word, 0x66, gave_up);
         fa_fence_after();
         float s[FA_KEYS];
@@ -260,27 +263,54 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_free[buffer]);
 
-        float tile_max = -INFINITY;
+        // scores stay unscaled until the exponent: p = 2^(s * scale - max), one multiply-add each
+        // (four interleaved chains for the max and the sum: a single chain of 64 dependent
+        // operations would cost more than all the exponentials)
+        if (!(warp_full && key0 + FA_KEYS - 1 <= warp_first && key0 >= warp_lo)) {
 #pragma unroll
-        for (int c = 0; c < FA_KEYS; ++c) {
-          const int key = key0 + c;
-          s[c] = (key >= limit_lo && key <= limit_hi) ? s[c] * scale_log2 : -INFINITY;
-          tile_max = fmaxf(tile_max, s[c]);
+          for (int c = 0; c < FA_KEYS; ++c) {
+            const int key = key0 + c;
+            if (!(key >= limit_lo && key <= limit_hi)) s[c] = -INFINITY;
+          }
         }
-        const float m_new = fmaxf(m, tile_max);
+        float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < FA_KEYS; c += 4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) part_max[e] = fmaxf(part_max[e], s[c + e]);
+        }
+        const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
+        const float m_new = fmaxf(m, tile_max * scale_log2);       // the scale is positive
         const float base = m_new == -INFINITY ? 0.f : m_new;       // nothing visible yet: keep everything at zero
-        const float alpha = exp2f(m - base);                       // m = -inf gives 0
+        const float alpha = fa_exp2(m - base);                     // m = -inf gives 0
         m = m_new;
-        float row_sum = 0.f;
+        float part_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < FA_KEYS; ++c) {
-          s[c] = exp2f(s[c] - base);                               // -inf gives 0
-          row_sum += s[c];
+        for (int c = 0; c < FA_KEYS; c += 4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[c + e] = fa_exp2(fmaf(s[c + e], scale_log2, -base));   // -inf gives 0
+            part_sum[e] += s[c + e];
+          }
         }
-        l = l * alpha + row_sum;
+        l = l * alpha + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
         if (alpha != 1.f) {
 #pragma unroll
           for (int d = 0; d < FA_D; ++d) o[d] *= alpha;
+        }
+        if (j > 0) {
+          // the previous tile's P V, which ran while this tile's exponentials were taken; it is
+          // relative to the previous max, so it takes this tile's factor too
+          fa_wait(&pv_ready, (t - 1) & 1u, error_word, 0x67, gave_up);
+          fa_fence_after();
+#pragma unroll
+          for (int c = 0; c < FA_D; c += 16) {
+            float pv[16];
+            fa_tmem_load16(lane_base + (2 + ((t - 1) & 1u)) * FA_KEYS + c, reinterpret_cast<uint32_t*>(pv));
+            fa_tmem_wait_ld();
+#pragma unroll
+            for (int d = 0; d < 16; ++d) o[c + d] = fmaf(pv[d], alpha, o[c + d]);
+          }
         }
 
         if (key0 < lowest || key0 + FA_KEYS - 1 > last_pos) {
@@ -295,7 +325,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         }
         // probabilities of this tile, bfloat16, row r of the swizzled A operand
         {
-          uint8_t* p_row = reinterpret_cast<uint8_t*>(p_tile) + r * 128;
+          uint8_t* p_row = p_tiles + (t & 1u) * FA_Q_BYTES + r * 128;
 #pragma unroll
           for (int chunk = 0; chunk < 8; ++chunk) {
             uint32_t packed[4];
@@ -319,7 +349,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         fa_fence_after();
         float pv[FA_D];
 #pragma unroll
-        for (int c = 0; c < FA_D; c += 16) fa_tmem_load16(lane_base + 2 * FA_KEYS + c, reinterpret_cast<uint32_t*>(pv) + c);
+        for (int c = 0; c < FA_D; c += 16) fa_tmem_load16(lane_base + (2 + (t & 1u)) * FA_KEYS + c, reinterpret_cast<uint32_t*>(pv) + c);
         fa_tmem_wait_ld();
         fa_fence_before();
         if (r < rows) {
@@ -408,7 +438,7 @@ MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, 
   if (!fa_make_map(&q_map, q, q_rows, (long long)heads * FA_D, FA_ROWS) ||
       !fa_make_map(&k_map, k_pool, pool_rows, FA_D, box_rows) || !fa_make_map(&v_map, v_pool, pool_rows, FA_D, box_rows))
     return MLR_BAD_SIZE;
-  const size_t shared = 1024 + 2 * (size_t)FA_Q_BYTES + (size_t)FA_STAGES * 2 * FA_KV_TILE_BYTES;
+  const size_t shared = 1024 + 3 * (size_t)FA_Q_BYTES + (size_t)FA_STAGES * 2 * FA_KV_TILE_BYTES;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
