@@ -1031,12 +1031,12 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
   const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
   if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;           // tile coordinates are 32-bit
   if ((size_t)(2 * 16 * max_splits + 16) > (size_t)ATTN_WARPS * 16 * (head_dim + 2)) return MLR_TOO_LARGE;
-  CUtensorMap k_map, v_map;
   const int tile_keys = (head_dim == 64 && stages < 10) || stages == 21 ? 64 : 32;
   const int box_rows = page_size >= tile_keys ? tile_keys : page_size;
-  if (!make_tile_map(&k_map, k_pool, pool_rows, head_dim, box_rows) ||
-      !make_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
-    return MLR_BAD_SIZE;
+  const CUtensorMap* k_cached = cached_tile_map(k_pool, pool_rows, head_dim, box_rows);
+  const CUtensorMap* v_cached = cached_tile_map(v_pool, pool_rows, head_dim, box_rows);
+  if (k_cached == nullptr || v_cached == nullptr) return MLR_BAD_SIZE;
+  const CUtensorMap k_map = *k_cached, v_map = *v_cached;
   dim3 grid(max_splits, kv_heads, rows);
   int status;
 #define MLR_LAUNCH_DECODE_TMA(D_, T_, S_)                                                                  \
@@ -1097,11 +1097,11 @@ MLR_EXPORT int mlr_attention_prefill_tma(const void* q, const void* k_pool, cons
   if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)q & 15)) return MLR_BAD_ALIGNMENT;
   const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
   if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;
-  CUtensorMap k_map, v_map;
   const int box_rows = page_size >= TILE_KV ? TILE_KV : page_size;
-  if (!make_tile_map(&k_map, k_pool, pool_rows, head_dim, box_rows) ||
-      !make_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
-    return MLR_BAD_SIZE;
+  const CUtensorMap* k_cached = cached_tile_map(k_pool, pool_rows, head_dim, box_rows);
+  const CUtensorMap* v_cached = cached_tile_map(v_pool, pool_rows, head_dim, box_rows);
+  if (k_cached == nullptr || v_cached == nullptr) return MLR_BAD_SIZE;
+  const CUtensorMap k_map = *k_cached, v_map = *v_cached;
   int status;
 #define MLR_LAUNCH_PREFILL_TMA(D_, S_, PER_SM_)                                                             \
   do {                                                                                                      \

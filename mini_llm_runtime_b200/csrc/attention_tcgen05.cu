@@ -93,6 +93,29 @@ __device__ __forceinline__ float fa_exp2(float x) {
   return y;
 }
 
+// 2^x for x <= 0 on the multiply-add pipes, for part of the exponentials, should the special-function
+// unit (8 cycles per warp and exponential) ever bound the kernel.  Measured with every second
+// exponential emulated: slower (2,048 rows: 62.5 -> 70 us), the kernel is bound by its instruction
+// stream, not by that unit; so it is off.  x is split
+// into an integer n (rounded to nearest by adding 1.5 * 2^23) and f in [-0.5, 0.5]; 2^f is a
+// degree-4 polynomial (relative error below 5e-5, far inside bfloat16's 4e-3); n goes into the
+// exponent field.  Arguments below -126 are clamped: the result is then 2^-126, which stands for 0.
+#ifndef FA_POLY_EVERY
+#define FA_POLY_EVERY 0      // 0: none, 1: all, 2: every second exponential of a row
+#endif
+__device__ __forceinline__ float fa_exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float magic = 12582912.f;                       // 1.5 * 2^23
+  const float shifted = x + magic;                      // integer part of x in the low mantissa bits
+  const float n = shifted - magic;
+  const float f = x - n;
+  float p = fmaf(f, 0.00961813f, 0.05550411f);
+  p = fmaf(f, p, 0.24022651f);
+  p = fmaf(f, p, 0.69314718f);
+  p = fmaf(f, p, 1.f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(shifted) << 23));
+}
+
 // Bounded wait that remembers a failure: after the first wait that ran out, later waits return at once.
 __device__ __forceinline__ void fa_wait(uint64_t* bar, uint32_t parity, int* error_word, int code, bool& gave_up) {
   if (!gave_up) gave_up = !mbar_wait(bar, parity, error_word, code);
@@ -289,7 +312,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         for (int c = 0; c < FA_KEYS; c += 4) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            s[c + e] = fa_exp2(fmaf(s[c + e], scale_log2, -base));   // -inf gives 0
+            const float x = fmaf(s[c + e], scale_log2, -base);
+            s[c + e] = (FA_POLY_EVERY != 0 && e % (FA_POLY_EVERY == 0 ? 1 : FA_POLY_EVERY) == 0) ? fa_exp2_poly(x) : fa_exp2(x);
             part_sum[e] += s[c + e];
           }
         }
@@ -304,12 +328,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
           fa_wait(&pv_ready, (t - 1) & 1u, error_word, 0x67, gave_up);
           fa_fence_after();
 #pragma unroll
-          for (int c = 0; c < FA_D; c += 16) {
-            float pv[16];
+          for (int c = 0; c < FA_D; c += 32) {         // two loads in flight per wait
+            float pv[32];
             fa_tmem_load16(lane_base + (2 + ((t - 1) & 1u)) * FA_KEYS + c, reinterpret_cast<uint32_t*>(pv));
+            fa_tmem_load16(lane_base + (2 + ((t - 1) & 1u)) * FA_KEYS + c + 16, reinterpret_cast<uint32_t*>(pv) + 16);
             fa_tmem_wait_ld();
 #pragma unroll
-            for (int d = 0; d < 16; ++d) o[c + d] = fmaf(pv[d], alpha, o[c + d]);
+            for (int d = 0; d < 32; ++d) o[c + d] = fmaf(pv[d], alpha, o[c + d]);
           }
         }
 
@@ -393,19 +418,6 @@ static int fa_shift_of(int page_size) {
   return -1;
 }
 
-// rows x width bfloat16, row-major; box = [box_rows x 64 columns], 128-byte swizzle.
-static bool fa_make_map(CUtensorMap* map, const void* base, long long rows, long long width, int box_rows) {
-  auto encode = encode_tiled();
-  if (encode == nullptr) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)width * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-  cuuint32_t element_strides[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 }  // namespace mlr
 
 using namespace mlr;
@@ -433,11 +445,12 @@ MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, 
   if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)q & 15)) return MLR_BAD_ALIGNMENT;
   const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
   if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;
-  CUtensorMap q_map, k_map, v_map;
   const int box_rows = page_size >= FA_KEYS ? FA_KEYS : page_size;
-  if (!fa_make_map(&q_map, q, q_rows, (long long)heads * FA_D, FA_ROWS) ||
-      !fa_make_map(&k_map, k_pool, pool_rows, FA_D, box_rows) || !fa_make_map(&v_map, v_pool, pool_rows, FA_D, box_rows))
-    return MLR_BAD_SIZE;
+  const CUtensorMap* q_cached = cached_tile_map(q, q_rows, (long long)heads * FA_D, FA_ROWS);
+  const CUtensorMap* k_cached = cached_tile_map(k_pool, pool_rows, FA_D, box_rows);
+  const CUtensorMap* v_cached = cached_tile_map(v_pool, pool_rows, FA_D, box_rows);
+  if (q_cached == nullptr || k_cached == nullptr || v_cached == nullptr) return MLR_BAD_SIZE;
+  const CUtensorMap q_map = *q_cached, k_map = *k_cached, v_map = *v_cached;
   const size_t shared = 1024 + 3 * (size_t)FA_Q_BYTES + (size_t)FA_STAGES * 2 * FA_KV_TILE_BYTES;
   static bool configured = false;
   if (!configured) {

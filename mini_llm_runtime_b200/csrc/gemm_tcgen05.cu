@@ -458,12 +458,13 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
     if (err != cudaSuccess) return (int)err;
     configured = shared;
   }
-  CUtensorMap map_a, map_b;
   const void* a_base = SWAP ? w : x;
   const void* b_base = SWAP ? x : w;
   const int a_rows = SWAP ? p.N : p.M, b_rows = SWAP ? p.M : p.N;
-  if (!make_tile_map(&map_a, a_base, a_rows, p.K, TILE_ROWS) || !make_tile_map(&map_b, b_base, b_rows, p.K, BN))
-    return MLR_BAD_ALIGNMENT;
+  const CUtensorMap* a_cached = cached_tile_map(a_base, a_rows, p.K, TILE_ROWS);
+  const CUtensorMap* b_cached = cached_tile_map(b_base, b_rows, p.K, BN);
+  if (a_cached == nullptr || b_cached == nullptr) return MLR_BAD_ALIGNMENT;
+  const CUtensorMap map_a = *a_cached, map_b = *b_cached;
   dim3 grid((a_rows + TILE_ROWS - 1) / TILE_ROWS, (b_rows + BN - 1) / BN, splits);
   launch_kernel(gemm_tcgen05_kernel<BN, SWAP, SWIGLU>, dim3(grid), dim3(GEMM_THREADS), shared, stream, map_a, map_b, p);
   return launch_status();

@@ -89,4 +89,44 @@ static inline bool make_tile_map(CUtensorMap* map, const void* base, long long r
                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same through a small cache: encoding a map costs a few microseconds on the host, and a model
+// step asks for the same maps (weights, cache pools, activation buffers the allocator hands out
+// again) over and over.  Keyed by everything the map depends on; 256 entries, replaced in turn.
+// Not thread-safe: the kernels are launched from one host thread.
+struct TileMapKey {
+  const void* base;
+  long long rows;
+  long long width;
+  int box_rows;
+  bool operator==(const TileMapKey& other) const {
+    return base == other.base && rows == other.rows && width == other.width && box_rows == other.box_rows;
+  }
+};
+
+static inline const CUtensorMap* cached_tile_map(const void* base, long long rows, long long width, int box_rows) {
+  constexpr int SLOTS = 256;
+  static TileMapKey keys[SLOTS];
+  static CUtensorMap maps[SLOTS];
+  static int used = 0, next = 0;
+  const TileMapKey key{base, rows, width, box_rows};
+  for (int i = 0; i < used; ++i)
+    if (keys[i] == key) return &maps[i];
+  auto encode = encode_tiled();
+  if (encode == nullptr) return nullptr;
+  const int slot = used < SLOTS ? used : next;
+  cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t element_strides[2] = {1, 1};
+  if (encode(&maps[slot], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+             element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    if (slot < used) keys[slot] = TileMapKey{nullptr, 0, 0, 0};
+    return nullptr;
+  }
+  keys[slot] = key;
+  if (used < SLOTS) ++used; else next = (next + 1) % SLOTS;
+  return &maps[slot];
+}
+
 }  // namespace mlr

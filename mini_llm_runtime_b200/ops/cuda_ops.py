@@ -12,6 +12,7 @@ The reference reaches its one kernel through a similar checked wrapper
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -127,7 +128,8 @@ class CudaOps:
         self.use_fused_norm = True
         self.use_tma_attention = True
         self.use_fused_rope = True
-        self.use_tcgen05_attention = False
+        # MLR_TCGEN05_ATTENTION=0 in the environment keeps prompt attention on the mma.sync kernels
+        self.use_tcgen05_attention = os.environ.get("MLR_TCGEN05_ATTENTION", "1") != "0"
         self.decode_stages = None      # tiles in flight per CTA of the bulk-copy decode kernel (None: its default)
         self.decode_chunk: int | None = None      # None: chosen per call from the batch's shape
         self.decode_max_splits: int | None = None  # None: just enough for the longest context

@@ -505,22 +505,23 @@ def test_prefill_attention_tensor_cores(heads, kv_heads, head_dim, page, window)
     assert torch.equal(got, again), "tiles drawn from the queue in any order give the same bits"
     # tiles loaded by cp.async and one CTA per tile (the compiler contracts the unmasked softmax of
     # interior tiles differently, so the two agree to rounding, not to the bit)
-    cuda().use_tma_attention = False
+    cuda().use_tma_attention = cuda().use_tcgen05_attention = False
     try:
         other, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
     finally:
-        cuda().use_tma_attention = True
-    assert_close(got, other, torch.bfloat16, "bulk-copy prefill kernel against the cp.async prefill kernel")
-    if head_dim == 64 and page >= 8:
-        # S = Q K^T and P V on tcgen05, softmax with one thread per row
+        cuda().use_tma_attention = cuda().use_tcgen05_attention = True
+    assert_close(got, other, torch.bfloat16, "default prefill kernel against the cp.async prefill kernel")
+    # head_dim 64 with such pages took the tcgen05 kernel above (S = Q K^T and P V in tensor memory, one
+    # thread per query row); the mma.sync kernel with bulk-copy loaders must agree with it
+    cuda().use_tcgen05_attention = False
+    try:
+        third, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+        torch.cuda.synchronize()
+        cuda().raise_if_device_error()
+    finally:
         cuda().use_tcgen05_attention = True
-        try:
-            third, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
-            torch.cuda.synchronize()
-            cuda().raise_if_device_error()
-        finally:
-            cuda().use_tcgen05_attention = False
-        assert_close(third, want, torch.bfloat16, f"tcgen05 prefill attention window={window}")
+    assert_close(third, want, torch.bfloat16, f"mma.sync prefill attention window={window}")
+    assert_close(third, got, torch.bfloat16, "mma.sync prefill kernel against the default kernel")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
