@@ -180,7 +180,8 @@ def time_decode(runner, request_ids, vocab, steps, warmup, clocks=None):
     tokens = random_tokens(batch, vocab, 7)
 
     def one_step():
-        return runner.step([StepEntry(rid, [tokens[i]], [0]) for i, rid in enumerate(request_ids)], sampling)
+        # borrow: the step hands out its own output buffers (what the engine does too), no copies
+        return runner.step([StepEntry(rid, [tokens[i]], [0]) for i, rid in enumerate(request_ids)], sampling, borrow=True)
 
     for _ in range(warmup):
         one_step()
@@ -259,8 +260,11 @@ def time_e2e(layers, batch, steps, warmup):
     config = Qwen2Config(**dict(SIZES, num_hidden_layers=layers))
     model = random_model(config, seed=0, dtype=torch.bfloat16, device="cuda:0")
     prefix = CONTEXT_MEAN - (steps + warmup) // 2
+    # step_ahead: the engine launches each decode step behind the previous one, fed on the device
+    # with the tokens it chose; every step() still returns that step's tokens on the host
     engine = ContinuousBatchEngine.from_model(model, block_size=BLOCK_SIZE, max_running_requests=batch,
-                                              max_batch_tokens=PREFILL_TOKENS, max_model_len=CONTEXT + 1024)
+                                              max_batch_tokens=PREFILL_TOKENS, max_model_len=CONTEXT + 1024,
+                                              step_ahead=True)
     # Requests that finish their prompt early decode while the others still prefill; leave room
     # for those extra tokens so that all of them are alive through the timed steps.
     slack = batch * (-(-prefix // PREFILL_TOKENS) + 1)

@@ -47,6 +47,8 @@ def build_parser() -> argparse.ArgumentParser:
         sub.add_argument("--max-running-requests", type=int, default=4)
         sub.add_argument("--max-batch-tokens", type=int, default=2048)
         sub.add_argument("--max-mixed-prefill-tokens", type=int, default=None)
+        sub.add_argument("--step-ahead", action="store_true",
+                         help="launch each decode step before the previous one's tokens have reached the host")
         sub.add_argument("--max-model-len", type=int, default=None)
         sub.add_argument("--temperature", type=float, default=0.0, help="0 selects greedy")
         sub.add_argument("--seed", type=int, default=0)
@@ -88,7 +90,7 @@ def _engine(args):
         args.model, dtype=args.dtype, device=args.device, block_size=args.block_size,
         total_blocks=args.total_blocks, max_running_requests=args.max_running_requests,
         max_batch_tokens=args.max_batch_tokens, max_mixed_prefill_tokens=args.max_mixed_prefill_tokens,
-        max_model_len=args.max_model_len)
+        max_model_len=args.max_model_len, step_ahead=args.step_ahead)
 
 
 def _write(args, record: dict) -> None:

@@ -40,6 +40,18 @@ def _nvtx_range(enabled: bool, message: str) -> Iterator[None]:
             torch.cuda.nvtx.range_pop()
 
 
+@dataclass
+class _StepAhead:
+    """A decode step launched before the host had the previous step's tokens: its input ids came
+    from the device.  ``request_ids`` in row order; ``host`` receives the tokens (pinned), ``event``
+    marks the end of that copy."""
+
+    request_ids: tuple[str, ...]
+    tokens: torch.Tensor
+    host: torch.Tensor
+    event: "torch.cuda.Event | None"
+
+
 @dataclass(frozen=True)
 class EngineStepResult:
     batch: SchedulerBatch
@@ -54,7 +66,8 @@ class ContinuousBatchEngine:
     def __init__(self, *, scheduler: RequestScheduler, runner: ModelRunner,
                  admission: PagedBlockAdmissionController,
                  clock_ns: Callable[[], int] = time.perf_counter_ns,
-                 metrics: RequestMetricsCollector | None = None, enable_nvtx: bool = False) -> None:
+                 metrics: RequestMetricsCollector | None = None, enable_nvtx: bool = False,
+                 step_ahead: bool = False) -> None:
         if admission.manager is not runner.cache:
             raise ValueError("the admission controller and the runner must share one cache manager")
         if enable_nvtx and runner.device.type != "cuda":
@@ -65,6 +78,15 @@ class ContinuousBatchEngine:
         self._clock_ns = clock_ns
         self.metrics = metrics or RequestMetricsCollector()
         self.enable_nvtx = enable_nvtx
+        # Stepping ahead: when a step decodes only, the same requests' next decode step is launched
+        # right behind it, fed on the device with the tokens it chooses, before the host reads them.
+        # The host's work between two steps then runs beside the GPU instead of idling it.  What
+        # step() returns does not change; a request that ends on a stop token has computed one
+        # token too many, which is dropped with its pages.
+        self.step_ahead = step_ahead
+        self._ahead: _StepAhead | None = None
+        self._token_buffers: list[torch.Tensor] = []
+        self._token_buffer_cursor = 0
 
     # ------------------------------------------------------------------ assembly
     @classmethod
@@ -72,7 +94,8 @@ class ContinuousBatchEngine:
                    max_running_requests: int = 8, max_batch_tokens: int = 2048,
                    max_mixed_prefill_tokens: int | None = None, max_model_len: int | None = None,
                    batching_policy: BatchingPolicy = BatchingPolicy.CONTINUOUS,
-                   chunked_prefill: bool = True, enable_nvtx: bool = False) -> "ContinuousBatchEngine":
+                   chunked_prefill: bool = True, enable_nvtx: bool = False,
+                   step_ahead: bool = False) -> "ContinuousBatchEngine":
         max_model_len = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
         if total_blocks is None:
             total_blocks = max_running_requests * -(-max_model_len // block_size)
@@ -87,7 +110,7 @@ class ContinuousBatchEngine:
                                      admission_callback=admission.try_admit,
                                      batching_policy=batching_policy, chunked_prefill=chunked_prefill)
         return cls(scheduler=scheduler, runner=ModelRunner(model, manager), admission=admission,
-                   enable_nvtx=enable_nvtx)
+                   enable_nvtx=enable_nvtx, step_ahead=step_ahead)
 
     @classmethod
     def from_model_dir(cls, model_dir, *, dtype="bfloat16", device="cuda:0", **options) -> "ContinuousBatchEngine":
@@ -131,10 +154,15 @@ class ContinuousBatchEngine:
             return self._execute_batch(batch, started_ns)
 
     def _execute_batch(self, batch: SchedulerBatch, started_ns: int) -> EngineStepResult:
+        ahead, self._ahead = self._ahead, None
+        ahead_row = {rid: row for row, rid in enumerate(ahead.request_ids)} if ahead is not None else {}
         try:
             self.metrics.require_registered(tuple(item.request_id for item in batch.items))
+            # Decodes whose step is already on the GPU take their token from it; the rest is launched now.
             entries, temperatures, seeds, indices, emitting = [], [], [], [], []
             for item in batch.items:
+                if item.kind is WorkKind.DECODE and item.request_id in ahead_row:
+                    continue
                 want = [len(item.input_token_ids) - 1] if item.emits_token else []
                 entries.append(StepEntry(item.request_id, item.input_token_ids, want))
                 if item.newly_admitted:
@@ -145,20 +173,36 @@ class ContinuousBatchEngine:
                     seeds.append(request.seed)
                     indices.append(len(request.generated_token_ids))
                     emitting.append(item.request_id)
-            with _nvtx_range(self.enable_nvtx, f"model.step:tokens={batch.token_count}"):
-                _, tokens = self.runner.step(entries, SamplingRows(temperatures, seeds, indices), borrow=True)
+            tokens = None
+            if entries:
+                with _nvtx_range(self.enable_nvtx, f"model.step:tokens={sum(len(e.tokens) for e in entries)}"):
+                    _, tokens = self.runner.step(entries, SamplingRows(temperatures, seeds, indices), borrow=True)
         except Exception:
             with _nvtx_range(self.enable_nvtx, "engine.rollback"):
                 admitted = tuple(rid for rid in batch.admitted_request_ids
                                  if rid in self.manager.requests)
                 self.admission.release_admitted(admitted)
                 self.scheduler.abort_step()
+            self._ahead = ahead         # its decodes are done and stay valid for the retried step
             raise
 
+        launched = self._start_token_copy(tuple(emitting), tokens) if emitting else None
+        if self.step_ahead:
+            self._launch_ahead(batch, ahead, launched)
+
         with _nvtx_range(self.enable_nvtx, "token.d2h_sync"):
-            host_tokens = tokens.cpu().tolist() if emitting else []
+            generated: dict[str, int] = {}
+            for source in (ahead, launched):
+                if source is None:
+                    continue
+                if source.event is not None:
+                    source.event.synchronize()
+                values = source.host[:len(source.request_ids)].tolist()
+                for rid, token in zip(source.request_ids, values, strict=True):
+                    generated[rid] = int(token)
+            wanted = batch.emitting_request_ids
+            generated = {rid: generated[rid] for rid in wanted}     # drops rows of requests that have ended
         tokens_ready_ns = self._clock_ns()
-        generated = {rid: int(token) for rid, token in zip(emitting, host_tokens, strict=True)}
         with _nvtx_range(self.enable_nvtx, "scheduler.apply_and_release"):
             update = self.scheduler.apply_step_results(generated)
             released = self.admission.release_finished(update.finished_request_ids)
@@ -167,6 +211,48 @@ class ContinuousBatchEngine:
         self.metrics.record_completed(update.finished_request_ids, completed_ns)
         return EngineStepResult(batch, update, tuple(released.items()), started_ns, tokens_ready_ns,
                                 completed_ns)
+
+    def _start_token_copy(self, request_ids: tuple[str, ...], tokens: torch.Tensor) -> _StepAhead:
+        """Begin the device-to-host copy of a step's tokens; the caller waits on the event."""
+        if tokens.device.type != "cuda":
+            return _StepAhead(request_ids, tokens, tokens.to(torch.int32), None)
+        if not self._token_buffers:
+            size = max(64, self.scheduler.max_running_requests)
+            self._token_buffers = [torch.empty(size, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        host = self._token_buffers[self._token_buffer_cursor]
+        self._token_buffer_cursor = (self._token_buffer_cursor + 1) % len(self._token_buffers)
+        if host.numel() < tokens.numel():
+            host = torch.empty(tokens.numel(), dtype=torch.int32, pin_memory=True)
+        host[:tokens.numel()].copy_(tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return _StepAhead(request_ids, tokens, host, event)
+
+    def _launch_ahead(self, batch: SchedulerBatch, ahead: _StepAhead | None, launched: _StepAhead | None) -> None:
+        """Launch the next decode step of this batch's requests behind the current one, if the
+        current one decodes only, all of its tokens lie in one device tensor in the batch's order,
+        and none of its requests reaches its token limit with this step."""
+        rids = tuple(item.request_id for item in batch.items)
+        if not batch.items or any(item.kind is not WorkKind.DECODE for item in batch.items):
+            return
+        if ahead is not None and launched is None and ahead.request_ids == rids:
+            source = ahead
+        elif ahead is None and launched is not None and launched.request_ids == rids:
+            source = launched
+        else:
+            return
+        requests = [self.scheduler.get_request(rid) for rid in rids]
+        if any(len(r.generated_token_ids) + 1 >= r.max_new_tokens for r in requests):
+            return
+        entries = [StepEntry(rid, [0], [0]) for rid in rids]
+        sampling = SamplingRows([r.temperature for r in requests], [r.seed for r in requests],
+                                [len(r.generated_token_ids) + 1 for r in requests])
+        try:
+            with _nvtx_range(self.enable_nvtx, f"model.step_ahead:tokens={len(entries)}"):
+                _, tokens = self.runner.step(entries, sampling, borrow=True, feed=source.tokens)
+        except Exception:
+            return          # nothing was launched and the cache is as before: go on step by step
+        self._ahead = self._start_token_copy(rids, tokens)
 
     # ------------------------------------------------------------------ conveniences
     def run(self) -> list[EngineStepResult]:

@@ -149,6 +149,7 @@ class _CapturedStep:
     tokens: torch.Tensor | None = None
     launches: int = 0      # kernels in the graph
     nbytes: int = 0
+    token_ids: torch.Tensor | None = None    # the input ids inside ``metadata`` (fixed address)
     # pinned staging buffers with numpy views of every array at its fixed offset, used in turn
     stagings: list = field(default_factory=list)
     cursor: int = 0
@@ -368,10 +369,10 @@ class ModelRunner:
                 and isinstance(ops.current(), ops.CudaOps)
                 and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
 
-    def _graph_step(self, entries, requests, sampling):
+    def _graph_step(self, entries, requests, sampling, feed=None):
         """A decode-only step through the captured graph of its batch size.  The first step of a
         size runs eagerly on the graph's fixed buffers and is then captured; later steps only
-        refresh the metadata buffer and replay."""
+        refresh the metadata buffer and replay.  ``feed``: see ``step``."""
         key = (len(entries), sampling is not None)
         kernels = ops.current()
         captured = self._graphs.get(key)
@@ -386,11 +387,16 @@ class ModelRunner:
             self._graphs[key] = captured
         if captured.graph is not None:
             self._refresh_captured(captured, entries, requests, sampling)
+            if feed is not None:
+                captured.token_ids.copy_(feed)       # after the metadata copy, before the replay reads it
             captured.graph.replay()
             self.graph_replays += 1
             return captured.logits, captured.tokens
         ctx = self._build_context(entries, requests, sampling, fixed_width=width,
                                   device_buffer=captured.metadata)
+        captured.token_ids = ctx.token_ids
+        if feed is not None:
+            ctx.token_ids.copy_(feed)
         self._prepare_stagings(captured)
         logits, tokens = self._forward(ctx, sampling)          # this step's real result, eagerly
         torch.cuda.synchronize(self.device)
@@ -458,21 +464,29 @@ class ModelRunner:
 
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry], sampling: SamplingRows | None = None, *,
-             borrow: bool = False):
+             borrow: bool = False, feed: torch.Tensor | None = None):
         """Run the entries as one batch.  Returns float32 logits [wanted places, vocab] on the
         device, in the order of the entries and of each entry's ``want``.  With ``sampling`` it
         returns ``(logits, tokens)``: one int32 token per wanted place, chosen on the device.
-        ``borrow=True`` may return buffers that the next step overwrites (no copy is made)."""
+        ``borrow=True`` may return buffers that the next step overwrites (no copy is made).
+        ``feed``: int32 device tensor with the input token of every entry (each entry then holds
+        exactly one placeholder token): the ids are taken from the device, e.g. from the tokens the
+        previous step chose, without the host having seen them."""
         self._validate(entries)
+        if feed is not None:
+            if any(len(e.tokens) != 1 for e in entries) or feed.shape != (len(entries),) or feed.dtype != torch.int32:
+                raise ValueError("feed needs one int32 token per entry and entries of one token each")
         requests = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
         try:
             if self._graph_eligible(entries):
-                logits, tokens = self._graph_step(entries, requests, sampling)
+                logits, tokens = self._graph_step(entries, requests, sampling, feed)
                 if not borrow:
                     logits = logits.clone()
                     tokens = tokens.clone() if tokens is not None else None
             else:
                 ctx = self._build_context(entries, requests, sampling)
+                if feed is not None:
+                    ctx.token_ids.copy_(feed)
                 logits, tokens = self._forward(ctx, sampling)
         except BaseException:
             self.cache.abort_step()

@@ -13,7 +13,7 @@ from mini_llm_runtime_b200 import ops
 from mini_llm_runtime_b200.cache import CacheManager
 from mini_llm_runtime_b200.config import register_architecture, unregister_architecture
 from mini_llm_runtime_b200.engine import (ContinuousBatchEngine, ModelRunner, StepEntry, greedy_generate)
-from mini_llm_runtime_b200.models import build_model
+from mini_llm_runtime_b200.models import build_model, random_model
 from mini_llm_runtime_b200.weights import random_tensors
 from tiny_configs import TINY
 
@@ -220,3 +220,40 @@ def test_toy_parts_register_build_and_step_without_touching_the_package():
                          torch.float32, f"toy {rid}")
     finally:
         unregister_architecture("ToyForCausalLM")
+
+
+def test_stepping_ahead_returns_the_same_results_step_by_step():
+    """With ``step_ahead`` the next decode step is launched before the host has the tokens of the
+    current one (fed on the device).  Every step() must return what it returns without it: tokens,
+    finished requests, step after step - with a request that samples, one that stops on a stop
+    token in mid-flight, one that reaches its token limit, and one submitted while others decode."""
+    config, page = TINY["B"]
+    histories = []
+    for ahead in (False, True):
+        with ops.use(FakeOps()):
+            model = random_model(config, seed=3, dtype=torch.float32, device="cpu")
+            engine = ContinuousBatchEngine.from_model(model, block_size=page, max_running_requests=4,
+                                                      max_batch_tokens=48, step_ahead=ahead)
+            engine.submit("a", [1, 2, 3, 4, 5], max_new_tokens=14)
+            engine.submit("b", [9, 8, 7], max_new_tokens=9, temperature=0.8, seed=5)
+            # a request that stops on the fourth token it generates (found with a trial run)
+            trial = ContinuousBatchEngine.from_model(model, block_size=page, max_running_requests=1, max_batch_tokens=48)
+            trial.submit("trial", [4, 4, 4, 4], max_new_tokens=6)
+            trial.run()
+            stop_token = trial.scheduler.get_request("trial").generated_token_ids[3]
+            engine.submit("stops", [4, 4, 4, 4], max_new_tokens=12, eos_token_ids=[stop_token])
+            history, steps = [], 0
+            while engine.scheduler.has_unfinished_requests:
+                if steps == 5:
+                    engine.submit("late", list(range(20, 75)), max_new_tokens=4)
+                result = engine.step()
+                steps += 1
+                history.append((result.update.emitted_tokens, result.update.finished_request_ids))
+                engine.manager.check_consistency()
+            assert not engine.manager.requests, "every finished request gave its pages back"
+            tokens = {rid: engine.scheduler.get_request(rid).generated_token_ids for rid in ("a", "b", "stops", "late")}
+            histories.append((history, tokens, engine.runner.steps_run))
+    assert histories[0][0] == histories[1][0]
+    assert histories[0][1] == histories[1][1]
+    assert len(histories[1][1]["stops"]) < 12, "the stop token must have ended the request early"
+    assert histories[1][2] > histories[0][2], "stepping ahead launches the dropped extra step of ended requests"

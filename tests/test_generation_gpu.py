@@ -91,6 +91,51 @@ def test_temperature_sampling_on_the_device_is_the_plain_sampler_and_ignores_the
         sequence.append(token)
 
 
+@pytest.mark.parametrize("name,dtype,eventful", [("A", torch.float32, True), ("C", torch.float32, True),
+                                                 ("D", torch.bfloat16, False), ("E", torch.bfloat16, False)])
+def test_stepping_ahead_on_the_device(name, dtype, eventful):
+    """The engine that launches the next decode step before it has read the current one's tokens
+    (captured graphs, input ids fed from the device) returns, call by call, what the step-by-step
+    engine returns.  In float32, where a row's result does not depend on its batch, with everything
+    that changes the batches: a sampled request, a stop token in mid-flight, a late arrival.  In
+    bfloat16 with requests that decode side by side to the end (there a step taken from the launch
+    ahead and the same step launched in another batch may differ in rounding)."""
+    config, page = TINY[name]
+    model = build_model(config, dtype)
+    model.load(random_tensors(model.expected_tensors(), 41), DEVICE)
+    prompts = {rid: random_prompt(config.vocab_size, n, 300 + n) for rid, n in (("a", 5), ("b", 33), ("c", 70), ("late", 41))}
+    stop_token = None
+    if eventful:
+        trial = ContinuousBatchEngine.from_model(model, block_size=page, max_running_requests=1, max_batch_tokens=128,
+                                                 max_model_len=256)
+        trial.submit("trial", prompts["c"], max_new_tokens=8)
+        trial.run()
+        stop_token = trial.scheduler.get_request("trial").generated_token_ids[5]
+    histories = []
+    for ahead in (False, True):
+        engine = ContinuousBatchEngine.from_model(model, block_size=page, max_running_requests=4, max_batch_tokens=128,
+                                                  max_model_len=256, step_ahead=ahead)
+        if eventful:
+            engine.submit("a", prompts["a"], max_new_tokens=40)
+            engine.submit("b", prompts["b"], max_new_tokens=25, temperature=0.7, seed=11)
+            engine.submit("c", prompts["c"], max_new_tokens=30, eos_token_ids=[stop_token])
+        else:
+            for rid in ("a", "b", "c"):
+                engine.submit(rid, prompts[rid], max_new_tokens=30)
+        history, steps = [], 0
+        while engine.scheduler.has_unfinished_requests:
+            if eventful and steps == 9:
+                engine.submit("late", prompts["late"], max_new_tokens=12)
+            result = engine.step()
+            steps += 1
+            history.append((result.update.emitted_tokens, result.update.finished_request_ids))
+        engine.manager.check_consistency()
+        assert not engine.manager.requests
+        histories.append((history, engine.runner.graph_replays))
+    assert histories[0][0] == histories[1][0]
+    assert histories[1][1] > 0, "decode steps must have gone through captured graphs"
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_toy_parts_on_the_device(dtype):
     import toy_parts
