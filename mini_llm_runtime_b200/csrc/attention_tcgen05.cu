@@ -128,7 +128,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
                                  const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
                                  const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
                                  int table_width, int num_tiles, int heads, int kv_heads, int page_size,
-                                 int page_shift, int window, float scale_log2, int* queue, int* error_word) {
+                                 int page_shift, int window, float scale_log2, int* queue, int* error_word,
+                                 int max_parts, int tiles_per_unit, float* __restrict__ scratch,
+                                 int* __restrict__ counters) {
   extern __shared__ uint8_t fa_shared_raw[];
   uint8_t* aligned = (uint8_t*)(((uintptr_t)fa_shared_raw + 1023) & ~(uintptr_t)1023);
   bf16* q_tile = reinterpret_cast<bf16*>(aligned);                                   // [128][64]
@@ -136,7 +138,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   uint8_t* kv_ring = aligned + 3 * FA_Q_BYTES;                                       // STAGES x (K, V)
   __shared__ uint64_t q_full, kv_full[FA_STAGES], kv_empty[FA_STAGES], s_ready[2], s_free[2], p_ready, pv_ready;
   __shared__ uint32_t tmem_holder;
-  __shared__ int item_shared;
+  __shared__ int item_shared, last_shared;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -162,6 +164,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   pdl_wait();                       // before the first draw from the queue, the first read of q and the first write
 
   const int total_items = num_tiles * heads;
+  const int total_units = total_items * max_parts;     // part p of every item, for p = 0, 1, ..: many are empty
   const int boxes = page_size >= FA_KEYS ? 1 : FA_KEYS >> page_shift;
   const int box_rows = page_size >= FA_KEYS ? FA_KEYS : page_size;
   unsigned tiles_before = 0;        // key tiles of this CTA's earlier items: rings and phases run on across items
@@ -171,8 +174,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   for (;;) {
     if (threadIdx.x == 0) item_shared = atomicAdd(&queue[0], 1);
     __syncthreads();
-    const int item = item_shared;
-    if (item >= total_items) break;
+    const int unit = item_shared;
+    if (unit >= total_units) break;
+    const int part = unit / total_items, item = unit - part * total_items;
     const int tile = item / heads, head = item - tile * heads;
     const int kv_head = head / (heads / kv_heads);
     const int seg = tile_seg[tile], row0 = tile_row0[tile];
@@ -181,8 +185,17 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     const int* table = block_table + (size_t)seg * table_width;
     const int first_pos = pos0 + row0, last_pos = first_pos + rows - 1;
     const int lowest = window > 0 ? max(0, first_pos - window + 1) : 0;
-    const int tile_begin = lowest / FA_KEYS, tile_end = last_pos / FA_KEYS;   // inclusive
-    const int tiles = tile_end - tile_begin + 1;
+    // An item with many key tiles is cut into parts of equal length; each part is a unit of its
+    // own (its state goes to scratch memory, the part that finishes last merges them in part order).
+    const int item_begin = lowest / FA_KEYS, item_tiles = last_pos / FA_KEYS - item_begin + 1;
+    const int parts = min(max_parts, (item_tiles + tiles_per_unit - 1) / tiles_per_unit);
+    if (part >= parts) {
+      __syncthreads();              // item_shared is rewritten by the next draw
+      continue;
+    }
+    const int per_part = (item_tiles + parts - 1) / parts;
+    const int tile_begin = item_begin + part * per_part;
+    const int tiles = min(per_part, item_tiles - part * per_part);
 
     if (warp == 4) {
       // ------------------------------------------------------------ loads and MMAs
@@ -377,19 +390,65 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         for (int c = 0; c < FA_D; c += 16) fa_tmem_load16(lane_base + (2 + (t & 1u)) * FA_KEYS + c, reinterpret_cast<uint32_t*>(pv) + c);
         fa_tmem_wait_ld();
         fa_fence_before();
-        if (r < rows) {
-          const float inv = 1.f / l;
-          bf16* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * FA_D;
+        if (parts == 1) {
+          if (r < rows) {
+            const float inv = 1.f / l;
+            bf16* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * FA_D;
 #pragma unroll
-          for (int chunk = 0; chunk < 8; ++chunk) {
-            uint32_t packed[4];
+            for (int chunk = 0; chunk < 8; ++chunk) {
+              uint32_t packed[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 pair = __floats2bfloat162_rn((o[chunk * 8 + 2 * e] + pv[chunk * 8 + 2 * e]) * inv,
-                                                          (o[chunk * 8 + 2 * e + 1] + pv[chunk * 8 + 2 * e + 1]) * inv);
-              packed[e] = *reinterpret_cast<uint32_t*>(&pair);
+              for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 pair = __floats2bfloat162_rn((o[chunk * 8 + 2 * e] + pv[chunk * 8 + 2 * e]) * inv,
+                                                            (o[chunk * 8 + 2 * e + 1] + pv[chunk * 8 + 2 * e + 1]) * inv);
+                packed[e] = *reinterpret_cast<uint32_t*>(&pair);
+              }
+              *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        } else {
+          // this part's state of row r: running max, sum, unnormalised output; laid out
+          // [value][row] so that the 128 threads write and read neighbouring addresses
+          constexpr int STATE = FA_D + 2;
+          float* states = scratch + (size_t)item * max_parts * STATE * FA_ROWS + r;
+          float* mine = states + (size_t)part * STATE * FA_ROWS;
+          mine[0] = m;
+          mine[FA_ROWS] = l;
+#pragma unroll
+          for (int d = 0; d < FA_D; ++d) mine[(2 + d) * FA_ROWS] = o[d] + pv[d];
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 0) last_shared = (atomicAdd(&counters[item], 1) == parts - 1);
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (last_shared) {
+            __threadfence();
+            float m_all = -INFINITY;
+            for (int q = 0; q < parts; ++q) m_all = fmaxf(m_all, __ldcg(states + (size_t)q * STATE * FA_ROWS));
+            if (r < rows && m_all != -INFINITY) {
+              float l_all = 0.f;
+#pragma unroll
+              for (int d = 0; d < FA_D; ++d) o[d] = 0.f;
+              for (int q = 0; q < parts; ++q) {              // in part order
+                const float* theirs = states + (size_t)q * STATE * FA_ROWS;
+                const float factor = fa_exp2(__ldcg(theirs) - m_all);      // a part that saw nothing: 0
+                l_all = fmaf(__ldcg(theirs + FA_ROWS), factor, l_all);
+#pragma unroll
+                for (int d = 0; d < FA_D; ++d) o[d] = fmaf(__ldcg(theirs + (2 + d) * FA_ROWS), factor, o[d]);
+              }
+              const float inv = 1.f / l_all;
+              bf16* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * FA_D;
+#pragma unroll
+              for (int chunk = 0; chunk < 8; ++chunk) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 pair = __floats2bfloat162_rn(o[chunk * 8 + 2 * e] * inv, o[chunk * 8 + 2 * e + 1] * inv);
+                  packed[e] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              }
+            }
+            if (threadIdx.x == 0) counters[item] = 0;       // ready for the next launch
           }
         }
       }
@@ -424,16 +483,24 @@ using namespace mlr;
 
 MLR_DEFINE_PDL_SWITCH
 
+// Units of work aimed at per resident CTA when items are cut into parts (for measurements).
+static int units_per_cta = 2;
+MLR_EXPORT void mlr_attention_prefill_tcgen05_tune(int units) { units_per_cta = units < 1 ? 1 : units; }
+
 // Prompt portions, head_dim 64, page_size a power of two >= 8.  q, out: [q_rows, heads * 64]
 // bfloat16; pools [pool_pages, kv_heads, page_size, 64]; tile_seg / tile_row0: tiles of up to 128 rows
 // of one segment, best ordered by falling key count; queue: two zeroed ints in device memory
-// (left zeroed); error_word: host-visible int that receives a code if a wait runs out.
+// (left zeroed); error_word: host-visible int that receives a code if a wait runs out; max_kv_len:
+// the longest key range of the step; scratch (scratch_bytes) and counters (counters_len zeroed ints,
+// left zeroed): room for the states of items that are cut into parts, may be null.
 MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out,
                                              const int* tile_seg, const int* tile_row0, const int* seg_q_start,
                                              const int* seg_q_len, const int* seg_pos0, const int* block_table,
                                              int table_width, int tiles, int q_rows, int heads, int kv_heads,
                                              int head_dim, int page_size, int pool_pages, int window, float scale,
-                                             int* queue, int* error_word, cudaStream_t stream) {
+                                             int max_kv_len, int* queue, int* error_word, void* scratch,
+                                             long long scratch_bytes, int* counters, int counters_len,
+                                             cudaStream_t stream) {
   if (tiles == 0) return MLR_OK;
   if (tiles < 0 || q_rows <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 ||
       table_width <= 0 || pool_pages <= 0 || queue == nullptr || error_word == nullptr)
@@ -459,9 +526,27 @@ MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, 
     configured = true;
   }
   const long long items = (long long)tiles * heads;
-  const int ctas = (int)(items < 148 * 2 ? items : 148 * 2);
+  // Few items with long key ranges (one prompt of a few thousand tokens) would leave the launch as
+  // long as its heaviest item: cut items into up to 8 parts so that about two units per resident CTA
+  // exist.  Needs scratch for the parts' states and one counter per item; without them, no cutting.
+  const int resident = 148 * 2;
+  const int max_key_tiles = max_kv_len > 0 ? max_kv_len / FA_KEYS + 1 : 1;
+  int parts_target = (int)((units_per_cta * resident + items - 1) / items);
+  parts_target = parts_target < 1 ? 1 : (parts_target > 8 ? 8 : parts_target);
+  int tiles_per_unit = (max_key_tiles + parts_target - 1) / parts_target;
+  if (tiles_per_unit < 4) tiles_per_unit = 4;
+  int max_parts = (max_key_tiles + tiles_per_unit - 1) / tiles_per_unit;
+  if (max_parts > 8) max_parts = 8;
+  const long long need = items * max_parts * FA_ROWS * (FA_D + 2) * (long long)sizeof(float);
+  if (max_parts > 1 && (scratch == nullptr || counters == nullptr || need > scratch_bytes || items > counters_len)) {
+    max_parts = 1;
+    tiles_per_unit = 1 << 30;
+  }
+  const long long units = items * max_parts;
+  const int ctas = (int)(units < resident ? units : resident);
   launch_kernel(prefill_attention_tcgen05_kernel, dim3(ctas), dim3(FA_THREADS), shared, stream, q_map, k_map, v_map,
                 (bf16*)out, tile_seg, tile_row0, seg_q_start, seg_q_len, seg_pos0, block_table, table_width, tiles, heads,
-                kv_heads, page_size, page_shift, window, scale * 1.4426950408889634f, queue, error_word);
+                kv_heads, page_size, page_shift, window, scale * 1.4426950408889634f, queue, error_word, max_parts,
+                tiles_per_unit, (float*)scratch, counters);
   return launch_status();
 }

@@ -128,6 +128,7 @@ class CudaOps:
         self.use_fused_norm = True
         self.use_tma_attention = True
         self.use_fused_rope = True
+        self.split_prefill_items = True     # the tcgen05 prompt attention may cut long items into parts
         # MLR_TCGEN05_ATTENTION=0 in the environment keeps prompt attention on the mma.sync kernels
         self.use_tcgen05_attention = os.environ.get("MLR_TCGEN05_ATTENTION", "1") != "0"
         self.decode_stages = None      # tiles in flight per CTA of the bulk-copy decode kernel (None: its default)
@@ -145,6 +146,9 @@ class CudaOps:
                 # written by a kernel whose bounded wait ran out; read by the host without a copy
                 "error_word": torch.zeros(1, dtype=torch.int32).pin_memory(),
                 "prefill_queue": torch.zeros(2, dtype=torch.int32, device=device),
+                # states of prompt-attention items that are cut into parts, and one counter per item
+                "prefill_scratch": torch.empty(64 << 20, dtype=torch.uint8, device=device),
+                "prefill_counters": torch.zeros(1 << 16, dtype=torch.int32, device=device),
             }
         return self._workspaces[index]
 
@@ -454,7 +458,10 @@ class CudaOps:
                     _ptr(batch.big_tile_row0), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
                     _ptr(batch.block_table), batch.block_table.shape[1], batch.num_big_tiles, q.shape[0], num_heads,
                     num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0), ctypes.c_float(scale),
-                    _ptr(space["prefill_queue"]), _ptr(space["error_word"]), _stream()),
+                    int(batch.max_kv_len), _ptr(space["prefill_queue"]), _ptr(space["error_word"]),
+                    _ptr(space["prefill_scratch"] if self.split_prefill_items else None),
+                    ctypes.c_longlong(space["prefill_scratch"].numel()),
+                    _ptr(space["prefill_counters"]), space["prefill_counters"].numel(), _stream()),
                     "prefill attention (tcgen05)")
             elif (batch.num_wide_tiles > 0 and self.use_tma_attention and page_size >= 8
                     and page_size & (page_size - 1) == 0):
