@@ -524,6 +524,37 @@ def test_prefill_attention_tensor_cores(heads, kv_heads, head_dim, page, window)
     assert_close(third, got, torch.bfloat16, "mma.sync prefill kernel against the default kernel")
 
 
+@pytest.mark.parametrize("heads,kv_heads,page", [(2, 1, 16), (6, 2, 64)])
+@pytest.mark.parametrize("window", [None, 333])
+def test_prefill_attention_items_cut_into_parts(heads, kv_heads, page, window):
+    """Few query tiles with long key ranges: the tcgen05 kernel cuts each item's keys into up to
+    eight parts that different CTAs take and the last one merges.  One far key is made dominant so
+    that a part that is dropped or merged with the wrong weight shows."""
+    head_dim = 64
+    segments = [(0, 1500), (1900, 150), (640, 1)]
+    q, k_pool, v_pool, batch, table = make_attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, segments, 57)
+    if window is None:
+        # row 1499 of the first request: key 70 dominates (its k is the scaled query of head 0)
+        direction = q[1499, :head_dim].float()
+        pg, off = table[0, 70 // page], 70 % page
+        k_pool[pg, 0, off] = (direction * (40.0 / direction.norm() ** 2 * math.sqrt(head_dim))).to(torch.bfloat16)
+        v_pool[pg, 0, off] = torch.full((head_dim,), 100.0).to(torch.bfloat16)
+    got, want = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    assert_close(got, want, torch.bfloat16, f"prompt attention with items in parts, window={window}")
+    if window is None:
+        assert float(got[1499, :head_dim].float().mean()) > 90.0, "the dominant far key was lost"
+    again, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+    assert torch.equal(got, again), "parts are merged in part order: same bits every time"
+    cuda().split_prefill_items = False
+    try:
+        whole, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, window)
+    finally:
+        cuda().split_prefill_items = True
+    assert_close(got, whole, torch.bfloat16, "items in parts against whole items")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 5, 16, 33, 1000])
 def test_attention_window_edge(dtype, window):
