@@ -40,9 +40,32 @@ sample_kernel(const float* logits, const float* __restrict__ temperatures,
   // ---- argmax with the lowest index on ties (also gives the softmax's max)
   float best = -INFINITY;
   int best_index = vocab;
-  for (int i = threadIdx.x; i < vocab; i += SAMPLE_THREADS) {
-    const float v = row[i];
-    if (v > best) { best = v; best_index = i; }  // ascending i: the first maximum is kept
+  if ((vocab & 3) == 0) {
+    // 16-byte loads, four rounds in flight: the row is walked by one CTA, so the loop is a chain of
+    // load latencies and fewer, wider rounds are what shortens it
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int pieces = vocab >> 2;
+    for (int p0 = threadIdx.x; p0 < pieces; p0 += 4 * SAMPLE_THREADS) {
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int p = p0 + j * SAMPLE_THREADS;
+        v[j] = p < pieces ? row4[p] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {              // ascending index within the thread: the first maximum is kept
+        const int i = (p0 + j * SAMPLE_THREADS) * 4;
+        if (v[j].x > best) { best = v[j].x; best_index = i; }
+        if (v[j].y > best) { best = v[j].y; best_index = i + 1; }
+        if (v[j].z > best) { best = v[j].z; best_index = i + 2; }
+        if (v[j].w > best) { best = v[j].w; best_index = i + 3; }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += SAMPLE_THREADS) {
+      const float v = row[i];
+      if (v > best) { best = v; best_index = i; }  // ascending i: the first maximum is kept
+    }
   }
 #pragma unroll
   for (int offset = 16; offset > 0; offset >>= 1) {
