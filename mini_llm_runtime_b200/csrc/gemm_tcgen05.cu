@@ -476,7 +476,7 @@ struct GemmPlan { int bn, tiles, splits, stages, kb_per_split; };
 // Overrides for measurements (0 = the planner decides): tile width and ring depth of many-row products.
 static int forced_bn = 0, forced_stages = 0, forced_splits = 0;
 
-static GemmPlan plan_gemm(int M, int N, int K) {
+static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
   GemmPlan plan;
   const int total_kb = (K + TILE_K - 1) / TILE_K;
   if (M <= 128) {
@@ -513,7 +513,16 @@ static GemmPlan plan_gemm(int M, int N, int K) {
       if (cost < best) { best = cost; splits = candidate; }
     }
   }
-  if (M <= 128 && forced_splits >= 1 && forced_splits <= 16 && forced_splits <= total_kb) splits = forced_splits;
+  if (M > 128 && M <= 1024 && plan.tiles < 148 && total_kb >= 32 && !swiglu) {   // (that epilogue reads tensor memory only)
+    // A prompt portion of a few hundred rows times a long K has too few tiles for the SMs: cut K.
+    // Measured 896 x 4864: 512 rows 29.1 -> 19.4 us with 4 splits, 1,024 rows 30.2 -> 24.8 us with 2;
+    // at 2,048 rows (112 tiles) the reduction costs more than it saves (31 -> 39 us).
+    splits = 148 / plan.tiles;          // one CTA per SM: more splits only add to the reduction
+    if (splits > 4) splits = 4;
+    if (splits < 1) splits = 1;
+    while (splits > 1 && (long long)plan.tiles * splits * plan.bn * TILE_ROWS * 4 > (24ll << 20)) --splits;
+  }
+  if (forced_splits >= 1 && forced_splits <= 16 && forced_splits <= total_kb && !(swiglu && M > 128)) splits = forced_splits;
   plan.kb_per_split = (total_kb + splits - 1) / splits;
   plan.splits = (total_kb + plan.kb_per_split - 1) / plan.kb_per_split;   // no empty split
   // A ring as deep as the split is long (at most 6 stages) leaves room for several CTAs per SM,
@@ -550,8 +559,8 @@ MLR_EXPORT void mlr_gemm_tcgen05_tune_splits(int splits) { forced_splits = split
 
 // Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
 // `splits_out` receives the split count the launcher will use, `tiles_out` the number of tiles.
-MLR_EXPORT long long mlr_gemm_tcgen05_plan(int M, int N, int K, int* splits_out, int* tiles_out) {
-  const GemmPlan plan = plan_gemm(M, N, K);
+MLR_EXPORT long long mlr_gemm_tcgen05_plan(int M, int N, int K, int swiglu, int* splits_out, int* tiles_out) {
+  const GemmPlan plan = plan_gemm(M, N, K, swiglu != 0);
   if (splits_out) *splits_out = plan.splits;
   if (tiles_out) *tiles_out = plan.tiles;
   return plan.splits > 1 ? (long long)plan.tiles * plan.splits * plan.bn * TILE_ROWS * 4 : 0;
@@ -569,7 +578,7 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
   if (M < 0 || N <= 0 || K <= 0) return MLR_BAD_SIZE;
   if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MLR_BAD_ALIGNMENT;
   if (swiglu && (N % 128 != 0 || bias != nullptr || out_f32)) return MLR_BAD_SIZE;
-  const GemmPlan plan = plan_gemm(M, N, K);
+  const GemmPlan plan = plan_gemm(M, N, K, swiglu != 0);
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.k_blocks_per_split = plan.kb_per_split;

@@ -371,7 +371,7 @@ class CudaOps:
         lib = build.load_library("gemm_tcgen05")
         lib.mlr_gemm_tcgen05_plan.restype = ctypes.c_longlong
         splits, tiles = ctypes.c_int(0), ctypes.c_int(0)
-        need = lib.mlr_gemm_tcgen05_plan(M, N, K, ctypes.byref(splits), ctypes.byref(tiles))
+        need = lib.mlr_gemm_tcgen05_plan(M, N, K, int(swiglu), ctypes.byref(splits), ctypes.byref(tiles))
         space = self._workspace(x.device)
         if need > space["gemm_scratch"].numel() or (splits.value > 1 and tiles.value > space["gemm_counters"].numel()):
             return None
