@@ -90,6 +90,7 @@ class StepContext:
     segment_slots: torch.Tensor      # int32 [segments]: each request's state slot
     views: dict[int, CacheView] = field(default_factory=dict)
     sampling: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None
+    wanted_all_rows: bool = False    # wanted_rows is 0, 1, .., rows-1 (a decode step): no gather needed
 
     def cache_view(self, entry: int) -> CacheView:
         return self.views[entry]
@@ -307,7 +308,9 @@ class ModelRunner:
                             int(position_start[i])) for i, e in enumerate(entries)]
         ctx = StepContext(ops=ops.current(), num_rows=total, num_wanted=int(wanted_rows.shape[0]),
                           segments=segments, token_ids=dev["token_ids"], positions=dev["positions"],
-                          wanted_rows=dev["wanted_rows"], segment_slots=dev["seg_slots"])
+                          wanted_rows=dev["wanted_rows"], segment_slots=dev["seg_slots"],
+                          wanted_all_rows=(wanted_rows.shape[0] == total
+                                           and bool((wanted_rows == np.arange(total, dtype=np.int32)).all())))
         if sampling is not None:
             ctx.sampling = (dev["temperatures"], dev["seeds"], dev["token_indices"])
         batches = {}

@@ -108,9 +108,12 @@ class DecoderModel:
         if ctx.num_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
         k = ctx.ops
-        rows = k.gather_rows(residual, ctx.wanted_rows)
+        everything = getattr(ctx, "wanted_all_rows", False)      # every row in order (a decode step)
+        rows = residual if everything else k.gather_rows(residual, ctx.wanted_rows)
         if pending is None:
             normed = self.final_norm.forward(rows)
         else:
-            normed = self.final_norm.add_forward(rows, k.gather_rows(pending, ctx.wanted_rows))
+            delta = pending if everything else k.gather_rows(pending, ctx.wanted_rows)
+            # the stream itself must stay as it is only if it is read again; it is not after the last layer
+            normed = self.final_norm.add_forward(rows, delta)
         return self.head.forward(normed, self.embedding)
