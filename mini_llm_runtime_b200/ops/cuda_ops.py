@@ -120,6 +120,8 @@ class CudaOps:
 
     def __init__(self) -> None:
         self._workspaces: dict[int, dict[str, torch.Tensor]] = {}
+        # Switches for tests and measurements: each takes one kernel family out, and the next one
+        # in line (see the dispatch in linear / paged_attention) serves instead.
         self.use_tensor_cores = True
         self.use_decode_kernel = True
         self.use_mma_attention = True
