@@ -1,20 +1,26 @@
 #!/usr/bin/env python3
-"""Benchmark of the engine on one B200: decode tokens per second at batch 8 (the headline value),
-the same through the Python entry point with host tokens in and out (``e2e``), decode at batch 1
-and 64, a 2,048-token prefill, and the fraction of the roofline each reaches.
+"""Benchmark of the engine on one B200.
 
     python bench.py --gpus 1 --steps K --warmup W          # this engine
     python bench.py --impl reference ...                   # the unmodified reference, if installed
 
-The model has the layer sizes of Qwen2.5-0.5B (BASELINE.json configs[2]) with seeded random
-weights; prompts are seeded uniform-random token ids.  A step is one decode step of the whole
-batch.  Requests start from a prefix chosen so that the timed steps are centred on a context of
-3,072 tokens (a 2,048-token prefix growing to 4,096).  One JSON line is printed.
+The headline is decode tokens per second at batch 8 on the layer sizes of Qwen2.5-0.5B (24 layers,
+context 4,096, random weights; ``--size`` picks 7b or 14b instead), timed on the device as R regions
+of exactly K decode steps each; the median region is the value and the raw samples are listed.  The
+same line carries: the same metric through the Python entry point with host tokens in and out
+(``e2e``), a 2,048-token prefill, decode at batch 1 and 64, the fraction of the measured roofline
+each reaches, and (unless ``--skip-sizes``) points for the 7B and 14B layer sizes: decode at batch
+1 / 8 / 64, prefill, a mixed step of 8 decodes beside a 512-token prompt portion (7B), and a
+continuous-batching run of 64 requests (14B).  One JSON line is printed.
+
+A step is one decode step of the whole batch.  Requests start from a prefix chosen so that the
+timed steps are centred on a context of 3,072 tokens (a 2,048-token prefix growing to 4,096).
 """
 
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -37,29 +43,33 @@ MODEL_SIZES = {
                 rms_norm_eps=1e-5, rope_theta=1000000.0, hidden_act="silu", tie_word_embeddings=False),
 }
 MODEL_NAMES = {"0.5b": "Qwen2.5-0.5B sizes", "7b": "Qwen2.5-7B sizes", "14b": "Qwen2.5-14B sizes"}
-SIZES = MODEL_SIZES["0.5b"]      # the default workload (BASELINE.json configs[2]); --size replaces it
 CONTEXT = 4096
 CONTEXT_MEAN = 3072
 PREFILL_TOKENS = 2048
 BLOCK_SIZE = 16
+REPEATS = 5
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
 def parse_args():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--steps", type=int, default=32)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--size", choices=sorted(MODEL_SIZES), default="0.5b",
-                        help="layer sizes: Qwen2.5-0.5B (default, the headline workload), 7B or 14B")
+                        help="layer sizes of the headline: Qwen2.5-0.5B (default), 7B or 14B")
     parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the model has (both numbers are reported)")
+    parser.add_argument("--repeats", type=int, default=REPEATS, help="timed regions of --steps steps each")
     parser.add_argument("--skip-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--skip-sizes", action="store_true", help="skip the points at the 7B and 14B layer sizes")
     parser.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profiling)")
+    parser.add_argument("--no-arena", action="store_true",
+                        help="place the weights without first touching one block of their total size (A/B)")
     parser.add_argument("--context-mean", type=int, default=CONTEXT_MEAN,
                         help="context length the timed steps are centred on (default 3072)")
     return parser.parse_args()
@@ -79,13 +89,17 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks, utilisation and throttle reasons with nvidia-smi from start to stop; the
+    summary is taken over the samples during which the GPU was busy."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    QUERY = ("clocks.sm,clocks.max.sm,utilization.gpu,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self):
         self.process = None
+        self.samples = []
 
     def __enter__(self):
         try:
@@ -97,7 +111,6 @@ class ClockSampler:
         return self
 
     def __exit__(self, *exc):
-        self.samples = []
         if self.process is None:
             return
         self.process.terminate()
@@ -108,16 +121,49 @@ class ClockSampler:
             output, _ = self.process.communicate()
         for line in output.splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6 and parts[0].isdigit():
+            if len(parts) == 7 and parts[0].isdigit():
                 self.samples.append(parts)
 
     def summary(self):
-        if not getattr(self, "samples", None):
+        if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [name for i, name in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": statistics.median(int(s[0]) for s in self.samples),
-                "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons}
+        busy = [s for s in self.samples if s[2].isdigit() and int(s[2]) >= 10] or self.samples
+        reasons = [name for i, name in enumerate(self.NAMES) if any(s[3 + i].lower().startswith("active") for s in busy)]
+        return {"sm_mhz": statistics.median(int(s[0]) for s in busy), "sm_max_mhz": int(busy[0][1]),
+                "reasons": reasons, "samples": len(busy)}
+
+
+def environment():
+    """Where the number was taken: GPU, driver, CUDA, torch, and what source it was (the git head
+    where the checkout has one, else a hash over the package's sources)."""
+    import torch
+
+    record = {"torch": torch.__version__, "cuda": torch.version.cuda, "python": sys.version.split()[0]}
+    try:
+        record["gpu"] = torch.cuda.get_device_name(0)
+        record["sm_count"] = torch.cuda.get_device_properties(0).multi_processor_count
+        record["driver"] = subprocess.run(["nvidia-smi", "--query-gpu=driver_version", "--format=csv,noheader"],
+                                          capture_output=True, text=True, timeout=20).stdout.strip().splitlines()[0]
+    except Exception:  # noqa: BLE001
+        pass
+    try:
+        head = subprocess.run(["git", "-C", ROOT, "rev-parse", "--short=12", "HEAD"], capture_output=True, text=True,
+                              timeout=20)
+        if head.returncode == 0 and head.stdout.strip():
+            record["git_head"] = head.stdout.strip()
+    except Exception:  # noqa: BLE001
+        pass
+    digest = hashlib.sha256()
+    package = os.path.join(ROOT, "mini_llm_runtime_b200")
+    for folder, _, files in sorted(os.walk(package)):
+        if "_build" in folder or "__pycache__" in folder:
+            continue
+        for name in sorted(files):
+            if name.endswith((".py", ".cu", ".cuh", ".h")):
+                with open(os.path.join(folder, name), "rb") as handle:
+                    digest.update(name.encode() + handle.read())
+    record["source_sha16"] = digest.hexdigest()[:16]
+    return record
 
 
 def model_numbers(config, layers):
@@ -125,29 +171,12 @@ def model_numbers(config, layers):
     hq, hkv, d = config.num_attention_heads, config.num_key_value_heads, config.head_dim
     per_layer = (hq + 2 * hkv) * d * h + (hq + 2 * hkv) * d + h * hq * d + 3 * h * i + 2 * h
     head = v * h          # the head's matrix is read once per step, tied to the embedding or not
-    weight_bytes = 2 * (layers * per_layer + head + h)
-    kv_bytes_per_token = 2 * layers * hkv * d * 2
-    linear_flops_per_token = 2 * layers * ((hq + 2 * hkv) * d * h + h * hq * d + 3 * h * i)
-    return {"weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token,
-            "linear_flops_per_token": linear_flops_per_token, "head_flops_per_row": 2 * head,
-            "attention_flops_per_layer": lambda t: 2 * t * t * hq * d}
-
-
-def build_runner(layers, max_requests, tokens_per_request):
-    import torch
-
-    from mini_llm_runtime_b200.cache import CacheManager
-    from mini_llm_runtime_b200.config import Qwen2Config
-    from mini_llm_runtime_b200.engine import ModelRunner
-    from mini_llm_runtime_b200.models import random_model
-
-    config = Qwen2Config(**dict(SIZES, num_hidden_layers=layers))
-    model = random_model(config, seed=0, dtype=torch.bfloat16, device="cuda:0")
-    pages = max_requests * -(-tokens_per_request // BLOCK_SIZE)
-    cache = CacheManager(model.cache_needs(), page_size=BLOCK_SIZE, num_pages=pages, max_requests=max_requests,
-                         max_tokens_per_request=tokens_per_request, dtype=torch.bfloat16, device="cuda:0",
-                         max_step_tokens=PREFILL_TOKENS)
-    return config, model, ModelRunner(model, cache)
+    return {"weight_bytes": 2 * (layers * per_layer + head + h),
+            "kv_bytes_per_token": 2 * layers * hkv * d * 2,
+            "linear_flops_per_token": 2 * layers * ((hq + 2 * hkv) * d * h + h * hq * d + 3 * h * i),
+            "head_flops_per_row": 2 * head,
+            # causal attention of `rows` new rows on top of `before` cached ones: QK^T and PV
+            "attention_flops": lambda rows, before=0: layers * 4 * hq * d * (rows * before + rows * (rows + 1) // 2)}
 
 
 def random_tokens(count, vocab, seed):
@@ -157,80 +186,129 @@ def random_tokens(count, vocab, seed):
     return torch.randint(0, vocab, (count,), generator=generator).tolist()
 
 
-def fill(runner, request_ids, prefix, vocab):
-    """Bring every request's cache to ``prefix`` tokens with real prefill steps."""
+class Workbench:
+    """One model of the given layer sizes with random weights drawn on the device, and runners on it."""
+
+    def __init__(self, size, layers=None, arena=True):
+        import torch
+
+        from mini_llm_runtime_b200.config import Qwen2Config
+        from mini_llm_runtime_b200.models import random_model
+
+        self.size = size
+        self.sizes = MODEL_SIZES[size]
+        self.layers = layers or self.sizes["num_hidden_layers"]
+        self.config = Qwen2Config(**dict(self.sizes, num_hidden_layers=self.layers))
+        self.model = random_model(self.config, seed=0, dtype=torch.bfloat16, device="cuda:0", draw_on_device=True,
+                                  arena=arena)
+        self.numbers = model_numbers(self.config, self.layers)
+
+    def runner(self, max_requests, tokens_per_request, pages=None):
+        import torch
+
+        from mini_llm_runtime_b200.cache import CacheManager
+        from mini_llm_runtime_b200.engine import ModelRunner
+
+        pages = pages or max_requests * -(-tokens_per_request // BLOCK_SIZE)
+        cache = CacheManager(self.model.cache_needs(), page_size=BLOCK_SIZE, num_pages=pages,
+                             max_requests=max_requests, max_tokens_per_request=tokens_per_request,
+                             dtype=torch.bfloat16, device="cuda:0", max_step_tokens=PREFILL_TOKENS)
+        return ModelRunner(self.model, cache)
+
+    def close(self):
+        import torch
+
+        self.model = None
+        torch.cuda.empty_cache()
+
+
+def fill(runner, request_ids, prefix, vocab, real_prefill):
+    """Bring every request's cache to ``prefix`` tokens: with real prefill steps, or (for the large
+    sizes, where prefill of every request would take longer than everything timed) by declaring the
+    length and filling the pools with random keys and values; a decode step reads the same bytes
+    either way."""
     from mini_llm_runtime_b200.engine import StepEntry
 
     for index, rid in enumerate(request_ids):
         runner.cache.create_request(rid)
-        tokens = random_tokens(prefix, vocab, 1000 + index)
-        for start in range(0, prefix, PREFILL_TOKENS):
-            runner.step([StepEntry(rid, tokens[start:start + PREFILL_TOKENS], [])])
+        if real_prefill:
+            tokens = random_tokens(prefix, vocab, 1000 + index)
+            for start in range(0, prefix, PREFILL_TOKENS):
+                runner.step([StepEntry(rid, tokens[start:start + PREFILL_TOKENS], [])])
+        else:
+            runner.cache.adopt(rid, prefix)
+    if not real_prefill:
+        for group in runner.cache.groups:
+            group.key.normal_(0.0, 0.5)
+            group.value.normal_(0.0, 0.5)
 
 
-def time_decode(runner, request_ids, vocab, steps, warmup, clocks=None):
-    """Device time of ``steps`` decode steps of the whole batch (CUDA events), after ``warmup``."""
+def time_regions(run_region, repeats):
+    """Device time (CUDA events) of ``repeats`` regions; returns the samples in ms."""
     import torch
 
-    from mini_llm_runtime_b200.engine import SamplingRows, StepEntry
+    samples = []
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        run_region()
+        end.record()
+        torch.cuda.synchronize()
+        samples.append(start.elapsed_time(end))
+    return samples
+
+
+def decode_point(bench, batch, steps, warmup, repeats, context_mean=CONTEXT_MEAN, graphs=True, real_prefill=True):
+    """Median device time per decode step at this batch size, the raw samples, kernels launched in
+    one region, and the bytes a step has to read."""
+    import torch
+
+    from mini_llm_runtime_b200.engine import StepEntry
     from mini_llm_runtime_b200.ops import cuda_ops
 
-    batch = len(request_ids)
-    sampling = SamplingRows([0.0] * batch, [0] * batch, [0] * batch)
-    tokens = random_tokens(batch, vocab, 7)
+    total_steps = warmup + repeats * steps
+    prefix = max(1, context_mean - total_steps // 2)
+    runner = bench.runner(batch, max(CONTEXT, prefix + total_steps + 1))
+    runner.use_graphs = runner.use_graphs and graphs
+    ids = [f"d{i}" for i in range(batch)]
+    fill(runner, ids, prefix, bench.config.vocab_size, real_prefill)
+    entries = [StepEntry(rid, [0], [0]) for rid in ids]
 
     def one_step():
-        # borrow: the step hands out its own output buffers (what the engine does too), no copies
-        return runner.step([StepEntry(rid, [tokens[i]], [0]) for i, rid in enumerate(request_ids)], sampling, borrow=True)
+        # As the engine runs a decode step: tokens sampled on the device by slot, each request's input
+        # taken from its slot record (feed), the step's own output buffers handed out (borrow).
+        runner.step(entries, sample=True, borrow=True, feed=True)
 
     for _ in range(warmup):
         one_step()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches_before = cuda_ops.launches
-    replays_before = runner.graph_replays
-    if clocks is not None:
-        clocks.__enter__()            # sample clocks during the timed steps only
+    launches_before, replays_before = cuda_ops.launches, runner.graph_replays
     host_started = time.perf_counter()
-    start.record()
-    for _ in range(steps):
-        one_step()
-    end.record()
+    samples = time_regions(lambda: [one_step() for _ in range(steps)], repeats)
     host_ms = (time.perf_counter() - host_started) * 1e3
-    torch.cuda.synchronize()
-    if clocks is not None:
-        clocks.__exit__(None, None, None)
     launched = cuda_ops.launches - launches_before
-    launched += (runner.graph_replays - replays_before) * runner.launches_per_replay(batch, True)
-    print(f"[bench] batch {batch}: device {start.elapsed_time(end) / steps:.3f} ms/step, host issue "
-          f"{host_ms / steps:.3f} ms/step, graph replays {runner.graph_replays - replays_before}", file=sys.stderr)
-    return start.elapsed_time(end), launched
-
-
-def decode_point(layers, batch, steps, warmup, context_mean=CONTEXT_MEAN, graphs=True, clocks=None):
-    import torch
-
-    prefix = max(1, context_mean - (steps + warmup) // 2)
-    config, model, runner = build_runner(layers, batch, CONTEXT)
-    runner.use_graphs = runner.use_graphs and graphs
-    ids = [f"d{i}" for i in range(batch)]
-    fill(runner, ids, prefix, config.vocab_size)
-    torch.cuda.synchronize()
-    ms, launches = time_decode(runner, ids, config.vocab_size, steps, warmup, clocks)
+    launched += (runner.graph_replays - replays_before) * runner.launches_per_replay(batch, True, True)
+    runner.check_device()
     for rid in ids:
         runner.cache.release(rid)
-    del runner, model
+    del runner
     torch.cuda.empty_cache()
-    return ms, launches, prefix
+    ms_per_step = statistics.median(samples) / steps
+    step_bytes = bench.numbers["weight_bytes"] + batch * context_mean * bench.numbers["kv_bytes_per_token"]
+    print(f"[bench] {bench.size} batch {batch}: {ms_per_step:.3f} ms/step (median of {repeats} x {steps} steps; "
+          f"host {host_ms / (repeats * steps):.3f} ms/step)", file=sys.stderr)
+    return {"ms_per_step": ms_per_step, "samples_ms_per_step": [round(s / steps, 4) for s in samples],
+            "launches": launched // repeats, "prefix": prefix, "step_bytes": step_bytes,
+            "tokens_per_s": batch / (ms_per_step / 1e3)}
 
 
-def time_prefill(layers, repeats=5, warmup=3):
+def time_prefill(bench, repeats=REPEATS, warmup=3):
     import torch
 
     from mini_llm_runtime_b200.engine import StepEntry
 
-    config, model, runner = build_runner(layers, 2, PREFILL_TOKENS)
-    tokens = random_tokens(PREFILL_TOKENS, config.vocab_size, 99)
+    runner = bench.runner(2, PREFILL_TOKENS)
+    tokens = random_tokens(PREFILL_TOKENS, bench.config.vocab_size, 99)
     samples = []
     for attempt in range(warmup + repeats):
         runner.cache.create_request("p")
@@ -243,52 +321,170 @@ def time_prefill(layers, repeats=5, warmup=3):
         runner.cache.release("p")
         if attempt >= warmup:
             samples.append(start.elapsed_time(end))
-    del runner, model
+    runner.check_device()
+    del runner
     torch.cuda.empty_cache()
-    return statistics.median(samples)
+    ms = statistics.median(samples)
+    flops = (PREFILL_TOKENS * bench.numbers["linear_flops_per_token"] + bench.numbers["head_flops_per_row"]
+             + bench.numbers["attention_flops"](PREFILL_TOKENS))
+    return ms, flops, samples
 
 
-def time_e2e(layers, batch, steps, warmup):
-    """Decode tokens per second through ContinuousBatchEngine.step(): host token ids in, host
-    token ids out, every step copies its inputs from pinned memory and reads its tokens back."""
+def time_mixed_step(bench, peak, decodes=8, portion=512, context=CONTEXT_MEAN, repeats=REPEATS, warmup=3):
+    """One step of ``decodes`` decoded tokens (context ``context``) beside a ``portion``-token piece
+    of a longer prompt that already has tokens cached."""
     import torch
 
-    from mini_llm_runtime_b200.config import Qwen2Config
-    from mini_llm_runtime_b200.engine import ContinuousBatchEngine
-    from mini_llm_runtime_b200.models import random_model
+    from mini_llm_runtime_b200.engine import StepEntry
 
-    config = Qwen2Config(**dict(SIZES, num_hidden_layers=layers))
-    model = random_model(config, seed=0, dtype=torch.bfloat16, device="cuda:0")
-    prefix = CONTEXT_MEAN - (steps + warmup) // 2
-    # step_ahead: the engine launches each decode step behind the previous one, fed on the device
-    # with the tokens it chose; every step() still returns that step's tokens on the host
-    engine = ContinuousBatchEngine.from_model(model, block_size=BLOCK_SIZE, max_running_requests=batch,
+    runner = bench.runner(decodes + 1, max(CONTEXT, portion * (3 + warmup + repeats)))
+    ids = [f"m{i}" for i in range(decodes)]
+    fill(runner, ids, context, bench.config.vocab_size, real_prefill=False)
+    prompt = random_tokens(portion * (2 + warmup + repeats), bench.config.vocab_size, 5)
+    runner.cache.create_request("prompt")
+    runner.step([StepEntry("prompt", prompt[:portion], [])])
+    samples, cursor = [], portion
+    for attempt in range(warmup + repeats):
+        entries = [StepEntry(rid, [1], [0]) for rid in ids] + [StepEntry("prompt", prompt[cursor:cursor + portion], [])]
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step(entries, sample=True, borrow=True)
+        end.record()
+        torch.cuda.synchronize()
+        cursor += portion
+        if attempt >= warmup:
+            samples.append(start.elapsed_time(end))
+    runner.check_device()
+    del runner
+    torch.cuda.empty_cache()
+    ms = statistics.median(samples)
+    before = portion * (1 + warmup + repeats // 2)            # tokens the prompt has cached at the median sample
+    numbers = bench.numbers
+    rows = decodes + portion
+    flops = rows * numbers["linear_flops_per_token"] + decodes * numbers["head_flops_per_row"] \
+        + numbers["attention_flops"](portion, before) + decodes * numbers["attention_flops"](1, context)
+    step_bytes = numbers["weight_bytes"] + (decodes * context + before) * numbers["kv_bytes_per_token"]
+    return {"ms": round(ms, 3), "tokens": rows, "hbm_frac": round(step_bytes / (ms / 1e3) / 1e9 / peak["hbm_gbs"], 4),
+            "flops_frac": round(flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
+            "samples_ms": [round(s, 3) for s in samples]}
+
+
+def continuous_batching(bench, requests=64, budget=2048, seed=3):
+    """The engine under load: ``requests`` requests arrive at once, prompt lengths uniform in
+    [128, 2048], generation lengths cycling 32/64/128/256, at most ``budget`` tokens per step."""
+    import random
+
+    import torch
+
+    from mini_llm_runtime_b200.engine import ContinuousBatchEngine
+
+    rng = random.Random(seed)
+    lengths = [rng.randint(128, 2048) for _ in range(requests)]
+    generate = [(32, 64, 128, 256)[i % 4] for i in range(requests)]
+    engine = ContinuousBatchEngine.from_model(bench.model, block_size=BLOCK_SIZE, max_running_requests=requests,
+                                              max_batch_tokens=budget, max_model_len=2048 + 256, step_ahead=True)
+    engine.generate([random_tokens(64, bench.config.vocab_size, 1)] * 2, max_new_tokens=4)     # warm-up
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    for index in range(requests):
+        engine.submit(f"c{index}", random_tokens(lengths[index], bench.config.vocab_size, 3000 + index),
+                      max_new_tokens=generate[index])
+    steps = engine.run()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - started
+    timelines = [engine.metrics.get(f"c{index}") for index in range(requests)]
+    tokens = sum(len(t.token_ids) for t in timelines)
+    del engine
+    torch.cuda.empty_cache()
+    return {"tokens_per_s": round(tokens / seconds, 1), "seconds": round(seconds, 3), "steps": len(steps),
+            "generated_tokens": tokens, "prompt_tokens": sum(lengths),
+            "ttft_ms_median": round(statistics.median(t.ttft_ms for t in timelines), 2),
+            "tpot_ms_median": round(statistics.median(t.median_tpot_ms for t in timelines), 3)}
+
+
+def time_e2e(bench, batch, steps, warmup, repeats):
+    """Decode tokens per second through ContinuousBatchEngine.step(): host token ids in at submit,
+    host token ids out of every step; whatever a step has to send is copied from pinned memory, and
+    its tokens are read back.  The bytes sent are counted by the runner, not assumed."""
+    import torch
+
+    from mini_llm_runtime_b200.engine import ContinuousBatchEngine
+
+    total_steps = warmup + repeats * steps
+    prefix = CONTEXT_MEAN - total_steps // 2
+    # step_ahead: the engine launches each decode step behind the previous one (the device takes the
+    # inputs from the slot records); every step() still returns that step's tokens on the host
+    engine = ContinuousBatchEngine.from_model(bench.model, block_size=BLOCK_SIZE, max_running_requests=batch,
                                               max_batch_tokens=PREFILL_TOKENS, max_model_len=CONTEXT + 1024,
                                               step_ahead=True)
     # Requests that finish their prompt early decode while the others still prefill; leave room
     # for those extra tokens so that all of them are alive through the timed steps.
     slack = batch * (-(-prefix // PREFILL_TOKENS) + 1)
     for index in range(batch):
-        engine.submit(f"e{index}", random_tokens(prefix, config.vocab_size, 2000 + index),
-                      max_new_tokens=steps + warmup + 1 + slack)
-    while any(not engine.scheduler.get_request(f"e{i}").prefilled for i in range(batch)):
+        engine.submit(f"e{index}", random_tokens(prefix, bench.config.vocab_size, 2000 + index),
+                      max_new_tokens=total_steps + 1 + slack)
+    while any(not engine.scheduler.get_request(f"e{i}").prompt_done for i in range(batch)):
         engine.step()
     for _ in range(warmup):
         engine.step()
-    torch.cuda.synchronize()
-    started = time.perf_counter()
-    for _ in range(steps):
-        result = engine.step()
-        assert len(result.update.emitted_tokens) == batch
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - started
-    # per step: token ids, positions, segment table, slots, block tables ... (one packed buffer);
-    # back: one int32 token per request
-    table_width = -(-CONTEXT // BLOCK_SIZE)
-    h2d = 4 * batch * 8 + 8 * batch + 4 * batch * table_width + 20 * batch
-    del engine, model
+    samples = []
+    sent_before = engine.runner.bytes_sent
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        for _ in range(steps):
+            result = engine.step()
+            assert len(result.outcome.emitted_tokens) == batch
+        torch.cuda.synchronize()
+        samples.append(time.perf_counter() - started)
+    h2d = (engine.runner.bytes_sent - sent_before) / (repeats * steps)
+    del engine
     torch.cuda.empty_cache()
-    return batch * steps / seconds, h2d, 4 * batch
+    return (batch * steps / statistics.median(samples), round(h2d, 1), 4 * batch,
+            [round(batch * steps / s, 1) for s in samples])
+
+
+def headline_config(size, config, layers, batch, context_mean, peak_source):
+    """The flat ``config`` both arms print (at most 20 keys)."""
+    return {"model": MODEL_NAMES[size], "layers": layers, "layers_of_model": MODEL_SIZES[size]["num_hidden_layers"],
+            "hidden": config.hidden_size, "q_heads": config.num_attention_heads,
+            "kv_heads": config.num_key_value_heads, "head_dim": config.hidden_size // config.num_attention_heads,
+            "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+            "tied_head": config.tie_word_embeddings, "global_batch": batch, "seq_len": CONTEXT,
+            "context_mean": context_mean, "block_size": BLOCK_SIZE,
+            "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (weights + KV > 1 GB)", "peaks": peak_source}
+
+
+def size_points(size, args, peak, record):
+    """Points at another model size: decode at batch 1 / 8 / 64, prefill of 2,048 tokens, and the
+    workload named for that size (7B: a mixed step; 14B: continuous batching of 64 requests)."""
+    bench = Workbench(size, arena=not args.no_arena)
+    steps, repeats = min(args.steps, 16), 3
+    detail = {"layers": bench.layers, "weight_gb": round(bench.numbers["weight_bytes"] / 1e9, 2)}
+    for batch in (1, 8, 64):
+        point = decode_point(bench, batch, steps, 3, repeats, real_prefill=False)
+        achieved = point["step_bytes"] / (point["ms_per_step"] / 1e3) / 1e9
+        record["points"][f"{size}_decode_b{batch}"] = round(point["tokens_per_s"], 1)
+        record["points"][f"{size}_decode_b{batch}_hbm_frac"] = round(achieved / peak["hbm_gbs"], 4)
+        detail[f"decode_b{batch}"] = {"ms": round(point["ms_per_step"], 3),
+                                      "gb_per_step": round(point["step_bytes"] / 1e9, 2),
+                                      "hbm_frac": round(achieved / peak["hbm_gbs"], 4),
+                                      "samples_ms": point["samples_ms_per_step"]}
+    ms, flops, samples = time_prefill(bench, repeats=3, warmup=2)
+    frac = round(flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)
+    record["points"][f"{size}_prefill_2048"] = round(PREFILL_TOKENS / (ms / 1e3), 1)
+    record["points"][f"{size}_prefill_2048_frac"] = frac
+    detail["prefill_2048"] = {"ms": round(ms, 3), "frac": frac, "samples_ms": [round(s, 3) for s in samples]}
+    if size == "7b":
+        detail["mixed_8_decodes_512_portion"] = time_mixed_step(bench, peak)
+        record["points"]["7b_mixed_step_ms"] = detail["mixed_8_decodes_512_portion"]["ms"]
+    if size == "14b":
+        detail["continuous_64_requests"] = continuous_batching(bench)
+        record["points"]["14b_continuous_tokens_per_s"] = detail["continuous_64_requests"]["tokens_per_s"]
+    bench.close()
+    return detail
 
 
 def run_ours(args):
@@ -297,57 +493,54 @@ def run_ours(args):
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
         return 1
-    from mini_llm_runtime_b200.config import Qwen2Config
-
     peak = peaks()
-    layers = args.layers
-    config = Qwen2Config(**dict(SIZES, num_hidden_layers=layers))
-    numbers = model_numbers(config, layers)
-
-    clocks = ClockSampler()
-    ms, launches, prefix = decode_point(layers, args.batch, args.steps, args.warmup, args.context_mean,
-                                        not args.no_graphs, clocks)
-    ms_per_step = ms / args.steps
-    value = args.batch * args.steps / (ms / 1e3)
-    step_bytes = numbers["weight_bytes"] + args.batch * args.context_mean * numbers["kv_bytes_per_token"]
-    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
-
-    record = {
-        "metric": f"decode tokens/s (batch {args.batch}, context 4096)", "value": round(value, 1), "unit": "tokens/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic (seeded random weights and token ids)", "impl": "ours",
-        "config": {"model": MODEL_NAMES[args.size], "layers": layers, "layers_of_model": SIZES["num_hidden_layers"],
-                   "hidden": config.hidden_size, "q_heads": config.num_attention_heads,
-                   "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
-                   "intermediate": config.intermediate_size, "vocab": config.vocab_size, "tied_head": config.tie_word_embeddings,
-                   "global_batch": args.batch, "seq_len": CONTEXT, "context_mean": args.context_mean,
-                   "prefix": prefix, "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS,
-                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights + KV > 1 GB)",
-                   "peaks": peak["source"]},
-        "clocks": clocks.summary(),
-        "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / peak["hbm_gbs"], 4)},
-    }
-    if not args.skip_prefill:
-        prefill_ms = time_prefill(layers)
-        flops = PREFILL_TOKENS * numbers["linear_flops_per_token"] + numbers["head_flops_per_row"] \
-            + layers * numbers["attention_flops_per_layer"](PREFILL_TOKENS)
-        record["prefill"] = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
-                             "ms": round(prefill_ms, 3),
-                             "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)}
-    if not args.skip_points:
-        points = {}
-        for batch in (1, 64):
-            steps = min(args.steps, 64)
-            point_ms, _, _ = decode_point(layers, batch, steps, args.warmup)
-            points[f"decode_b{batch}"] = round(batch * steps / (point_ms / 1e3), 1)
-        record["points"] = points
-    if not args.skip_e2e:
-        e2e, h2d, d2h = time_e2e(layers, args.batch, args.steps, args.warmup)
-        record["e2e"] = {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                         "d2h_bytes_per_step": d2h}
+    with ClockSampler() as clocks:
+        bench = Workbench(args.size, args.layers, arena=not args.no_arena)
+        config, layers = bench.config, bench.layers
+        small = args.size == "0.5b"
+        head = decode_point(bench, args.batch, args.steps, args.warmup, args.repeats, args.context_mean,
+                            not args.no_graphs, real_prefill=small)
+        ms_per_step = head["ms_per_step"]
+        achieved = head["step_bytes"] / (ms_per_step / 1e3) / 1e9
+        record = {
+            "metric": f"decode tokens/s (batch {args.batch}, context 4096)", "value": round(head["tokens_per_s"], 1),
+            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)", "impl": "ours",
+            "config": headline_config(args.size, config, layers, args.batch, args.context_mean, peak["source"]),
+            "prefix": head["prefix"], "repeats": args.repeats, "samples_ms_per_step": head["samples_ms_per_step"],
+            "gpu_launches": head["launches"],
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / peak["hbm_gbs"], 4)},
+        }
+        if not args.skip_prefill:
+            prefill_ms, flops, samples = time_prefill(bench)
+            record["prefill"] = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                                 "ms": round(prefill_ms, 3),
+                                 "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
+                                 "samples_ms": [round(s, 3) for s in samples]}
+        record["points"] = {}
+        if not args.skip_points:
+            for batch in (1, 64):
+                point = decode_point(bench, batch, min(args.steps, 32), args.warmup, 3, real_prefill=small)
+                record["points"][f"decode_b{batch}"] = round(point["tokens_per_s"], 1)
+                record["points"][f"decode_b{batch}_hbm_frac"] = round(
+                    point["step_bytes"] / (point["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4)
+        if not args.skip_e2e:
+            e2e, h2d, d2h, samples = time_e2e(bench, args.batch, args.steps, args.warmup, args.repeats)
+            record["e2e"] = {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                             "d2h_bytes_per_step": d2h, "samples": samples}
+        bench.close()
+        if not args.skip_sizes and small:
+            record["sizes"] = {}
+            for size in ("7b", "14b"):
+                try:
+                    record["sizes"][size] = size_points(size, args, peak, record)
+                except Exception as error:  # noqa: BLE001  (a point that fails must not lose the headline)
+                    record["sizes"][size] = {"error": f"{type(error).__name__}: {error}"[:300]}
+                    torch.cuda.empty_cache()
+    record["clocks"] = clocks.summary()
+    record["environment"] = environment()
     print(json.dumps(record))
     return 0
 
@@ -362,11 +555,15 @@ def run_reference(args):
         print(json.dumps({"impl": "reference", "unavailable": why}))
         return 0
 
+    sizes = MODEL_SIZES[args.size]
     ref_root = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "mini_llm_runtime")):
         return unavailable("baseline/_ref holds no installed reference (pip install --no-deps --target baseline/_ref)")
     if not os.path.isfile(os.path.join(ROOT, "baseline", "csrc", "paged_attention_cuda.cu")):
         return unavailable("baseline/csrc (the reference's kernel sources) is missing, its CUDA extension cannot be built")
+    if not sizes["tie_word_embeddings"]:
+        return unavailable("the reference rejects checkpoints with an untied head (qwen_config.py:43-44); "
+                           "only the 0.5B sizes can run on it")
     try:
         import torch
         if not torch.cuda.is_available():
@@ -385,7 +582,7 @@ def run_reference(args):
     try:
         device = torch.device("cuda:0")
         layers = args.layers
-        config = QwenConfig(**dict(SIZES, num_hidden_layers=layers))
+        config = QwenConfig(**dict(sizes, num_hidden_layers=layers))
         generator = torch.Generator(device=device).manual_seed(0)
 
         def rand(*shape, mean=0.0):
@@ -436,15 +633,13 @@ def run_reference(args):
 
     value = batch * steps / (ms / 1e3)
     print(json.dumps({
-        "metric": "decode tokens/s (batch 8, context 4096)", "value": round(value, 1), "unit": "tokens/s",
+        "metric": f"decode tokens/s (batch {batch}, context 4096)", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (the reference kernel's only dtype)",
         "data": "synthetic (random weights and token ids)", "impl": "reference",
-        "config": {"model": MODEL_NAMES[args.size], "layers": layers, "layers_of_model": SIZES["num_hidden_layers"],
-                   "global_batch": batch, "seq_len": CONTEXT, "context_mean": args.context_mean, "prefix": prefix,
-                   "block_size": BLOCK_SIZE, "parallelism": "single GPU",
-                   "path": "ContinuousBatchEngine + paged_cuda decode kernel"},
-        "clocks": clocks.summary(),
+        "path": "ContinuousBatchEngine + paged_cuda decode kernel",
+        "config": headline_config(args.size, config, layers, batch, args.context_mean, peaks()["source"]),
+        "prefix": prefix, "clocks": clocks.summary(),
         "e2e": {"value": round(batch * steps / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": 8 * batch * 2,
                 "d2h_bytes_per_step": 8 * batch},
     }))
@@ -452,11 +647,9 @@ def run_reference(args):
 
 
 def main():
-    global SIZES
     args = parse_args()
-    SIZES = MODEL_SIZES[args.size]
     if args.layers is None:
-        args.layers = SIZES["num_hidden_layers"]
+        args.layers = MODEL_SIZES[args.size]["num_hidden_layers"]
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2

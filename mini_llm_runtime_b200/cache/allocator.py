@@ -6,7 +6,9 @@ Same contract as the reference's ``FixedBlockAllocator``
 ``free`` detects ids that are not held (double free, foreign id), and the lowest free id is
 always handed out first so that runs are reproducible.  On top of that sits a count of
 *promised* items: admission promises a request the pages of its whole lifetime without taking
-them, so a running request can never find the pool empty.
+them, so a running request can never find the pool empty.  An allocation made on behalf of a
+promise draws the promise down; one made without a promise is refused if it would leave fewer
+free items than the promises still outstanding.
 """
 
 from __future__ import annotations
@@ -28,6 +30,7 @@ class PoolAllocator:
         self._free = list(range(self.total))  # already a valid min-heap
         self._held: set[int] = set()
         self._promised = 0
+        self._drawn = 0        # items currently held on behalf of promises
 
     # ---- physical items
     @property
@@ -42,22 +45,34 @@ class PoolAllocator:
     def held(self) -> frozenset[int]:
         return frozenset(self._held)
 
-    def allocate(self, count: int) -> list[int]:
+    def allocate(self, count: int, *, promised: bool = False) -> list[int]:
+        """``promised=True``: the items were promised to the caller before (``promise``)."""
         if count < 0:
             raise ValueError("cannot allocate a negative count")
-        if count > len(self._free):
-            raise OutOfPages(f"{count} {self.what}s wanted, {len(self._free)} of {self.total} free")
+        available = len(self._free)
+        if not promised:
+            available -= max(0, self._promised - self._drawn)     # keep what is promised to others
+        if count > available:
+            raise OutOfPages(f"{count} {self.what}s wanted, {len(self._free)} of {self.total} free"
+                             + ("" if promised else f", {max(0, self._promised - self._drawn)} of them promised"))
         taken = [heapq.heappop(self._free) for _ in range(count)]
         self._held.update(taken)
+        if promised:
+            self._drawn += count
         return taken
 
-    def free(self, ids: Iterable[int]) -> None:
+    def free(self, ids: Iterable[int], *, promised: bool = False) -> None:
+        """``promised=True``: the items had been taken with ``allocate(promised=True)``."""
         ids = list(ids)
         if len(set(ids)) != len(ids):
             raise ValueError(f"the same {self.what} is freed twice in one call: {sorted(ids)}")
         foreign = [i for i in ids if i not in self._held]
         if foreign:
             raise ValueError(f"{self.what}s {sorted(foreign)} are not held (double free or foreign id)")
+        if promised:
+            if len(ids) > self._drawn:
+                raise ValueError(f"more {self.what}s returned under a promise than were taken under one")
+            self._drawn -= len(ids)
         for i in ids:
             self._held.discard(i)
             heapq.heappush(self._free, i)
@@ -83,4 +98,6 @@ class PoolAllocator:
     def unpromise(self, count: int) -> None:
         if count < 0 or count > self._promised:
             raise ValueError(f"cannot take back {count} promises, {self._promised} are out")
+        if self._promised - count < self._drawn:
+            raise ValueError(f"{self._drawn} {self.what}s are still held under the promises being taken back")
         self._promised -= count

@@ -19,6 +19,13 @@ begin/commit/abort (src/mini_llm_runtime/paged_kv_cache.py:202-243, paged_batch.
 a request is released, when a step is aborted, and - for windowed groups - at commit, once every
 position that could still look at a page has moved past it.
 
+What the device keeps.  Each group's block table ``[max_requests, max_pages_per_request]`` and
+the slot records (cache/slots.py) stay on the device; the host holds a mirror and remembers which
+rows changed (a page taken, a page given back, a request admitted or released).
+``take_resident_updates`` hands those rows out as snapshots, and the step function sends them
+along with its own metadata; a step that changes no row sends none.  Kernels reach a request's
+row through its slot.
+
 Two admission modes.  With a *promise* (``create_request(..., lifetime_tokens=n)``) the pages of
 the request's whole life are counted against the pool at creation, as the reference reserves them
 (src/mini_llm_runtime/block_admission.py:35-67), so the pool cannot run dry mid-request; pages are
@@ -36,6 +43,7 @@ import torch
 
 from ..parts.base import KVCacheNeed, StateNeed
 from .allocator import OutOfPages, PoolAllocator
+from .slots import SLOT_WORDS, slot_record
 
 
 def _ceil_div(a: int, b: int) -> int:
@@ -54,7 +62,9 @@ class CacheGroup:
     allocator: PoolAllocator
     key: torch.Tensor | None = None    # [entries, pages, kv_heads, page_size, head_dim]
     value: torch.Tensor | None = None
-    table: np.ndarray | None = None    # int32 [max_requests, max_pages_per_request], -1 = no page
+    table: np.ndarray | None = None    # host mirror: int32 [max_requests, max_pages_per_request], -1 = no page
+    device_table: torch.Tensor | None = None   # the same table where the kernels read it
+    dirty: set = field(default_factory=set)    # slots whose row differs from the device's copy
 
     @property
     def window(self) -> int | None:
@@ -135,6 +145,12 @@ class CacheManager:
                 shape = (len(group.entries), count, group.need.num_kv_heads, self.page_size, group.need.head_dim)
                 group.key = torch.zeros(shape, dtype=dtype, device=self.device)
                 group.value = torch.zeros(shape, dtype=dtype, device=self.device)
+                if self.device.type == "cuda":
+                    group.device_table = torch.full((self.max_requests, self.max_pages_per_request), -1,
+                                                    dtype=torch.int32, device=self.device)
+                else:
+                    # a stand-in backend on the host reads the mirror itself: nothing to send
+                    group.device_table = torch.from_numpy(group.table)
 
         # ---- fixed-size state per request
         self.slots = PoolAllocator(self.max_requests, "slot")
@@ -144,8 +160,21 @@ class CacheManager:
                 self.state[entry] = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype,
                                                 device=self.device)
 
+        # ---- slot records (length, last token, counter, temperature, seed): device + host mirror
+        self.slot_mirror = np.zeros((self.max_requests, SLOT_WORDS), dtype=np.int32)
+        self.slot_state: torch.Tensor | None = None
+        self._new_records: set[int] = set()
+        self._unconfirmed: tuple[list[set], set] | None = None    # rows handed out but not yet reported sent
+        self._shares_host_memory = self.device.type != "cuda"
+        if allocate_device_memory:
+            if self._shares_host_memory:
+                self.slot_state = torch.from_numpy(self.slot_mirror)
+            else:
+                self.slot_state = torch.zeros((self.max_requests, SLOT_WORDS), dtype=torch.int32, device=self.device)
+
         self.requests: dict[str, RequestCache] = {}
         self._step: list[tuple[RequestCache, int]] | None = None
+        self._state_backup: tuple[torch.Tensor, dict[int, torch.Tensor]] | None = None
 
     # ------------------------------------------------------------------ sizing
     def pages_for_lifetime(self, group: CacheGroup, lifetime_tokens: int) -> int:
@@ -165,9 +194,11 @@ class CacheManager:
         return all(n <= g.num_pages for g, n in zip(self.groups, self.lifetime_pages(lifetime_tokens)))
 
     # ------------------------------------------------------------------ requests
-    def create_request(self, request_id: str, *, lifetime_tokens: int | None = None) -> RequestCache | None:
+    def create_request(self, request_id: str, *, lifetime_tokens: int | None = None,
+                       temperature: float = 0.0, seed: int = 0) -> RequestCache | None:
         """Register a request and give it a slot.  With ``lifetime_tokens`` its pages are promised
-        now; returns None (nothing changed) if the promise cannot be kept or no slot is free."""
+        now; returns None (nothing changed) if the promise cannot be kept or no slot is free.
+        ``temperature`` and ``seed`` go into the slot's record for the sampling kernel."""
         if request_id in self.requests:
             raise ValueError(f"request {request_id!r} already has a cache")
         if self.slots.free_count == 0:
@@ -202,6 +233,8 @@ class CacheManager:
         self.requests[request_id] = request
         for tensor in self.state.values():
             tensor[slot].zero_()
+        self.slot_mirror[slot] = slot_record(temperature=temperature, seed=seed)
+        self._new_records.add(slot)
         return request
 
     def get(self, request_id: str) -> RequestCache:
@@ -218,9 +251,10 @@ class CacheManager:
         freed: dict[int, list[int]] = {}
         for group in self.groups:
             ids = [p for p in request.pages[group.index] if p >= 0]
-            group.allocator.free(ids)
+            group.allocator.free(ids, promised=bool(request.promised[group.index]))
             group.allocator.unpromise(request.promised[group.index])
             group.table[request.slot, :] = -1
+            group.dirty.add(request.slot)
             freed[group.index] = ids
         self.slots.free([request.slot])
         del self.requests[request_id]
@@ -258,7 +292,7 @@ class CacheManager:
                     if limit and request.held(group.index) + missing > limit:
                         raise OutOfPages(f"request {request.request_id!r} would exceed the {limit} pages "
                                          f"promised to it in group {group.index}")
-                    new_ids = group.allocator.allocate(missing)
+                    new_ids = group.allocator.allocate(missing, promised=bool(limit))
                     for page_id in new_ids:
                         pages.append(page_id)
                         taken.append((request, group, len(pages) - 1, page_id))
@@ -266,14 +300,20 @@ class CacheManager:
             for request, group, logical, page_id in reversed(taken):
                 popped = request.pages[group.index].pop()
                 assert popped == page_id and len(request.pages[group.index]) == logical
-                group.allocator.free([page_id])
+                group.allocator.free([page_id], promised=bool(request.promised[group.index]))
             raise
         for request, group, logical, page_id in taken:
             group.table[request.slot, logical] = page_id
+            group.dirty.add(request.slot)
             request.step_new_pages[group.index].append(page_id)
         for request, count in plan:
             request.pending = (request.committed, request.committed + count)
         self._step = plan
+        if self.state:
+            # fixed-size state is overwritten in place by the step: keep what an abort must restore
+            index = torch.tensor([request.slot for request, _ in plan], dtype=torch.long, device=self.device)
+            self._state_backup = (index, {entry: tensor.index_select(0, index)
+                                          for entry, tensor in self.state.items()})
         return [request for request, _ in plan]
 
     def commit_step(self) -> dict[str, dict[int, list[int]]]:
@@ -299,13 +339,25 @@ class CacheManager:
                         gone.append(pages[logical])
                         pages[logical] = -1
                         group.table[request.slot, logical] = -1
+                        group.dirty.add(request.slot)
                 request.first_live[group.index] = max(request.first_live[group.index],
                                                       min(first_needed_page, len(pages)))
                 if gone:
-                    group.allocator.free(gone)
+                    group.allocator.free(gone, promised=bool(request.promised[group.index]))
                     released.setdefault(request.request_id, {})[group.index] = gone
+            self.slot_mirror[request.slot, 0] = request.committed
         self._step = None
+        self._state_backup = None
         return released
+
+    def adopt(self, request_id: str, tokens: int) -> None:
+        """Declare that the cache already holds ``tokens`` more tokens of the request: the pages are
+        taken and the length is committed as after a step, but no kernel runs; what those positions
+        hold is whatever the pools hold.  For caches filled by other means (benchmarks that do not
+        want to time a prefill first, a cache restored from elsewhere)."""
+        request = self.begin_step([(request_id, tokens)])[0]
+        self.commit_step()
+        self._new_records.add(request.slot)      # the device learns the new length with the next step
 
     def abort_step(self) -> None:
         """Forget the step: its tokens never become visible, its new pages go back."""
@@ -320,14 +372,50 @@ class CacheManager:
                         popped = pages.pop()
                         assert popped == page_id
                         group.table[request.slot, len(pages)] = -1
-                    group.allocator.free(new_ids)
+                    group.dirty.add(request.slot)
+                    group.allocator.free(new_ids, promised=bool(request.promised[group.index]))
                 request.step_new_pages[group.index] = []
             request.pending = None
+        if self._state_backup is not None:
+            index, saved = self._state_backup
+            for entry, rows in saved.items():
+                self.state[entry].index_copy_(0, index, rows)
+            self._state_backup = None
         self._step = None
 
     @property
     def step_in_flight(self) -> bool:
         return self._step is not None
+
+    # ------------------------------------------------------------------ what the device must learn
+    def take_resident_updates(self) -> list[tuple[torch.Tensor, np.ndarray, np.ndarray]]:
+        """Rows of the resident tables that changed since the last call, as snapshots:
+        ``(device table, row indices int32 [n], rows int32 [n, width])`` for each block table with
+        changed rows and for the slot records of newly admitted requests.  The caller sends them
+        and scatters them before the step's first kernel.  Empty when nothing changed, and always
+        empty when the device tables share the host's memory.  The caller reports with
+        ``resident_updates_sent`` once the rows are on their way; rows handed out but never reported
+        (the step failed before it could send them) are handed out again."""
+        if self._unconfirmed is not None:
+            lost_rows, lost_records = self._unconfirmed
+            for group, rows in zip(self.groups, lost_rows):
+                group.dirty |= rows
+            self._new_records |= lost_records
+        self._unconfirmed = ([set(group.dirty) for group in self.groups], set(self._new_records))
+        updates = []
+        for group in self.groups:
+            if group.dirty and group.device_table is not None and not self._shares_host_memory:
+                rows = np.fromiter(sorted(group.dirty), dtype=np.int32, count=len(group.dirty))
+                updates.append((group.device_table, rows, group.table[rows]))
+            group.dirty.clear()
+        if self._new_records and self.slot_state is not None and not self._shares_host_memory:
+            rows = np.fromiter(sorted(self._new_records), dtype=np.int32, count=len(self._new_records))
+            updates.append((self.slot_state, rows, self.slot_mirror[rows].copy()))
+        self._new_records.clear()
+        return updates
+
+    def resident_updates_sent(self) -> None:
+        self._unconfirmed = None
 
     # ------------------------------------------------------------------ views and numbers
     def entry_pools(self, entry: int) -> tuple[torch.Tensor, torch.Tensor, CacheGroup]:

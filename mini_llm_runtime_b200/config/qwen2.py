@@ -180,8 +180,9 @@ def qwen2_model_spec(config: Qwen2Config) -> ModelSpec:
             )
         )
     sizes = {"vocab_size": config.vocab_size, "hidden_size": config.hidden_size}
+    embedding_prefix = "model.embed_tokens."
     if config.tie_word_embeddings:
-        head = PartSpec("tied_head", sizes, "lm_head.")
+        head = PartSpec("tied_head", {**sizes, "tied_to": embedding_prefix + "weight"}, "lm_head.")
     else:
         head = PartSpec("linear_head", sizes, "lm_head.")
     return ModelSpec(
@@ -189,7 +190,7 @@ def qwen2_model_spec(config: Qwen2Config) -> ModelSpec:
         vocab_size=config.vocab_size,
         hidden_size=config.hidden_size,
         max_positions=config.max_position_embeddings,
-        embedding=PartSpec("token_embedding", sizes, "model.embed_tokens."),
+        embedding=PartSpec("token_embedding", sizes, embedding_prefix),
         layers=tuple(layers),
         run_order=tuple(RunStep(layer=i, cache=i) for i in range(config.num_hidden_layers)),
         final_norm=PartSpec("rms_norm", norm_args, "model.norm."),

@@ -17,6 +17,10 @@
 // head_dim 64 or 128, up to 8 query heads per kv head; other sizes use the generic kernel.
 #include "common.cuh"
 
+#pragma GCC visibility push(default)
+#include "attention_decode_static.h"
+#pragma GCC visibility pop
+
 namespace mlr {
 
 constexpr int GROUP_MAX = 8;
@@ -37,7 +41,7 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32)
 decode_attention_kernel(const bf16* q, const bf16* k_pool,
                         const bf16* v_pool, bf16* __restrict__ out,
                         const int* __restrict__ decode_seg, const int* __restrict__ seg_q_start,
-                        const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
+                        const int* __restrict__ seg_pos0, const int* __restrict__ block_table, const int* __restrict__ seg_slot,
                         int table_width, int heads, int kv_heads, int page_size, int window, float scale,
                         int chunk, float* __restrict__ scratch, int* __restrict__ counters, int max_splits) {
   pdl_trigger();
@@ -57,11 +61,13 @@ decode_attention_kernel(const bf16* q, const bf16* k_pool,
   const int position = seg_pos0[seg];                       // the row's own position; it sees keys <= position
   const int lowest = window > 0 ? max(0, position - window + 1) : 0;
   const int first_chunk = lowest / chunk;
-  const int splits = position / chunk - first_chunk + 1;
+  // A context that needs more chunks than the grid has CTAs for it (position >= max_splits *
+  // chunk) is still covered: the last CTA walks on to the row's own position.
+  const int splits = min(position / chunk - first_chunk + 1, max_splits);
   if (split >= splits) return;
   const int k_begin = max(lowest, (first_chunk + split) * chunk);
-  const int k_end = min(position + 1, (first_chunk + split + 1) * chunk);
-  const int* table = block_table + (size_t)seg * table_width;
+  const int k_end = split == splits - 1 ? position + 1 : (first_chunk + split + 1) * chunk;
+  const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   for (int i = threadIdx.x; i < group * D; i += blockDim.x) {
@@ -232,29 +238,36 @@ MLR_EXPORT long long mlr_attention_decode_scratch(int rows, int heads, int head_
 }
 
 // q, out: [all rows of the step, heads, head_dim] bfloat16; decode_seg: the segments (of one row
-// each) this launch handles; max_splits >= ceil(longest context / chunk) sizes the grid, so a
-// captured launch stays valid while contexts grow up to max_splits * chunk.
-MLR_EXPORT int mlr_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                    const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
-                                    const int* block_table, int table_width, int rows, int heads, int kv_heads,
-                                    int head_dim, int page_size, int window, float scale, int chunk,
-                                    int max_splits, void* scratch, int* counters, cudaStream_t stream) {
-  if (rows == 0) return MLR_OK;
+// each) this launch handles; max_splits sizes the grid: with max_splits >= ceil(longest context /
+// chunk) every chunk has its own CTA; beyond that the last CTA of a row takes the rest.
+static int decode_arguments_status(int rows, int heads, int kv_heads, int head_dim, int page_size, int chunk,
+                                   int max_splits, int table_width) {
   if (rows < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 || chunk <= 0 ||
       chunk % 32 != 0 || max_splits <= 0 || table_width <= 0)
     return MLR_BAD_SIZE;
-  if (heads / kv_heads > GROUP_MAX || rows > 65535 || kv_heads > 65535) return MLR_TOO_LARGE;
   if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
+  if (heads / kv_heads > GROUP_MAX || rows > 65535 || kv_heads > 65535) return MLR_TOO_LARGE;
+  return MLR_OK;
+}
+
+MLR_EXPORT int mlr_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                    const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
+                                    const int* block_table, const int* seg_slot, int table_width, int rows, int heads, int kv_heads,
+                                    int head_dim, int page_size, int window, float scale, int chunk,
+                                    int max_splits, void* scratch, int* counters, cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  const int refused = decode_arguments_status(rows, heads, kv_heads, head_dim, page_size, chunk, max_splits, table_width);
+  if (refused != MLR_OK) return refused;
   dim3 grid(max_splits, kv_heads, rows);
   if (head_dim == 64)
     launch_kernel(decode_attention_kernel<64>, dim3(grid), dim3(DECODE_WARPS * 32), 0, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
-        block_table, table_width, heads, kv_heads, page_size, window, scale, chunk, (float*)scratch, counters,
+        block_table, seg_slot, table_width, heads, kv_heads, page_size, window, scale, chunk, (float*)scratch, counters,
         max_splits);
   else
     launch_kernel(decode_attention_kernel<128>, dim3(grid), dim3(DECODE_WARPS * 32), 0, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg, seg_q_start, seg_pos0,
-        block_table, table_width, heads, kv_heads, page_size, window, scale, chunk, (float*)scratch, counters,
+        block_table, seg_slot, table_width, heads, kv_heads, page_size, window, scale, chunk, (float*)scratch, counters,
         max_splits);
   return launch_status();
 }
@@ -283,8 +296,9 @@ MLR_EXPORT int mlr_attention_decode_static(const void* q, const void* k_pool, co
                                            int kv_heads, int head_dim, int page_size, int window, float scale,
                                            int chunk, int max_splits, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
-  if (rows < 0 || heads <= 0 || kv_heads <= 0 || max_splits <= 0 || (head_dim != 64 && head_dim != 128))
-    return MLR_BAD_SIZE;
+  // every check of the ordinary entry comes first, so that a refused call enqueues nothing at all
+  const int refused = decode_arguments_status(rows, heads, kv_heads, head_dim, page_size, chunk, max_splits, table_width);
+  if (refused != MLR_OK) return refused;
   // Refuse what does not fit the fixed array: the caller cannot be given more, and must not be
   // given less than the kernel will write.
   if (mlr_attention_decode_scratch(rows, heads, head_dim, max_splits) > (long long)STATIC_STATE_BYTES ||
@@ -307,7 +321,7 @@ MLR_EXPORT int mlr_attention_decode_static(const void* q, const void* k_pool, co
   // The array keeps whatever the previous call left; the counters must start at zero.
   err = cudaMemsetAsync(counters, 0, (size_t)rows * kv_heads * sizeof(int), stream);
   if (err != cudaSuccess) return (int)err;
-  return mlr_attention_decode(q, k_pool, v_pool, out, decode_seg, seg_q_start, seg_pos0, block_table,
+  return mlr_attention_decode(q, k_pool, v_pool, out, decode_seg, seg_q_start, seg_pos0, block_table, nullptr,
                               table_width, rows, heads, kv_heads, head_dim, page_size, window, scale, chunk,
                               max_splits, base, counters, stream);
 }

@@ -17,8 +17,10 @@
  *
  * First call.  The first call on each device asks the CUDA runtime for the array's address on
  * that device (cudaGetSymbolAddress, with that device current) and remembers it; make that first
- * call outside any stream capture.  Later calls only enqueue a memset of the counters and the
- * kernel on `stream`.  No call allocates or frees device or host memory.
+ * call outside any stream capture, and from one thread: the remembered address is not guarded by a
+ * lock.  Later calls only enqueue a memset of the counters and the kernel on `stream`.  No call
+ * allocates or frees device or host memory.  A call that is refused (any negative code) enqueues
+ * nothing.
  *
  * Sharing.  All calls on a device use the same array, which still holds the previous call's
  * contents; the counters are cleared by each call, the states are overwritten before they are
@@ -31,7 +33,9 @@
  *   decode_seg    int32 [rows]: indices into the seg_* arrays of the one-row segments to process
  *   seg_q_start   int32: row of each segment in q/out;  seg_pos0: its position (= keys before it)
  *   block_table   int32 [segments, table_width], page ids of each request
- *   chunk         keys per CTA (multiple of 32); max_splits >= ceil(longest context / chunk)
+ *   chunk         keys per CTA (multiple of 32); max_splits CTAs per (row, kv head): choose it
+ *                 >= ceil(longest context / chunk) for full parallelism; a longer context is still
+ *                 computed correctly, its last CTA walking the remaining keys
  * Returns 0, a negative MLR_* code, or a positive cudaError_t.
  */
 #pragma once

@@ -30,7 +30,7 @@ attention_generic_kernel(const T* q, const T* k_pool,
                          const T* v_pool, T* __restrict__ out,
                          const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                          const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
-                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
+                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table, const int* __restrict__ seg_slot,
                          int table_width, int heads, int kv_heads, int head_dim, int page_size,
                          int window, float scale) {
   pdl_trigger();
@@ -47,7 +47,7 @@ attention_generic_kernel(const T* q, const T* k_pool,
   const int seg = tile_seg[tile], row0 = tile_row0[tile];
   const int q_start = seg_q_start[seg], q_len = seg_q_len[seg], pos0 = seg_pos0[seg];
   const int rows = min(ROWS_PER_TILE, q_len - row0);
-  const int* table = block_table + (size_t)seg * table_width;
+  const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
   for (int idx = threadIdx.x; idx < ROWS_PER_TILE * D; idx += blockDim.x) {
@@ -136,7 +136,7 @@ attention_generic_kernel(const T* q, const T* k_pool,
 template <typename T>
 int attention_generic_launch(const void* q, const void* k_pool, const void* v_pool, void* out,
                              const int* tile_seg, const int* tile_row0, const int* seg_q_start,
-                             const int* seg_q_len, const int* seg_pos0, const int* block_table,
+                             const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
                              int table_width, int tiles, int heads, int kv_heads, int head_dim,
                              int page_size, int window, float scale, cudaStream_t stream) {
   const size_t shared = sizeof(float) * ((size_t)ROWS_PER_TILE * head_dim + (size_t)KEYS_PER_TILE * (head_dim + 1) +
@@ -149,7 +149,7 @@ int attention_generic_launch(const void* q, const void* k_pool, const void* v_po
   dim3 grid(tiles, heads);
   launch_kernel(attention_generic_kernel<T>, dim3(grid), dim3(128), shared, stream, 
       (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, tile_seg, tile_row0, seg_q_start,
-      seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, head_dim, page_size, window, scale);
+      seg_q_len, seg_pos0, block_table, seg_slot, table_width, heads, kv_heads, head_dim, page_size, window, scale);
   return launch_status();
 }
 
@@ -164,7 +164,7 @@ MLR_DEFINE_PDL_SWITCH
 // window <= 0 means every earlier key is visible.
 MLR_EXPORT int mlr_attention_generic(const void* q, const void* k_pool, const void* v_pool, void* out,
                                      const int* tile_seg, const int* tile_row0, const int* seg_q_start,
-                                     const int* seg_q_len, const int* seg_pos0, const int* block_table,
+                                     const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
                                      int table_width, int tiles, int heads, int kv_heads, int head_dim,
                                      int page_size, int window, float scale, int dtype,
                                      cudaStream_t stream) {
@@ -175,11 +175,11 @@ MLR_EXPORT int mlr_attention_generic(const void* q, const void* k_pool, const vo
   if (head_dim > MAX_HEAD_DIM || heads > 65535) return MLR_TOO_LARGE;
   if (dtype == MLR_F32)
     return attention_generic_launch<float>(q, k_pool, v_pool, out, tile_seg, tile_row0, seg_q_start,
-                                           seg_q_len, seg_pos0, block_table, table_width, tiles, heads,
+                                           seg_q_len, seg_pos0, block_table, seg_slot, table_width, tiles, heads,
                                            kv_heads, head_dim, page_size, window, scale, stream);
   if (dtype == MLR_BF16)
     return attention_generic_launch<bf16>(q, k_pool, v_pool, out, tile_seg, tile_row0, seg_q_start,
-                                          seg_q_len, seg_pos0, block_table, table_width, tiles, heads,
+                                          seg_q_len, seg_pos0, block_table, seg_slot, table_width, tiles, heads,
                                           kv_heads, head_dim, page_size, window, scale, stream);
   return MLR_BAD_DTYPE;
 }

@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(ATTN_THREADS)
 prefill_attention_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
                          bf16* __restrict__ out, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                          const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
-                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table, int table_width,
+                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table, const int* __restrict__ seg_slot, int table_width,
                          int heads, int kv_heads, int page_size, int page_shift, int window, float scale_log2) {
   pdl_trigger();
   pdl_wait();
@@ -210,7 +210,7 @@ prefill_attention_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
   const int seg = tile_seg[tile], row0 = tile_row0[tile];
   const int q_start = seg_q_start[seg], q_len = seg_q_len[seg], pos0 = seg_pos0[seg];
   const int rows = min(TILE_Q, q_len - row0);
-  const int* table = block_table + (size_t)seg * table_width;
+  const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const int first_pos = pos0 + row0, last_pos = first_pos + rows - 1;
@@ -309,7 +309,7 @@ prefill_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              const bf16* q, bf16* __restrict__ out, const int* __restrict__ tile_seg,
                              const int* __restrict__ tile_row0, const int* __restrict__ seg_q_start,
                              const int* __restrict__ seg_q_len, const int* __restrict__ seg_pos0,
-                             const int* __restrict__ block_table, int table_width, int num_tiles, int heads,
+                             const int* __restrict__ block_table, const int* __restrict__ seg_slot, int table_width, int num_tiles, int heads,
                              int kv_heads, int page_size, int page_shift, int window, float scale_log2,
                              int* queue, int* error_word) {
   constexpr int HALVES = D / 64;
@@ -350,7 +350,7 @@ prefill_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
     const int seg = tile_seg[tile], row0 = tile_row0[tile];
     const int q_start = seg_q_start[seg], q_len = seg_q_len[seg], pos0 = seg_pos0[seg];
     const int rows = min(TILE_Q, q_len - row0);
-    const int* table = block_table + (size_t)seg * table_width;
+    const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
     const int first_pos = pos0 + row0, last_pos = first_pos + rows - 1;
     const int lowest = window > 0 ? max(0, first_pos - window + 1) : 0;
     const int tile_begin = lowest / TILE_KV, tile_end = last_pos / TILE_KV;   // inclusive
@@ -600,7 +600,7 @@ __global__ void __launch_bounds__(ATTN_THREADS)
 decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_pool,
                             bf16* __restrict__ out, const int* __restrict__ decode_seg,
                             const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
-                            const int* __restrict__ block_table, int table_width, int heads, int kv_heads,
+                            const int* __restrict__ block_table, const int* __restrict__ seg_slot, int table_width, int heads, int kv_heads,
                             int page_size, int page_shift, int window, float scale_log2, int chunk,
                             float* __restrict__ scratch,
                             int* __restrict__ counters, int max_splits) {
@@ -625,7 +625,7 @@ decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_poo
   if (split >= splits) return;
   const int k_begin = max(lowest, (first_chunk + split) * chunk);
   const int k_end = min(position + 1, (first_chunk + split + 1) * chunk);   // exclusive
-  const int* table = block_table + (size_t)seg * table_width;
+  const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_begin = k_begin / TILE_KV, tile_end = (k_end - 1) / TILE_KV;   // inclusive
   const int tiles = tile_end - tile_begin + 1;
@@ -727,7 +727,7 @@ __global__ void __launch_bounds__(ATTN_THREADS)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                             const bf16* q, bf16* __restrict__ out, const int* __restrict__ decode_seg,
                             const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
-                            const int* __restrict__ block_table, int table_width, int heads, int kv_heads,
+                            const int* __restrict__ block_table, const int* __restrict__ seg_slot, int table_width, int heads, int kv_heads,
                             int page_size, int page_shift, int window, float scale_log2, int chunk_arg,
                             int even_split, float* __restrict__ scratch, int* __restrict__ counters,
                             int max_splits, int* error_word, const bf16* qkv, const float* __restrict__ inv_freq,
@@ -769,7 +769,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   if (split >= splits) return;
   const int k_begin = max(lowest, (first_chunk + split) * chunk);
   const int k_end = min(position + 1, (first_chunk + split + 1) * chunk);   // exclusive
-  const int* table = block_table + (size_t)seg * table_width;
+  const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
   const int tile_begin = k_begin / TKV, tile_end = (k_end - 1) / TKV;       // inclusive
   const int tiles = tile_end - tile_begin + 1;
   const int my_tiles = tiles > warp ? (tiles - warp + ATTN_WARPS - 1) / ATTN_WARPS : 0;   // tiles warp, warp + 4, ..
@@ -939,7 +939,7 @@ static int shift_of(int page_size) {
 // Prompt portions: tiles of up to 64 rows of one segment (tile_seg, tile_row0).
 MLR_EXPORT int mlr_attention_prefill_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                          const int* tile_seg, const int* tile_row0, const int* seg_q_start,
-                                         const int* seg_q_len, const int* seg_pos0, const int* block_table,
+                                         const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
                                          int table_width, int tiles, int heads, int kv_heads, int head_dim,
                                          int page_size, int window, float scale, cudaStream_t stream) {
   if (tiles == 0) return MLR_OK;
@@ -955,12 +955,12 @@ MLR_EXPORT int mlr_attention_prefill_mma(const void* q, const void* k_pool, cons
     if ((status = set_shared(prefill_attention_kernel<64>, shared)) != MLR_OK) return status;
     launch_kernel(prefill_attention_kernel<64>, dim3(grid), dim3(ATTN_THREADS), shared, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, tile_seg, tile_row0, seg_q_start,
-        seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E);
+        seg_q_len, seg_pos0, block_table, seg_slot, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E);
   } else {
     if ((status = set_shared(prefill_attention_kernel<128>, shared)) != MLR_OK) return status;
     launch_kernel(prefill_attention_kernel<128>, dim3(grid), dim3(ATTN_THREADS), shared, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, tile_seg, tile_row0, seg_q_start,
-        seg_q_len, seg_pos0, block_table, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E);
+        seg_q_len, seg_pos0, block_table, seg_slot, table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E);
   }
   return launch_status();
 }
@@ -968,7 +968,7 @@ MLR_EXPORT int mlr_attention_prefill_mma(const void* q, const void* k_pool, cons
 // Decoded tokens: same contract as mlr_attention_decode (same scratch layout and counters).
 MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                         const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
-                                        const int* block_table, int table_width, int rows, int heads, int kv_heads,
+                                        const int* block_table, const int* seg_slot, int table_width, int rows, int heads, int kv_heads,
                                         int head_dim, int page_size, int window, float scale, int chunk,
                                         int max_splits, void* scratch, int* counters, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
@@ -980,7 +980,7 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
   // the final merge keeps 2 * 16 * max_splits + 16 floats in the warps' merge area
   if ((size_t)(2 * 16 * max_splits + 16) > (size_t)ATTN_WARPS * 16 * (head_dim + 2)) return MLR_TOO_LARGE;
   // long chunks on a grid of several waves: fewer stages, more CTAs per SM
-  const bool deep = chunk <= 4 * TILE_KV || (long long)max_splits * kv_heads * rows <= 2 * 148;
+  const bool deep = chunk <= 4 * TILE_KV || (long long)max_splits * kv_heads * rows <= 2 * sm_count();
   const int stages = deep ? 4 : 2;
   const size_t shared = (size_t)(16 + 2 * stages * TILE_KV) * head_dim * 2 +
                         (size_t)ATTN_WARPS * 16 * (head_dim + 2) * sizeof(float);
@@ -992,7 +992,7 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
     if ((status = set_shared(decode_attention_mma_kernel<D_, S_>, shared)) != MLR_OK) return status;       \
     launch_kernel(decode_attention_mma_kernel<D_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream,     \
                   (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, decode_seg,        \
-                  seg_q_start, seg_pos0, block_table, table_width, heads, kv_heads, page_size, page_shift, \
+                  seg_q_start, seg_pos0, block_table, seg_slot, table_width, heads, kv_heads, page_size, page_shift, \
                   window, scale * LOG2_E, chunk, (float*)scratch, counters, max_splits);                   \
   } while (0)
   if (head_dim == 64) {
@@ -1013,7 +1013,7 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
 // int64, page * page_size + offset of each token's cache slot; write_kv = 0 leaves the pages alone).
 MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                         const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
-                                        const int* block_table, int table_width, int rows, int heads, int kv_heads,
+                                        const int* block_table, const int* seg_slot, int table_width, int rows, int heads, int kv_heads,
                                         int head_dim, int page_size, int pool_pages, int window, float scale,
                                         int chunk, int even_split, int max_splits, int stages, void* scratch,
                                         int* counters, int* error_word, const void* qkv, const float* inv_freq,
@@ -1033,10 +1033,10 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
   if ((size_t)(2 * 16 * max_splits + 16) > (size_t)ATTN_WARPS * 16 * (head_dim + 2)) return MLR_TOO_LARGE;
   const int tile_keys = (head_dim == 64 && stages < 10) || stages == 21 ? 64 : 32;
   const int box_rows = page_size >= tile_keys ? tile_keys : page_size;
-  const CUtensorMap* k_cached = cached_tile_map(k_pool, pool_rows, head_dim, box_rows);
-  const CUtensorMap* v_cached = cached_tile_map(v_pool, pool_rows, head_dim, box_rows);
-  if (k_cached == nullptr || v_cached == nullptr) return MLR_BAD_SIZE;
-  const CUtensorMap k_map = *k_cached, v_map = *v_cached;
+  CUtensorMap k_map, v_map;
+  if (!cached_tile_map(&k_map, k_pool, pool_rows, head_dim, box_rows) ||
+      !cached_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
+    return MLR_BAD_SIZE;
   dim3 grid(max_splits, kv_heads, rows);
   int status;
 #define MLR_LAUNCH_DECODE_TMA(D_, T_, S_)                                                                  \
@@ -1045,7 +1045,7 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
     static_assert((size_t)ATTN_WARPS * 16 * (D_ + 2) * 4 <= (size_t)2 * ATTN_WARPS * S_ * T_ * D_ * 2, "merge area"); \
     if ((status = set_shared(decode_attention_tma_kernel<D_, T_, S_>, shared)) != MLR_OK) return status;   \
     launch_kernel(decode_attention_tma_kernel<D_, T_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream, \
-                  k_map, v_map, (const bf16*)q, (bf16*)out, decode_seg, seg_q_start, seg_pos0, block_table, \
+                  k_map, v_map, (const bf16*)q, (bf16*)out, decode_seg, seg_q_start, seg_pos0, block_table, seg_slot, \
                   table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk,      \
                   even_split, (float*)scratch, counters, max_splits, error_word, (const bf16*)qkv, inv_freq, \
                   slots, (bf16*)const_cast<void*>(k_pool), (bf16*)const_cast<void*>(v_pool), write_kv);    \
@@ -1082,7 +1082,7 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
 // int that receives a code if a wait runs out.  The tile list is best ordered by falling key count.
 MLR_EXPORT int mlr_attention_prefill_tma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                          const int* tile_seg, const int* tile_row0, const int* seg_q_start,
-                                         const int* seg_q_len, const int* seg_pos0, const int* block_table,
+                                         const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
                                          int table_width, int tiles, int heads, int kv_heads, int head_dim,
                                          int page_size, int pool_pages, int window, float scale, int* queue,
                                          int* error_word, cudaStream_t stream) {
@@ -1098,20 +1098,20 @@ MLR_EXPORT int mlr_attention_prefill_tma(const void* q, const void* k_pool, cons
   const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
   if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;
   const int box_rows = page_size >= TILE_KV ? TILE_KV : page_size;
-  const CUtensorMap* k_cached = cached_tile_map(k_pool, pool_rows, head_dim, box_rows);
-  const CUtensorMap* v_cached = cached_tile_map(v_pool, pool_rows, head_dim, box_rows);
-  if (k_cached == nullptr || v_cached == nullptr) return MLR_BAD_SIZE;
-  const CUtensorMap k_map = *k_cached, v_map = *v_cached;
+  CUtensorMap k_map, v_map;
+  if (!cached_tile_map(&k_map, k_pool, pool_rows, head_dim, box_rows) ||
+      !cached_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
+    return MLR_BAD_SIZE;
   int status;
 #define MLR_LAUNCH_PREFILL_TMA(D_, S_, PER_SM_)                                                             \
   do {                                                                                                      \
     const size_t shared = 1024 + (size_t)(TILE_Q + 2 * S_ * TILE_KV) * D_ * 2;                              \
     if ((status = set_shared(prefill_attention_tma_kernel<D_, S_>, shared)) != MLR_OK) return status;       \
     const long long items = (long long)tiles * heads;                                                       \
-    const int ctas = (int)(items < 148 * PER_SM_ ? items : 148 * PER_SM_);                                  \
+    const int ctas = (int)(items < sm_count() * PER_SM_ ? items : sm_count() * PER_SM_);                                  \
     launch_kernel(prefill_attention_tma_kernel<D_, S_>, dim3(ctas), dim3(ATTN_THREADS), shared, stream,     \
                   k_map, v_map, (const bf16*)q, (bf16*)out, tile_seg, tile_row0, seg_q_start, seg_q_len,    \
-                  seg_pos0, block_table, table_width, tiles, heads, kv_heads, page_size, page_shift, window, \
+                  seg_pos0, block_table, seg_slot, table_width, tiles, heads, kv_heads, page_size, page_shift, window, \
                   scale * LOG2_E, queue, error_word);                                                       \
   } while (0)
   if (head_dim == 64) MLR_LAUNCH_PREFILL_TMA(64, 3, 3); else MLR_LAUNCH_PREFILL_TMA(128, 2, 2);

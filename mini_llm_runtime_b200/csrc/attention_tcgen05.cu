@@ -126,7 +126,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
                                  const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out,
                                  const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                                  const int* __restrict__ seg_q_start, const int* __restrict__ seg_q_len,
-                                 const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
+                                 const int* __restrict__ seg_pos0, const int* __restrict__ block_table, const int* __restrict__ seg_slot,
                                  int table_width, int num_tiles, int heads, int kv_heads, int page_size,
                                  int page_shift, int window, float scale_log2, int* queue, int* error_word,
                                  int max_parts, int tiles_per_unit, float* __restrict__ scratch,
@@ -182,7 +182,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     const int seg = tile_seg[tile], row0 = tile_row0[tile];
     const int q_start = seg_q_start[seg], q_len = seg_q_len[seg], pos0 = seg_pos0[seg];
     const int rows = min(FA_ROWS, q_len - row0);
-    const int* table = block_table + (size_t)seg * table_width;
+    const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
     const int first_pos = pos0 + row0, last_pos = first_pos + rows - 1;
     const int lowest = window > 0 ? max(0, first_pos - window + 1) : 0;
     // An item with many key tiles is cut into parts of equal length; each part is a unit of its
@@ -495,7 +495,7 @@ MLR_EXPORT void mlr_attention_prefill_tcgen05_tune(int units) { units_per_cta = 
 // left zeroed): room for the states of items that are cut into parts, may be null.
 MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out,
                                              const int* tile_seg, const int* tile_row0, const int* seg_q_start,
-                                             const int* seg_q_len, const int* seg_pos0, const int* block_table,
+                                             const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
                                              int table_width, int tiles, int q_rows, int heads, int kv_heads,
                                              int head_dim, int page_size, int pool_pages, int window, float scale,
                                              int max_kv_len, int* queue, int* error_word, void* scratch,
@@ -513,11 +513,11 @@ MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, 
   const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
   if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;
   const int box_rows = page_size >= FA_KEYS ? FA_KEYS : page_size;
-  const CUtensorMap* q_cached = cached_tile_map(q, q_rows, (long long)heads * FA_D, FA_ROWS);
-  const CUtensorMap* k_cached = cached_tile_map(k_pool, pool_rows, FA_D, box_rows);
-  const CUtensorMap* v_cached = cached_tile_map(v_pool, pool_rows, FA_D, box_rows);
-  if (q_cached == nullptr || k_cached == nullptr || v_cached == nullptr) return MLR_BAD_SIZE;
-  const CUtensorMap q_map = *q_cached, k_map = *k_cached, v_map = *v_cached;
+  CUtensorMap q_map, k_map, v_map;
+  if (!cached_tile_map(&q_map, q, q_rows, (long long)heads * FA_D, FA_ROWS) ||
+      !cached_tile_map(&k_map, k_pool, pool_rows, FA_D, box_rows) ||
+      !cached_tile_map(&v_map, v_pool, pool_rows, FA_D, box_rows))
+    return MLR_BAD_SIZE;
   const size_t shared = 1024 + 3 * (size_t)FA_Q_BYTES + (size_t)FA_STAGES * 2 * FA_KV_TILE_BYTES;
   static bool configured = false;
   if (!configured) {
@@ -529,7 +529,7 @@ MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, 
   // Few items with long key ranges (one prompt of a few thousand tokens) would leave the launch as
   // long as its heaviest item: cut items into up to 8 parts so that about two units per resident CTA
   // exist.  Needs scratch for the parts' states and one counter per item; without them, no cutting.
-  const int resident = 148 * 2;
+  const int resident = sm_count() * 2;
   const int max_key_tiles = max_kv_len > 0 ? max_kv_len / FA_KEYS + 1 : 1;
   int parts_target = (int)((units_per_cta * resident + items - 1) / items);
   parts_target = parts_target < 1 ? 1 : (parts_target > 8 ? 8 : parts_target);
@@ -545,7 +545,7 @@ MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, 
   const long long units = items * max_parts;
   const int ctas = (int)(units < resident ? units : resident);
   launch_kernel(prefill_attention_tcgen05_kernel, dim3(ctas), dim3(FA_THREADS), shared, stream, q_map, k_map, v_map,
-                (bf16*)out, tile_seg, tile_row0, seg_q_start, seg_q_len, seg_pos0, block_table, table_width, tiles, heads,
+                (bf16*)out, tile_seg, tile_row0, seg_q_start, seg_q_len, seg_pos0, block_table, seg_slot, table_width, tiles, heads,
                 kv_heads, page_size, page_shift, window, scale * 1.4426950408889634f, queue, error_word, max_parts,
                 tiles_per_unit, (float*)scratch, counters);
   return launch_status();

@@ -17,7 +17,7 @@
 #define MLR_TOO_LARGE (-4)
 #define MLR_DEVICE_FLAG (-5)
 
-// dtype codes shared with ops/library.py
+// dtype codes shared with ops/cuda_ops.py
 #define MLR_F32 0
 #define MLR_BF16 1
 
@@ -26,6 +26,20 @@
 namespace mlr {
 
 typedef __nv_bfloat16 bf16;
+
+// What the device keeps of one live request, indexed by the request's slot: eight 32-bit words, so
+// that the host can scatter whole records with the same kernel that scatters block-table rows.
+// `length` is the number of tokens the cache holds (= the position of the request's next token);
+// `counter` is the index of the token the request samples next (the counter of its random stream).
+struct SlotState {
+  int length;
+  int last_token;
+  int counter;
+  float temperature;
+  unsigned int seed_low, seed_high;
+  int spare[2];
+};
+static_assert(sizeof(SlotState) == 32, "the host packs slot records as eight 32-bit words");
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
@@ -117,6 +131,21 @@ inline void launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, 
 // One switch per library (each .cu is its own shared object).
 #define MLR_DEFINE_PDL_SWITCH \
   MLR_EXPORT void mlr_set_pdl(int enabled) { mlr::pdl_enabled() = enabled != 0; }
+
+// Streaming multiprocessors of the current device, asked once per process and device; planners
+// size grids and split counts from it.
+inline int sm_count() {
+  static int cached[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  if (cached[device] == 0) {
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+      count = 148;
+    cached[device] = count;
+  }
+  return cached[device];
+}
 
 inline int launch_status() {
   cudaError_t err = cudaGetLastError();

@@ -243,6 +243,57 @@ __global__ void rope_kv_write_kernel(const T* qkv, const int* __restrict__ posit
   }
 }
 
+
+// ---------------------------------------------------------------- resident tables and slot state
+// The three kernels below write the step's metadata on the device.  Later kernels of the same
+// step read that metadata before their own griddepcontrol.wait, so these kernels never let their
+// successor start early: they do not call pdl_trigger(), and the next kernel is launched only
+// once they have completed and their writes are visible.
+
+// dst[row_index[i]] = src[i] for rows of `width` 32-bit words: changed block-table rows and new
+// slot records, sent by the host in one buffer, land in the tables that stay on the device.
+__global__ void scatter_rows_kernel(int* __restrict__ dst, const int* __restrict__ row_index,
+                                    const int* __restrict__ src, int width) {
+  pdl_wait();
+  const int* from = src + (size_t)blockIdx.x * width;
+  int* to = dst + (size_t)row_index[blockIdx.x] * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = from[i];
+}
+
+// A step of decoded tokens, described by the slots of its requests alone: position (and segment
+// start) = the slot's length, input token = the slot's last sampled token (if token_ids is given),
+// and the place where the new key and value go = page of that position in the slot's table row.
+__global__ void decode_prepare_kernel(const int* __restrict__ seg_slot, const SlotState* state, int count,
+                                      int* token_ids, int* positions, int* seg_pos0,
+                                      const int* table, int table_width, int page_size, long long* kv_slots) {
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const int slot = seg_slot[i];
+  const int position = state[slot].length;
+  if (token_ids != nullptr) token_ids[i] = state[slot].last_token;
+  if (positions != nullptr) positions[i] = position;
+  if (seg_pos0 != nullptr) seg_pos0[i] = position;
+  if (kv_slots != nullptr) {
+    const int logical = position / page_size;
+    const int page = logical < table_width ? table[(size_t)slot * table_width + logical] : -1;
+    kv_slots[i] = page >= 0 ? (long long)page * page_size + (position - logical * page_size) : -1;
+  }
+}
+
+// After a step: every request of it holds seg_q_len more tokens.  With seg_pos0 the new length is
+// set from the host's figures (pos0 + len); without, the slot's own length grows by len (or by one
+// when seg_q_len is null).
+__global__ void advance_slots_kernel(const int* __restrict__ seg_slot, const int* __restrict__ seg_q_len,
+                                     const int* __restrict__ seg_pos0, int count, SlotState* state) {
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const int grow = seg_q_len != nullptr ? seg_q_len[i] : 1;
+  SlotState* mine = state + seg_slot[i];
+  mine->length = (seg_pos0 != nullptr ? seg_pos0[i] : mine->length) + grow;
+}
+
 template <typename T>
 int rope_kv_write_launch(const void* qkv, const int* positions, const float* inv_freq,
                          const long long* slots, void* q_out, void* k_pool, void* v_pool,
@@ -351,7 +402,7 @@ MLR_EXPORT int mlr_add_inplace(void* target, const void* delta, long long total,
   if (total == 0) return MLR_OK;
   if (total < 0) return MLR_BAD_SIZE;
   size_t blocks = ((size_t)total + 255) / 256;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
   if (dtype == MLR_F32)
     launch_kernel(add_inplace_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)target, (const float*)delta, (size_t)total);
   else if (dtype == MLR_BF16)
@@ -368,7 +419,7 @@ MLR_EXPORT int mlr_swiglu(const void* gate_up, void* out, long long rows, int in
   const size_t total = (size_t)rows * inner;
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
   if (dtype == MLR_F32)
     launch_kernel(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inner, block, total);
   else if (dtype == MLR_BF16)
@@ -392,4 +443,36 @@ MLR_EXPORT int mlr_rope_kv_write(const void* qkv, const int* positions, const fl
     return rope_kv_write_launch<bf16>(qkv, positions, inv_freq, slots, q_out, k_pool, v_pool, tokens,
                                       heads, kv_heads, head_dim, page_size, write_kv, stream);
   return MLR_BAD_DTYPE;
+}
+
+// dst: int32 [table rows, width]; row_index int32 [count]; src int32 [count, width].
+MLR_EXPORT int mlr_scatter_rows(int* dst, const int* row_index, const int* src, int count, int width,
+                                cudaStream_t stream) {
+  if (count == 0) return MLR_OK;
+  if (count < 0 || width <= 0) return MLR_BAD_SIZE;
+  launch_kernel(scatter_rows_kernel, dim3(count), dim3(width >= 256 ? 256 : 64), 0, stream, dst, row_index, src, width);
+  return launch_status();
+}
+
+// state: SlotState records (eight 32-bit words each).  token_ids, positions, seg_pos0 and kv_slots
+// may each be null; a model with several cache groups calls once per group with its table.
+MLR_EXPORT int mlr_decode_prepare(const int* seg_slot, const void* state, int count, int* token_ids,
+                                  int* positions, int* seg_pos0, const int* table, int table_width,
+                                  int page_size, long long* kv_slots, cudaStream_t stream) {
+  if (count == 0) return MLR_OK;
+  if (count < 0 || (kv_slots != nullptr && (table == nullptr || table_width <= 0 || page_size <= 0)))
+    return MLR_BAD_SIZE;
+  launch_kernel(decode_prepare_kernel, dim3((count + 127) / 128), dim3(128), 0, stream, seg_slot,
+                (const SlotState*)state, count, token_ids, positions, seg_pos0, table, table_width, page_size,
+                kv_slots);
+  return launch_status();
+}
+
+MLR_EXPORT int mlr_advance_slots(const int* seg_slot, const int* seg_q_len, const int* seg_pos0, int count,
+                                 void* state, cudaStream_t stream) {
+  if (count == 0) return MLR_OK;
+  if (count < 0) return MLR_BAD_SIZE;
+  launch_kernel(advance_slots_kernel, dim3((count + 127) / 128), dim3(128), 0, stream, seg_slot, seg_q_len,
+                seg_pos0, count, (SlotState*)state);
+  return launch_status();
 }

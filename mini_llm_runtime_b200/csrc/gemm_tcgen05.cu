@@ -461,10 +461,9 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
   const void* a_base = SWAP ? w : x;
   const void* b_base = SWAP ? x : w;
   const int a_rows = SWAP ? p.N : p.M, b_rows = SWAP ? p.M : p.N;
-  const CUtensorMap* a_cached = cached_tile_map(a_base, a_rows, p.K, TILE_ROWS);
-  const CUtensorMap* b_cached = cached_tile_map(b_base, b_rows, p.K, BN);
-  if (a_cached == nullptr || b_cached == nullptr) return MLR_BAD_ALIGNMENT;
-  const CUtensorMap map_a = *a_cached, map_b = *b_cached;
+  CUtensorMap map_a, map_b;
+  if (!cached_tile_map(&map_a, a_base, a_rows, p.K, TILE_ROWS) || !cached_tile_map(&map_b, b_base, b_rows, p.K, BN))
+    return MLR_BAD_ALIGNMENT;
   dim3 grid((a_rows + TILE_ROWS - 1) / TILE_ROWS, (b_rows + BN - 1) / BN, splits);
   launch_kernel(gemm_tcgen05_kernel<BN, SWAP, SWIGLU>, dim3(grid), dim3(GEMM_THREADS), shared, stream, map_a, map_b, p);
   return launch_status();
@@ -478,6 +477,7 @@ static int forced_bn = 0, forced_stages = 0, forced_splits = 0;
 
 static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
   GemmPlan plan;
+  const int sms = sm_count();
   const int total_kb = (K + TILE_K - 1) / TILE_K;
   if (M <= 128) {
     plan.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
@@ -485,13 +485,13 @@ static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
   } else {
     // Wide tiles cut the operand traffic per flop by a quarter; worth it once they still fill the
     // SMs and K is long enough for the main loop, not the epilogue, to set the time.
-    plan.bn = (N >= 256 && total_kb > 16 && ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + 255) / 256) >= 148) ? 256 : 128;
+    plan.bn = (N >= 256 && total_kb > 16 && ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + 255) / 256) >= sms) ? 256 : 128;
     if (forced_bn == 128 || (forced_bn == 256 && N >= 256)) plan.bn = forced_bn;
     plan.tiles = ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + plan.bn - 1) / plan.bn);
   }
   int splits = 1;
   if (M <= 128) {
-    // Few tiles cannot keep 148 SMs streaming weights, so K is cut; but the CTA that arrives last
+    // Few tiles cannot keep every SM streaming weights, so K is cut; but the CTA that arrives last
     // for a tile re-reads every split's partial tile (splits x bn x 512 bytes), which soon costs
     // more than the streaming saves when there are many token rows.  Estimate both and take the
     // cheapest count (microseconds; one CTA of this kernel streams about 50 GB/s - measured: 56 CTAs
@@ -504,8 +504,8 @@ static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
     double best = 1e30;
     for (int candidate = 1; candidate <= most; ++candidate) {
       const double ctas = (double)plan.tiles * candidate;
-      const double resident = ctas < 296 ? ctas : 296;
-      const double waves = ctas <= 296 ? 1.0 : ctas / 296.0;
+      const double resident = ctas < 2 * sms ? ctas : 2 * sms;
+      const double waves = ctas <= 2 * sms ? 1.0 : ctas / (2.0 * sms);
       double rate = all_bytes_per_us / resident;
       if (rate > sm_bytes_per_us) rate = sm_bytes_per_us;
       double cost = waves * tile_bytes / candidate / rate;
@@ -513,11 +513,11 @@ static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
       if (cost < best) { best = cost; splits = candidate; }
     }
   }
-  if (M > 128 && M <= 1024 && plan.tiles < 148 && total_kb >= 32 && !swiglu) {   // (that epilogue reads tensor memory only)
+  if (M > 128 && M <= 1024 && plan.tiles < sms && total_kb >= 32 && !swiglu) {   // (that epilogue reads tensor memory only)
     // A prompt portion of a few hundred rows times a long K has too few tiles for the SMs: cut K.
     // Measured 896 x 4864: 512 rows 29.1 -> 19.4 us with 4 splits, 1,024 rows 30.2 -> 24.8 us with 2;
     // at 2,048 rows (112 tiles) the reduction costs more than it saves (31 -> 39 us).
-    splits = 148 / plan.tiles;          // one CTA per SM: more splits only add to the reduction
+    splits = sms / plan.tiles;          // one CTA per SM: more splits only add to the reduction
     if (splits > 4) splits = 4;
     if (splits < 1) splits = 1;
     while (splits > 1 && (long long)plan.tiles * splits * plan.bn * TILE_ROWS * 4 > (24ll << 20)) --splits;
@@ -539,7 +539,7 @@ static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
   // 64 rows: 86 us with one CTA per SM, 64 us with two).
   const size_t few_rows_stage = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
   if (M <= 128 && forced_stages >= 2) stages = forced_stages <= MAX_STAGES ? forced_stages : MAX_STAGES;
-  else if (M <= 128 && plan.tiles * plan.splits > 148)
+  else if (M <= 128 && plan.tiles * plan.splits > sms)
     while (stages > 2 && stages * few_rows_stage > 110 * 1024) --stages;
   if (M > 128 && forced_stages >= 2 && forced_stages <= MAX_STAGES) stages = forced_stages;
   const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;

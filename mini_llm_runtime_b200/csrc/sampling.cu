@@ -26,7 +26,13 @@ __device__ __forceinline__ float uniform_from_seed(unsigned long long seed, long
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* logits, const float* __restrict__ temperatures,
               const long long* __restrict__ seeds, const long long* __restrict__ counters,
-              int* __restrict__ tokens, int vocab) {
+              int* __restrict__ tokens, int vocab, const int* __restrict__ row_slot, SlotState* state,
+              int advance) {
+  // With `state`, a row's temperature, seed and counter come from the slot record of its request
+  // (row_slot[row]); the chosen token is also written there as the request's last token, the
+  // counter grows by one and, with `advance`, so does the slot's length (a step in which every
+  // request brought exactly one token).  The record was written by the previous step's launch of
+  // this kernel, hence plain loads after the wait.
   pdl_trigger();
   pdl_wait();
   __shared__ float scratch[32];
@@ -35,7 +41,8 @@ sample_kernel(const float* logits, const float* __restrict__ temperatures,
   __shared__ int chosen;
   const float* row = logits + (size_t)blockIdx.x * vocab;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const float temperature = temperatures[blockIdx.x];
+  SlotState* record = state != nullptr ? state + row_slot[blockIdx.x] : nullptr;
+  const float temperature = record != nullptr ? record->temperature : temperatures[blockIdx.x];
 
   // ---- argmax with the lowest index on ties (also gives the softmax's max)
   float best = -INFINITY;
@@ -89,7 +96,14 @@ sample_kernel(const float* logits, const float* __restrict__ temperatures,
   __syncthreads();
   const float row_max = scratch[0];
   if (!(temperature > 0.f)) {
-    if (threadIdx.x == 0) tokens[blockIdx.x] = scratch_index[0];
+    if (threadIdx.x == 0) {
+      tokens[blockIdx.x] = scratch_index[0];
+      if (record != nullptr) {
+        record->last_token = scratch_index[0];
+        record->counter += 1;
+        if (advance) record->length += 1;
+      }
+    }
     return;
   }
 
@@ -112,7 +126,10 @@ sample_kernel(const float* logits, const float* __restrict__ temperatures,
     if (w == warp) before = everything;
     everything += warp_totals[w];
   }
-  const float u = uniform_from_seed((unsigned long long)seeds[blockIdx.x], counters[blockIdx.x]);
+  const unsigned long long seed = record != nullptr
+      ? ((unsigned long long)record->seed_high << 32) | record->seed_low : (unsigned long long)seeds[blockIdx.x];
+  const long long counter = record != nullptr ? (long long)record->counter : counters[blockIdx.x];
+  const float u = uniform_from_seed(seed, counter);
   const float target = u * everything;
   const bool mine = target >= before && (target < before + total);
   if (mine) {
@@ -136,7 +153,13 @@ sample_kernel(const float* logits, const float* __restrict__ temperatures,
   __syncthreads();
   if (threadIdx.x == 0) {
     // Rounding can leave the target just past the last stretch; take the last token then.
-    tokens[blockIdx.x] = chosen >= 0 ? chosen : vocab - 1;
+    const int token = chosen >= 0 ? chosen : vocab - 1;
+    tokens[blockIdx.x] = token;
+    if (record != nullptr) {
+      record->last_token = token;
+      record->counter += 1;
+      if (advance) record->length += 1;
+    }
   }
 }
 
@@ -152,6 +175,20 @@ MLR_EXPORT int mlr_sample(const float* logits, const float* temperatures, const 
                           cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || vocab <= 0) return MLR_BAD_SIZE;
-  launch_kernel(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, temperatures, seeds, counters, tokens, vocab);
+  launch_kernel(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, temperatures, seeds, counters,
+                tokens, vocab, (const int*)nullptr, (SlotState*)nullptr, 0);
+  return launch_status();
+}
+
+// The same choice with the sampling parameters taken from, and the result recorded in, the slot
+// records of the rows' requests: row_slot int32 [rows], state: SlotState records.  A request must
+// not own two rows of one call.
+MLR_EXPORT int mlr_sample_slots(const float* logits, const int* row_slot, void* state, int* tokens, int rows,
+                                int vocab, int advance, cudaStream_t stream) {
+  if (rows == 0) return MLR_OK;
+  if (rows < 0 || vocab <= 0 || row_slot == nullptr || state == nullptr) return MLR_BAD_SIZE;
+  launch_kernel(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, (const float*)nullptr,
+                (const long long*)nullptr, (const long long*)nullptr, tokens, vocab, row_slot, (SlotState*)state,
+                advance);
   return launch_status();
 }

@@ -89,10 +89,12 @@ static inline bool make_tile_map(CUtensorMap* map, const void* base, long long r
                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// The same through a small cache: encoding a map costs a few microseconds on the host, and a model
-// step asks for the same maps (weights, cache pools, activation buffers the allocator hands out
-// again) over and over.  Keyed by everything the map depends on; 256 entries, replaced in turn.
-// Not thread-safe: the kernels are launched from one host thread.
+// The same through a cache: encoding a map costs a few microseconds on the host, and a model step
+// asks for the same maps (weights, cache pools, activation buffers the allocator hands out again)
+// over and over.  A direct-mapped table keyed by everything the map depends on; an entry that
+// another key hashes onto is simply encoded again.  The map is copied out to the caller, so that a
+// later lookup can never change a map that an earlier lookup returned.  Not thread-safe: the
+// kernels are launched from one host thread.
 struct TileMapKey {
   const void* base;
   long long rows;
@@ -103,30 +105,31 @@ struct TileMapKey {
   }
 };
 
-static inline const CUtensorMap* cached_tile_map(const void* base, long long rows, long long width, int box_rows) {
-  constexpr int SLOTS = 256;
+static inline bool cached_tile_map(CUtensorMap* out, const void* base, long long rows, long long width, int box_rows) {
+  constexpr int SLOTS = 4096;
   static TileMapKey keys[SLOTS];
   static CUtensorMap maps[SLOTS];
-  static int used = 0, next = 0;
   const TileMapKey key{base, rows, width, box_rows};
-  for (int i = 0; i < used; ++i)
-    if (keys[i] == key) return &maps[i];
-  auto encode = encode_tiled();
-  if (encode == nullptr) return nullptr;
-  const int slot = used < SLOTS ? used : next;
-  cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)width * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-  cuuint32_t element_strides[2] = {1, 1};
-  if (encode(&maps[slot], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-             element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-    if (slot < used) keys[slot] = TileMapKey{nullptr, 0, 0, 0};
-    return nullptr;
+  unsigned long long h = (unsigned long long)(uintptr_t)base * 0x9E3779B97F4A7C15ull;
+  h ^= (unsigned long long)rows * 0xBF58476D1CE4E5B9ull + (unsigned long long)width * 0x94D049BB133111EBull +
+       (unsigned long long)box_rows;
+  const int slot = (int)((h >> 40) % SLOTS);
+  if (!(keys[slot] == key) || base == nullptr) {
+    auto encode = encode_tiled();
+    if (encode == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t element_strides[2] = {1, 1};
+    keys[slot] = TileMapKey{nullptr, 0, 0, 0};
+    if (encode(&maps[slot], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+    keys[slot] = key;
   }
-  keys[slot] = key;
-  if (used < SLOTS) ++used; else next = (next + 1) % SLOTS;
-  return &maps[slot];
+  *out = maps[slot];
+  return true;
 }
 
 }  // namespace mlr

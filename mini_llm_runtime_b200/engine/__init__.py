@@ -1,14 +1,12 @@
-from .admission import BlockReservation, PagedBlockAdmissionController
 from .engine import ContinuousBatchEngine, EngineStepResult, GreedyGenerationOutput, greedy_generate
 from .metrics import RequestMetricsCollector, RequestTimeline
-from .scheduler import (BatchingPolicy, FinishReason, RequestScheduler, RequestState, RequestStatus,
-                        ScheduledRequest, SchedulerBatch, SchedulerStepUpdate, WorkKind)
-from .step import CacheView, ModelRunner, SamplingRows, Segment, StepContext, StepEntry
+from .scheduler import (BatchingPolicy, CacheGate, FinishReason, Request, RequestScheduler, RequestStatus,
+                        StepOutcome, StepPlan, WorkItem, WorkKind)
+from .step import CacheView, HostBatch, ModelRunner, Segment, StepContext, StepEntry
 
 __all__ = [
-    "BatchingPolicy", "BlockReservation", "CacheView", "ContinuousBatchEngine", "EngineStepResult",
-    "FinishReason", "GreedyGenerationOutput", "ModelRunner", "PagedBlockAdmissionController",
-    "RequestMetricsCollector", "RequestScheduler", "RequestState", "RequestStatus", "RequestTimeline",
-    "SamplingRows", "ScheduledRequest", "SchedulerBatch", "SchedulerStepUpdate", "Segment",
-    "StepContext", "StepEntry", "WorkKind", "greedy_generate",
+    "BatchingPolicy", "CacheGate", "CacheView", "ContinuousBatchEngine", "EngineStepResult", "FinishReason",
+    "GreedyGenerationOutput", "HostBatch", "ModelRunner", "Request", "RequestMetricsCollector",
+    "RequestScheduler", "RequestStatus", "RequestTimeline", "Segment", "StepContext", "StepEntry",
+    "StepOutcome", "StepPlan", "WorkItem", "WorkKind", "greedy_generate",
 ]

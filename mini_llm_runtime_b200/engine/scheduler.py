@@ -1,33 +1,44 @@
-"""CPU request scheduler: waiting -> running -> finished, decode first, strict FIFO admission under
-token, request and page budgets, and prompts cut into portions.
+"""The request scheduler: who runs in the next step, with how many tokens.
 
-The state machine, names and rules are the reference's ``RequestScheduler``
-(src/mini_llm_runtime/scheduler.py:96-373): every running request decodes once per step before
-anything is admitted (:217-227); waiting prompts are admitted from the head of the queue only, and
-the queue stops at the first request that does not fit, never skipping it (:240-262);
-``max_mixed_prefill_tokens`` bounds prompt tokens in steps that began with running requests
-(:247-255); ``schedule_step`` and ``apply_step_results`` alternate (:207-208); ``abort_step`` puts
-newly admitted requests back at the head of the queue and does not consume the step index
-(:341-373); EOS wins over the length limit (:318-321).
+It keeps the rules of the reference's ``RequestScheduler``
+(src/mini_llm_runtime/scheduler.py:205-288 for scheduling, :290-373 for results and abort, and
+block_admission.py:35-93 for page admission) on a data model of its own:
 
-What is new here is the *portion*: the reference refuses prompts longer than the token budget
-(:181-185).  Here a prompt that does not fit the rest of the step's budget is admitted with as
-many tokens as fit and stays running, "prefilling", getting further portions in later steps; it
-emits its first token in the step that consumes its last prompt token.  ``chunked_prefill=False``
-restores the reference's whole-prompt behaviour.
+* every request that has consumed its prompt decodes once per step, before anything else is
+  considered (decode first);
+* prompts that are already under way get their next portion, in arrival order;
+* waiting prompts are admitted from the head of the queue only; the first one that does not fit
+  (no free place, no token budget left, or the page gate says no) stops admission for this step and
+  is never overtaken (strict FIFO, head-of-line blocking);
+* a step that began with running requests may spend at most ``max_mixed_prefill_tokens`` on prompt
+  tokens, so that decodes are not starved by long prompts;
+* ``STATIC`` batching admits only while nothing is running (a cohort drains before the next);
+* a stop token ends a request even on the step that reaches its token limit;
+* scheduling and results alternate; an aborted step returns the requests it admitted to the head of
+  the queue in their order and the step keeps its index.
 
-When pages run out the decision is the reference's: the admission callback says no, the request
-waits at the head of the queue (and everything behind it waits too) until a finished request
-gives pages back; nothing is preempted, swapped or recomputed.  Because admission promises a
-request the pages of its whole life, a running request never runs out.
+New here is the *portion*: the reference refuses prompts longer than the token budget
+(scheduler.py:181-185).  Here such a prompt is admitted with as many tokens as fit, stays running
+while it consumes further portions, and emits its first token with its last portion.
+``chunked_prefill=False`` restores the reference's whole-prompt rule.
+
+Pages.  The scheduler owns admission: before a request leaves the queue it asks the *gate* (the
+cache manager, through ``CacheGate``) for a slot and a promise of the pages of the request's whole
+life, and it gives both back when the request finishes, is aborted or fails.  When pages run out
+the decision is the reference's: the head of the queue waits, and everything behind it, until a
+finished request frees pages; nothing is preempted, swapped or recomputed.  Because the promise
+covers a request's whole life, a running request never finds the pool empty.
 """
 
 from __future__ import annotations
 
 from collections import deque
-from collections.abc import Callable, Collection, Mapping, Sequence
+from collections.abc import Collection, Mapping, Sequence
 from dataclasses import dataclass, field
 from enum import Enum
+from typing import Protocol
+
+from ..sampling import GREEDY, SamplingParams
 
 
 class RequestStatus(str, Enum):
@@ -39,6 +50,7 @@ class RequestStatus(str, Enum):
 class FinishReason(str, Enum):
     EOS = "eos"
     MAX_TOKENS = "max_tokens"
+    ERROR = "error"            # the step that ran it reported a device error; its output is cut short
 
 
 class WorkKind(str, Enum):
@@ -53,326 +65,376 @@ class BatchingPolicy(str, Enum):
     STATIC = "static"
 
 
+def _token(value, what: str) -> int:
+    if isinstance(value, bool) or not isinstance(value, int) or value < 0:
+        raise ValueError(f"{what} must be non-negative integers, got {value!r}")
+    return value
+
+
 @dataclass
-class RequestState:
-    """What the scheduler knows of one request; it holds no device memory."""
+class Request:
+    """One request as the scheduler sees it.  It holds no device memory; ``slot`` names the place
+    the cache manager gave it while it runs."""
 
     request_id: str
-    prompt_token_ids: tuple[int, ...]
+    prompt: tuple[int, ...]
     max_new_tokens: int
-    eos_token_ids: frozenset[int]
-    arrival_index: int
-    temperature: float = 0.0
-    seed: int = 0
+    stop_tokens: frozenset[int]
+    sampling: SamplingParams
+    order: int                                  # arrival number: the queue's order
     status: RequestStatus = RequestStatus.WAITING
-    prefill_cursor: int = 0           # prompt tokens already run
+    cursor: int = 0                             # prompt tokens consumed by applied steps
+    output: list[int] = field(default_factory=list, repr=False)
     finish_reason: FinishReason | None = None
-    _generated_token_ids: list[int] = field(default_factory=list, repr=False)
+    slot: int | None = None
 
     @property
-    def prefilled(self) -> bool:
-        return self.prefill_cursor >= len(self.prompt_token_ids)
+    def prompt_token_ids(self) -> tuple[int, ...]:
+        return self.prompt
 
     @property
     def generated_token_ids(self) -> tuple[int, ...]:
-        return tuple(self._generated_token_ids)
+        return tuple(self.output)
 
     @property
-    def max_cache_tokens(self) -> int:
-        # The last generated token is never fed back, so it is never cached
-        # (reference: scheduler.py:52-55).
-        return len(self.prompt_token_ids) + self.max_new_tokens - 1
+    def prompt_done(self) -> bool:
+        return self.cursor >= len(self.prompt)
+
+    @property
+    def lifetime_tokens(self) -> int:
+        """Most tokens the cache ever holds for it: the last generated token is never fed back
+        (reference: scheduler.py:52-55)."""
+        return len(self.prompt) + self.max_new_tokens - 1
+
+    @property
+    def temperature(self) -> float:
+        return self.sampling.temperature
+
+    @property
+    def seed(self) -> int:
+        return self.sampling.seed
 
 
 @dataclass(frozen=True)
-class ScheduledRequest:
+class WorkItem:
     """One request's input to the model in one step."""
 
     request_id: str
     kind: WorkKind
-    input_token_ids: tuple[int, ...]
-    emits_token: bool = True          # False for a prompt portion that is not the last
-    newly_admitted: bool = False
-
-    @property
-    def token_cost(self) -> int:
-        return len(self.input_token_ids)
+    tokens: tuple[int, ...]
+    emits: bool = True          # False for a prompt portion that is not the last
+    admitted: bool = False      # the request left the queue in this step
+    slot: int | None = None
 
 
 @dataclass(frozen=True)
-class SchedulerBatch:
-    step_index: int
-    items: tuple[ScheduledRequest, ...]
-    token_count: int
+class StepPlan:
+    index: int
+    items: tuple[WorkItem, ...]
+
+    @property
+    def token_count(self) -> int:
+        return sum(len(item.tokens) for item in self.items)
+
+    def ids(self, *, kind: WorkKind | None = None, admitted: bool | None = None,
+            emits: bool | None = None) -> tuple[str, ...]:
+        return tuple(item.request_id for item in self.items
+                     if (kind is None or item.kind is kind)
+                     and (admitted is None or item.admitted == admitted)
+                     and (emits is None or item.emits == emits))
 
     @property
     def prefill_request_ids(self) -> tuple[str, ...]:
-        return tuple(item.request_id for item in self.items if item.kind is WorkKind.PREFILL)
+        return self.ids(kind=WorkKind.PREFILL)
 
     @property
     def decode_request_ids(self) -> tuple[str, ...]:
-        return tuple(item.request_id for item in self.items if item.kind is WorkKind.DECODE)
+        return self.ids(kind=WorkKind.DECODE)
 
     @property
     def admitted_request_ids(self) -> tuple[str, ...]:
-        return tuple(item.request_id for item in self.items if item.newly_admitted)
+        return self.ids(admitted=True)
 
     @property
     def emitting_request_ids(self) -> tuple[str, ...]:
-        return tuple(item.request_id for item in self.items if item.emits_token)
+        return self.ids(emits=True)
+
+    @property
+    def decode_only(self) -> bool:
+        return all(item.kind is WorkKind.DECODE for item in self.items)
 
 
 @dataclass(frozen=True)
-class SchedulerStepUpdate:
-    step_index: int
+class StepOutcome:
+    index: int
     emitted_tokens: tuple[tuple[str, int], ...]
     finished_request_ids: tuple[str, ...]
+    freed: Mapping[str, object] = field(default_factory=dict)    # what the gate gave back per finished request
+
+
+class Gate(Protocol):
+    """Where admitted requests get their resources.  ``admit`` answers with the request's slot, or
+    None having changed nothing; ``release`` gives everything back."""
+
+    def admit(self, request: Request) -> int | None: ...
+
+    def release(self, request_id: str) -> object: ...
+
+
+class CacheGate:
+    """The cache manager as the scheduler's gate: a slot and a promise of pages for the request's
+    whole life (prompt + max_new_tokens - 1 tokens), sampling parameters into the slot's record."""
+
+    def __init__(self, cache) -> None:
+        self.cache = cache
+
+    def admit(self, request: Request) -> int | None:
+        held = self.cache.create_request(request.request_id, lifetime_tokens=request.lifetime_tokens,
+                                         temperature=request.sampling.temperature, seed=request.sampling.seed)
+        return None if held is None else held.slot
+
+    def release(self, request_id: str):
+        return self.cache.release(request_id) if request_id in self.cache.requests else {}
+
+
+class _Budget:
+    """What is left of a step's limits while the step is put together."""
+
+    def __init__(self, tokens: int, prompt_tokens: int | None) -> None:
+        self.tokens = tokens
+        self.prompt_tokens = prompt_tokens      # None: prompt tokens are limited by ``tokens`` only
+
+    def room_for_prompt(self) -> int:
+        return self.tokens if self.prompt_tokens is None else min(self.tokens, self.prompt_tokens)
+
+    def spend(self, count: int, *, prompt: bool) -> None:
+        self.tokens -= count
+        if prompt and self.prompt_tokens is not None:
+            self.prompt_tokens -= count
 
 
 class RequestScheduler:
     def __init__(self, *, max_running_requests: int, max_batch_tokens: int,
-                 max_mixed_prefill_tokens: int | None = None,
-                 admission_callback: Callable[[RequestState], bool] | None = None,
+                 max_mixed_prefill_tokens: int | None = None, gate: Gate | None = None,
                  batching_policy: BatchingPolicy = BatchingPolicy.CONTINUOUS,
                  chunked_prefill: bool = True) -> None:
-        if max_running_requests <= 0 or max_batch_tokens <= 0:
-            raise ValueError("max_running_requests and max_batch_tokens must be > 0")
+        for name, value in (("max_running_requests", max_running_requests), ("max_batch_tokens", max_batch_tokens)):
+            if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
+                raise ValueError(f"{name} must be a positive integer")
         if max_running_requests > max_batch_tokens:
-            raise ValueError("max_running_requests must not exceed max_batch_tokens, or a running "
-                             "request could miss its decode step")
-        if not isinstance(batching_policy, BatchingPolicy):
-            raise ValueError("batching_policy must be a BatchingPolicy")
+            raise ValueError("max_running_requests must not exceed max_batch_tokens: every running request "
+                             "needs one token of the budget to decode")
         if max_mixed_prefill_tokens is not None and (
                 isinstance(max_mixed_prefill_tokens, bool) or not isinstance(max_mixed_prefill_tokens, int)
                 or max_mixed_prefill_tokens <= 0):
             raise ValueError("max_mixed_prefill_tokens must be a positive integer or None")
+        if not isinstance(batching_policy, BatchingPolicy):
+            raise ValueError("batching_policy must be a BatchingPolicy")
         self.max_running_requests = max_running_requests
         self.max_batch_tokens = max_batch_tokens
         self.max_mixed_prefill_tokens = max_mixed_prefill_tokens
         self.batching_policy = batching_policy
         self.chunked_prefill = chunked_prefill
-        self._admission_callback = admission_callback
-        self._requests: dict[str, RequestState] = {}
-        self._waiting: deque[str] = deque()
-        self._running: list[str] = []
-        self._finished: list[str] = []
-        self._next_arrival_index = 0
-        self._next_step_index = 0
-        self._outstanding: SchedulerBatch | None = None
+        self.gate = gate
+        self._by_id: dict[str, Request] = {}
+        self._queue: deque[Request] = deque()           # waiting, arrival order
+        self._live: dict[str, Request] = {}             # running, admission order
+        self._done: list[str] = []
+        self._arrivals = 0
+        self._step_index = 0
+        self._plan: StepPlan | None = None
 
-    # ------------------------------------------------------------------ views
+    # ------------------------------------------------------------------ what is where
     @property
     def waiting_request_ids(self) -> tuple[str, ...]:
-        return tuple(self._waiting)
+        return tuple(request.request_id for request in self._queue)
 
     @property
     def running_request_ids(self) -> tuple[str, ...]:
-        return tuple(self._running)
+        return tuple(self._live)
 
     @property
     def finished_request_ids(self) -> tuple[str, ...]:
-        return tuple(self._finished)
+        return tuple(self._done)
 
     @property
-    def outstanding_batch(self) -> SchedulerBatch | None:
-        return self._outstanding
+    def outstanding_plan(self) -> StepPlan | None:
+        return self._plan
 
     @property
     def has_unfinished_requests(self) -> bool:
-        return bool(self._waiting or self._running or self._outstanding)
+        return bool(self._queue or self._live or self._plan)
 
-    def get_request(self, request_id: str) -> RequestState:
+    def get_request(self, request_id: str) -> Request:
         try:
-            return self._requests[request_id]
+            return self._by_id[request_id]
         except KeyError:
             raise KeyError(f"unknown request_id={request_id!r}") from None
 
-    # ------------------------------------------------------------------ submit
+    # ------------------------------------------------------------------ arrival
     def submit(self, request_id: str, prompt_token_ids: Sequence[int], *, max_new_tokens: int,
                eos_token_ids: int | Collection[int] | None = None, temperature: float = 0.0,
-               seed: int = 0) -> RequestState:
-        """Append a request to the waiting queue (allowed while a batch is outstanding)."""
+               seed: int = 0, sampling: SamplingParams | None = None) -> Request:
+        """Queue a request; allowed at any time, also while a plan is outstanding."""
         if not request_id:
             raise ValueError("request_id must not be empty")
-        if request_id in self._requests:
+        if request_id in self._by_id:
             raise ValueError(f"request_id={request_id!r} already exists")
-        prompt = self._validate_token_sequence(prompt_token_ids, "prompt_token_ids")
+        prompt = tuple(_token(t, "prompt_token_ids") for t in prompt_token_ids)
+        if not prompt:
+            raise ValueError("prompt_token_ids must not be empty")
         if not self.chunked_prefill and len(prompt) > self.max_batch_tokens:
-            raise ValueError(f"prompt length={len(prompt)} exceeds max_batch_tokens="
-                             f"{self.max_batch_tokens} and chunked prefill is off")
+            raise ValueError(f"prompt length={len(prompt)} exceeds max_batch_tokens={self.max_batch_tokens} "
+                             "and chunked prefill is off")
         if isinstance(max_new_tokens, bool) or not isinstance(max_new_tokens, int) or max_new_tokens <= 0:
             raise ValueError("max_new_tokens must be a positive integer")
-        if not isinstance(temperature, (int, float)) or isinstance(temperature, bool) or temperature < 0:
-            raise ValueError("temperature must be a number >= 0 (0 selects greedy)")
-        if isinstance(seed, bool) or not isinstance(seed, int) or not 0 <= seed < (1 << 63):
-            raise ValueError("seed must be an integer in [0, 2^63)")
-        request = RequestState(
-            request_id=request_id, prompt_token_ids=prompt, max_new_tokens=int(max_new_tokens),
-            eos_token_ids=self._normalize_eos(eos_token_ids), arrival_index=self._next_arrival_index,
-            temperature=float(temperature), seed=int(seed))
-        self._next_arrival_index += 1
-        self._requests[request_id] = request
-        self._waiting.append(request_id)
+        if eos_token_ids is None:
+            stop = frozenset()
+        else:
+            stop = frozenset(_token(t, "eos_token_ids")
+                             for t in ((eos_token_ids,) if isinstance(eos_token_ids, int) else eos_token_ids))
+        if sampling is None:
+            sampling = SamplingParams(temperature, seed) if (temperature or seed) else GREEDY
+        request = Request(request_id, prompt, max_new_tokens, stop, sampling, order=self._arrivals)
+        self._arrivals += 1
+        self._by_id[request_id] = request
+        self._queue.append(request)
         return request
 
-    # ------------------------------------------------------------------ schedule
-    def schedule_step(self) -> SchedulerBatch | None:
-        """Decodes of all running requests first, then further portions of running prompts, then
-        strict-FIFO admission of waiting prompts with what is left of the budgets."""
-        if self._outstanding is not None:
-            raise RuntimeError("the previous scheduler batch has not been applied or aborted")
-        if not self._running and not self._waiting:
+    # ------------------------------------------------------------------ the next step
+    def schedule_step(self) -> StepPlan | None:
+        if self._plan is not None:
+            raise RuntimeError("the previous plan has been neither applied nor aborted")
+        if not self._live and not self._queue:
             return None
+        began_with_running = bool(self._live)
+        budget = _Budget(self.max_batch_tokens,
+                         self.max_mixed_prefill_tokens if began_with_running else None)
+        items: list[WorkItem] = []
 
-        items: list[ScheduledRequest] = []
-        running_at_step_start = bool(self._running)
-        for request_id in self._running:
-            request = self._requests[request_id]
-            if request.prefilled:
-                if not request._generated_token_ids:
-                    raise RuntimeError(f"running request {request_id!r} has no prefill result")
-                items.append(ScheduledRequest(request_id, WorkKind.DECODE,
-                                              (request._generated_token_ids[-1],)))
-        token_count = len(items)
-        mixed_prefill_tokens = 0
+        for request in self._live.values():                 # 1. decodes
+            if request.prompt_done:
+                if not request.output:
+                    raise RuntimeError(f"running request {request.request_id!r} has consumed its prompt "
+                                       "but has no token to feed back")
+                items.append(WorkItem(request.request_id, WorkKind.DECODE, (request.output[-1],), slot=request.slot))
+                budget.spend(1, prompt=False)
 
-        def portion_budget() -> int:
-            budget = self.max_batch_tokens - token_count
-            if running_at_step_start and self.max_mixed_prefill_tokens is not None:
-                budget = min(budget, self.max_mixed_prefill_tokens - mixed_prefill_tokens)
-            return budget
-
-        # Prompts already running go on before anything new is admitted (arrival order).
-        for request_id in self._running:
-            request = self._requests[request_id]
-            if request.prefilled:
+        for request in self._live.values():                 # 2. prompts under way
+            if request.prompt_done:
                 continue
-            budget = portion_budget()
-            if budget <= 0:
+            room = budget.room_for_prompt()
+            if room <= 0:
                 break
-            remaining = len(request.prompt_token_ids) - request.prefill_cursor
-            count = min(remaining, budget)
-            start = request.prefill_cursor
-            items.append(ScheduledRequest(request_id, WorkKind.PREFILL,
-                                          request.prompt_token_ids[start:start + count],
-                                          emits_token=(count == remaining)))
-            token_count += count
-            mixed_prefill_tokens += count
+            items.append(self._portion(request, room, admitted=False))
+            budget.spend(len(items[-1].tokens), prompt=True)
 
-        available_slots = self.max_running_requests - len(self._running)
-        may_admit = self.batching_policy is BatchingPolicy.CONTINUOUS or not running_at_step_start
-        while may_admit and self._waiting and available_slots > 0:
-            request_id = self._waiting[0]
-            request = self._requests[request_id]
-            prompt_cost = len(request.prompt_token_ids)
-            budget = portion_budget()
-            if self.chunked_prefill:
-                if budget <= 0:
-                    break
-                count = min(prompt_cost, budget)
-            else:
-                # Whole prompts only: the head of the queue that does not fit stops admission.
-                if prompt_cost > budget:
-                    break
-                count = prompt_cost
-            # The callback must have no effect when it answers False and must have reserved the
-            # request's resources when it answers True.
-            if self._admission_callback is not None and not self._admission_callback(request):
+        may_admit = self.batching_policy is BatchingPolicy.CONTINUOUS or not began_with_running
+        while may_admit and self._queue and len(self._live) < self.max_running_requests:   # 3. admission
+            request = self._queue[0]
+            room = budget.room_for_prompt()
+            if room <= 0 or (not self.chunked_prefill and len(request.prompt) > room):
                 break
-            self._waiting.popleft()
+            if self.gate is not None:
+                slot = self.gate.admit(request)
+                if slot is None:
+                    break
+                request.slot = slot
+            self._queue.popleft()
             request.status = RequestStatus.RUNNING
-            self._running.append(request_id)
-            items.append(ScheduledRequest(request_id, WorkKind.PREFILL, request.prompt_token_ids[:count],
-                                          emits_token=(count == prompt_cost), newly_admitted=True))
-            token_count += count
-            if running_at_step_start:
-                mixed_prefill_tokens += count
-            available_slots -= 1
+            self._live[request.request_id] = request
+            items.append(self._portion(request, room, admitted=True))
+            budget.spend(len(items[-1].tokens), prompt=True)
 
         if not items:
             return None
-        batch = SchedulerBatch(self._next_step_index, tuple(items), token_count)
-        self._next_step_index += 1
-        self._outstanding = batch
-        return batch
-
-    # ------------------------------------------------------------------ results
-    def apply_step_results(self, generated_tokens: Mapping[str, int]) -> SchedulerStepUpdate:
-        """Write back one token for every item that emits one; validated before any change."""
-        batch = self._outstanding
-        if batch is None:
-            raise RuntimeError("no scheduler batch is waiting for results")
-        expected_ids = batch.emitting_request_ids
-        actual_ids = tuple(generated_tokens)
-        if set(actual_ids) != set(expected_ids) or len(actual_ids) != len(expected_ids):
-            missing = sorted(set(expected_ids) - set(actual_ids))
-            extra = sorted(set(actual_ids) - set(expected_ids))
-            raise ValueError(f"step results do not match the batch: missing={missing}, extra={extra}")
-        validated = {rid: self._validate_token(generated_tokens[rid], "generated token") for rid in expected_ids}
-
-        finished: list[str] = []
-        emitted: list[tuple[str, int]] = []
-        for item in batch.items:
-            request = self._requests[item.request_id]
-            if item.kind is WorkKind.PREFILL:
-                request.prefill_cursor += len(item.input_token_ids)
-            if not item.emits_token:
-                continue
-            token = validated[item.request_id]
-            request._generated_token_ids.append(token)
-            emitted.append((item.request_id, token))
-            if token in request.eos_token_ids:
-                request.finish_reason = FinishReason.EOS
-            elif len(request._generated_token_ids) >= request.max_new_tokens:
-                request.finish_reason = FinishReason.MAX_TOKENS
-            if request.finish_reason is not None:
-                request.status = RequestStatus.FINISHED
-                finished.append(item.request_id)
-        if finished:
-            gone = set(finished)
-            self._running = [rid for rid in self._running if rid not in gone]
-            self._finished.extend(finished)
-        self._outstanding = None
-        return SchedulerStepUpdate(batch.step_index, tuple(emitted), tuple(finished))
-
-    def abort_step(self) -> SchedulerBatch:
-        """Undo the outstanding batch so that the step can be tried again.  Requests admitted in
-        it return to the head of the waiting queue in their order; running requests had not
-        changed.  The cache side is released by the engine before this is called."""
-        batch = self._outstanding
-        if batch is None:
-            raise RuntimeError("no scheduler batch to abort")
-        admitted = batch.admitted_request_ids
-        for request_id in admitted:
-            request = self._requests[request_id]
-            if request.prefill_cursor or request._generated_token_ids:
-                raise RuntimeError(f"request {request_id!r} already has results; the step cannot be aborted")
-            request.status = RequestStatus.WAITING
-        gone = set(admitted)
-        self._running = [rid for rid in self._running if rid not in gone]
-        for request_id in reversed(admitted):
-            self._waiting.appendleft(request_id)
-        self._outstanding = None
-        self._next_step_index = batch.step_index
-        return batch
-
-    # ------------------------------------------------------------------ validation helpers
-    @classmethod
-    def _validate_token_sequence(cls, values: Sequence[int], name: str) -> tuple[int, ...]:
-        tokens = tuple(values)
-        if not tokens:
-            raise ValueError(f"{name} must not be empty")
-        return tuple(cls._validate_token(token, name) for token in tokens)
+        self._plan = StepPlan(self._step_index, tuple(items))
+        self._step_index += 1
+        return self._plan
 
     @staticmethod
-    def _validate_token(value: int, name: str) -> int:
-        if isinstance(value, bool) or not isinstance(value, int) or value < 0:
-            raise ValueError(f"{name} must be non-negative integers")
-        return value
+    def _portion(request: Request, room: int, *, admitted: bool) -> WorkItem:
+        left = len(request.prompt) - request.cursor
+        count = min(left, room)
+        tokens = request.prompt[request.cursor:request.cursor + count]
+        return WorkItem(request.request_id, WorkKind.PREFILL, tokens, emits=count == left, admitted=admitted,
+                        slot=request.slot)
 
-    @classmethod
-    def _normalize_eos(cls, values: int | Collection[int] | None) -> frozenset[int]:
-        if values is None:
-            return frozenset()
-        raw = (values,) if isinstance(values, int) else tuple(values)
-        return frozenset(cls._validate_token(value, "eos_token_ids") for value in raw)
+    # ------------------------------------------------------------------ what the step produced
+    def apply_step_results(self, generated_tokens: Mapping[str, int]) -> StepOutcome:
+        """One token for every item that emits one.  Everything is checked before anything changes."""
+        plan = self._plan
+        if plan is None:
+            raise RuntimeError("no plan is waiting for results")
+        expected = plan.emitting_request_ids
+        if len(generated_tokens) != len(expected) or set(generated_tokens) != set(expected):
+            missing = sorted(set(expected) - set(generated_tokens))
+            extra = sorted(set(generated_tokens) - set(expected))
+            raise ValueError(f"step results do not match the plan: missing={missing}, extra={extra}")
+        checked = {rid: _token(generated_tokens[rid], "generated tokens") for rid in expected}
+
+        emitted: list[tuple[str, int]] = []
+        finished: list[str] = []
+        for item in plan.items:
+            request = self._by_id[item.request_id]
+            if item.kind is WorkKind.PREFILL:
+                request.cursor += len(item.tokens)
+            if not item.emits:
+                continue
+            token = checked[item.request_id]
+            request.output.append(token)
+            emitted.append((item.request_id, token))
+            if token in request.stop_tokens:
+                request.finish_reason = FinishReason.EOS
+            elif len(request.output) >= request.max_new_tokens:
+                request.finish_reason = FinishReason.MAX_TOKENS
+            if request.finish_reason is not None:
+                finished.append(item.request_id)
+        freed = {rid: self._retire(self._by_id[rid]) for rid in finished}
+        self._plan = None
+        return StepOutcome(plan.index, tuple(emitted), tuple(finished), freed)
+
+    def _retire(self, request: Request):
+        request.status = RequestStatus.FINISHED
+        self._live.pop(request.request_id, None)
+        self._done.append(request.request_id)
+        slot, request.slot = request.slot, None
+        return self.gate.release(request.request_id) if self.gate is not None and slot is not None else {}
+
+    def abort_step(self) -> StepPlan:
+        """Take the outstanding plan back so that the step can be tried again.  Requests it admitted
+        give their slot and pages back and return to the head of the queue in their order; the
+        others had not changed.  The step keeps its index."""
+        plan = self._plan
+        if plan is None:
+            raise RuntimeError("no plan to abort")
+        returned = [self._by_id[rid] for rid in plan.admitted_request_ids]
+        for request in returned:
+            if request.cursor or request.output:
+                raise RuntimeError(f"request {request.request_id!r} already has results; its step cannot be aborted")
+        for request in reversed(returned):
+            del self._live[request.request_id]
+            if self.gate is not None and request.slot is not None:
+                self.gate.release(request.request_id)
+            request.slot = None
+            request.status = RequestStatus.WAITING
+            self._queue.appendleft(request)
+        self._plan = None
+        self._step_index = plan.index
+        return plan
+
+    def fail_requests(self, request_ids: Collection[str]) -> tuple[str, ...]:
+        """End the named requests with ``FinishReason.ERROR`` wherever they are, give their resources
+        back and drop the outstanding plan.  For results that cannot be trusted (a device error)."""
+        failed = []
+        for request_id in request_ids:
+            request = self._by_id[request_id]
+            if request.status is RequestStatus.FINISHED:
+                continue
+            if request.status is RequestStatus.WAITING:
+                self._queue.remove(request)
+            request.finish_reason = FinishReason.ERROR
+            self._retire(request)
+            failed.append(request_id)
+        self._plan = None
+        return tuple(failed)

@@ -11,9 +11,17 @@ reference's result rows follow scheduler item order (engine.py:256-261).  The st
 the reference's: pages are taken for all requests or none, and a failure anywhere leaves every
 request's visible length unchanged (paged_batch.py:89-114, engine.py:249-254).
 
-Host-side work per step is one packed metadata buffer (token ids, positions, segment table,
-attention tiles, per-group slot mapping and block tables) written into pinned memory and sent
-with a single host-to-device copy.
+What the step function knows: segments (which rows belong to which request), positions, slots and
+wanted rows.  It knows nothing of attention: work lists that a mixer's kernels need are made by
+the mixer (``Mixer.step_plan``) and travel opaquely in the step's one metadata buffer.
+
+What crosses to the device per step.  Block tables and slot records live on the device (the cache
+manager owns them); only rows that changed are sent.  A mixed step sends one packed buffer (token
+ids, positions, the segment table, the places of new keys and values, work lists, changed rows).
+A step of decoded tokens only is described by the slots of its requests: a first small kernel
+derives positions, input tokens (the ones the sampling kernel stored) and cache places from the
+slot records, so a captured decode step is replayed without sending anything unless the set of
+requests changed, the host supplies the tokens, or a request crossed into a new page.
 """
 
 from __future__ import annotations
@@ -25,13 +33,8 @@ import numpy as np
 import torch
 
 from .. import ops
-from ..cache.manager import CacheGroup, CacheManager, RequestCache
+from ..cache.manager import CacheManager, RequestCache
 from ..models.decoder import DecoderModel
-from ..ops.cuda_ops import AttentionBatch
-
-ROWS_PER_TILE = 16    # rows one CTA of the generic attention kernel handles
-WIDE_TILE_ROWS = 64   # rows one CTA of the tensor-core prefill kernel handles
-BIG_TILE_ROWS = 128   # rows of one work item of the tcgen05 prefill kernel
 
 
 @dataclass
@@ -44,16 +47,6 @@ class StepEntry:
 
 
 @dataclass
-class SamplingRows:
-    """Per wanted row: temperature (0 = greedy), the request's seed, and the index of the token
-    being produced (the counter of the request's random stream)."""
-
-    temperatures: Sequence[float]
-    seeds: Sequence[int]
-    token_indices: Sequence[int]
-
-
-@dataclass
 class Segment:
     request_id: str
     slot: int
@@ -63,17 +56,33 @@ class Segment:
 
 
 @dataclass
+class HostBatch:
+    """The step's shape as the host knows it before anything is sent: one entry per request."""
+
+    lengths: np.ndarray          # int32: rows each request brings
+    row_start: np.ndarray        # int32: its first row in the packed batch
+    position_start: np.ndarray   # int32: position of its first row
+    num_rows: int
+
+    @property
+    def num_segments(self) -> int:
+        return int(self.lengths.shape[0])
+
+
+@dataclass
 class CacheView:
     """What a mixer sees of its cache entry during one step."""
 
     entry: int
-    k_pool: torch.Tensor | None = None     # [pages, kv_heads, page_size, head_dim]
+    k_pool: torch.Tensor | None = None       # [pages, kv_heads, page_size, head_dim]
     v_pool: torch.Tensor | None = None
-    slots: torch.Tensor | None = None      # int64 [rows]: where each row's k and v go
-    batch: AttentionBatch | None = None
+    slots: torch.Tensor | None = None        # int64 [rows]: where each row's k and v go
+    block_table: torch.Tensor | None = None  # int32 [request slots, pages per request]; row = the request's slot
     page_size: int = 0
     window: int | None = None
-    state: torch.Tensor | None = None      # [max_requests, ...] for a fixed-size-state entry
+    state: torch.Tensor | None = None        # [request slots, ...] for a fixed-size-state entry
+    group: int = -1                          # entries of one group share pages, table and ``shared``
+    shared: dict = field(default_factory=dict)   # per step and group: mixers may keep derived objects here
 
 
 @dataclass
@@ -87,10 +96,24 @@ class StepContext:
     token_ids: torch.Tensor          # int32 [rows]
     positions: torch.Tensor          # int32 [rows]
     wanted_rows: torch.Tensor        # int32 [wanted]
-    segment_slots: torch.Tensor      # int32 [segments]: each request's state slot
+    seg_q_start: torch.Tensor        # int32 [segments]: first row of each request
+    seg_q_len: torch.Tensor          # int32 [segments]: its rows
+    seg_pos0: torch.Tensor           # int32 [segments]: position of its first row
+    seg_slot: torch.Tensor           # int32 [segments]: its slot (row of resident tables and state)
+    max_q_len: int = 0
+    max_kv_len: int = 0
     views: dict[int, CacheView] = field(default_factory=dict)
-    sampling: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None
+    plans: dict = field(default_factory=dict)       # plan key -> (device arrays by name, counts by name)
     wanted_all_rows: bool = False    # wanted_rows is 0, 1, .., rows-1 (a decode step): no gather needed
+    wanted_slot: torch.Tensor | None = None     # int32 [wanted]: slot of each wanted row's request (sampling)
+
+    @property
+    def num_segments(self) -> int:
+        return len(self.segments)
+
+    @property
+    def segment_slots(self) -> torch.Tensor:
+        return self.seg_slot
 
     def cache_view(self, entry: int) -> CacheView:
         return self.views[entry]
@@ -142,17 +165,17 @@ class _Packer:
 
 @dataclass
 class _CapturedStep:
-    """A decode step of one batch size as a CUDA graph with its fixed metadata buffer."""
+    """A decode step of one batch size as a CUDA graph.  Its metadata buffer has a fixed layout;
+    the first bytes hold what the host may have to refresh: the requests' slots, then the input
+    tokens (only when the host supplies them)."""
 
     metadata: torch.Tensor
     graph: "torch.cuda.CUDAGraph | None" = None
     logits: torch.Tensor | None = None
     tokens: torch.Tensor | None = None
-    launches: int = 0      # kernels in the graph
-    nbytes: int = 0
-    token_ids: torch.Tensor | None = None    # the input ids inside ``metadata`` (fixed address)
-    # pinned staging buffers with numpy views of every array at its fixed offset, used in turn
-    stagings: list = field(default_factory=list)
+    launches: int = 0                      # kernels in the graph
+    slots_now: tuple[int, ...] = ()        # the slots the device copy currently holds
+    stagings: list = field(default_factory=list)     # pinned [2 * batch] int32 buffers with their events
     cursor: int = 0
 
 
@@ -173,16 +196,15 @@ class ModelRunner:
         self.max_positions = model.spec.max_positions
         self._ring = _PinnedRing(self.device)
         self._device_meta: torch.Tensor | None = None
-        self._last_layout_bytes = 0
-        self._last_layout: list = []
         self.steps_run = 0
+        self.bytes_sent = 0        # host-to-device bytes of all steps so far (metadata and changed rows)
         # Decode-only steps (one token per request, its logits wanted) are captured into CUDA
         # graphs, one per batch size, and replayed: a decode step is some two hundred small
         # kernels, and launching them one by one from the host costs more than running them.
         self.use_graphs = (self.device.type == "cuda"
                            and all(getattr(part, "graph_safe", False) for part in model.parts()))
         self.graph_max_batch = 256
-        self._graphs: dict[tuple[int, bool], _CapturedStep] = {}
+        self._graphs: dict[tuple[int, bool, bool], _CapturedStep] = {}
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ metadata
@@ -203,134 +225,123 @@ class ModelRunner:
             raise RuntimeError("a captured step's metadata outgrew its buffer")
         device_buffer[:nbytes].copy_(staging[:nbytes], non_blocking=True)
         self._ring.sent(index)
+        self.bytes_sent += nbytes
         out = {}
         for name, array, offset in packer.items:
             flat = device_buffer[offset:offset + array.nbytes].view(_TORCH_OF[array.dtype])
             out[name] = flat.view(array.shape)
         return out
 
-    def _build_context(self, entries: Sequence[StepEntry], requests: list[RequestCache],
-                       sampling: SamplingRows | None = None, *, fixed_width: int | None = None,
-                       device_buffer: torch.Tensor | None = None) -> StepContext:
-        """Host-side description of the step, sent to the device.  ``fixed_width`` pins the block
-        tables' width (and with it the whole buffer layout for a given batch shape), which a
-        captured graph needs; ``device_buffer`` is that graph's own metadata buffer."""
-        cache = self.cache
+    def _pack_resident_updates(self, packer: _Packer) -> list[tuple[torch.Tensor, str, str]]:
+        """Changed rows of the resident tables join the step's buffer; returns what to scatter."""
+        pending = []
+        for number, (table, rows, values) in enumerate(self.cache.take_resident_updates()):
+            packer.add(f"update{number}.rows", rows)
+            packer.add(f"update{number}.values", values)
+            pending.append((table, f"update{number}.rows", f"update{number}.values"))
+        return pending
+
+    def _scatter_resident_updates(self, pending, dev) -> None:
+        kernels = ops.current()
+        for table, rows, values in pending:
+            kernels.scatter_rows(table, dev[rows], dev[values])
+        self.cache.resident_updates_sent()
+
+    def _send_resident_updates(self) -> None:
+        """The same for a step whose own metadata is not sent (a replayed decode step)."""
+        packer = _Packer()
+        pending = self._pack_resident_updates(packer)
+        if pending:
+            self._scatter_resident_updates(pending, self._upload(packer))
+
+    def _host_batch(self, entries: Sequence[StepEntry], requests: list[RequestCache]) -> HostBatch:
         lengths = np.array([len(e.tokens) for e in entries], dtype=np.int32)
         row_start = np.zeros(len(entries), dtype=np.int32)
         np.cumsum(lengths[:-1], out=row_start[1:])
         position_start = np.array([r.pending[0] for r in requests], dtype=np.int32)
-        total = int(lengths.sum())
+        return HostBatch(lengths, row_start, position_start, int(lengths.sum()))
 
+    def _step_plans(self, host: HostBatch) -> dict:
+        """Work lists from the mixers, one per plan key (mixers with equal keys share one)."""
+        plans = {}
+        for block in self.model.blocks:
+            key = getattr(block.mixer, "plan_key", None)
+            if key is not None and key not in plans:
+                plans[key] = block.mixer.step_plan(host)
+        return plans
+
+    def _pack(self, entries: Sequence[StepEntry], requests: list[RequestCache], *, want_slots: bool, fixed: bool):
+        """Lay the step's metadata out on the host.  ``fixed``: the layout of a captured decode step
+        (the requests' slots first, then the token ids: what a replay may have to refresh)."""
+        cache = self.cache
+        host = self._host_batch(entries, requests)
+        lengths, row_start, position_start, total = host.lengths, host.row_start, host.position_start, host.num_rows
         token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
         segment_of_row = np.repeat(np.arange(len(entries), dtype=np.int32), lengths)
         positions = (np.arange(total, dtype=np.int32) - row_start[segment_of_row]
                      + position_start[segment_of_row]).astype(np.int32)
         wanted = [row_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
         wanted_rows = np.concatenate(wanted).astype(np.int32) if wanted else np.zeros(0, dtype=np.int32)
-
-        # Attention tiles of at most 16 rows: segments longer than one row first, then the
-        # single-row (decode) segments, which a split-KV kernel may take instead.
-        decode_seg = np.flatnonzero(lengths == 1).astype(np.int32)
-        order = np.concatenate([np.flatnonzero(lengths != 1), decode_seg]).astype(np.int32)
-        tiles_per_segment = ((lengths + ROWS_PER_TILE - 1) // ROWS_PER_TILE)[order]
-        tile_seg = np.repeat(order, tiles_per_segment)
-        tile_first = np.zeros(len(entries), dtype=np.int32)
-        np.cumsum(tiles_per_segment[:-1], out=tile_first[1:])
-        tile_row0 = ((np.arange(len(tile_seg), dtype=np.int32) - np.repeat(tile_first, tiles_per_segment))
-                     * ROWS_PER_TILE).astype(np.int32)
-
-        # tiles of at most 64 rows over the longer segments, for the tensor-core prefill kernel
-        longer = np.flatnonzero(lengths != 1).astype(np.int32)
-        wide_per_segment = (lengths[longer] + WIDE_TILE_ROWS - 1) // WIDE_TILE_ROWS
-        wide_tile_seg = np.repeat(longer, wide_per_segment)
-        wide_first = np.zeros(len(longer), dtype=np.int32)
-        np.cumsum(wide_per_segment[:-1], out=wide_first[1:])
-        wide_tile_row0 = ((np.arange(len(wide_tile_seg), dtype=np.int32) - np.repeat(wide_first, wide_per_segment))
-                          * WIDE_TILE_ROWS).astype(np.int32)
-        # heaviest first (most keys to walk): the kernel that draws tiles from a queue ends evenly
-        if len(wide_tile_seg) > 1:
-            keys = position_start[wide_tile_seg] + np.minimum(wide_tile_row0 + WIDE_TILE_ROWS, lengths[wide_tile_seg])
-            heavy_first = np.argsort(-keys, kind="stable")
-            wide_tile_seg = np.ascontiguousarray(wide_tile_seg[heavy_first])
-            wide_tile_row0 = np.ascontiguousarray(wide_tile_row0[heavy_first])
-
-        # and tiles of at most 128 rows, heaviest first, for the tcgen05 prefill kernel
-        big_per_segment = (lengths[longer] + BIG_TILE_ROWS - 1) // BIG_TILE_ROWS
-        big_tile_seg = np.repeat(longer, big_per_segment)
-        big_first = np.zeros(len(longer), dtype=np.int32)
-        np.cumsum(big_per_segment[:-1], out=big_first[1:])
-        big_tile_row0 = ((np.arange(len(big_tile_seg), dtype=np.int32) - np.repeat(big_first, big_per_segment))
-                         * BIG_TILE_ROWS).astype(np.int32)
-        if len(big_tile_seg) > 1:
-            keys = position_start[big_tile_seg] + np.minimum(big_tile_row0 + BIG_TILE_ROWS, lengths[big_tile_seg])
-            heavy_first = np.argsort(-keys, kind="stable")
-            big_tile_seg = np.ascontiguousarray(big_tile_seg[heavy_first])
-            big_tile_row0 = np.ascontiguousarray(big_tile_row0[heavy_first])
-
         slots = np.array([r.slot for r in requests], dtype=np.int32)
-        kv_end = position_start + lengths
-        table_width = fixed_width or max(1, int(-(-int(kv_end.max()) // cache.page_size)))
 
         packer = _Packer()
+        packer.add("seg_slot", slots)
         packer.add("token_ids", token_ids)
         packer.add("positions", positions)
         packer.add("wanted_rows", wanted_rows)
         packer.add("seg_q_start", row_start)
         packer.add("seg_q_len", lengths)
         packer.add("seg_pos0", position_start)
-        packer.add("seg_slots", slots)
-        packer.add("tile_seg", tile_seg)
-        packer.add("tile_row0", tile_row0)
-        packer.add("decode_seg", decode_seg)
-        packer.add("wide_tile_seg", wide_tile_seg)
-        packer.add("wide_tile_row0", wide_tile_row0)
-        packer.add("big_tile_seg", big_tile_seg)
-        packer.add("big_tile_row0", big_tile_row0)
+        if want_slots and not fixed:      # in a decode step the wanted rows' slots are the segments' slots
+            packer.add("wanted_slot", slots[segment_of_row[wanted_rows]] if len(wanted_rows) else wanted_rows)
         for group in cache.groups:
-            rows_slots = np.concatenate([
+            places = np.concatenate([
                 cache.slot_mapping(group, request, int(position_start[i]), int(lengths[i]))
                 for i, request in enumerate(requests)])
-            packer.add(f"slots{group.index}", rows_slots.astype(np.int64))
-            packer.add(f"table{group.index}", group.table[slots, :table_width])
-        if sampling is not None:
-            if not (len(sampling.temperatures) == len(sampling.seeds) == len(sampling.token_indices)
-                    == wanted_rows.shape[0]):
-                raise ValueError("sampling needs one temperature, seed and token index per wanted row")
-            packer.add("temperatures", np.asarray(sampling.temperatures, dtype=np.float32))
-            packer.add("seeds", np.asarray(sampling.seeds, dtype=np.int64))
-            packer.add("token_indices", np.asarray(sampling.token_indices, dtype=np.int64))
+            packer.add(f"places{group.index}", places.astype(np.int64))
+        plans = self._step_plans(host)
+        for key, (arrays, _) in plans.items():
+            for name, array in arrays.items():
+                packer.add(f"plan.{key}.{name}", array)
+        pending = self._pack_resident_updates(packer)
+        return packer, host, slots, wanted_rows, plans, pending
+
+    def _build_context(self, entries: Sequence[StepEntry], requests: list[RequestCache], *,
+                       want_slots: bool = False, fixed: bool = False, packed=None,
+                       device_buffer: torch.Tensor | None = None) -> StepContext:
+        """Host-side description of the step, sent to the device.  ``fixed``: a captured decode step
+        (contexts as long as the cache allows, so that every kernel plans against the cache's
+        capacity); ``device_buffer`` is that graph's own metadata buffer.  ``want_slots`` adds the
+        slot of every wanted row (for sampling by slot)."""
+        cache = self.cache
+        packer, host, slots, wanted_rows, plans, pending = packed or self._pack(
+            entries, requests, want_slots=want_slots, fixed=fixed)
+        lengths, row_start, position_start, total = host.lengths, host.row_start, host.position_start, host.num_rows
         dev = self._upload(packer, device_buffer)
-        self._last_layout_bytes = packer.size
-        self._last_layout = [(name, array.dtype, array.shape, offset, array) for name, array, offset in packer.items]
+        self._scatter_resident_updates(pending, dev)
 
         segments = [Segment(e.request_id, int(slots[i]), int(row_start[i]), int(lengths[i]),
                             int(position_start[i])) for i, e in enumerate(entries)]
-        ctx = StepContext(ops=ops.current(), num_rows=total, num_wanted=int(wanted_rows.shape[0]),
-                          segments=segments, token_ids=dev["token_ids"], positions=dev["positions"],
-                          wanted_rows=dev["wanted_rows"], segment_slots=dev["seg_slots"],
-                          wanted_all_rows=(wanted_rows.shape[0] == total
-                                           and bool((wanted_rows == np.arange(total, dtype=np.int32)).all())))
-        if sampling is not None:
-            ctx.sampling = (dev["temperatures"], dev["seeds"], dev["token_indices"])
-        batches = {}
-        for group in cache.groups:
-            batches[group.index] = AttentionBatch(
-                seg_q_start=dev["seg_q_start"], seg_q_len=dev["seg_q_len"], seg_pos0=dev["seg_pos0"],
-                block_table=dev[f"table{group.index}"], tile_seg=dev["tile_seg"], tile_row0=dev["tile_row0"],
-                num_segments=len(entries), num_tiles=int(tile_seg.shape[0]),
-                max_q_len=int(lengths.max()),
-                max_kv_len=int(kv_end.max()) if fixed_width is None else fixed_width * cache.page_size,
-                decode_seg=dev["decode_seg"], num_decode=int(decode_seg.shape[0]),
-                wide_tile_seg=dev["wide_tile_seg"], wide_tile_row0=dev["wide_tile_row0"],
-                num_wide_tiles=int(wide_tile_seg.shape[0]),
-                big_tile_seg=dev["big_tile_seg"], big_tile_row0=dev["big_tile_row0"],
-                num_big_tiles=int(big_tile_seg.shape[0]))
+        ctx = StepContext(
+            ops=ops.current(), num_rows=total, num_wanted=int(wanted_rows.shape[0]), segments=segments,
+            token_ids=dev["token_ids"], positions=dev["positions"], wanted_rows=dev["wanted_rows"],
+            seg_q_start=dev["seg_q_start"], seg_q_len=dev["seg_q_len"], seg_pos0=dev["seg_pos0"],
+            seg_slot=dev["seg_slot"], max_q_len=int(lengths.max()),
+            max_kv_len=(cache.max_pages_per_request * cache.page_size if fixed
+                        else int((position_start + lengths).max())),
+            wanted_all_rows=(wanted_rows.shape[0] == total
+                             and bool((wanted_rows == np.arange(total, dtype=np.int32)).all())))
+        if want_slots:
+            ctx.wanted_slot = dev["seg_slot"] if fixed else dev["wanted_slot"]
+        for key, (arrays, counts) in plans.items():
+            ctx.plans[key] = ({name: dev[f"plan.{key}.{name}"] for name in arrays}, counts)
+        shared_by_group: dict[int, dict] = {group.index: {} for group in cache.groups}
         for entry, need in enumerate(cache.needs):
             if entry in cache.entry_group:
                 k_pool, v_pool, group = cache.entry_pools(entry)
-                ctx.views[entry] = CacheView(entry, k_pool, v_pool, dev[f"slots{group.index}"],
-                                             batches[group.index], cache.page_size, group.window)
+                ctx.views[entry] = CacheView(entry, k_pool, v_pool, dev[f"places{group.index}"],
+                                             group.device_table, cache.page_size, group.window,
+                                             group=group.index, shared=shared_by_group[group.index])
             else:
                 ctx.views[entry] = CacheView(entry, state=cache.state.get(entry))
         return ctx
@@ -362,9 +373,21 @@ class ModelRunner:
                 raise ValueError(f"request {entry.request_id!r} would reach {held + count} positions, "
                                  f"the model allows {self.max_positions}")
 
-    def _forward(self, ctx: StepContext, sampling: SamplingRows | None):
+    def _forward(self, ctx: StepContext, sample: bool, *, lengths_by_device: bool):
+        """The model, then the choice of tokens, then the slots' new lengths.  ``lengths_by_device``:
+        every request brought one token and the device's own lengths are advanced by one (inside the
+        sampling kernel when it runs); otherwise they are set from the host's figures."""
+        kernels = ctx.ops
+        state = self.cache.slot_state
         logits = self.model.forward(ctx)
-        tokens = ctx.ops.sample(logits, *ctx.sampling) if sampling is not None else None
+        tokens = None
+        if sample:
+            tokens = kernels.sample_slots(logits, ctx.wanted_slot, state, advance=lengths_by_device)
+        if lengths_by_device:
+            if not sample:
+                kernels.advance_slots(ctx.seg_slot, state)
+        else:
+            kernels.advance_slots(ctx.seg_slot, state, ctx.seg_q_len, ctx.seg_pos0)
         return logits, tokens
 
     def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
@@ -372,128 +395,127 @@ class ModelRunner:
                 and isinstance(ops.current(), ops.CudaOps)
                 and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
 
-    def _graph_step(self, entries, requests, sampling, feed=None):
+    def _prepare_decode(self, ctx: StepContext, feed: bool) -> None:
+        """Positions, cache places and (with ``feed``) input tokens of a decode step, derived on the
+        device from the slot records; one launch per cache group."""
+        kernels = ctx.ops
+        state = self.cache.slot_state
+        first = True
+        for group in self.cache.groups:
+            places = next(view.slots for view in ctx.views.values() if view.group == group.index)
+            kernels.decode_prepare(ctx.seg_slot, state,
+                                   token_ids=ctx.token_ids if (feed and first) else None,
+                                   positions=ctx.positions if first else None,
+                                   seg_pos0=ctx.seg_pos0 if first else None,
+                                   table=group.device_table, page_size=self.cache.page_size, kv_slots=places)
+            first = False
+        if first:      # a model without paged groups still needs positions and tokens
+            kernels.decode_prepare(ctx.seg_slot, state, token_ids=ctx.token_ids if feed else None,
+                                   positions=ctx.positions, seg_pos0=ctx.seg_pos0)
+
+    def _graph_step(self, entries, requests, sample: bool, feed: bool):
         """A decode-only step through the captured graph of its batch size.  The first step of a
-        size runs eagerly on the graph's fixed buffers and is then captured; later steps only
-        refresh the metadata buffer and replay.  ``feed``: see ``step``."""
-        key = (len(entries), sampling is not None)
-        kernels = ops.current()
+        size runs eagerly on the graph's fixed buffers and is then captured; later steps refresh at
+        most the slots and the host's tokens, send changed table rows, and replay."""
+        count = len(entries)
+        key = (count, sample, feed)
         captured = self._graphs.get(key)
-        # The context is built at the block table's full width, so every kernel plans its grid
-        # against the cache's capacity, not against this step's contexts.
-        width = self.cache.max_pages_per_request
-        if captured is None:
-            # learn the layout's size with a throw-away packing, then give the graph its own buffer
-            probe = self._build_context(entries, requests, sampling, fixed_width=width)
-            del probe
-            captured = _CapturedStep(torch.empty(self._last_layout_bytes + 64, dtype=torch.uint8, device=self.device))
-            self._graphs[key] = captured
-        if captured.graph is not None:
-            self._refresh_captured(captured, entries, requests, sampling)
-            if feed is not None:
-                captured.token_ids.copy_(feed)       # after the metadata copy, before the replay reads it
+        slots = tuple(r.slot for r in requests)
+        if captured is not None and captured.graph is not None:
+            self._send_resident_updates()
+            refresh_slots = slots != captured.slots_now
+            if refresh_slots or not feed:
+                staging = captured.stagings[captured.cursor]
+                captured.cursor = (captured.cursor + 1) % len(captured.stagings)
+                buffer, event = staging
+                if event is not None:
+                    event.synchronize()
+                view = buffer.numpy().view(np.int32)
+                aligned = (count * 4 + 15) // 16 * 4       # token ids start at the next 16-byte boundary
+                view[:count] = slots
+                nbytes = count * 4
+                if not feed:
+                    view[aligned:aligned + count] = np.fromiter((e.tokens[0] for e in entries), np.int32, count)
+                    nbytes = (aligned + count) * 4
+                captured.metadata[:nbytes].copy_(buffer[:nbytes], non_blocking=True)
+                self.bytes_sent += nbytes
+                if event is None:
+                    staging[1] = event = torch.cuda.Event()
+                event.record()
+                captured.slots_now = slots
             captured.graph.replay()
             self.graph_replays += 1
             return captured.logits, captured.tokens
-        ctx = self._build_context(entries, requests, sampling, fixed_width=width,
+
+        # first time at this size: give the graph its own buffer for the step's layout, run the
+        # step eagerly on it, then capture
+        packed = self._pack(entries, requests, want_slots=sample, fixed=True)
+        captured = _CapturedStep(torch.empty(packed[0].size + 64, dtype=torch.uint8, device=self.device))
+        captured.stagings = [[torch.empty((2 * count + 8) * 4, dtype=torch.uint8, pin_memory=True), None]
+                             for _ in range(3)]
+        ctx = self._build_context(entries, requests, want_slots=sample, fixed=True, packed=packed,
                                   device_buffer=captured.metadata)
-        captured.token_ids = ctx.token_ids
-        if feed is not None:
-            ctx.token_ids.copy_(feed)
-        self._prepare_stagings(captured)
-        logits, tokens = self._forward(ctx, sampling)          # this step's real result, eagerly
+        self._graphs[key] = captured
+        captured.slots_now = slots
+        self._prepare_decode(ctx, feed)
+        logits, tokens = self._forward(ctx, sample, lengths_by_device=True)     # this step's real result
         torch.cuda.synchronize(self.device)
+        # Capturing runs nothing: the records keep the lengths this step gave them.
         graph = torch.cuda.CUDAGraph()
         from ..ops import cuda_ops
         before = cuda_ops.launches
         with torch.cuda.graph(graph):
-            captured.logits, captured.tokens = self._forward(ctx, sampling)
+            self._prepare_decode(ctx, feed)
+            captured.logits, captured.tokens = self._forward(ctx, sample, lengths_by_device=True)
         captured.launches = cuda_ops.launches - before
         captured.graph = graph
         return logits, tokens
 
-    def _prepare_stagings(self, captured: "_CapturedStep") -> None:
-        """Pinned copies of the step's metadata layout, each with numpy views of its arrays.  What
-        depends only on the batch size (segment table, tiles, wanted rows) is written once."""
-        captured.nbytes = max(self._last_layout_bytes, 16)
-        captured.stagings = []
-        for _ in range(3):
-            buffer = torch.empty(captured.nbytes, dtype=torch.uint8, pin_memory=True)
-            host = buffer.numpy()
-            views = {}
-            for name, dtype, shape, offset, array in self._last_layout:
-                view = host[offset:offset + array.nbytes].view(dtype).reshape(shape)
-                view[...] = array
-                views[name] = view
-            captured.stagings.append([buffer, views, None])
-
-    def _refresh_captured(self, captured: "_CapturedStep", entries, requests, sampling) -> None:
-        """Write what changes from one decode step to the next (tokens, positions, slots, block
-        tables, sampling rows) into the next pinned copy and send it in one transfer."""
-        staging = captured.stagings[captured.cursor]
-        captured.cursor = (captured.cursor + 1) % len(captured.stagings)
-        buffer, views, event = staging
-        if event is not None:
-            event.synchronize()
-        count = len(entries)
-        cache = self.cache
-        views["token_ids"][:] = np.fromiter((e.tokens[0] for e in entries), np.int32, count)
-        positions = np.fromiter((r.pending[0] for r in requests), np.int32, count)
-        slots = np.fromiter((r.slot for r in requests), np.int32, count)
-        views["positions"][:] = positions
-        views["seg_pos0"][:] = positions
-        views["seg_slots"][:] = slots
-        logical = positions // cache.page_size
-        offsets = positions - logical * cache.page_size
-        for group in cache.groups:
-            pages = group.table[slots, logical].astype(np.int64)
-            if (pages < 0).any():
-                raise RuntimeError("a request has no page for the token it is writing")
-            views[f"slots{group.index}"][:] = pages * cache.page_size + offsets
-            np.take(group.table, slots, axis=0, out=views[f"table{group.index}"])
-        if sampling is not None:
-            views["temperatures"][:] = sampling.temperatures
-            views["seeds"][:] = sampling.seeds
-            views["token_indices"][:] = sampling.token_indices
-        captured.metadata[:captured.nbytes].copy_(buffer, non_blocking=True)
-        if staging[2] is None:
-            staging[2] = torch.cuda.Event()
-        staging[2].record()
-
-    def launches_per_replay(self, batch: int, sampling: bool) -> int:
+    def launches_per_replay(self, batch: int, sampling: bool, feed: bool | None = None) -> int:
         """Kernels one replay of the captured step of this batch size launches (0 if not captured)."""
-        captured = self._graphs.get((batch, sampling))
-        return captured.launches if captured is not None and captured.graph is not None else 0
+        for (count, sample, fed), captured in self._graphs.items():
+            if count == batch and sample == sampling and (feed is None or fed == feed) and captured.graph is not None:
+                return captured.launches
+        return 0
+
+    def check_device(self) -> None:
+        """Raise if a kernel reported, through its error word, that a bounded wait ran out since the
+        last check.  To be called where the host has just synchronised with the device."""
+        check = getattr(ops.current(), "raise_if_device_error", None)
+        if check is not None:
+            check()
 
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry], sampling: SamplingRows | None = None, *,
-             borrow: bool = False, feed: torch.Tensor | None = None):
+    def step(self, entries: Sequence[StepEntry], *, sample: bool = False, borrow: bool = False,
+             feed: bool = False):
         """Run the entries as one batch.  Returns float32 logits [wanted places, vocab] on the
-        device, in the order of the entries and of each entry's ``want``.  With ``sampling`` it
-        returns ``(logits, tokens)``: one int32 token per wanted place, chosen on the device.
-        ``borrow=True`` may return buffers that the next step overwrites (no copy is made).
-        ``feed``: int32 device tensor with the input token of every entry (each entry then holds
-        exactly one placeholder token): the ids are taken from the device, e.g. from the tokens the
-        previous step chose, without the host having seen them."""
+        device, in the order of the entries and of each entry's ``want``.  With ``sample`` it
+        returns ``(logits, tokens)``: one int32 token per wanted place (at most one per request),
+        chosen on the device with the temperature, seed and counter of the request's slot record,
+        which also receives the token.  ``borrow=True`` may return buffers that the next step
+        overwrites (no copy is made).  ``feed=True``: every entry holds one placeholder token and the
+        real input is the token the request sampled last, taken from its slot record on the device
+        without the host having seen it."""
         self._validate(entries)
-        if feed is not None:
-            if any(len(e.tokens) != 1 for e in entries) or feed.shape != (len(entries),) or feed.dtype != torch.int32:
-                raise ValueError("feed needs one int32 token per entry and entries of one token each")
+        if feed and any(len(e.tokens) != 1 for e in entries):
+            raise ValueError("feed needs entries of exactly one token each")
+        if sample and any(len(e.want) > 1 for e in entries):
+            raise ValueError("sampling takes at most one wanted place per request")
         requests = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
         try:
             if self._graph_eligible(entries):
-                logits, tokens = self._graph_step(entries, requests, sampling, feed)
+                logits, tokens = self._graph_step(entries, requests, sample, feed)
                 if not borrow:
                     logits = logits.clone()
                     tokens = tokens.clone() if tokens is not None else None
             else:
-                ctx = self._build_context(entries, requests, sampling)
-                if feed is not None:
-                    ctx.token_ids.copy_(feed)
-                logits, tokens = self._forward(ctx, sampling)
+                ctx = self._build_context(entries, requests, want_slots=sample)
+                if feed:
+                    ctx.ops.decode_prepare(ctx.seg_slot, self.cache.slot_state, token_ids=ctx.token_ids)
+                logits, tokens = self._forward(ctx, sample, lengths_by_device=False)
         except BaseException:
             self.cache.abort_step()
             raise
         self.cache.commit_step()
         self.steps_run += 1
-        return logits if sampling is None else (logits, tokens)
+        return (logits, tokens) if sample else logits

@@ -8,7 +8,6 @@ one ``forward`` over a ragged step batch.
 
 from __future__ import annotations
 
-import math
 from typing import Mapping
 
 import torch
@@ -60,29 +59,11 @@ class DecoderModel:
         expected = self.expected_tensors()
         check_tensors(expected, tensors)
         self.device = torch.device(device)
-        if self.device.type == "cuda":
-            self._prepare_device_memory(expected)
         for part in self.parts():
             part.load(tensors, self.device)
         for block in self.blocks:
             block.finish_load(self.compute_dtype)
         return self
-
-    def _prepare_device_memory(self, expected) -> None:
-        """One allocation of about the model's size, written once and handed back to torch's pool,
-        before any weight is placed: the weights are then carved out of device memory that has been
-        touched as one large block.  Measured on a B200 with the 0.5B sizes: a decode step takes
-        0.81 ms with it and 0.85 ms with the tensors allocated one by one into untouched memory
-        (the first model of a process); allocating without writing, or a small block, does not help."""
-        itemsize = torch.empty((), dtype=self.compute_dtype).element_size()
-        nbytes = sum(math.prod(spec.shape) for spec in expected.values()) * itemsize
-        nbytes = int(nbytes * 1.5) + (256 << 20)
-        free, _ = torch.cuda.mem_get_info(self.device)
-        if nbytes > free // 2:
-            return
-        block = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
-        block.zero_()
-        del block
 
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> list[KVCacheNeed | StateNeed | None]:

@@ -95,7 +95,7 @@ def build_directory() -> Path:
 def _source_hash(name: str, flags: tuple[str, ...]) -> str:
     digest = hashlib.sha256()
     digest.update((CSRC / f"{name}.cu").read_bytes())
-    for header in sorted(CSRC.glob("*.cuh")):
+    for header in sorted([*CSRC.glob("*.cuh"), *CSRC.glob("*.h")]):
         digest.update(header.name.encode())
         digest.update(header.read_bytes())
     digest.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + flags).encode())

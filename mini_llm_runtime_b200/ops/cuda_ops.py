@@ -15,6 +15,7 @@ import ctypes
 import os
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from . import build
@@ -76,33 +77,74 @@ def _stream() -> ctypes.c_void_p:
 class AttentionBatch:
     """Device-side description of one step's ragged batch for one cache group.
 
-    ``seg_*`` have one entry per request in the step; ``tile_*`` cut every segment into tiles
-    of at most 16 rows (the unit one CTA of the generic kernel works on), the tiles of segments
-    longer than one row first.  ``decode_seg`` lists the segments of exactly one row (decoded
-    tokens), which a split-KV kernel may take instead of the last ``num_decode`` tiles.
-    ``block_table`` is int32 [segments, table_width] with -1 where the request holds no page.
+    ``seg_*`` have one entry per request in the step.  ``block_table`` is the group's resident
+    table, int32 [request slots, table_width] with -1 where a request holds no page; segment i
+    reads row ``seg_slot[i]`` of it.  ``plan`` holds the work lists of the attention kernels
+    (``plan_attention`` below builds them on the host, the step function sends them with the rest of
+    its metadata) and ``counts`` their lengths.
     """
 
     seg_q_start: torch.Tensor
     seg_q_len: torch.Tensor
     seg_pos0: torch.Tensor
+    seg_slot: torch.Tensor
     block_table: torch.Tensor
-    tile_seg: torch.Tensor
-    tile_row0: torch.Tensor
     num_segments: int
-    num_tiles: int
     max_q_len: int
     max_kv_len: int
-    decode_seg: torch.Tensor | None = None
-    num_decode: int = 0
-    # tiles of at most 64 rows over the segments longer than one row (tensor-core prefill kernel)
-    wide_tile_seg: torch.Tensor | None = None
-    wide_tile_row0: torch.Tensor | None = None
-    num_wide_tiles: int = 0
-    # the same in tiles of at most 128 rows (tcgen05 prefill kernel)
-    big_tile_seg: torch.Tensor | None = None
-    big_tile_row0: torch.Tensor | None = None
-    num_big_tiles: int = 0
+    plan: dict
+    counts: dict
+
+    @property
+    def num_decode(self) -> int:
+        return self.counts.get("decode", 0)
+
+
+# Rows of one work item of the three prompt-attention kernels.
+GENERIC_TILE_ROWS = 16    # attention_generic.cu: one CTA
+MMA_TILE_ROWS = 64        # attention_mma.cu: one CTA of the mma.sync kernel
+TCGEN05_TILE_ROWS = 128   # attention_tcgen05.cu: one work item
+
+
+def _tiles(lengths: np.ndarray, segments: np.ndarray, rows: int, position_start: np.ndarray | None):
+    """Cut the given segments into tiles of at most ``rows`` rows: (segment of each tile, its first
+    row).  With ``position_start`` the tiles are ordered heaviest first (most keys to walk), so that
+    kernels drawing tiles from a queue end evenly."""
+    per_segment = (lengths[segments] + rows - 1) // rows
+    tile_seg = np.repeat(segments, per_segment)
+    first = np.zeros(len(segments), dtype=np.int32)
+    np.cumsum(per_segment[:-1], out=first[1:])
+    row0 = ((np.arange(len(tile_seg), dtype=np.int32) - np.repeat(first, per_segment)) * rows).astype(np.int32)
+    if position_start is not None and len(tile_seg) > 1:
+        keys = position_start[tile_seg] + np.minimum(row0 + rows, lengths[tile_seg])
+        heavy_first = np.argsort(-keys, kind="stable")
+        tile_seg = np.ascontiguousarray(tile_seg[heavy_first])
+        row0 = np.ascontiguousarray(row0[heavy_first])
+    return tile_seg.astype(np.int32), row0
+
+
+def plan_attention(lengths: np.ndarray, position_start: np.ndarray) -> tuple[dict, dict]:
+    """Work lists of the attention kernels for a step whose request i brings ``lengths[i]`` rows
+    starting at position ``position_start[i]``: int32 arrays by name, and counts by name.
+
+    ``tile_*``: tiles of at most 16 rows, those of segments longer than one row first, so that a
+    split-KV kernel may take the one-row segments (``decode_seg``, ``counts["decode"]`` of them)
+    instead of the last tiles.  ``wide_*`` / ``big_*``: tiles of 64 / 128 rows over the longer
+    segments only, heaviest first."""
+    lengths = np.asarray(lengths, dtype=np.int32)
+    position_start = np.asarray(position_start, dtype=np.int32)
+    decode_seg = np.flatnonzero(lengths == 1).astype(np.int32)
+    longer = np.flatnonzero(lengths != 1).astype(np.int32)
+    tile_seg, tile_row0 = _tiles(lengths, np.concatenate([longer, decode_seg]).astype(np.int32),
+                                 GENERIC_TILE_ROWS, None)
+    wide_seg, wide_row0 = _tiles(lengths, longer, MMA_TILE_ROWS, position_start)
+    big_seg, big_row0 = _tiles(lengths, longer, TCGEN05_TILE_ROWS, position_start)
+    arrays = {"tile_seg": tile_seg, "tile_row0": tile_row0, "decode_seg": decode_seg,
+              "wide_tile_seg": wide_seg, "wide_tile_row0": wide_row0,
+              "big_tile_seg": big_seg, "big_tile_row0": big_row0}
+    counts = {"tiles": int(tile_seg.shape[0]), "decode": int(decode_seg.shape[0]),
+              "wide": int(wide_seg.shape[0]), "big": int(big_seg.shape[0])}
+    return arrays, counts
 
 
 class CudaOps:
@@ -117,6 +159,9 @@ class CudaOps:
     GEMM_SCRATCH_BYTES = 32 << 20
     GEMM_COUNTERS = 1 << 15
     ATTENTION_COUNTERS = 1 << 16
+    # Partial states of the split-KV decode attention.  The buffer is never replaced: captured
+    # launches keep its address, so a call that would need more lowers its split count instead.
+    ATTENTION_SCRATCH_BYTES = 64 << 20
 
     def __init__(self) -> None:
         self._workspaces: dict[int, dict[str, torch.Tensor]] = {}
@@ -144,7 +189,8 @@ class CudaOps:
                 "gemm_scratch": torch.empty(self.GEMM_SCRATCH_BYTES, dtype=torch.uint8, device=device),
                 "gemm_counters": torch.zeros(self.GEMM_COUNTERS, dtype=torch.int32, device=device),
                 "attention_counters": torch.zeros(self.ATTENTION_COUNTERS, dtype=torch.int32, device=device),
-                "attention_scratch": torch.empty(8 << 20, dtype=torch.uint8, device=device),
+                "attention_scratch": torch.empty(self.ATTENTION_SCRATCH_BYTES, dtype=torch.uint8, device=device),
+                "sm_count": torch.cuda.get_device_properties(device).multi_processor_count,
                 # written by a kernel whose bounded wait ran out; read by the host without a copy
                 "error_word": torch.zeros(1, dtype=torch.int32).pin_memory(),
                 "prefill_queue": torch.zeros(2, dtype=torch.int32, device=device),
@@ -155,12 +201,20 @@ class CudaOps:
         return self._workspaces[index]
 
     def raise_if_device_error(self) -> None:
-        """Call after a synchronisation point: raises if a kernel gave up on a bounded wait."""
+        """Call after a synchronisation point: raises if a kernel gave up on a bounded wait.  Such
+        a kernel may have left its work queue and its split counters half-used, which every later
+        launch would trip over, so they are cleared before the exception leaves."""
         for space in self._workspaces.values():
             code = int(space["error_word"][0])
             if code != 0:
                 space["error_word"][0] = 0
-                raise KernelError(f"a kernel's bounded wait ran out (code {code}); its results are invalid")
+                for name in ("gemm_counters", "attention_counters", "prefill_queue", "prefill_counters"):
+                    space[name].zero_()
+                raise KernelError(f"a kernel's bounded wait ran out (code {code}); the results of the "
+                                  "steps since the last check are invalid")
+
+    def sm_count(self, device: torch.device) -> int:
+        return self._workspace(device)["sm_count"]
 
     # ------------------------------------------------------------------ elementwise
     def embedding(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
@@ -297,6 +351,65 @@ class CudaOps:
                                      _stream()), "rope_kv_write")
         return q
 
+    # ------------------------------------------------------------------ resident tables and slot records
+    def plan_attention(self, lengths, position_start):
+        """Host-side work lists for this object's attention kernels (see ``plan_attention``)."""
+        return plan_attention(lengths, position_start)
+
+    def scatter_rows(self, table: torch.Tensor, row_index: torch.Tensor, rows: torch.Tensor) -> None:
+        """table[row_index[i]] = rows[i] for int32 tables that stay on the device."""
+        _need(table, "table", torch.int32, 2)
+        _need(row_index, "row_index", torch.int32, 1)
+        _need(rows, "rows", torch.int32, 2)
+        if rows.shape != (row_index.shape[0], table.shape[1]):
+            raise KernelError("scatter_rows needs one row of the table's width per index")
+        _check(build.load_library("elementwise").mlr_scatter_rows(
+            _ptr(table), _ptr(row_index), _ptr(rows), row_index.shape[0], table.shape[1], _stream()), "scatter_rows")
+
+    def decode_prepare(self, seg_slot: torch.Tensor, slot_state: torch.Tensor, *, token_ids=None, positions=None,
+                       seg_pos0=None, table=None, page_size: int = 0, kv_slots=None) -> None:
+        """Fill a decode step's metadata from the slot records of its requests: positions (the slot's
+        length), input tokens (the slot's last sampled token) and where the new key and value go."""
+        _need(seg_slot, "seg_slot", torch.int32, 1)
+        _need(slot_state, "slot_state", torch.int32, 2)
+        count = seg_slot.shape[0]
+        for name, tensor, dtype in (("token_ids", token_ids, torch.int32), ("positions", positions, torch.int32),
+                                    ("seg_pos0", seg_pos0, torch.int32), ("kv_slots", kv_slots, torch.int64)):
+            if tensor is not None:
+                _need(tensor, name, dtype, 1)
+                if tensor.shape[0] != count:
+                    raise KernelError(f"{name} needs one entry per segment")
+        if kv_slots is not None:
+            _need(table, "table", torch.int32, 2)
+        _check(build.load_library("elementwise").mlr_decode_prepare(
+            _ptr(seg_slot), _ptr(slot_state), count, _ptr(token_ids), _ptr(positions), _ptr(seg_pos0), _ptr(table),
+            0 if table is None else table.shape[1], int(page_size), _ptr(kv_slots), _stream()), "decode_prepare")
+
+    def advance_slots(self, seg_slot: torch.Tensor, slot_state: torch.Tensor, seg_q_len=None, seg_pos0=None) -> None:
+        """The slots' lengths after a step: pos0 + len where the host's figures are given, else the
+        slot's own length plus len (plus one without ``seg_q_len``)."""
+        _need(seg_slot, "seg_slot", torch.int32, 1)
+        _need(slot_state, "slot_state", torch.int32, 2)
+        _check(build.load_library("elementwise").mlr_advance_slots(
+            _ptr(seg_slot), _ptr(seg_q_len), _ptr(seg_pos0), seg_slot.shape[0], _ptr(slot_state), _stream()),
+            "advance_slots")
+
+    def sample_slots(self, logits: torch.Tensor, row_slot: torch.Tensor, slot_state: torch.Tensor,
+                     advance: bool = False) -> torch.Tensor:
+        """``sample`` with temperature, seed and counter read from the slot record of each row's
+        request; the record receives the token and its counter grows by one (with ``advance`` its
+        length too).  A request may own at most one row."""
+        _need(logits, "logits", torch.float32, 2)
+        _need(row_slot, "row_slot", torch.int32, 1)
+        _need(slot_state, "slot_state", torch.int32, 2)
+        if row_slot.shape[0] != logits.shape[0]:
+            raise KernelError("row_slot needs one entry per logits row")
+        tokens = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+        _check(build.load_library("sampling").mlr_sample_slots(
+            _ptr(logits), _ptr(row_slot), _ptr(slot_state), _ptr(tokens), logits.shape[0], logits.shape[1],
+            int(bool(advance)), _stream()), "sample_slots")
+        return tokens
+
     # ------------------------------------------------------------------ matrix product
     def linear(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
                out_dtype: torch.dtype | None = None, rms_eps: float | None = None,
@@ -337,8 +450,7 @@ class CudaOps:
     SKINNY_ROWS_SMALL_WEIGHT = 32     # rows up to which matrices of at most SKINNY_SMALL_WEIGHT elements stay with it
     SKINNY_SMALL_WEIGHT = 2 << 20
     TMA_MIN_CHUNK = 256               # keys per CTA of the bulk-copy decode attention, at least
-    TMA_RESIDENT_CTAS = 3 * 148       # its CTAs that are resident at once (three per SM)
-    SKINNY_WEIGHT_ROWS = 148 * 128   # beyond this the 128-row tensor-memory tiles fill every SM
+    TMA_CTAS_PER_SM = 3               # its CTAs that are resident at once on one SM
 
     def _skinny_fits(self, x, weight, swiglu=False) -> bool:
         """Few rows and a weight too small for one 128-row tile per SM: the latency-lean kernel.
@@ -346,7 +458,9 @@ class CudaOps:
         measured at 1152 x 896 and 32 rows, 3.0 against 7.1 us; a batch-32 decode step 1.50 -> 1.44 ms.
         (At 64 rows it wins alone, 6.3 against 8.4 us, but loses inside a step: 1.96 -> 2.20 ms.)"""
         rows = x.shape[0]
-        if not self.use_skinny or weight.shape[0] >= self.SKINNY_WEIGHT_ROWS or (swiglu and x.shape[1] > 2048):
+        # a weight with a 128-row tile for every SM keeps the tcgen05 kernel's tensor-memory tiles busy
+        if (not self.use_skinny or weight.shape[0] >= 128 * self.sm_count(x.device)
+                or (swiglu and x.shape[1] > 2048)):
             return False
         if rows <= self.SKINNY_ROWS:
             return True
@@ -405,7 +519,7 @@ class CudaOps:
         fused = (self.use_fused_rope and self.use_mma_attention and self.use_tma_attention
                  and self.decode_chunk is None
                  and qkv.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 16
-                 and batch.decode_seg is not None and 0 < batch.num_decode == batch.num_segments
+                 and "decode_seg" in batch.plan and 0 < batch.num_decode == batch.num_segments
                  and page_size >= 8 and page_size & (page_size - 1) == 0
                  and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS)
         if not fused:
@@ -441,69 +555,65 @@ class CudaOps:
         if k_pool.shape[1] != num_kv_heads or k_pool.shape[3] != head_dim or k_pool.shape != v_pool.shape:
             raise KernelError(f"page pools have shape {tuple(k_pool.shape)}, expected "
                               f"[pages, {num_kv_heads}, page_size, {head_dim}]")
+        if "tile_seg" not in batch.plan:
+            raise KernelError("the batch carries no attention work lists (plan_attention)")
         out = torch.empty_like(q)
-        generic_tiles = batch.num_tiles
+        plan, counts = batch.plan, batch.counts
+        generic_tiles = counts["tiles"]
         group = num_heads // num_kv_heads
+        page_size = k_pool.shape[2]
+        paged_by_tma = page_size >= 8 and page_size & (page_size - 1) == 0
+        common = (_ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
+                  _ptr(batch.seg_slot), batch.block_table.shape[1])
         if (self.use_mma_attention and q.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 16
-                and batch.decode_seg is not None and batch.wide_tile_seg is not None
                 and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS):
             if batch.num_decode > 0:
                 self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale,
                                        window, mma=True)
-            page_size = k_pool.shape[2]
-            if (batch.num_big_tiles > 0 and self.use_tcgen05_attention and head_dim == 64 and page_size >= 8
-                    and page_size & (page_size - 1) == 0 and batch.big_tile_seg is not None):
+            if counts["big"] > 0 and self.use_tcgen05_attention and head_dim == 64 and paged_by_tma:
                 # S = Q K^T and P V on tcgen05 with tensor-memory accumulators
                 space = self._workspace(q.device)
                 _check(build.load_library("attention_tcgen05").mlr_attention_prefill_tcgen05(
-                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.big_tile_seg),
-                    _ptr(batch.big_tile_row0), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
-                    _ptr(batch.block_table), batch.block_table.shape[1], batch.num_big_tiles, q.shape[0], num_heads,
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(plan["big_tile_seg"]),
+                    _ptr(plan["big_tile_row0"]), *common, counts["big"], q.shape[0], num_heads,
                     num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0), ctypes.c_float(scale),
                     int(batch.max_kv_len), _ptr(space["prefill_queue"]), _ptr(space["error_word"]),
                     _ptr(space["prefill_scratch"] if self.split_prefill_items else None),
                     ctypes.c_longlong(space["prefill_scratch"].numel()),
                     _ptr(space["prefill_counters"]), space["prefill_counters"].numel(), _stream()),
                     "prefill attention (tcgen05)")
-            elif (batch.num_wide_tiles > 0 and self.use_tma_attention and page_size >= 8
-                    and page_size & (page_size - 1) == 0):
+            elif counts["wide"] > 0 and self.use_tma_attention and paged_by_tma:
                 space = self._workspace(q.device)
                 _check(build.load_library("attention_mma").mlr_attention_prefill_tma(
-                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.wide_tile_seg),
-                    _ptr(batch.wide_tile_row0), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
-                    _ptr(batch.block_table), batch.block_table.shape[1], batch.num_wide_tiles, num_heads,
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(plan["wide_tile_seg"]),
+                    _ptr(plan["wide_tile_row0"]), *common, counts["wide"], num_heads,
                     num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0), ctypes.c_float(scale),
                     _ptr(space["prefill_queue"]), _ptr(space["error_word"]), _stream()),
                     "prefill attention (TMA)")
-            elif batch.num_wide_tiles > 0:
-                lib = build.load_library("attention_mma")
-                _check(lib.mlr_attention_prefill_mma(
-                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.wide_tile_seg),
-                    _ptr(batch.wide_tile_row0), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
-                    _ptr(batch.block_table), batch.block_table.shape[1], batch.num_wide_tiles, num_heads,
-                    num_kv_heads, head_dim, k_pool.shape[2], int(window or 0), ctypes.c_float(scale), _stream()),
+            elif counts["wide"] > 0:
+                _check(build.load_library("attention_mma").mlr_attention_prefill_mma(
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(plan["wide_tile_seg"]),
+                    _ptr(plan["wide_tile_row0"]), *common, counts["wide"], num_heads,
+                    num_kv_heads, head_dim, page_size, int(window or 0), ctypes.c_float(scale), _stream()),
                     "prefill attention")
             return out
-        if (self.use_decode_kernel and batch.num_decode > 0 and batch.decode_seg is not None
+        if (self.use_decode_kernel and batch.num_decode > 0
                 and q.dtype == torch.bfloat16 and head_dim in (64, 128) and group <= 8
                 and batch.num_decode * num_kv_heads <= self.ATTENTION_COUNTERS):
             self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window)
             generic_tiles -= batch.num_decode
         if generic_tiles > 0:
-            lib = build.load_library("attention_generic")
-            _check(lib.mlr_attention_generic(
-                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.tile_seg), _ptr(batch.tile_row0),
-                _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
-                batch.block_table.shape[1], generic_tiles, num_heads, num_kv_heads, head_dim,
-                k_pool.shape[2], int(window or 0), ctypes.c_float(scale), _code(q.dtype), _stream()),
+            _check(build.load_library("attention_generic").mlr_attention_generic(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(plan["tile_seg"]), _ptr(plan["tile_row0"]),
+                *common, generic_tiles, num_heads, num_kv_heads, head_dim,
+                page_size, int(window or 0), ctypes.c_float(scale), _code(q.dtype), _stream()),
                 "paged_attention")
         return out
 
-    @staticmethod
-    def plan_decode(num_decode: int, num_kv_heads: int, longest: int) -> tuple[int, int]:
+    def plan_decode(self, num_decode: int, num_kv_heads: int, longest: int, sms: int) -> tuple[int, int]:
         """(chunk, splits): keys per CTA so that the grid has about two CTAs per SM."""
         chunk = 512
-        while chunk > 128 and num_decode * num_kv_heads * -(-longest // chunk) < 2 * 148:
+        while chunk > 128 and num_decode * num_kv_heads * -(-longest // chunk) < 2 * sms:
             chunk //= 2
         while -(-longest // chunk) > 64:      # the final merge handles at most 64 chunks per request
             chunk *= 2
@@ -512,33 +622,43 @@ class CudaOps:
     def _decode_attention(self, q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale, window,
                           mma=False, rope=None):
         page_size = k_pool.shape[2]
+        space = self._workspace(out.device)
+        sms = space["sm_count"]
         tma = mma and self.use_tma_attention and page_size >= 8 and page_size & (page_size - 1) == 0
         even_split = tma and self.decode_chunk is None
+        # float32 partial states of one split of every (row, head); the scratch buffer is fixed
+        per_split = batch.num_decode * num_heads * (head_dim + 2) * 4
+        most_splits = space["attention_scratch"].numel() // max(1, per_split)
+        if most_splits < 1:
+            raise KernelError(f"{batch.num_decode} decode rows of {num_heads} heads do not fit the "
+                              f"{space['attention_scratch'].numel() >> 20} MiB of split-KV scratch")
         if even_split:
             # the kernel divides each request's context over `splits` chunks of at least `chunk` keys
             chunk = self.TMA_MIN_CHUNK
-            splits = max(1, min(64, self.TMA_RESIDENT_CTAS // max(1, batch.num_decode * num_kv_heads),
+            splits = max(1, min(64, most_splits, self.TMA_CTAS_PER_SM * sms // max(1, batch.num_decode * num_kv_heads),
                                 -(-batch.max_kv_len // chunk)))
         else:
-            chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len)
-        if self.decode_chunk is not None:
-            chunk = self.decode_chunk
-            splits = max(1, -(-batch.max_kv_len // chunk))
-        if self.decode_max_splits is not None:
-            splits = max(splits, self.decode_max_splits)
-        need = batch.num_decode * num_heads * splits * (head_dim + 2) * 4    # float32 partial states
-        space = self._workspace(out.device)
-        if need > space["attention_scratch"].numel():
-            space["attention_scratch"] = torch.empty(int(need * 1.5), dtype=torch.uint8, device=out.device)
+            chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len, sms)
+            if self.decode_chunk is not None:
+                chunk = self.decode_chunk
+                splits = max(1, -(-batch.max_kv_len // chunk))
+            if self.decode_max_splits is not None:
+                splits = max(splits, self.decode_max_splits)
+            while splits > most_splits:        # longer chunks until the states fit the fixed buffer
+                chunk *= 2
+                splits = max(1, -(-batch.max_kv_len // chunk))
+        if even_split and self.decode_max_splits is not None:
+            splits = min(most_splits, max(splits, self.decode_max_splits))
         if rope is not None and not tma:
             raise KernelError("the fused position encoding needs the bulk-copy decode kernel")
         qkv, inv_freq, slots, write_kv = rope if rope is not None else (None, None, None, False)
+        decode_seg = batch.plan["decode_seg"]
         if tma:
             # pages arrive by the tensor memory accelerator, one bulk copy per page and kv head
             _check(build.load_library("attention_mma").mlr_attention_decode_tma(
-                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.decode_seg), _ptr(batch.seg_q_start),
-                _ptr(batch.seg_pos0), _ptr(batch.block_table), batch.block_table.shape[1], batch.num_decode,
-                num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(decode_seg), _ptr(batch.seg_q_start),
+                _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1],
+                batch.num_decode, num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
                 ctypes.c_float(scale), chunk, int(even_split), splits, int(self.decode_stages or 0),
                 _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _ptr(space["error_word"]),
                 _ptr(qkv), _ptr(inv_freq), _ptr(slots), int(bool(write_kv)), _stream()),
@@ -547,10 +667,11 @@ class CudaOps:
         entry = (build.load_library("attention_mma").mlr_attention_decode_mma if mma
                  else build.load_library("attention_decode").mlr_attention_decode)
         _check(entry(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.decode_seg), _ptr(batch.seg_q_start),
-            _ptr(batch.seg_pos0), _ptr(batch.block_table), batch.block_table.shape[1], batch.num_decode,
-            num_heads, num_kv_heads, head_dim, k_pool.shape[2], int(window or 0), ctypes.c_float(scale), chunk,
-            splits, _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _stream()),
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(decode_seg), _ptr(batch.seg_q_start),
+            _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1],
+            batch.num_decode, num_heads, num_kv_heads, head_dim, k_pool.shape[2], int(window or 0),
+            ctypes.c_float(scale), chunk, splits, _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]),
+            _stream()),
             "decode attention")
 
     # ------------------------------------------------------------------ sampling

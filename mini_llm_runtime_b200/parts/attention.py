@@ -13,12 +13,14 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..ops import AttentionBatch
 from .base import KVCacheNeed, Mixer, TensorSpec, build_part, register_part
 
 
 class GQAAttention(Mixer):
     graph_safe = True
     supports_norm_fusion = True
+    plan_key = "paged_attention"     # every attention layer of a model reads the same work lists
 
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
@@ -35,7 +37,9 @@ class GQAAttention(Mixer):
         if self.window is not None and int(self.window) <= 0:
             raise ValueError("an attention window must be positive")
         self.scale = float(self.head_dim) ** -0.5
-        self.position = build_part("position", a["position"], compute_dtype)
+        # the position encoding is optional: without one, q and k are used as projected
+        self.position = build_part("position", a["position"], compute_dtype) if a.get("position") else None
+        self._no_rotation: torch.Tensor | None = None
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
         self.input_norm_eps: float | None = None     # set once the preceding norm's weight is folded in
 
@@ -71,20 +75,49 @@ class GQAAttention(Mixer):
         self.w_o = self._to_compute(tensors[p + "o_proj.weight"], device)
         if self.out_bias:
             self.b_o = self._to_compute(tensors[p + "o_proj.bias"], device)
-        self.position.load({}, device)
+        if self.position is not None:
+            self.position.load({}, device)
+        else:
+            self._no_rotation = torch.zeros(self.head_dim // 2, dtype=torch.float32, device=device)
 
     def absorb_input_norm(self, weight, eps):
         folded = self.w_qkv.float() * weight.to(self.w_qkv.device).float()[None, :]
         self.w_qkv = folded.to(self.compute_dtype).contiguous()
         self.input_norm_eps = float(eps)
 
+    def step_plan(self, host):
+        return ops.current().plan_attention(host.lengths, host.position_start)
+
+    def _batch(self, ctx, view) -> AttentionBatch:
+        """The step's ragged batch as the attention kernels want it; built once per step and cache
+        group and shared by the layers of that group."""
+        batch = view.shared.get("attention_batch")
+        if batch is None:
+            arrays, counts = ctx.plans.get(self.plan_key, ({}, {}))
+            batch = AttentionBatch(
+                seg_q_start=ctx.seg_q_start, seg_q_len=ctx.seg_q_len, seg_pos0=ctx.seg_pos0, seg_slot=ctx.seg_slot,
+                block_table=view.block_table, num_segments=ctx.num_segments, max_q_len=ctx.max_q_len,
+                max_kv_len=ctx.max_kv_len, plan=arrays, counts=counts)
+            view.shared["attention_batch"] = batch
+        return batch
+
     def forward(self, x, ctx, view, writes_cache, raw_input=False, residual=None):
         """``raw_input``: x is the un-normalised stream and the q/k/v product applies the row scale
         of the folded norm.  ``residual``: the output product adds into it in place."""
         k = ops.current()
         qkv = k.linear(x, self.w_qkv, self.b_qkv, rms_eps=self.input_norm_eps if raw_input else None)
-        mixed = self.position.attend(qkv, ctx, view, self.num_heads, self.num_kv_heads, self.head_dim,
-                                     self.scale, self.window, writes_cache)
+        batch = self._batch(ctx, view)
+        frequencies = self._no_rotation if self.position is None else self.position.rotary_frequencies()
+        if frequencies is not None:
+            # a plain rotary encoding (or none): rotation, cache write and attention may share kernels
+            mixed = k.rope_paged_attention(qkv, ctx.positions, frequencies, view.slots, view.k_pool, view.v_pool,
+                                           batch, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
+                                           self.window, writes_cache)
+        else:
+            q = self.position.rotate_and_store(qkv, ctx, view, self.num_heads, self.num_kv_heads, self.head_dim,
+                                               writes_cache)
+            mixed = k.paged_attention(q, view.k_pool, view.v_pool, batch, self.num_heads, self.num_kv_heads,
+                                      self.head_dim, self.scale, self.window)
         return k.linear(mixed, self.w_o, self.b_o, residual=residual)
 
 

@@ -113,6 +113,8 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """Used by a mixer as a component: it turns q and k by their positions and stores k and v."""
+
     category = "position"
 
     def rotate_and_store(self, qkv: torch.Tensor, ctx, view, num_heads: int, num_kv_heads: int,
@@ -121,14 +123,12 @@ class PositionEncoding(Part):
         store k and v into the cache view's pages, return q [rows, heads*head_dim]."""
         raise NotImplementedError
 
-    def attend(self, qkv: torch.Tensor, ctx, view, num_heads: int, num_kv_heads: int, head_dim: int,
-               scale: float, window: int | None, write_kv: bool) -> torch.Tensor:
-        """``rotate_and_store`` followed by attention over the cache, [rows, heads*head_dim].
-        An encoding whose kernels can do both at once overrides this; the default is the two steps."""
-        from .. import ops
-        q = self.rotate_and_store(qkv, ctx, view, num_heads, num_kv_heads, head_dim, write_kv)
-        return ops.current().paged_attention(q, view.k_pool, view.v_pool, view.batch, num_heads, num_kv_heads,
-                                             head_dim, scale, window)
+    def rotary_frequencies(self) -> torch.Tensor | None:
+        """If the encoding is "turn pair (i, i + head_dim/2) by position * f[i]": the float32
+        frequencies f [head_dim/2] on the device, which lets a mixer use kernels that rotate, store
+        and attend in one launch.  None (the default) for any other encoding; the mixer then calls
+        ``rotate_and_store`` and its attention kernel one after the other."""
+        return None
 
 
 class Mixer(Part):
@@ -137,9 +137,18 @@ class Mixer(Part):
     # ``residual=`` in forward: the block may hand it the un-normalised stream (the part applies the
     # row scale inside its first product) and let it add its output into the stream in place.
     supports_norm_fusion = False
+    # Mixers whose kernels need host-made work lists name them here; mixers with equal keys share
+    # one list per step.  The step function calls ``step_plan`` once per key and step, sends the
+    # arrays with its own metadata and hands the device copies back in ``ctx.plans[plan_key]``.
+    plan_key: str | None = None
 
     def cache_need(self) -> KVCacheNeed | StateNeed | None:
         return None
+
+    def step_plan(self, host) -> tuple[dict, dict]:
+        """``host`` (``HostBatch``): rows, first row and first position of every request of the
+        step.  Returns (int32/int64/float32 numpy arrays by name, plain counts by name)."""
+        return {}, {}
 
     def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool) -> torch.Tensor:
         """x: [rows, hidden] of this step; ``view`` is this run step's cache entry."""

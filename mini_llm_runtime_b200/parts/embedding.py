@@ -34,8 +34,9 @@ class TokenEmbedding(Embedding):
 
 
 class TiedHead(Head):
-    """logits = x E^T.  A checkpoint may still carry ``lm_head.weight``; it must then equal the
-    embedding (reference rule: src/mini_llm_runtime/qwen_weights.py:113-119)."""
+    """logits = x E^T.  A checkpoint may still carry the head's own matrix; it must then equal the
+    embedding's tensor, whose checkpoint name the spec gives as ``tied_to`` (reference rule:
+    src/mini_llm_runtime/qwen_weights.py:113-119).  Without ``tied_to`` nothing is compared."""
 
     graph_safe = True
 
@@ -43,20 +44,20 @@ class TiedHead(Head):
         super().__init__(spec, compute_dtype)
         self.vocab_size = int(self.args["vocab_size"])
         self.hidden_size = int(self.args["hidden_size"])
-        self.tied_to = "model.embed_tokens.weight"
+        self.tied_to = self.args.get("tied_to")
 
     def tensors(self):
         return {self.prefix + "weight": TensorSpec((self.vocab_size, self.hidden_size), optional=True)}
 
     def load(self, tensors, device):
         copy = tensors.get(self.prefix + "weight")
-        original = tensors.get(self.tied_to)
+        original = tensors.get(self.tied_to) if self.tied_to else None
         if copy is not None and original is not None and not torch.equal(copy, original):
             raise ValueError(f"{self.prefix}weight is present but differs from {self.tied_to} "
                              "although tie_word_embeddings is true")
 
     def extra_inputs(self):
-        return (self.tied_to,)
+        return (self.tied_to,) if self.tied_to else ()
 
     def forward(self, x, embedding):
         return ops.current().linear(x, embedding.weight, None, out_dtype=torch.float32)

@@ -37,14 +37,8 @@ class RotateHalfRope(PositionEncoding):
         return ops.current().rope_kv_write(qkv, ctx.positions, self.inv_freq, view.slots, view.k_pool,
                                            view.v_pool, num_heads, num_kv_heads, head_dim, write_kv)
 
-
-    def attend(self, qkv, ctx, view, num_heads, num_kv_heads, head_dim, scale, window, write_kv):
-        """Rotation, cache write and attention in one call: the kernels fuse them where they can."""
-        if head_dim != self.head_dim:
-            raise ValueError(f"position encoding was built for head_dim {self.head_dim}, mixer has {head_dim}")
-        return ops.current().rope_paged_attention(qkv, ctx.positions, self.inv_freq, view.slots, view.k_pool,
-                                                  view.v_pool, view.batch, num_heads, num_kv_heads, head_dim,
-                                                  scale, window, write_kv)
+    def rotary_frequencies(self):
+        return self.inv_freq
 
 
 register_part("position", "rope_half", RotateHalfRope)

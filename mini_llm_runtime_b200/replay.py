@@ -91,6 +91,7 @@ def main(argv=None) -> int:
                 host.astype("<f4", copy=False).tofile(out_dir / f"{step}.f32")
             else:
                 torch.cuda.synchronize()
+            runner.check_device()       # the host has just waited for the step: a kernel that gave up shows here
         for request_id in record.get("end", []):
             cache.release(str(request_id))
         print(f"done {step}", flush=True)

@@ -1,3 +1,3 @@
-from .sampler import Sampler
+from .params import GREEDY, SamplingParams
 
-__all__ = ["Sampler"]
+__all__ = ["GREEDY", "SamplingParams"]

@@ -5,7 +5,9 @@ The reference has no such mode; its tests draw a tiny state dict from a seeded g
 (tests/test_qwen_weights.py:25-65 there).  Distributions: matrices ~ N(0, 0.02), norm weights
 ~ 1 + N(0, 0.02), biases ~ N(0, 0.02), integer tables uniform below their bound.  Tensors are
 drawn one by one in sorted-name order from one CPU generator, in float32, then rounded to the
-storage dtype, so a given (configuration, seed, dtype) always yields the same bytes.
+storage dtype, so a given (configuration, seed, dtype) always yields the same bytes.  For models
+of many gigabytes ``device=`` draws from that device's generator instead (other bytes, the same
+distributions, seconds instead of minutes); model folders are always written from the CPU stream.
 """
 
 from __future__ import annotations
@@ -23,8 +25,9 @@ STD = 0.02
 
 
 def random_tensors(expected: Mapping[str, "TensorSpec"], seed: int,
-                   dtype: torch.dtype = torch.bfloat16) -> dict[str, torch.Tensor]:
-    generator = torch.Generator(device="cpu")
+                   dtype: torch.dtype = torch.bfloat16, device: str | torch.device = "cpu") -> dict[str, torch.Tensor]:
+    device = torch.device(device)
+    generator = torch.Generator(device=device)
     generator.manual_seed(int(seed))
     tensors: dict[str, torch.Tensor] = {}
     for name in sorted(expected):
@@ -34,9 +37,9 @@ def random_tensors(expected: Mapping[str, "TensorSpec"], seed: int,
         shape = tuple(spec.shape)
         if spec.storage == "int" or spec.init == "table":
             tensors[name] = torch.randint(0, max(int(spec.high), 1), shape, generator=generator,
-                                          dtype=torch.int32)
+                                          dtype=torch.int32, device=device)
             continue
-        values = torch.randn(shape, generator=generator, dtype=torch.float32) * STD
+        values = torch.randn(shape, generator=generator, dtype=torch.float32, device=device) * STD
         if spec.init == "norm":
             values = values + 1.0
         elif spec.init not in ("matrix", "bias"):

@@ -8,11 +8,67 @@ the GPU tests do not use it.
 
 from __future__ import annotations
 
+import numpy as np
 import torch
+
+from mini_llm_runtime_b200.cache.slots import COUNTER, LAST_TOKEN, LENGTH, read_record
 
 
 class FakeOps:
     name = "fake-cpu"
+    error_code = 0      # tests set this to make the next device check fail
+
+    def raise_if_device_error(self):
+        if self.error_code:
+            code, self.error_code = self.error_code, 0
+            from mini_llm_runtime_b200.ops import KernelError
+            raise KernelError(f"a kernel's bounded wait ran out (code {code}); the results of the "
+                              "steps since the last check are invalid")
+
+    # ---- resident tables and slot records
+    def plan_attention(self, lengths, position_start):
+        return {}, {}
+
+    def scatter_rows(self, table, row_index, rows):
+        table[row_index.long()] = rows
+
+    def decode_prepare(self, seg_slot, slot_state, *, token_ids=None, positions=None, seg_pos0=None, table=None,
+                       page_size=0, kv_slots=None):
+        for i, slot in enumerate(seg_slot.tolist()):
+            position = int(slot_state[slot, LENGTH])
+            if token_ids is not None:
+                token_ids[i] = int(slot_state[slot, LAST_TOKEN])
+            if positions is not None:
+                positions[i] = position
+            if seg_pos0 is not None:
+                seg_pos0[i] = position
+            if kv_slots is not None:
+                page = int(table[slot, position // page_size])
+                kv_slots[i] = page * page_size + position % page_size if page >= 0 else -1
+
+    def advance_slots(self, seg_slot, slot_state, seg_q_len=None, seg_pos0=None):
+        for i, slot in enumerate(seg_slot.tolist()):
+            grow = 1 if seg_q_len is None else int(seg_q_len[i])
+            base = int(slot_state[slot, LENGTH]) if seg_pos0 is None else int(seg_pos0[i])
+            slot_state[slot, LENGTH] = base + grow
+
+    def sample_slots(self, logits, row_slot, slot_state, advance=False):
+        from plain_qwen2 import temperature_sample, uniform_from_seed
+
+        tokens = torch.empty(logits.shape[0], dtype=torch.int32)
+        for row, slot in enumerate(row_slot.tolist()):
+            record = read_record(slot_state[slot].numpy())
+            if record["temperature"] <= 0:
+                token = int(torch.argmax(logits[row]))
+            else:
+                u = uniform_from_seed(record["seed"], record["counter"])
+                token = int(temperature_sample(logits[row], record["temperature"], u)[0])
+            tokens[row] = token
+            slot_state[slot, LAST_TOKEN] = token
+            slot_state[slot, COUNTER] += 1
+            if advance:
+                slot_state[slot, LENGTH] += 1
+        return tokens
 
     def embedding(self, ids, table):
         return table[ids.long()].clone()
@@ -100,7 +156,7 @@ class FakeOps:
         for seg in range(batch.num_segments):
             start, length, pos0 = (int(batch.seg_q_start[seg]), int(batch.seg_q_len[seg]),
                                    int(batch.seg_pos0[seg]))
-            table = batch.block_table[seg]
+            table = batch.block_table[int(batch.seg_slot[seg])]
             for r in range(length):
                 p = pos0 + r
                 low = max(0, p - window + 1) if window else 0

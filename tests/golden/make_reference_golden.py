@@ -11,7 +11,15 @@ only built on first kernel call and is never touched here), builds
   every position of a 33-token prompt and the hidden state after every layer;
 * tiny configuration B (untied head, which the reference's config class rejects): the reference's
   ``_decoder_layer`` function is called layer by layer on B's weights, giving the hidden state
-  after every layer; the untied head has no counterpart and rests on its formula.
+  after every layer; the logits are the reference's ``_rms_norm`` of the last hidden state times
+  ``lm_head.weight`` (the one product the reference does not have: it always multiplies by the
+  embedding, qwen_model_runner.py:289-290);
+* tiny configuration D (a sliding window on the layers from ``max_window_layers`` on, which the
+  reference never reads): the reference's ``_decoder_layer`` with its ``packed_causal_mask``
+  argument, given a mask that lets position p see the keys p-window+1 .. p on the windowed
+  layers and 0 .. p on the others; logits through the tied head as the reference computes them.
+  So the arithmetic of a windowed layer is the reference's own; only the rule which keys a window
+  hides, and which layers have one, is this repository's reading of the config.json keys.
 Weights come from this repository's seeded random-weights mode (seed 5, float32), the prompt from
 ``harness.random_prompt``.  The outputs are stored next to this script as float32 ``.npy`` files;
 ``tests/test_plain.py`` compares the plain implementation with them without needing the reference.
@@ -30,7 +38,7 @@ sys.path.insert(0, os.path.dirname(HERE))
 from harness import random_prompt  # noqa: E402
 from mini_llm_runtime_b200.models import build_model  # noqa: E402
 from mini_llm_runtime_b200.weights import random_tensors  # noqa: E402
-from tiny_configs import TINY_A, TINY_B  # noqa: E402
+from tiny_configs import TINY_A, TINY_B, TINY_D  # noqa: E402
 
 SEED = 5
 
@@ -43,7 +51,7 @@ def tensors_for(config):
 def main() -> None:
     sys.path.insert(0, sys.argv[1])
     from mini_llm_runtime.qwen_config import QwenConfig
-    from mini_llm_runtime.qwen_model_runner import QwenPrefillRunner, _decoder_layer
+    from mini_llm_runtime.qwen_model_runner import QwenPrefillRunner, _decoder_layer, _rms_norm
     from mini_llm_runtime.qwen_weights import QwenWeights
 
     # ---- A: whole model through the reference's runner
@@ -76,6 +84,35 @@ def main() -> None:
             x = _decoder_layer(x, positions, layer, config_b, apply_causal_mask=True)
             layers.append(x[0].clone())
     np.save(os.path.join(HERE, "tiny_b_layers.npy"), torch.stack(layers).numpy().astype(np.float32))
+    with torch.inference_mode():
+        normed = _rms_norm(x, weights_b.final_norm, config_b.rms_norm_eps)
+        logits_b = torch.nn.functional.linear(normed, tensors_b["lm_head.weight"])[0]
+    np.save(os.path.join(HERE, "tiny_b_logits.npy"), logits_b.numpy().astype(np.float32))
+
+    # ---- D: windowed layers through the reference's layer function and its mask argument
+    assert TINY_D.head_dim == TINY_D.hidden_size // TINY_D.num_attention_heads   # the reference derives it
+    config_d = QwenConfig(**{k: getattr(TINY_D, k) for k in keys})
+    tensors_d = tensors_for(TINY_D)
+    weights_d = QwenWeights.from_state_dict(config_d, tensors_d)
+    prompt_d = random_prompt(TINY_D.vocab_size, 150, 302)
+    ids = torch.tensor([prompt_d])
+    x = torch.nn.functional.embedding(ids, weights_d.embedding)
+    positions = torch.arange(len(prompt_d)).unsqueeze(0)
+    query, key = positions[0].unsqueeze(1), positions[0].unsqueeze(0)
+    causal = key <= query
+    windowed = causal & (key > query - TINY_D.sliding_window)
+    layers = []
+    with torch.inference_mode():
+        for index, layer in enumerate(weights_d.layers):
+            has_window = TINY_D.use_sliding_window and index >= TINY_D.max_window_layers
+            x = _decoder_layer(x, positions, layer, config_d, apply_causal_mask=False,
+                               packed_causal_mask=windowed if has_window else causal)
+            layers.append(x[0].clone())
+        normed = _rms_norm(x, weights_d.final_norm, config_d.rms_norm_eps)
+        logits_d = torch.nn.functional.linear(normed, weights_d.embedding)[0]
+    # positions 100..149 only (all past the window of 70, so the window decides what they see)
+    np.save(os.path.join(HERE, "tiny_d_layers.npy"), torch.stack(layers)[:, 100:].numpy().astype(np.float32))
+    np.save(os.path.join(HERE, "tiny_d_logits.npy"), logits_d[-8:].numpy().astype(np.float32))
     print("golden files written to", HERE)
 
 

@@ -68,12 +68,12 @@ def causal_attention(q, k, v, *, window: int | None = None) -> torch.Tensor:
     k = k.repeat_interleave(group, dim=0)
     v = v.repeat_interleave(group, dim=0)
     scores = torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(head_dim)
-    query_pos = torch.arange(length).unsqueeze(1)
-    key_pos = torch.arange(length).unsqueeze(0)
+    query_pos = torch.arange(length, device=q.device).unsqueeze(1)
+    key_pos = torch.arange(length, device=q.device).unsqueeze(0)
     hidden = key_pos > query_pos
     if window is not None:
         hidden = hidden | (key_pos <= query_pos - window)
-    scores = scores.masked_fill(hidden.to(scores.device), float("-inf"))
+    scores = scores.masked_fill(hidden, float("-inf"))
     probabilities = torch.softmax(scores.float(), dim=-1)
     return torch.matmul(probabilities, v)
 
@@ -131,17 +131,20 @@ def decoder_layer(x, positions, tensors, layer, cfg) -> torch.Tensor:
     return h + swiglu_mlp(normed, tensors, prefix)
 
 
-def forward_logits(tensors: dict, cfg: dict, token_ids, *, return_layers: bool = False):
+def forward_logits(tensors: dict, cfg: dict, token_ids, *, return_layers: bool = False, rows=None):
     """qwen_model_runner.py:263-290 — embedding gather, the layers in order, final norm, then
     logits = x @ E^T (tied) or x @ lm_head^T (untied; ours).  Returns [S, vocab] float32 for
-    one request given whole; every position's logits."""
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
-    x = tensors["model.embed_tokens.weight"].float()[ids]
-    positions = torch.arange(ids.shape[0])
+    one request given whole; every position's logits (``rows``: only those positions')."""
+    table = tensors["model.embed_tokens.weight"]
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=table.device)
+    x = table[ids].float()
+    positions = torch.arange(ids.shape[0], device=table.device)
     captured = []
     for layer in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, positions, tensors, layer, cfg)
         captured.append(x)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long, device=x.device)]
     x = rms_norm(x, tensors["model.norm.weight"], cfg["rms_norm_eps"])
     head = tensors["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else tensors["lm_head.weight"]
     logits = x @ head.float().T

@@ -214,3 +214,109 @@ def test_random_orders_never_lose_or_share_a_page(seed):
         m.release(rid)
     assert all(g.allocator.free_count == g.num_pages and g.allocator.promised == 0 for g in m.groups)
     assert m.slots.free_count == 5
+
+
+def test_requests_without_a_promise_cannot_take_what_is_promised_to_others():
+    """A request admitted with a promise and one created without (replay, greedy_generate) on one
+    manager: the second may only take pages that no promise covers."""
+    m = manager(needs=(FULL,), pages=6, page=4, tokens=24, step=8)
+    assert m.create_request("promised", lifetime_tokens=16) is not None      # 4 of the 6 pages
+    m.create_request("free-rider")
+    m.begin_step([("free-rider", 8)])                                        # the 2 uncovered pages
+    m.commit_step()
+    with pytest.raises(OutOfPages):
+        m.begin_step([("free-rider", 1)])                                    # a third would cut into the promise
+    for _ in range(4):                                                       # the promise is honoured to its end
+        m.begin_step([("promised", 4)])
+        m.commit_step()
+    assert m.groups[0].allocator.free_count == 0
+    m.release("promised")
+    m.begin_step([("free-rider", 1)])
+    m.commit_step()
+    m.check_consistency()
+    pool = PoolAllocator(4)
+    assert pool.promise(3)
+    taken = pool.allocate(2, promised=True)
+    with pytest.raises(ValueError):
+        pool.unpromise(3)                    # two pages are still held under it
+    pool.free(taken, promised=True)
+    pool.unpromise(3)
+
+
+def resident(needs=(FULL, WINDOW), **options):
+    """A manager on the CPU that believes its tables live elsewhere, so that it reports changed rows."""
+    defaults = dict(page_size=4, num_pages=16, max_requests=3, max_tokens_per_request=64, dtype=torch.float32,
+                    device="cpu", max_step_tokens=16)
+    defaults.update(options)
+    m = CacheManager(list(needs), **defaults)
+    m._shares_host_memory = False
+    for group in m.groups:
+        group.device_table = group.device_table.clone()
+    m.slot_state = m.slot_state.clone()
+    return m
+
+
+def apply_updates(m):
+    updates = m.take_resident_updates()
+    for table, rows, values in updates:
+        table[torch.from_numpy(rows).long()] = torch.from_numpy(values)
+    m.resident_updates_sent()
+    return updates
+
+
+def test_only_changed_rows_of_the_resident_tables_are_handed_out():
+    from mini_llm_runtime_b200.cache import read_record
+
+    m = resident()
+    a = m.create_request("a", temperature=0.5, seed=(7 << 32) | 9)
+    m.create_request("b")
+    m.begin_step([("a", 6), ("b", 2)])
+    updates = apply_updates(m)
+    assert [int(table.shape[1]) for table, _, _ in updates] == [16, 16, 8]    # two block tables, the slot records
+    assert [rows.tolist() for _, rows, _ in updates] == [[0, 1], [0, 1], [0, 1]]
+    record = read_record(m.slot_state[a.slot].numpy())
+    assert record == {"length": 0, "last_token": 0, "counter": 0, "temperature": 0.5, "seed": (7 << 32) | 9}
+    m.commit_step()
+    for _ in range(2):                       # a fills its second page: no row changes, nothing to send
+        m.begin_step([("a", 1)])
+        assert m.take_resident_updates() == []
+        m.resident_updates_sent()
+        m.commit_step()
+    m.begin_step([("a", 1)])                 # a crosses into a third page: its row alone, in both groups
+    updates = apply_updates(m)
+    assert [rows.tolist() for _, rows, _ in updates] == [[a.slot], [a.slot]]
+    m.commit_step()
+    for group in m.groups:
+        assert torch.equal(group.device_table, torch.from_numpy(group.table))
+    m.release("b")
+    assert [rows.tolist() for _, rows, _ in apply_updates(m)] == [[1], [1]]
+
+
+def test_rows_handed_out_but_never_sent_are_handed_out_again():
+    m = resident(needs=(FULL,))
+    m.create_request("a")
+    m.begin_step([("a", 5)])
+    first = m.take_resident_updates()        # the step fails before it can send them
+    m.abort_step()
+    m.begin_step([("a", 5)])
+    again = m.take_resident_updates()
+    assert [rows.tolist() for _, rows, _ in again] == [rows.tolist() for _, rows, _ in first] == [[0], [0]]
+    m.resident_updates_sent()
+    m.commit_step()
+    assert m.take_resident_updates() == []
+
+
+def test_an_aborted_step_restores_fixed_size_state():
+    m = CacheManager([FULL, StateNeed((3,))], page_size=4, num_pages=8, max_requests=3,
+                     max_tokens_per_request=32, dtype=torch.float32, device="cpu")
+    a, b = m.create_request("a"), m.create_request("b")
+    m.state[1][a.slot] = torch.tensor([1.0, 2.0, 3.0])
+    m.begin_step([("a", 2)])
+    m.state[1][a.slot] += 10                 # a mixer writes its state in place during the step
+    m.state[1][b.slot] += 1                  # b is not part of the step: not the manager's to restore
+    m.abort_step()
+    assert m.state[1][a.slot].tolist() == [1.0, 2.0, 3.0] and m.state[1][b.slot].tolist() == [1.0, 1.0, 1.0]
+    m.begin_step([("a", 2)])
+    m.state[1][a.slot] += 10
+    m.commit_step()
+    assert m.state[1][a.slot].tolist() == [11.0, 12.0, 13.0]

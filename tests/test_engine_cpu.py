@@ -93,8 +93,8 @@ def test_continuous_batching_reproduces_plain_greedy_generation(name):
     for i, (rid, prompt) in enumerate(prompts.items()):
         engine.submit(rid, prompt, max_new_tokens=3 + i % 4)
     results = engine.run()
-    assert any(len(r.batch.prefill_request_ids) and len(r.batch.decode_request_ids) for r in results)
-    assert any(not item.emits_token for r in results for item in r.batch.items)     # some prompt was cut
+    assert any(len(r.plan.prefill_request_ids) and len(r.plan.decode_request_ids) for r in results)
+    assert any(not item.emits for r in results for item in r.plan.items)     # some prompt was cut
     for i, (rid, prompt) in enumerate(prompts.items()):
         want = plain.greedy_tokens(tensors, config.to_dict(), prompt, 3 + i % 4)
         assert list(engine.scheduler.get_request(rid).generated_token_ids) == want, rid
@@ -160,7 +160,7 @@ def test_a_failed_step_rolls_back_scheduler_and_cache_and_can_be_retried():
     assert not engine.manager.step_in_flight
     engine.manager.check_consistency()
     result = engine.step()
-    assert result.batch.step_index == 1 and set(result.batch.admitted_request_ids) == {"b"}
+    assert result.plan.index == 1 and set(result.plan.admitted_request_ids) == {"b"}
     engine.run()
     for rid, seed, length, count in (("a", 1, 6, 3), ("b", 2, 4, 2)):
         want = plain.greedy_tokens(tensors, config.to_dict(), random_prompt(config.vocab_size, length, seed), count)
@@ -248,7 +248,7 @@ def test_stepping_ahead_returns_the_same_results_step_by_step():
                     engine.submit("late", list(range(20, 75)), max_new_tokens=4)
                 result = engine.step()
                 steps += 1
-                history.append((result.update.emitted_tokens, result.update.finished_request_ids))
+                history.append((result.outcome.emitted_tokens, result.outcome.finished_request_ids))
                 engine.manager.check_consistency()
             assert not engine.manager.requests, "every finished request gave its pages back"
             tokens = {rid: engine.scheduler.get_request(rid).generated_token_ids for rid in ("a", "b", "stops", "late")}
@@ -257,3 +257,92 @@ def test_stepping_ahead_returns_the_same_results_step_by_step():
     assert histories[0][1] == histories[1][1]
     assert len(histories[1][1]["stops"]) < 12, "the stop token must have ended the request early"
     assert histories[1][2] > histories[0][2], "stepping ahead launches the dropped extra step of ended requests"
+
+
+def test_a_device_error_ends_the_steps_requests_and_leaves_the_engine_usable():
+    """A kernel whose bounded wait ran out reports through an error word that the engine reads where
+    it waits for the step's tokens.  The requests of that step end with an error and give their
+    pages back; a request that was still waiting runs afterwards and gets the right tokens."""
+    from mini_llm_runtime_b200.engine import FinishReason
+
+    config, tensors, engine = build_engine("A", max_running_requests=2)
+    kernels = ops.current()
+    prompts = {rid: random_prompt(config.vocab_size, n, seed) for rid, n, seed in (("a", 6, 1), ("b", 9, 2), ("c", 5, 3))}
+    for rid, prompt in prompts.items():
+        engine.submit(rid, prompt, max_new_tokens=4)
+    engine.step()                                   # a and b prefill; c waits for a place
+    kernels.error_code = 3
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        engine.step()
+    for rid in ("a", "b"):
+        request = engine.scheduler.get_request(rid)
+        assert request.finish_reason is FinishReason.ERROR and len(request.generated_token_ids) == 1
+    assert not engine.manager.requests and engine.scheduler.outstanding_plan is None
+    engine.manager.check_consistency()
+    assert engine.scheduler.waiting_request_ids == ("c",)
+    engine.run()
+    assert list(engine.scheduler.get_request("c").generated_token_ids) == \
+        plain.greedy_tokens(tensors, config.to_dict(), prompts["c"], 4)
+    # the single-request loop checks after each step too
+    kernels.error_code = 5
+    with pytest.raises(ops.KernelError):
+        greedy_generate(engine.runner, prompts["a"], max_new_tokens=2)
+    assert not engine.manager.requests
+
+
+def test_slot_records_follow_the_requests():
+    """What the device keeps per slot (length, last token, counter) after every step equals what the
+    host knows of the request, through prompt portions, decodes fed from the records and slot reuse."""
+    from mini_llm_runtime_b200.cache import read_record
+
+    config, tensors, engine = build_engine("B", max_running_requests=2, max_batch_tokens=12)
+    for i, n in enumerate((20, 3, 7)):
+        engine.submit(f"r{i}", random_prompt(config.vocab_size, n, 80 + i), max_new_tokens=4 + i,
+                      temperature=0.5 * i, seed=11 * i)
+    while engine.scheduler.has_unfinished_requests:
+        engine.step()
+        for rid in engine.scheduler.running_request_ids:
+            request, held = engine.scheduler.get_request(rid), engine.manager.get(rid)
+            record = read_record(engine.manager.slot_state[held.slot].numpy())
+            assert record["length"] == held.committed
+            assert record["counter"] == len(request.generated_token_ids)
+            assert record["temperature"] == request.temperature and record["seed"] == request.seed
+            if request.generated_token_ids:
+                assert record["last_token"] == request.generated_token_ids[-1]
+
+
+def test_a_step_that_fails_after_a_stateful_mixer_ran_leaves_its_state_as_it_was():
+    """The toy mixer overwrites its per-request state in place.  A failure later in the same step
+    must not leave the half-advanced state behind: the retried step gives the logits of a run that
+    never failed."""
+    import toy_parts
+
+    toy_parts.register_toys()
+    register_architecture("ToyForCausalLM", toy_parts.ToyConfig.from_dict, toy_parts.toy_model_spec, replace=True)
+    try:
+        config = toy_parts.ToyConfig()
+        model = build_model(config, torch.float32)
+        tensors = random_tensors(model.expected_tensors(), 4, torch.float32)
+        model.load(tensors, "cpu")
+        cache = CacheManager(model.cache_needs(), page_size=8, num_pages=16, max_requests=2,
+                             max_tokens_per_request=64, dtype=torch.float32, device="cpu")
+        runner = ModelRunner(model, cache)
+        tokens = random_prompt(97, 20, 6)
+        cache.create_request("x")
+        first = runner.step([StepEntry("x", tokens[:9], list(range(9)))])
+        last_block = model.blocks[2]
+        forward = last_block.forward
+
+        def failing(*args, **kwargs):
+            raise RuntimeError("injected failure after the stateful layers ran")
+
+        last_block.forward = failing
+        with pytest.raises(RuntimeError, match="injected"):
+            runner.step([StepEntry("x", tokens[9:], list(range(11)))])
+        last_block.forward = forward
+        assert cache.get("x").committed == 9 and not cache.step_in_flight
+        second = runner.step([StepEntry("x", tokens[9:], list(range(11)))])
+        assert_close(torch.cat([first, second]), toy_parts.plain_toy_logits(tensors, config, tokens),
+                     torch.float32, "toy after a failed step")
+    finally:
+        unregister_architecture("ToyForCausalLM")

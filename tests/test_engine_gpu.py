@@ -91,9 +91,9 @@ def test_mixed_with_reused_pages(setup, seed):
     original_allocate = [g.allocator.allocate for g in tight.cache.groups]
 
     def watch(group_index):
-        def allocate(count):
+        def allocate(count, **options):
             nonlocal reused
-            ids = original_allocate[group_index](count)
+            ids = original_allocate[group_index](count, **options)
             reused = reused or any((group_index, i) in handed_out for i in ids)
             handed_out.update((group_index, i) for i in ids)
             return ids

@@ -45,7 +45,7 @@ def test_greedy_generation_through_the_entry_point(name, dtype, tmp_path):
     for i, prompt in enumerate(prompts):
         engine.submit(f"g{i}", prompt, max_new_tokens=8)
     results = engine.run()
-    assert any(len(r.batch.prefill_request_ids) and len(r.batch.decode_request_ids) for r in results)
+    assert any(len(r.plan.prefill_request_ids) and len(r.plan.decode_request_ids) for r in results)
     for i, prompt in enumerate(prompts):
         want, gaps = greedy_with_margin(tensors, config.to_dict(), prompt, 8)
         got = list(engine.scheduler.get_request(f"g{i}").generated_token_ids)
@@ -128,7 +128,7 @@ def test_stepping_ahead_on_the_device(name, dtype, eventful):
                 engine.submit("late", prompts["late"], max_new_tokens=12)
             result = engine.step()
             steps += 1
-            history.append((result.update.emitted_tokens, result.update.finished_request_ids))
+            history.append((result.outcome.emitted_tokens, result.outcome.finished_request_ids))
         engine.manager.check_consistency()
         assert not engine.manager.requests
         histories.append((history, engine.runner.graph_replays))

@@ -16,7 +16,7 @@ from fake_ops import FakeOps
 from harness import assert_close
 from mini_llm_runtime_b200 import ops
 from mini_llm_runtime_b200.ops import cuda_ops
-from mini_llm_runtime_b200.ops.cuda_ops import AttentionBatch
+from mini_llm_runtime_b200.ops.cuda_ops import AttentionBatch, plan_attention
 
 pytestmark = pytest.mark.gpu
 
@@ -83,6 +83,24 @@ def test_swiglu(dtype):
     blocked = rnd((5, 2 * 192), dtype, 9, 3.0)
     got = cuda().swiglu(blocked.to(DEVICE), 64)
     assert_close(got, FAKE.swiglu(blocked.float(), 64), dtype, "swiglu, interleaved blocks")
+
+
+def test_many_distinct_operands_never_share_a_tensor_map():
+    """The tensor-core product looks its two tensor maps up in a host-side cache.  A model with more
+    distinct matrices than the cache has entries (14B sizes: some four hundred) must still get the
+    right map for each operand: with a cache that hands out pointers into its own table, the lookup
+    of the second operand could overwrite the entry the first lookup had just returned."""
+    generator = torch.Generator().manual_seed(77)
+    weights = [(torch.randn(128 + 16 * (i % 5), 64 + 64 * (i % 3), generator=generator) * 0.2).to(torch.bfloat16).to(DEVICE)
+               for i in range(700)]
+    inputs = {k: (torch.randn(40, k, generator=generator)).to(torch.bfloat16).to(DEVICE) for k in (64, 128, 192)}
+    for turn in range(2):                        # the second pass meets a full cache
+        outputs = [cuda().linear(inputs[w.shape[1]], w) for w in weights]
+        torch.cuda.synchronize()
+        cuda().raise_if_device_error()
+        for i in (0, 1, 255, 256, 257, 300, 511, 512, 699):
+            want = inputs[weights[i].shape[1]].double() @ weights[i].double().T
+            assert_close(outputs[i], want, torch.bfloat16, f"product {i}, pass {turn}")
 
 
 @pytest.mark.parametrize("m", [1, 8, 20, 40, 100, 128, 200, 700])
@@ -347,43 +365,19 @@ def make_attention_case(dtype, heads, kv_heads, head_dim, page, segments, seed, 
     for _, q_len in segments:
         q_start.append(row)
         row += q_len
-    # tiles of segments longer than one row first, single-row (decode) segments last
-    decode = [s for s, (_, q_len) in enumerate(segments) if q_len == 1]
-    order = [s for s, (_, q_len) in enumerate(segments) if q_len != 1] + decode
-    tile_seg, tile_row0 = [], []
-    for s in order:
-        for r0 in range(0, segments[s][1], 16):
-            tile_seg.append(s)
-            tile_row0.append(r0)
-
-    wide_seg, wide_row0 = [], []
-    for s, (_, q_len) in enumerate(segments):
-        if q_len != 1:
-            for r0 in range(0, q_len, 64):
-                wide_seg.append(s)
-                wide_row0.append(r0)
-
-    big_seg, big_row0 = [], []
-    for s, (_, q_len) in enumerate(segments):
-        if q_len != 1:
-            for r0 in range(0, q_len, 128):
-                big_seg.append(s)
-                big_row0.append(r0)
+    lengths = [q_len for _, q_len in segments]
+    starts = [pos0 for pos0, _ in segments]
+    arrays, counts = plan_attention(lengths, starts)
 
     def ints(values, device):
         return torch.tensor(values, dtype=torch.int32, device=device)
 
     def batch(device):
         return AttentionBatch(
-            seg_q_start=ints(q_start, device), seg_q_len=ints([q for _, q in segments], device),
-            seg_pos0=ints([p for p, _ in segments], device), block_table=table.to(device),
-            tile_seg=ints(tile_seg, device), tile_row0=ints(tile_row0, device),
-            num_segments=len(segments), num_tiles=len(tile_seg),
-            max_q_len=max(q for _, q in segments), max_kv_len=max(p + q for p, q in segments),
-            decode_seg=ints(decode, device), num_decode=len(decode),
-            wide_tile_seg=ints(wide_seg, device), wide_tile_row0=ints(wide_row0, device),
-            num_wide_tiles=len(wide_seg), big_tile_seg=ints(big_seg, device), big_tile_row0=ints(big_row0, device),
-            num_big_tiles=len(big_seg))
+            seg_q_start=ints(q_start, device), seg_q_len=ints(lengths, device), seg_pos0=ints(starts, device),
+            seg_slot=ints(list(range(len(segments))), device), block_table=table.to(device),
+            num_segments=len(segments), max_q_len=max(lengths), max_kv_len=max(p + q for p, q in segments),
+            plan={name: torch.from_numpy(array).to(device) for name, array in arrays.items()}, counts=counts)
 
     return q.to(dtype), k_pool.to(dtype), v_pool.to(dtype), batch, table
 
@@ -593,21 +587,20 @@ def test_attention_rows_do_not_depend_on_the_cut(dtype):
     q, k_pool, v_pool, batch, table = make_attention_case(dtype, heads, kv_heads, head_dim, page, [(0, 45)], 24)
     scale = head_dim ** -0.5
     qd, kd, vd = q.to(DEVICE), k_pool.to(DEVICE), v_pool.to(DEVICE)
-    cuda().use_mma_attention = cuda().use_decode_kernel = False
-    try:
-        whole = cuda().paged_attention(qd, kd, vd, batch(DEVICE), heads, kv_heads, head_dim, scale, None)
-    finally:
-        cuda().use_mma_attention = cuda().use_decode_kernel = True
-
     def piece(pos0, count):
-        tiles = list(range(0, count, 16))
         ints = lambda v: torch.tensor(v, dtype=torch.int32, device=DEVICE)
-        b = AttentionBatch(ints([0]), ints([count]), ints([pos0]), table.to(DEVICE), ints([0] * len(tiles)),
-                           ints(tiles), 1, len(tiles), count, pos0 + count)
+        arrays, counts = plan_attention([count], [pos0])
+        b = AttentionBatch(ints([0]), ints([count]), ints([pos0]), ints([0]), table.to(DEVICE), 1, count, pos0 + count,
+                           {name: torch.from_numpy(array).to(DEVICE) for name, array in arrays.items()}, counts)
         return cuda().paged_attention(qd[pos0:pos0 + count].contiguous(), kd, vd, b, heads, kv_heads, head_dim, scale, None)
 
-    assert torch.equal(torch.cat([piece(0, 17), piece(17, 28)]), whole)
-    assert torch.equal(torch.cat([piece(p, 1) for p in range(45)]), whole)
+    cuda().use_mma_attention = cuda().use_decode_kernel = False      # the generic kernel for every piece
+    try:
+        whole = cuda().paged_attention(qd, kd, vd, batch(DEVICE), heads, kv_heads, head_dim, scale, None)
+        assert torch.equal(torch.cat([piece(0, 17), piece(17, 28)]), whole)
+        assert torch.equal(torch.cat([piece(p, 1) for p in range(45)]), whole)
+    finally:
+        cuda().use_mma_attention = cuda().use_decode_kernel = True
 
 
 def test_sampling_greedy_takes_the_lowest_index_on_ties():

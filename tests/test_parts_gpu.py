@@ -32,11 +32,13 @@ def stored(tensors):
     return {name: value.to(torch.bfloat16) for name, value in tensors.items()}
 
 
-def context_for(need, dtype, tokens_per_step, page=8):
-    """A cache for one entry and a function that opens a step of ``n`` rows for request "r"."""
+def context_for(need, dtype, tokens_per_step, page=8, mixer=None):
+    """A cache for one entry and a function that opens a step of ``n`` rows for request "r".  The
+    stand-in model has the one ``mixer`` (if any), so that the step carries its work lists."""
     cache = CacheManager([need], page_size=page, num_pages=32, max_requests=2, max_tokens_per_request=200,
                          dtype=dtype, device=DEVICE)
-    stub = types.SimpleNamespace(device=torch.device(DEVICE), parts=lambda: [],
+    blocks = [types.SimpleNamespace(mixer=mixer)] if mixer is not None else []
+    stub = types.SimpleNamespace(device=torch.device(DEVICE), parts=lambda: [], blocks=blocks,
                                  spec=types.SimpleNamespace(vocab_size=1000, max_positions=4096))
     runner = ModelRunner(stub, cache)
     cache.create_request("r")
@@ -105,7 +107,7 @@ def test_attention_mixer_whole_and_continued(dtype, window):
     part.load(tensors, torch.device(DEVICE))
     need = part.cache_need()
     assert (need.num_kv_heads, need.head_dim, need.window) == (kv_heads, head_dim, window)
-    cache, open_step = context_for(need, dtype, 30)
+    cache, open_step = context_for(need, dtype, 30, mixer=part)
     x = rnd((30, hidden), 12).to(dtype)
     cfg = {"num_attention_heads": heads, "num_key_value_heads": kv_heads, "hidden_size": hidden,
            "head_dim": head_dim, "rope_theta": 10000.0}
@@ -179,7 +181,7 @@ def test_pre_norm_block(dtype, rows):
         part.load(tensors, torch.device(DEVICE))
     block.finish_load(dtype)
     assert block.folded == (dtype == torch.bfloat16)
-    cache, open_step = context_for(mixer.cache_need(), dtype, rows)
+    cache, open_step = context_for(mixer.cache_need(), dtype, rows, mixer=mixer)
     x = rnd((rows, hidden), 40).to(dtype)
     ctx = open_step(rows)
     residual, pending = block.forward(x.clone().to(DEVICE), None, ctx, ctx.cache_view(0), True)

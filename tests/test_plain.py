@@ -10,7 +10,7 @@ import plain_qwen2 as plain
 from harness import random_prompt
 from mini_llm_runtime_b200.models import build_model
 from mini_llm_runtime_b200.weights import random_tensors
-from tiny_configs import TINY_A, TINY_B, TINY_C
+from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -35,6 +35,28 @@ def test_tiny_b_decoder_stack_matches_the_reference_layer_function():
     _, layers = plain.forward_logits(tensors, TINY_B.to_dict(), prompt, return_layers=True)
     want_layers = torch.from_numpy(np.load(os.path.join(GOLDEN, "tiny_b_layers.npy")))
     assert torch.allclose(torch.stack(layers), want_layers, atol=2e-6, rtol=1e-5)
+
+
+def test_tiny_b_untied_head_is_the_reference_norm_times_the_head_matrix():
+    tensors = tensors_for(TINY_B)
+    prompt = random_prompt(TINY_B.vocab_size, 40, 301)
+    logits = plain.forward_logits(tensors, TINY_B.to_dict(), prompt)
+    want = torch.from_numpy(np.load(os.path.join(GOLDEN, "tiny_b_logits.npy")))
+    assert torch.allclose(logits, want, atol=5e-6, rtol=1e-5)
+
+
+def test_tiny_d_windowed_layers_match_the_reference_layer_function_under_a_window_mask():
+    tensors = tensors_for(TINY_D)
+    prompt = random_prompt(TINY_D.vocab_size, 150, 302)
+    logits, layers = plain.forward_logits(tensors, TINY_D.to_dict(), prompt, return_layers=True)
+    want_layers = torch.from_numpy(np.load(os.path.join(GOLDEN, "tiny_d_layers.npy")))
+    want_logits = torch.from_numpy(np.load(os.path.join(GOLDEN, "tiny_d_logits.npy")))
+    assert torch.allclose(torch.stack(layers)[:, 100:], want_layers, atol=5e-6, rtol=1e-5)
+    assert torch.allclose(logits[-8:], want_logits, atol=1e-5, rtol=1e-5)
+    # and the window matters there: without it the last layer's output differs
+    no_window = dict(TINY_D.to_dict(), use_sliding_window=False)
+    _, free = plain.forward_logits(tensors, no_window, prompt, return_layers=True)
+    assert not torch.allclose(free[-1][100:], want_layers[-1], atol=1e-3)
 
 
 def test_rms_norm_is_not_layer_norm():

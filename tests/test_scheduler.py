@@ -6,8 +6,8 @@ import pytest
 import torch
 
 from mini_llm_runtime_b200.cache import CacheManager
-from mini_llm_runtime_b200.engine import (BatchingPolicy, FinishReason, PagedBlockAdmissionController,
-                                          RequestScheduler, RequestStatus, WorkKind)
+from mini_llm_runtime_b200.engine import (BatchingPolicy, CacheGate, FinishReason, RequestScheduler, RequestStatus,
+                                          WorkKind)
 from mini_llm_runtime_b200.parts import KVCacheNeed
 
 
@@ -18,12 +18,12 @@ def scheduler(**options):
 
 
 def finish_step(s, token=1):
-    batch = s.outstanding_batch
+    batch = s.outstanding_plan
     return s.apply_step_results({rid: token for rid in batch.emitting_request_ids})
 
 
 def costs(batch):
-    return [(i.request_id, i.kind.value, i.token_cost, i.emits_token) for i in batch.items]
+    return [(i.request_id, i.kind.value, len(i.tokens), i.emits) for i in batch.items]
 
 
 def test_decode_first_then_fifo_admission():
@@ -37,7 +37,7 @@ def test_decode_first_then_fifo_admission():
     s.submit("c", [6], max_new_tokens=1)
     batch = s.schedule_step()
     assert costs(batch) == [("a", "decode", 1, True), ("b", "decode", 1, True), ("c", "prefill", 1, True)]
-    assert batch.items[0].input_token_ids == (7,)
+    assert batch.items[0].tokens == (7,)
     update = finish_step(s, 8)
     assert set(update.finished_request_ids) == {"b", "c"}
     assert s.get_request("b").finish_reason is FinishReason.MAX_TOKENS
@@ -52,10 +52,10 @@ def test_a_long_prompt_is_cut_into_portions_and_emits_once():
     assert costs(first) == [("long", "prefill", 8, False)]
     assert first.emitting_request_ids == ()
     s.apply_step_results({})
-    assert s.get_request("long").prefill_cursor == 8 and not s.get_request("long").prefilled
+    assert s.get_request("long").cursor == 8 and not s.get_request("long").prompt_done
     second = s.schedule_step()
     assert costs(second) == [("long", "prefill", 8, False)]
-    assert second.items[0].input_token_ids == tuple(range(8, 16)) and not second.items[0].newly_admitted
+    assert second.items[0].tokens == tuple(range(8, 16)) and not second.items[0].admitted
     s.apply_step_results({})
     third = s.schedule_step()          # the rest of the prompt, then the next request in what is left
     assert costs(third) == [("long", "prefill", 3, True), ("next", "prefill", 2, True)]
@@ -136,7 +136,7 @@ def test_abort_puts_new_requests_back_in_front_and_keeps_the_step_index():
     s.submit("b", [1, 2], max_new_tokens=1)
     s.submit("c", [3], max_new_tokens=1)
     batch = s.schedule_step()
-    assert batch.step_index == 1 and batch.admitted_request_ids == ("b", "c")
+    assert batch.index == 1 and batch.admitted_request_ids == ("b", "c")
     s.submit("d", [4], max_new_tokens=1)            # arrives while the batch is out
     with pytest.raises(RuntimeError):
         s.schedule_step()
@@ -144,7 +144,7 @@ def test_abort_puts_new_requests_back_in_front_and_keeps_the_step_index():
     assert s.waiting_request_ids == ("b", "c", "d") and s.running_request_ids == ("a",)
     assert s.get_request("b").status is RequestStatus.WAITING
     again = s.schedule_step()
-    assert again.step_index == 1 and [i.request_id for i in again.items] == ["a", "b", "c"]
+    assert again.index == 1 and [i.request_id for i in again.items] == ["a", "b", "c"]
 
 
 def test_submit_validation():
@@ -163,59 +163,69 @@ def test_submit_validation():
         s.submit("x", [1], max_new_tokens=1)
     with pytest.raises(ValueError):
         RequestScheduler(max_running_requests=5, max_batch_tokens=4)
-    assert s.get_request("x").max_cache_tokens == 1
+    assert s.get_request("x").lifetime_tokens == 1
 
 
 def page_limited(pages, page=4, tokens=64, **options):
     manager = CacheManager([KVCacheNeed(1, 8, None)], page_size=page, num_pages=pages, max_requests=4,
                            max_tokens_per_request=tokens, dtype=torch.float32, device="cpu",
                            allocate_device_memory=False)
-    admission = PagedBlockAdmissionController(manager)
-    s = scheduler(admission_callback=admission.try_admit, **options)
-    return manager, admission, s
+    return manager, scheduler(gate=CacheGate(manager), **options)
 
 
 def test_when_pages_run_out_the_head_of_the_queue_waits_and_blocks_those_behind_it():
-    manager, admission, s = page_limited(pages=4)
+    manager, s = page_limited(pages=4)
     s.submit("a", list(range(8)), max_new_tokens=5)      # 12 tokens -> 3 pages
     s.submit("b", list(range(5)), max_new_tokens=4)      # 8 tokens -> 2 pages: must wait
     s.submit("c", [1], max_new_tokens=1)                 # 1 page would fit, but may not overtake b
     batch = s.schedule_step()
     assert [i.request_id for i in batch.items] == ["a"]
-    assert admission.reservation_for("a").block_counts == (3,)
+    assert manager.get("a").promised == [3] and batch.items[0].slot == manager.get("a").slot
     assert manager.groups[0].allocator.promised == 3 and "b" not in manager.requests
     for _ in range(4):
         finish_step(s)
         assert [i.request_id for i in s.schedule_step().items] == ["a"]
-    update = finish_step(s)                               # a's fifth token: finished
-    assert update.finished_request_ids == ("a",)
-    admission.release_finished(update.finished_request_ids)
-    assert manager.groups[0].allocator.promised == 0
+    update = finish_step(s)                               # a's fifth token: finished, and its pages are back
+    assert update.finished_request_ids == ("a",) and "a" in update.freed
+    assert manager.groups[0].allocator.promised == 0 and "a" not in manager.requests
     batch = s.schedule_step()
     assert [i.request_id for i in batch.items] == ["b", "c"]
 
 
 def test_a_request_that_can_never_fit_is_an_error_not_a_wait():
-    manager, admission, s = page_limited(pages=2)
+    manager, s = page_limited(pages=2)
     s.submit("huge", list(range(9)), max_new_tokens=1)    # 3 pages, the pool has 2
     with pytest.raises(ValueError):
         s.schedule_step()
-    manager, admission, s = page_limited(pages=100, tokens=16)
+    manager, s = page_limited(pages=100, tokens=16)
     s.submit("long", list(range(16)), max_new_tokens=2)   # 17 tokens, requests are capped at 16
     with pytest.raises(ValueError):
         s.schedule_step()
 
 
-def test_release_admitted_rolls_a_failed_step_back():
-    manager, admission, s = page_limited(pages=8)
+def test_an_aborted_step_gives_slots_and_promises_back():
+    manager, s = page_limited(pages=8)
     s.submit("a", [1, 2], max_new_tokens=2)
     s.submit("b", [3], max_new_tokens=2)
-    batch = s.schedule_step()
-    admission.release_admitted(batch.admitted_request_ids)
+    s.schedule_step()
+    assert manager.stats().live_requests == 2
     s.abort_step()
     assert manager.stats().live_requests == 0 and manager.groups[0].allocator.promised == 0
-    assert s.waiting_request_ids == ("a", "b")
-    with pytest.raises(KeyError):
-        admission.release_admitted(("a",))
-    with pytest.raises(ValueError):
-        admission.release_admitted(("a", "a"))
+    assert s.waiting_request_ids == ("a", "b") and s.get_request("a").slot is None
+    with pytest.raises(RuntimeError):
+        s.abort_step()
+
+
+def test_failed_requests_end_with_an_error_and_free_everything():
+    manager, s = page_limited(pages=8)
+    s.submit("a", [1, 2], max_new_tokens=4)
+    s.submit("b", [3], max_new_tokens=4)
+    s.schedule_step()
+    finish_step(s)
+    s.submit("c", [5], max_new_tokens=1)
+    s.schedule_step()                                     # a and b decode, c is admitted
+    assert s.fail_requests(["a", "c"]) == ("a", "c")
+    assert s.get_request("a").finish_reason is FinishReason.ERROR
+    assert s.get_request("c").status is RequestStatus.FINISHED and s.outstanding_plan is None
+    assert set(manager.requests) == {"b"} and s.running_request_ids == ("b",)
+    assert [i.request_id for i in s.schedule_step().items] == ["b"]     # the engine goes on with the rest

@@ -45,9 +45,11 @@ def make_case(seed, rows, heads, kv_heads, head_dim, page, longest):
 def call(lib, name, case, heads, kv_heads, head_dim, page, chunk, splits, extra=()):
     out = torch.zeros_like(case["q"])
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the ordinary entry point also takes the table row of each segment (null: row = segment)
+    table_row = (ctypes.c_void_p(0),) if name == "mlr_attention_decode" else ()
     status = getattr(lib, name)(
         pointer(case["q"]), pointer(case["k"]), pointer(case["v"]), pointer(out), pointer(case["decode_seg"]),
-        pointer(case["q_start"]), pointer(case["pos0"]), pointer(case["table"]), case["table"].shape[1],
+        pointer(case["q_start"]), pointer(case["pos0"]), pointer(case["table"]), *table_row, case["table"].shape[1],
         case["q"].shape[0], heads, kv_heads, head_dim, page, 0, ctypes.c_float(head_dim ** -0.5), chunk, splits,
         *extra, stream)
     torch.cuda.synchronize()
@@ -103,3 +105,25 @@ def test_allocation_free_entry_point_refuses_what_its_array_cannot_hold():
     status, out = call(lib, "mlr_attention_decode_static", case, heads, kv_heads, head_dim, page, 32, 64)
     assert status == -4, "64 rows x 16 heads x 64 splits x 130 floats exceed the 4 MiB array"
     assert float(out.abs().sum()) == 0.0, "a refused call launches nothing"
+
+
+def test_allocation_free_entry_point_checks_everything_before_it_enqueues_anything():
+    """A chunk that is no multiple of 32 is refused by the kernel's own checks; the counters of the
+    fixed array must not have been touched by then (the memset comes after every check)."""
+    lib = build.load_library("attention_decode")
+    heads, kv_heads, head_dim, page = 14, 2, 64, 16
+    case = make_case(4, 4, heads, kv_heads, head_dim, page, 300)
+    status, out = call(lib, "mlr_attention_decode_static", case, heads, kv_heads, head_dim, page, 48, 8)
+    assert status == -2 and float(out.abs().sum()) == 0.0
+
+
+def test_a_context_longer_than_the_grid_was_sized_for_is_still_right():
+    """max_splits * chunk shorter than the longest context: the last CTA of a row walks on."""
+    lib = build.load_library("attention_decode")
+    heads, kv_heads, head_dim, page, chunk = 14, 2, 64, 16, 64
+    case = make_case(5, 6, heads, kv_heads, head_dim, page, 900)
+    status, out = call(lib, "mlr_attention_decode_static", case, heads, kv_heads, head_dim, page, chunk, 4)
+    assert status == 0
+    want = reference(case, heads, kv_heads, head_dim, page)
+    error = (out.float().cpu() - want).norm(dim=-1) / want.norm(dim=-1)
+    assert float(error.max()) <= 2e-2
