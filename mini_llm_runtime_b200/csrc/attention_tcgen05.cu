@@ -93,29 +93,6 @@ __device__ __forceinline__ float fa_exp2(float x) {
   return y;
 }
 
-// 2^x for x <= 0 on the multiply-add pipes, for part of the exponentials, should the special-function
-// unit (8 cycles per warp and exponential) ever bound the kernel.  Measured with every second
-// exponential emulated: slower (2,048 rows: 62.5 -> 70 us), the kernel is bound by its instruction
-// stream, not by that unit; so it is off.  x is split
-// into an integer n (rounded to nearest by adding 1.5 * 2^23) and f in [-0.5, 0.5]; 2^f is a
-// degree-4 polynomial (relative error below 5e-5, far inside bfloat16's 4e-3); n goes into the
-// exponent field.  Arguments below -126 are clamped: the result is then 2^-126, which stands for 0.
-#ifndef FA_POLY_EVERY
-#define FA_POLY_EVERY 0      // 0: none, 1: all, 2: every second exponential of a row
-#endif
-__device__ __forceinline__ float fa_exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float magic = 12582912.f;                       // 1.5 * 2^23
-  const float shifted = x + magic;                      // integer part of x in the low mantissa bits
-  const float n = shifted - magic;
-  const float f = x - n;
-  float p = fmaf(f, 0.00961813f, 0.05550411f);
-  p = fmaf(f, p, 0.24022651f);
-  p = fmaf(f, p, 0.69314718f);
-  p = fmaf(f, p, 1.f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(shifted) << 23));
-}
-
 // Bounded wait that remembers a failure: after the first wait that ran out, later waits return at once.
 __device__ __forceinline__ void fa_wait(uint64_t* bar, uint32_t parity, int* error_word, int code, bool& gave_up) {
   if (!gave_up) gave_up = !mbar_wait(bar, parity, error_word, code);
@@ -326,7 +303,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float x = fmaf(s[c + e], scale_log2, -base);
-            s[c + e] = (FA_POLY_EVERY != 0 && e % (FA_POLY_EVERY == 0 ? 1 : FA_POLY_EVERY) == 0) ? fa_exp2_poly(x) : fa_exp2(x);
+            s[c + e] = fa_exp2(x);
             part_sum[e] += s[c + e];
           }
         }
@@ -483,9 +460,8 @@ using namespace mlr;
 
 MLR_DEFINE_PDL_SWITCH
 
-// Units of work aimed at per resident CTA when items are cut into parts (for measurements).
-static int units_per_cta = 2;
-MLR_EXPORT void mlr_attention_prefill_tcgen05_tune(int units) { units_per_cta = units < 1 ? 1 : units; }
+// Units of work aimed at per resident CTA when items are cut into parts.
+static const int units_per_cta = 2;
 
 // Prompt portions, head_dim 64, page_size a power of two >= 8.  q, out: [q_rows, heads * 64]
 // bfloat16; pools [pool_pages, kv_heads, page_size, 64]; tile_seg / tile_row0: tiles of up to 128 rows

@@ -447,6 +447,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
+
 // ---------------------------------------------------------------- host side
 template <int BN, bool SWAP, bool SWIGLU>
 static int launch(const void* x, const void* w, const GemmParams& p, int splits, cudaStream_t stream) {
@@ -554,8 +555,12 @@ using namespace mlr;
 
 MLR_DEFINE_PDL_SWITCH
 
-MLR_EXPORT void mlr_gemm_tcgen05_tune(int bn, int stages) { forced_bn = bn; forced_stages = stages; }
-MLR_EXPORT void mlr_gemm_tcgen05_tune_splits(int splits) { forced_splits = splits; }
+// For measurements only (the engine never calls it): overrides of the planner; 0 leaves a choice to it.
+MLR_EXPORT void mlr_gemm_tcgen05_debug(int bn, int stages, int splits) {
+  forced_bn = bn;
+  forced_stages = stages;
+  forced_splits = splits;
+}
 
 // Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
 // `splits_out` receives the split count the launcher will use, `tiles_out` the number of tiles.

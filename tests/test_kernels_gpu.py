@@ -140,6 +140,37 @@ def test_linear(dtype, m, n, k):
     assert_close(got32, x.double() @ w.double().T, torch.float32 if dtype == torch.float32 else dtype, "linear f32 out")
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 4864, 896), (1500, 2500, 200), (129, 151936 // 4, 72), (2048, 1216, 136),
+                                   (3000, 1290, 4864)])
+def test_many_row_products(m, n, k, tcgen05_only):
+    """Prompt-sized products: more output tiles than SMs, tails in M, N and K, 128- and 256-wide
+    tiles, with bias and with float32 output."""
+    x = rnd((m, k), torch.bfloat16, 140 + m % 7)
+    w = rnd((n, k), torch.bfloat16, 141, 0.1)
+    b = rnd((n,), torch.bfloat16, 142)
+    xd, wd, bd = x.to(DEVICE), w.to(DEVICE), b.to(DEVICE)
+    want = x.double() @ w.double().T
+    got = cuda().linear(xd, wd, bd)
+    got32 = cuda().linear(xd, wd, None, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    assert_close(got, want + b.double(), torch.bfloat16, f"many rows {m}x{n}x{k}")
+    assert float((got32.double().cpu() - want).abs().max()) <= 1e-4 * float(want.abs().max()) + 1e-5
+
+
+@pytest.mark.parametrize("m,inner,k", [(2048, 4864, 896), (777, 1216, 200), (1300, 2560, 4864)])
+def test_many_row_swiglu(m, inner, k, tcgen05_only):
+    x = rnd((m, k), torch.bfloat16, 150)
+    gate = rnd((inner, k), torch.bfloat16, 151, 0.1)
+    up = rnd((inner, k), torch.bfloat16, 152, 0.1)
+    weight = torch.cat([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k)
+    want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
+    got = cuda().linear_swiglu(x.to(DEVICE), weight.to(DEVICE), 64)
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    assert_close(got, want, torch.bfloat16, f"many-row fused linear+swiglu {m}x{inner}x{k}")
+
+
 @pytest.mark.parametrize("m", [1, 8, 16, 17, 33, 64, 100, 128, 129, 300])
 @pytest.mark.parametrize("n,k", [(896, 896), (1152, 896), (200, 72), (896, 4864), (130, 64), (4000, 136)])
 def test_tensor_core_linear(m, n, k, tcgen05_only):
