@@ -23,13 +23,17 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: how the parts are arranged (``block``) and which parts they are."""
+    """One block: how the parts are arranged (``block``) and which parts they are.  Every block has
+    a mixer, a feed-forward and a norm before each; an arrangement that needs more (norms after the
+    mixer and the feed-forward, a gate, a second feed-forward) names them in ``extra_parts`` as
+    (name, category, spec) and finds them built in ``Block.extras[name]``."""
 
     block: str
     mixer: PartSpec
     feed_forward: PartSpec
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec
+    extra_parts: tuple[tuple[str, str, PartSpec], ...] = ()
 
 
 @dataclass(frozen=True)

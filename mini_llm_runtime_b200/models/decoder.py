@@ -27,11 +27,14 @@ class DecoderModel:
         self.blocks: list[Block] = []
         for layer in spec.layers:
             block_cls = part_factory("block", layer.block)
+            extras = {name: build_part(category, part_spec, compute_dtype)
+                      for name, category, part_spec in layer.extra_parts}
             self.blocks.append(block_cls(
                 build_part("mixer", layer.mixer, compute_dtype),
                 build_part("feed_forward", layer.feed_forward, compute_dtype),
                 build_part("norm", layer.mixer_norm, compute_dtype),
                 build_part("norm", layer.feed_forward_norm, compute_dtype),
+                **({"extras": extras} if extras else {}),
             ))
         self.final_norm = build_part("norm", spec.final_norm, compute_dtype)
         self.head = build_part("head", spec.head, compute_dtype)

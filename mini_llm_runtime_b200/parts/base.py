@@ -190,14 +190,16 @@ class Block:
 
     category = "block"
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm,
+                 extras: Mapping[str, Part] | None = None):
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
         self.feed_forward_norm = feed_forward_norm
+        self.extras = dict(extras or {})      # further parts the layer's spec names (``LayerSpec.extra_parts``)
 
     def parts(self) -> tuple[Part, ...]:
-        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, *self.extras.values())
 
     def finish_load(self, compute_dtype: torch.dtype) -> None:
         """Called once all four parts hold their tensors; an arrangement may fuse across them."""

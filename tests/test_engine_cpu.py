@@ -346,3 +346,66 @@ def test_a_step_that_fails_after_a_stateful_mixer_ran_leaves_its_state_as_it_was
                      torch.float32, "toy after a failed step")
     finally:
         unregister_architecture("ToyForCausalLM")
+
+
+def test_a_block_arrangement_with_further_parts_is_registered_from_outside():
+    """A "sandwich" arrangement defined here: a norm after the mixer and after the feed-forward as
+    well as before them.  The two further norms are named in the layer's spec, built by the model
+    like any other part, checked by the loader by their tensor names, and found by the block."""
+    from mini_llm_runtime_b200.config import LayerSpec, ModelSpec, PartSpec, RunStep
+    from mini_llm_runtime_b200.parts import register_part
+    from mini_llm_runtime_b200.parts.base import Block, unregister_part
+
+    class Sandwich(Block):
+        def forward(self, residual, pending, ctx, view, writes_cache):
+            kernels = ops.current()
+            if pending is not None:
+                residual = kernels.add_inplace(residual, pending)
+            mixed = self.mixer.forward(self.mixer_norm.forward(residual), ctx, view, writes_cache)
+            residual = kernels.add_inplace(residual, self.extras["after_mixer"].forward(mixed))
+            fed = self.feed_forward.forward(self.feed_forward_norm.forward(residual), ctx)
+            return residual, self.extras["after_feed_forward"].forward(fed)
+
+    register_part("block", "toy_sandwich", Sandwich, replace=True)
+    try:
+        h, vocab = 48, 61
+        norm = {"size": h, "eps": 1e-5}
+        attention = PartSpec("gqa_attention", {"hidden_size": h, "num_heads": 3, "num_kv_heads": 1, "head_dim": 16,
+                                               "qkv_bias": True, "out_bias": False, "window": None,
+                                               "position": PartSpec("rope_half", {"head_dim": 16, "theta": 1e4})},
+                             "model.layers.0.self_attn.")
+        layer = LayerSpec("toy_sandwich", attention,
+                          PartSpec("swiglu", {"hidden_size": h, "intermediate_size": 80}, "model.layers.0.mlp."),
+                          PartSpec("rms_norm", norm, "model.layers.0.input_layernorm."),
+                          PartSpec("rms_norm", norm, "model.layers.0.post_attention_layernorm."),
+                          extra_parts=(("after_mixer", "norm", PartSpec("rms_norm", norm, "model.layers.0.after_mixer.")),
+                                       ("after_feed_forward", "norm", PartSpec("rms_norm", norm, "model.layers.0.after_ffn."))))
+        sizes = {"vocab_size": vocab, "hidden_size": h}
+        spec = ModelSpec("ToySandwich", vocab, h, 128, PartSpec("token_embedding", sizes, "model.embed_tokens."),
+                         (layer,), (RunStep(0, 0),), PartSpec("rms_norm", norm, "model.norm."),
+                         PartSpec("tied_head", {**sizes, "tied_to": "model.embed_tokens.weight"}, "lm_head."))
+        from mini_llm_runtime_b200.models import DecoderModel
+        model = DecoderModel(spec, torch.float32)
+        assert "model.layers.0.after_mixer.weight" in model.expected_tensors()
+        tensors = random_tensors(model.expected_tensors(), 8, torch.float32)
+        model.load(tensors, "cpu")
+        cache = CacheManager(model.cache_needs(), page_size=8, num_pages=8, max_requests=2, max_tokens_per_request=64,
+                             dtype=torch.float32, device="cpu")
+        runner = ModelRunner(model, cache)
+        tokens = random_prompt(vocab, 23, 4)
+        cache.create_request("s")
+        got = torch.cat([runner.step([StepEntry("s", tokens[:10], list(range(10)))]),
+                         runner.step([StepEntry("s", tokens[10:], list(range(13)))])])
+        # the same, plainly
+        cfg = {"num_attention_heads": 3, "num_key_value_heads": 1, "hidden_size": h, "head_dim": 16, "rope_theta": 1e4}
+        t = {k: v.float() for k, v in tensors.items()}
+        x = t["model.embed_tokens.weight"][torch.tensor(tokens)]
+        p = "model.layers.0"
+        mixed = plain.attention_block(plain.rms_norm(x, t[p + ".input_layernorm.weight"], 1e-5), torch.arange(23), t, p, cfg)
+        x = x + plain.rms_norm(mixed, t[p + ".after_mixer.weight"], 1e-5)
+        fed = plain.swiglu_mlp(plain.rms_norm(x, t[p + ".post_attention_layernorm.weight"], 1e-5), t, p)
+        x = x + plain.rms_norm(fed, t[p + ".after_ffn.weight"], 1e-5)
+        want = plain.rms_norm(x, t["model.norm.weight"], 1e-5) @ t["model.embed_tokens.weight"].T
+        assert_close(got, want, torch.float32, "sandwich block")
+    finally:
+        unregister_part("block", "toy_sandwich")
