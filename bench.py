@@ -11,7 +11,8 @@ same line carries: the same metric through the Python entry point with host toke
 (``e2e``), a 2,048-token prefill, decode at batch 1 and 64, the fraction of the measured roofline
 each reaches, and (unless ``--skip-sizes``) points for the 7B and 14B layer sizes: decode at batch
 1 / 8 / 64, prefill, a mixed step of 8 decodes beside a 512-token prompt portion (7B), and a
-continuous-batching run of 64 requests (14B).  One JSON line is printed.
+continuous-batching run of 64 requests (14B); decode at contexts of 16k and 32k tokens and an 8k
+prompt in 2,048-token portions (0.5B and 7B).  One JSON line is printed.
 
 A step is one decode step of the whole batch.  Requests start from a prefix chosen so that the
 timed steps are centred on a context of 3,072 tokens (a 2,048-token prefix growing to 4,096).
@@ -67,6 +68,8 @@ def parse_args():
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--skip-sizes", action="store_true", help="skip the points at the 7B and 14B layer sizes")
+    parser.add_argument("--skip-long", action="store_true",
+                        help="skip decode at contexts of 16k and 32k tokens and the 8k prompt in portions")
     parser.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profiling)")
     parser.add_argument("--no-arena", action="store_true",
                         help="place the weights without first touching one block of their total size (A/B)")
@@ -330,6 +333,54 @@ def time_prefill(bench, repeats=REPEATS, warmup=3):
     return ms, flops, samples
 
 
+def time_portioned_prefill(bench, total=8192, portion=PREFILL_TOKENS, repeats=3, warmup=1):
+    """A prompt of ``total`` tokens fed in portions of ``portion`` (each attends to the cached ones
+    before it); returns the median time of the whole prompt and its flops."""
+    import torch
+
+    from mini_llm_runtime_b200.engine import StepEntry
+
+    runner = bench.runner(2, total)
+    tokens = random_tokens(total, bench.config.vocab_size, 98)
+    samples = []
+    for attempt in range(warmup + repeats):
+        runner.cache.create_request("p")
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for first in range(0, total, portion):
+            last = first + portion >= total
+            runner.step([StepEntry("p", tokens[first:first + portion], [portion - 1] if last else [])])
+        end.record()
+        torch.cuda.synchronize()
+        runner.cache.release("p")
+        if attempt >= warmup:
+            samples.append(start.elapsed_time(end))
+    runner.check_device()
+    del runner
+    torch.cuda.empty_cache()
+    flops = total * bench.numbers["linear_flops_per_token"] + bench.numbers["head_flops_per_row"] \
+        + sum(bench.numbers["attention_flops"](min(portion, total - first), first) for first in range(0, total, portion))
+    return statistics.median(samples), flops
+
+
+def long_context_points(bench, peak, record, prefix):
+    """Decode at batch 8 with contexts of 16k and 32k tokens, and an 8k prompt in 2,048-token portions."""
+    detail = {}
+    for context in (16384, 32768):
+        point = decode_point(bench, 8, 8, 3, 3, context_mean=context - 64, real_prefill=False)
+        achieved = point["step_bytes"] / (point["ms_per_step"] / 1e3) / 1e9
+        name = f"{prefix}decode_b8_ctx{context // 1024}k"
+        record["points"][name] = round(point["tokens_per_s"], 1)
+        record["points"][name + "_hbm_frac"] = round(achieved / peak["hbm_gbs"], 4)
+        detail[name] = {"ms": round(point["ms_per_step"], 3), "gb_per_step": round(point["step_bytes"] / 1e9, 2)}
+    ms, flops = time_portioned_prefill(bench)
+    record["points"][f"{prefix}prefill_8k_in_2k_portions"] = round(8192 / (ms / 1e3), 1)
+    record["points"][f"{prefix}prefill_8k_in_2k_portions_frac"] = round(flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)
+    detail[f"{prefix}prefill_8k"] = {"ms": round(ms, 3)}
+    return detail
+
+
 def time_mixed_step(bench, peak, decodes=8, portion=512, context=CONTEXT_MEAN, repeats=REPEATS, warmup=3):
     """One step of ``decodes`` decoded tokens (context ``context``) beside a ``portion``-token piece
     of a longer prompt that already has tokens cached."""
@@ -480,6 +531,8 @@ def size_points(size, args, peak, record):
     if size == "7b":
         detail["mixed_8_decodes_512_portion"] = time_mixed_step(bench, peak)
         record["points"]["7b_mixed_step_ms"] = detail["mixed_8_decodes_512_portion"]["ms"]
+        if not args.skip_long:
+            detail["long_contexts"] = long_context_points(bench, peak, record, "7b_")
     if size == "14b":
         detail["continuous_64_requests"] = continuous_batching(bench)
         record["points"]["14b_continuous_tokens_per_s"] = detail["continuous_64_requests"]["tokens_per_s"]
@@ -526,6 +579,8 @@ def run_ours(args):
                 record["points"][f"decode_b{batch}"] = round(point["tokens_per_s"], 1)
                 record["points"][f"decode_b{batch}_hbm_frac"] = round(
                     point["step_bytes"] / (point["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4)
+        if not args.skip_long and small:
+            record["long_contexts"] = long_context_points(bench, peak, record, "")
         if not args.skip_e2e:
             e2e, h2d, d2h, samples = time_e2e(bench, args.batch, args.steps, args.warmup, args.repeats)
             record["e2e"] = {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,

@@ -449,6 +449,7 @@ class CudaOps:
     SKINNY_ROWS = 16
     SKINNY_ROWS_SMALL_WEIGHT = 32     # rows up to which matrices of at most SKINNY_SMALL_WEIGHT elements stay with it
     SKINNY_SMALL_WEIGHT = 2 << 20
+    SKINNY_LARGE_WEIGHT = 32 << 20    # elements from which 9..16 rows go to the tcgen05 kernel
     TMA_MIN_CHUNK = 256               # keys per CTA of the bulk-copy decode attention, at least
     TMA_CTAS_PER_SM = 3               # its CTAs that are resident at once on one SM
 
@@ -461,6 +462,11 @@ class CudaOps:
         # a weight with a 128-row tile for every SM keeps the tcgen05 kernel's tensor-memory tiles busy
         if (not self.use_skinny or weight.shape[0] >= 128 * self.sm_count(x.device)
                 or (swiglu and x.shape[1] > 2048)):
+            return False
+        # More than 8 rows double this kernel's token blocks; on matrices of tens of megabytes it then
+        # loses to the tcgen05 kernel even with the separate norm and add kernels that path needs
+        # (7B down projection, 16 rows: 38.4 against 27.4 + 3 us; q|k|v and output projection stay).
+        if rows > 8 and weight.shape[0] * weight.shape[1] >= self.SKINNY_LARGE_WEIGHT:
             return False
         if rows <= self.SKINNY_ROWS:
             return True
