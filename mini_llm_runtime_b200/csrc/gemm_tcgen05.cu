@@ -65,6 +65,17 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The same load without the wait, so that several can be in flight; tmem_wait_loads() before the
+// registers are read.
+__device__ __forceinline__ void tmem_issue_load16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 struct GemmParams {
   int M, N, K;
   int k_blocks_per_split;   // 64-wide k blocks each split handles
@@ -370,67 +381,79 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int half = p.N >> 1;
       if (finish) {
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 2; cc += 16) {
+        for (int cc = 0; cc < BN / 2; cc += 32) {
           const int block = cc >> 6, c0 = cc & 63;           // which 128-column group, offset in it
-          uint32_t g[16], u[16];
-          tmem_load16(lane_base + block * 128 + c0, g);
-          tmem_load16(lane_base + block * 128 + 64 + c0, u);
+          uint32_t g[32], u[32];
+          tmem_issue_load16(lane_base + block * 128 + c0, g);
+          tmem_issue_load16(lane_base + block * 128 + c0 + 16, g + 16);
+          tmem_issue_load16(lane_base + block * 128 + 64 + c0, u);
+          tmem_issue_load16(lane_base + block * 128 + 64 + c0 + 16, u + 16);
+          tmem_wait_loads();
           if (m >= p.M) continue;
-          const int n0 = (blockIdx.y * (BN / 128) + block) * 64 + c0;
-          uint32_t packed[8];
 #pragma unroll
-          for (int c = 0; c < 16; c += 2)
-            packed[c >> 1] = [&] {
-              __nv_bfloat162 pair = __floats2bfloat162_rn(silu_times(__uint_as_float(g[c]), __uint_as_float(u[c])),
-                                                          silu_times(__uint_as_float(g[c + 1]), __uint_as_float(u[c + 1])));
-              return *reinterpret_cast<uint32_t*>(&pair);
-            }();
-          if ((half & 7) == 0 && n0 + 16 <= half) {
-            uint4* dst = reinterpret_cast<uint4*>(out_bf16 + (size_t)m * half + n0);
-            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-          } else {
-            const bf16* values = reinterpret_cast<const bf16*>(packed);
-            for (int c = 0; c < 16; ++c)
-              if (n0 + c < half) out_bf16[(size_t)m * half + n0 + c] = values[c];
+          for (int q = 0; q < 32; q += 16) {
+            const int n0 = (blockIdx.y * (BN / 128) + block) * 64 + c0 + q;
+            uint32_t packed[8];
+#pragma unroll
+            for (int c = 0; c < 16; c += 2) {
+              __nv_bfloat162 pair = __floats2bfloat162_rn(
+                  silu_times(__uint_as_float(g[q + c]), __uint_as_float(u[q + c])),
+                  silu_times(__uint_as_float(g[q + c + 1]), __uint_as_float(u[q + c + 1])));
+              packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            if ((half & 7) == 0 && n0 + 16 <= half) {
+              uint4* dst = reinterpret_cast<uint4*>(out_bf16 + (size_t)m * half + n0);
+              dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+              const bf16* values = reinterpret_cast<const bf16*>(packed);
+              for (int c = 0; c < 16; ++c)
+                if (n0 + c < half) out_bf16[(size_t)m * half + n0 + c] = values[c];
+            }
           }
         }
       }
     } else if (finish) {
+      // 64 columns per round: four tensor-memory loads in flight, one wait, then convert and store
+      // (a load and its wait per 16 columns made the epilogue as long as a short main loop)
+      constexpr int ROUND = BN >= 64 ? 64 : BN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
+      for (int c00 = 0; c00 < BN; c00 += ROUND) {
+        float v[ROUND];
         if (reduce) {
-          reduce_partials<BN>(partials, p.splits, c0, row, v);
-        } else {
-          uint32_t r[16];
-          tmem_load16(lane_base + c0, r);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+          for (int q = 0; q < ROUND; q += 16) reduce_partials<BN>(partials, p.splits, c00 + q, row, v + q);
+        } else {
+#pragma unroll
+          for (int q = 0; q < ROUND; q += 16) tmem_issue_load16(lane_base + c00 + q, reinterpret_cast<uint32_t*>(v) + q);
+          tmem_wait_loads();
         }
-        {
-          const int m = a_row0 + row;
-          const int n0 = b_row0 + c0;
-          if (m < p.M && !p.out_f32 && (p.N & 7) == 0 && n0 + 16 <= p.N) {
+        const int m = a_row0 + row;
+        if (m >= p.M) continue;
+#pragma unroll
+        for (int q = 0; q < ROUND; q += 16) {
+          const int n0 = b_row0 + c00 + q;
+          if (n0 >= p.N) break;
+          if (!p.out_f32 && (p.N & 7) == 0 && n0 + 16 <= p.N) {
             uint32_t packed[8];
 #pragma unroll
             for (int c = 0; c < 16; c += 2) {
               const float b0 = p.bias != nullptr ? to_float(p.bias[n0 + c]) : 0.f;
               const float b1 = p.bias != nullptr ? to_float(p.bias[n0 + c + 1]) : 0.f;
-              __nv_bfloat162 pair = __floats2bfloat162_rn(v[c] + b0, v[c + 1] + b1);
+              __nv_bfloat162 pair = __floats2bfloat162_rn(v[q + c] + b0, v[q + c + 1] + b1);
               packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
             uint4* dst = reinterpret_cast<uint4*>(out_bf16 + (size_t)m * p.N + n0);
             dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-          } else if (m < p.M) {
+          } else {
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
               const int n = n0 + c;
               if (n < p.N) {
                 const float b = p.bias != nullptr ? to_float(p.bias[n]) : 0.f;
-                if (p.out_f32) out_f32[(size_t)m * p.N + n] = v[c] + b;
-                else out_bf16[(size_t)m * p.N + n] = __float2bfloat16_rn(v[c] + b);
+                if (p.out_f32) out_f32[(size_t)m * p.N + n] = v[q + c] + b;
+                else out_bf16[(size_t)m * p.N + n] = __float2bfloat16_rn(v[q + c] + b);
               }
             }
           }
@@ -476,22 +499,74 @@ struct GemmPlan { int bn, tiles, splits, stages, kb_per_split; };
 // Overrides for measurements (0 = the planner decides): tile width and ring depth of many-row products.
 static int forced_bn = 0, forced_stages = 0, forced_splits = 0;
 
-static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
-  GemmPlan plan;
-  const int sms = sm_count();
+// Many rows (M > 128): tile width, ring depth and split count by a small model of the kernel,
+// in microseconds.  A CTA costs a fixed 1.5 us (barriers, tensor-memory allocation, first loads)
+// plus its k blocks plus its epilogue (1.5 us per 128 columns).  A k block costs the largest of
+//   the MMAs' time: 0.14 us per 128 columns, times the CTAs sharing the SM's tensor pipe;
+//   the load latency spread over the ring: (0.5 + 0.03 per KB of a stage) / stages
+//     (56 k blocks, one CTA per SM: 4 stages of 32 KB 23.5 us, 4 stages of 48 KB 31.6 us);
+//   the SM's operand bandwidth from L2, about 112 GB/s, shared by its CTAs
+//     (8,192^3 with two CTAs per SM and 48 KB stages: 0.43 us per k block and SM).
+// CTAs per SM follow from shared and tensor memory; a launch takes ceil(CTAs / resident) rounds; with
+// a single CTA per SM nothing hides a CTA's start and end, which costs about 4 us more per round.
+// Checked against: 9728 x 896 at 2,048 rows 45 (measured 44.6); 4608 x 3584 at 520 rows, 128 wide,
+// 4 stages 53 (47), 256 wide 31.7 (31.6); 37888 x 3584 with SwiGLU at 520 rows, two CTAs per SM 176
+// (168), one CTA per SM 178 (180).  It is there to tell a plan with two half-empty rounds from one
+// with a single round, no more.
+static GemmPlan plan_many_rows(int M, int N, int K, bool swiglu, int sms) {
   const int total_kb = (K + TILE_K - 1) / TILE_K;
-  if (M <= 128) {
-    plan.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-    plan.tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
-  } else {
-    // Wide tiles cut the operand traffic per flop by a quarter; worth it once they still fill the
-    // SMs and K is long enough for the main loop, not the epilogue, to set the time.
-    plan.bn = (N >= 256 && total_kb > 16 && ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + 255) / 256) >= sms) ? 256 : 128;
-    if (forced_bn == 128 || (forced_bn == 256 && N >= 256)) plan.bn = forced_bn;
-    plan.tiles = ((M + TILE_ROWS - 1) / TILE_ROWS) * ((N + plan.bn - 1) / plan.bn);
+  const int tiles_m = (M + TILE_ROWS - 1) / TILE_ROWS;
+  GemmPlan best = {128, tiles_m * ((N + 127) / 128), 1, 2, total_kb};
+  double best_cost = 1e30;
+  for (int bn = 128; bn <= 256; bn += 128) {
+    if (bn == 256 && N < 256) continue;
+    if (forced_bn != 0 && forced_bn != bn) continue;
+    const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)bn * TILE_K * 2;
+    const int tiles = tiles_m * ((N + bn - 1) / bn);
+    for (int stages = 2; stages <= MAX_STAGES; ++stages) {
+      const size_t shared = stages * stage_bytes + 2048;
+      if (shared > 225 * 1024) break;
+      if (forced_stages >= 2 && forced_stages != stages) continue;
+      int per_sm = (int)((227 * 1024) / shared);
+      const int by_tensor_memory = 512 / bn;
+      if (per_sm > by_tensor_memory) per_sm = by_tensor_memory;
+      if (per_sm > 3) per_sm = 3;
+      for (int splits = 1; splits <= 4; ++splits) {
+        if (splits > 1 && (swiglu || M > 1024 || total_kb < 8 * splits)) break;   // that epilogue reads tensor memory only
+        if (forced_splits >= 1 && forced_splits != splits) continue;
+        if (splits > 1 && (long long)tiles * splits * bn * TILE_ROWS * 4 > (24ll << 20)) break;
+        const long long ctas = (long long)tiles * splits;
+        const long long resident = (long long)per_sm * sms;
+        const long long rounds = (ctas + resident - 1) / resident;
+        const int sharing = (int)(ctas < resident ? (ctas + sms - 1) / sms : per_sm);   // CTAs that really share an SM
+        const double kb = (double)((total_kb + splits - 1) / splits);
+        const double stage_kb = (double)stage_bytes / 1024.0;
+        double per_kb = 0.14 * (bn / 128) * sharing;                                   // tensor pipe
+        if ((0.5 + 0.03 * stage_kb) / stages > per_kb) per_kb = (0.5 + 0.03 * stage_kb) / stages;   // load latency
+        if (sharing * stage_kb / 112.0 > per_kb) per_kb = sharing * stage_kb / 112.0;  // operand bandwidth of the SM
+        double cost = rounds * (1.5 + kb * per_kb + 1.5 * (bn / 128) + ((per_sm == 1 && rounds > 1) ? 4.0 : 0.0));
+        if (splits > 1) cost += 4.0 + (double)splits * bn * 512.0 / 50e3;
+        if (cost < best_cost) {
+          best_cost = cost;
+          best.bn = bn; best.tiles = tiles; best.splits = splits; best.stages = stages;
+        }
+      }
+    }
   }
+  best.kb_per_split = (total_kb + best.splits - 1) / best.splits;
+  best.splits = (total_kb + best.kb_per_split - 1) / best.kb_per_split;      // no empty split
+  return best;
+}
+
+static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
+  const int sms = sm_count();
+  if (M > 128) return plan_many_rows(M, N, K, swiglu, sms);
+  GemmPlan plan;
+  const int total_kb = (K + TILE_K - 1) / TILE_K;
+  plan.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  plan.tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
   int splits = 1;
-  if (M <= 128) {
+  {
     // Few tiles cannot keep every SM streaming weights, so K is cut; but the CTA that arrives last
     // for a tile re-reads every split's partial tile (splits x bn x 512 bytes), which soon costs
     // more than the streaming saves when there are many token rows.  Estimate both and take the
@@ -514,35 +589,19 @@ static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
       if (cost < best) { best = cost; splits = candidate; }
     }
   }
-  if (M > 128 && M <= 1024 && plan.tiles < sms && total_kb >= 32 && !swiglu) {   // (that epilogue reads tensor memory only)
-    // A prompt portion of a few hundred rows times a long K has too few tiles for the SMs: cut K.
-    // Measured 896 x 4864: 512 rows 29.1 -> 19.4 us with 4 splits, 1,024 rows 30.2 -> 24.8 us with 2;
-    // at 2,048 rows (112 tiles) the reduction costs more than it saves (31 -> 39 us).
-    splits = sms / plan.tiles;          // one CTA per SM: more splits only add to the reduction
-    if (splits > 4) splits = 4;
-    if (splits < 1) splits = 1;
-    while (splits > 1 && (long long)plan.tiles * splits * plan.bn * TILE_ROWS * 4 > (24ll << 20)) --splits;
-  }
-  if (forced_splits >= 1 && forced_splits <= 16 && forced_splits <= total_kb && !(swiglu && M > 128)) splits = forced_splits;
+  if (forced_splits >= 1 && forced_splits <= 16 && forced_splits <= total_kb) splits = forced_splits;
   plan.kb_per_split = (total_kb + splits - 1) / splits;
   plan.splits = (total_kb + plan.kb_per_split - 1) / plan.kb_per_split;   // no empty split
   // A ring as deep as the split is long (at most 6 stages) leaves room for several CTAs per SM,
   // so that one CTA's prologue and epilogue overlap another's streaming.
   int stages = plan.kb_per_split < 2 ? 2 : (plan.kb_per_split > 6 ? 6 : plan.kb_per_split);
-  // Many-row products: operands come from L2 and a CTA's epilogue (tensor memory -> registers ->
-  // global) is long, so what counts is that two or three CTAs share an SM and one's epilogue runs
-  // under another's main loop.  Two stages (96 KB at 256 columns, 64 KB at 128) allow that; only
-  // narrow tiles with a long K, which are too few to share SMs anyway, take a deeper ring.
-  // Measured at 2048 rows: 9728x896 with SwiGLU 75 -> 45 us, 37888x3584 628 -> 454 us, 8192^3 877 -> 791 us.
-  if (M > 128) stages = (plan.bn == 128 && total_kb > 16) ? 4 : 2;
   // Few rows but more CTAs than SMs (the head's matrix): keep the ring within 110 KB so that two
   // CTAs share an SM and one's epilogue runs while the other streams (measured on 151936 x 896 at
   // 64 rows: 86 us with one CTA per SM, 64 us with two).
   const size_t few_rows_stage = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
-  if (M <= 128 && forced_stages >= 2) stages = forced_stages <= MAX_STAGES ? forced_stages : MAX_STAGES;
-  else if (M <= 128 && plan.tiles * plan.splits > sms)
+  if (forced_stages >= 2) stages = forced_stages <= MAX_STAGES ? forced_stages : MAX_STAGES;
+  else if (plan.tiles * plan.splits > sms)
     while (stages > 2 && stages * few_rows_stage > 110 * 1024) --stages;
-  if (M > 128 && forced_stages >= 2 && forced_stages <= MAX_STAGES) stages = forced_stages;
   const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)plan.bn * TILE_K * 2;
   while (stages > 2 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
   plan.stages = stages;

@@ -204,7 +204,12 @@ class ModelRunner:
         self.use_graphs = (self.device.type == "cuda"
                            and all(getattr(part, "graph_safe", False) for part in model.parts()))
         self.graph_max_batch = 256
+        # A batch size is captured once it has come up this many times: capturing costs tens of
+        # milliseconds, which a size that passes by once (requests finishing one after another)
+        # never earns back.
+        self.graph_capture_after = 3
         self._graphs: dict[tuple[int, bool, bool], _CapturedStep] = {}
+        self._graph_seen: dict[tuple[int, bool, bool], int] = {}
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ metadata
@@ -390,10 +395,17 @@ class ModelRunner:
             kernels.advance_slots(ctx.seg_slot, state, ctx.seg_q_len, ctx.seg_pos0)
         return logits, tokens
 
-    def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
-        return (self.use_graphs and len(entries) <= self.graph_max_batch
+    def _graph_eligible(self, entries: Sequence[StepEntry], sample: bool, feed: bool) -> bool:
+        if not (self.use_graphs and len(entries) <= self.graph_max_batch
                 and isinstance(ops.current(), ops.CudaOps)
-                and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
+                and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)):
+            return False
+        key = (len(entries), sample, feed)
+        if key in self._graphs:
+            return True
+        seen = self._graph_seen.get(key, 0) + 1
+        self._graph_seen[key] = seen
+        return seen >= self.graph_capture_after
 
     def _prepare_decode(self, ctx: StepContext, feed: bool) -> None:
         """Positions, cache places and (with ``feed``) input tokens of a decode step, derived on the
@@ -503,7 +515,7 @@ class ModelRunner:
             raise ValueError("sampling takes at most one wanted place per request")
         requests = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
         try:
-            if self._graph_eligible(entries):
+            if self._graph_eligible(entries, sample, feed):
                 logits, tokens = self._graph_step(entries, requests, sample, feed)
                 if not borrow:
                     logits = logits.clone()

@@ -66,6 +66,7 @@ class TinyEngine:
                                   max_requests=max_requests, max_tokens_per_request=max_tokens,
                                   dtype=dtype, device=device, max_step_tokens=max_step_tokens)
         self.runner = ModelRunner(self.model, self.cache)
+        self.runner.graph_capture_after = 1          # tests want the captured step from the first recurrence on
 
     def plain_logits(self, tokens) -> torch.Tensor:
         return plain.forward_logits(self.tensors, self.config_dict, tokens)

@@ -168,3 +168,27 @@ def test_decode_steps_replay_a_captured_graph(setup):
     results = replay(fresh, prompts, steps)
     assert fresh.runner.graph_replays >= 18
     check_all(fresh, prompts, results, dtype, "graph replay")
+
+
+def test_a_batch_size_is_captured_only_once_it_recurs(setup):
+    """Capturing costs far more than one step, so a batch size that passes by (requests ending one
+    after another) runs eagerly; the size that stays is captured at its third step.  The logits are
+    the plain implementation's either way."""
+    name, dtype, engine, requests = setup
+    config, page = TINY[name]
+    fresh = TinyEngine(config, page, dtype, DEVICE, num_pages=64, max_requests=4, max_tokens=256,
+                       tensors=engine.tensors)
+    fresh.runner.graph_capture_after = 3
+    texts = {rid: random_prompt(config.vocab_size, n, 190 + n) for rid, n in (("u", 31), ("v", 22), ("w", 18))}
+    # three live for two steps, two for two more, then "u" alone for six
+    decoded = {"u": 10, "v": 2, "w": 4}
+    prompts = {rid: text[:len(text) - 10 + decoded[rid]] for rid, text in texts.items()}
+    steps = [{"entries": [(rid, 0, len(texts[rid]) - 10) for rid in texts], "end": []}]
+    for k in range(10):
+        live = [rid for rid in texts if k < decoded[rid]]
+        steps.append({"entries": [(rid, len(texts[rid]) - 10 + k, len(texts[rid]) - 9 + k) for rid in live],
+                      "end": [rid for rid in live if k == decoded[rid] - 1]})
+    results = replay(fresh, prompts, steps)
+    assert sorted(fresh.runner._graphs) == [(1, False, False)]
+    assert fresh.runner.graph_replays == 3          # of six steps: two eager, one captured, three replayed
+    check_all(fresh, prompts, results, dtype, "captured late")

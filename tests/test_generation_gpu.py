@@ -182,3 +182,58 @@ def test_toy_parts_on_the_device(dtype):
                 assert float(rel.median()) <= 2e-2 and float((rel <= 4e-2).float().mean()) >= 0.8, rel
     finally:
         unregister_architecture("ToyForCausalLM")
+
+
+def test_stepping_ahead_with_events_in_bfloat16():
+    """bfloat16, ``step_ahead`` on, and everything that changes the batches while steps are in
+    flight: a sampled request, a stop token in mid-flight, a late arrival that prefills in portions
+    beside the decodes.  A bfloat16 row may round differently in another batch, so the engine is
+    not compared with its step-by-step twin but with the plain implementation: greedy requests up
+    to the first step whose margin rounding could flip, the sampled request as long as its uniform
+    number stays clear of a boundary of the cumulative distribution."""
+    config, page = TINY["D"]
+    model = build_model(config, torch.bfloat16)
+    tensors = random_tensors(model.expected_tensors(), 43)
+    model.load(tensors, DEVICE)
+    cfg = config.to_dict()
+    prompts = {rid: random_prompt(config.vocab_size, n, 900 + n) for rid, n in (("a", 5), ("b", 33), ("c", 70), ("late", 90))}
+    want_c, gaps_c = greedy_with_margin(tensors, cfg, prompts["c"], 30)
+    sure_c = next((k for k, gap in enumerate(gaps_c) if gap < 2e-2), len(gaps_c))
+    assert sure_c >= 4, "the scenario needs a few sure steps to place a stop token in"
+    stop_at = min(sure_c - 1, 6)
+    stop_token = want_c[stop_at]
+    if stop_token in want_c[:stop_at]:
+        stop_at = want_c.index(stop_token)
+    engine = ContinuousBatchEngine.from_model(model, block_size=page, max_running_requests=4, max_batch_tokens=32,
+                                              max_model_len=256, step_ahead=True)
+    engine.submit("a", prompts["a"], max_new_tokens=40)
+    engine.submit("b", prompts["b"], max_new_tokens=25, temperature=0.7, seed=11)
+    engine.submit("c", prompts["c"], max_new_tokens=30, eos_token_ids=[stop_token])
+    steps = 0
+    while engine.scheduler.has_unfinished_requests:
+        if steps == 9:
+            engine.submit("late", prompts["late"], max_new_tokens=12)
+        engine.step()
+        steps += 1
+        engine.manager.check_consistency()
+    assert not engine.manager.requests and engine.runner.graph_replays > 0
+    got = {rid: list(engine.scheduler.get_request(rid).generated_token_ids) for rid in prompts}
+    # the stop token ended c where the plain implementation says, and nothing came after it
+    assert got["c"] == want_c[:stop_at + 1]
+    assert engine.scheduler.get_request("c").finish_reason.value == "eos"
+    for rid, count in (("a", 40), ("late", 12)):
+        want, gaps = greedy_with_margin(tensors, cfg, prompts[rid], count)
+        sure = next((k for k, gap in enumerate(gaps) if gap < 2e-2), len(gaps))
+        assert len(got[rid]) == count and got[rid][:sure] == want[:sure], (rid, got[rid], want, gaps)
+    # the sampled request: the plain sampler on the plain logits, while u is clear of a boundary
+    assert len(got["b"]) == 25
+    sequence = list(prompts["b"])
+    for index, token in enumerate(got["b"]):
+        logits = plain.forward_logits(tensors, cfg, sequence)[-1]
+        u = plain.uniform_from_seed(11, index)
+        expected, cdf = plain.temperature_sample(logits, 0.7, u)
+        low = float(cdf[expected - 1]) if expected > 0 else 0.0
+        if min(u - low, float(cdf[expected]) - u) < 2e-2:
+            break                                   # too close to call in bfloat16
+        assert token == expected, (index, token, expected)
+        sequence.append(token)
