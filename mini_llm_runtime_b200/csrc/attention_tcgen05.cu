@@ -1,20 +1,27 @@
 // Causal attention of prompt portions over the paged bfloat16 K/V cache on the 5th-generation
-// tensor cores (head_dim 64): S = Q K^T and P V run as tcgen05.mma with their results in tensor
-// memory; the online softmax runs on the CUDA cores, one thread per query row.
+// tensor cores (head_dim 64 or 128): S = Q K^T and O += P V run as tcgen05.mma with their results
+// in tensor memory; the online softmax runs on the CUDA cores, one thread per query row.
 //
 // One work item is 128 query rows of one head.  A CTA has five warps:
 //   warps 0..3  softmax: thread r owns query row r (tensor-memory lane r).  Per 64-key tile it reads
 //               its row of S from tensor memory (64 values), masks (causal limit, window, rows past
-//               the portion), keeps the running max and sum, writes the probabilities as bfloat16
-//               into a 128-byte-swizzled tile in shared memory (the A operand of P V; two buffers),
-//               and only then reads the previous tile's P V from tensor memory (two buffers) and adds
-//               it to its output row in registers, times the factor by which the max moved: the MMA
-//               runs under the next tile's exponentials.  No shuffles: a row lives in one thread.
-//   warp 4      loads and issues: Q by one bulk tensor copy per item, K and V page by page (one
-//               copy per page and kv head, as in the other attention kernels) into a ring of
-//               stages; one lane issues the MMAs: S_{j+1} = Q K_{j+1}^T goes out before the warp
-//               waits for tile j's probabilities (two S buffers), then P_j V_j.  K is the K-major B
-//               operand; V ([keys][head_dim], head_dim contiguous) is the MN-major B operand.
+//               the portion), keeps the running max and sum, and writes the probabilities as
+//               bfloat16 into a 128-byte-swizzled tile in shared memory (the A operand of P V).
+//               The output row stays in tensor memory, where the MMAs of all key tiles accumulate
+//               into it.  It is relative to a base exponent that follows the running max lazily:
+//               only when the max has moved by more than 2^8 since the base was set does the warp
+//               read its output rows, scale them and write them back (sum, probabilities and
+//               output always use the same base, so the result is exact either way).  On most
+//               tiles the softmax threads therefore never touch the output.  The arithmetic uses
+//               the paired float32 instructions (two multiply-adds or adds per issue slot) and the
+//               three-input max, because the instruction stream, not a pipe, bounds this loop.
+//               No shuffles: a row lives in one thread.
+//   warp 4      loads and issues: Q by bulk tensor copies per item, K and V page by page (one
+//               copy per page, kv head and 64-wide half of the head, as in the other attention
+//               kernels) into a ring of stages; one lane issues the MMAs: S_{j+1} = Q K_{j+1}^T
+//               goes out before the warp waits for tile j's probabilities (two S buffers), then
+//               O += P_j V_j.  K is the K-major B operand; V ([keys][head_dim], head_dim
+//               contiguous) is the MN-major B operand.
 // Items are drawn heaviest-first from a counter in global memory by the resident CTAs (two per SM,
 // so one CTA's MMAs run under the other's softmax).
 //
@@ -30,13 +37,35 @@ namespace mlr {
 
 constexpr int FA_ROWS = 128;        // query rows per item = MMA M
 constexpr int FA_KEYS = 64;         // keys per tile = MMA N of S, K of P V
-constexpr int FA_D = 64;            // head_dim
-constexpr int FA_STAGES = 3;
 constexpr int FA_SOFTMAX_THREADS = 128;
 constexpr int FA_THREADS = FA_SOFTMAX_THREADS + 32;
-constexpr uint32_t FA_TMEM_COLS = 256;   // S0 | S1 | PV0 | PV1
-constexpr int FA_KV_TILE_BYTES = FA_KEYS * FA_D * 2;       // one K or V tile
-constexpr int FA_Q_BYTES = FA_ROWS * FA_D * 2;
+constexpr uint32_t FA_TMEM_COLS = 256;   // S0 | S1 | O (head_dim columns)
+constexpr uint32_t FA_TMEM_O = 2 * FA_KEYS;
+constexpr int FA_P_BYTES = FA_ROWS * FA_KEYS * 2;          // one tile of probabilities
+constexpr float FA_LAZY = 8.f;      // the base exponent follows the running max in steps of more than this
+
+// Sizes that depend on the head size.  With 128 the shared memory of two resident CTAs only fits
+// with a two-stage ring and one buffer of probabilities.
+template <int D>
+struct FaShape {
+  static constexpr int HALVES = D / 64;                      // 64-wide (128-byte) column blocks of a row
+  static constexpr int STAGES = D == 64 ? 3 : 2;
+  static constexpr int P_BUFFERS = D == 64 ? 2 : 1;
+  static constexpr int Q_BYTES = FA_ROWS * D * 2;
+  static constexpr int Q_HALF_BYTES = FA_ROWS * 128;
+  static constexpr int KV_TILE_BYTES = FA_KEYS * D * 2;      // one K or V tile
+  static constexpr int KV_HALF_BYTES = FA_KEYS * 128;
+  static constexpr int DATA_BYTES = Q_BYTES + P_BUFFERS * FA_P_BYTES + STAGES * 2 * KV_TILE_BYTES;
+};
+
+// Barriers and the few words the warps share; behind the tiles in dynamic shared memory.
+struct FaControl {
+  uint64_t q_full, kv_full[3], kv_empty[3], s_ready[2], s_free[2], p_ready, pv_ready;
+  uint32_t tmem_holder;
+  int item, last;
+};
+constexpr int FA_CONTROL_BYTES = 256;
+static_assert(sizeof(FaControl) <= FA_CONTROL_BYTES, "control block");
 
 // K-major operand, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t fa_desc_k_major(uint32_t address) {
@@ -50,11 +79,11 @@ __device__ __forceinline__ uint64_t fa_desc_k_major(uint32_t address) {
 }
 // MN-major operand, 128-byte swizzle: each row of 128 bytes holds 64 MN-contiguous elements of one
 // k; 8 consecutive k (1024 bytes) form a swizzle atom; atoms along k follow one another (stride
-// 1024 bytes); along MN there is one atom only (leading offset unused, 1024 given).
-__device__ __forceinline__ uint64_t fa_desc_mn_major(uint32_t address) {
+// offset 1024 bytes); the next 64 elements along MN lie `mn_stride` bytes on (leading offset).
+__device__ __forceinline__ uint64_t fa_desc_mn_major(uint32_t address, uint32_t mn_stride) {
   uint64_t desc = 0;
   desc |= (uint64_t)((address & 0x3FFFFu) >> 4);
-  desc |= (uint64_t)(1024 >> 4) << 16;
+  desc |= (uint64_t)(mn_stride >> 4) << 16;
   desc |= (uint64_t)(1024 >> 4) << 32;
   desc |= (uint64_t)1 << 46;
   desc |= (uint64_t)2 << 61;
@@ -82,7 +111,15 @@ __device__ __forceinline__ void fa_tmem_load16(uint32_t taddr, uint32_t* r) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void fa_tmem_store16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void fa_tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fa_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -92,12 +129,32 @@ __device__ __forceinline__ float fa_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 
 // Bounded wait that remembers a failure: after the first wait that ran out, later waits return at once.
 __device__ __forceinline__ void fa_wait(uint64_t* bar, uint32_t parity, int* error_word, int code, bool& gave_up) {
   if (!gave_up) gave_up = !mbar_wait(bar, parity, error_word, code);
 }
 
+// 32 values of one output row, scaled, as bfloat16 to global memory.
+__device__ __forceinline__ void fa_store32(bf16* dst, const float* v, float factor) {
+#pragma unroll
+  for (int chunk = 0; chunk < 4; ++chunk) {
+    uint32_t packed[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat162 pair = __floats2bfloat162_rn(v[chunk * 8 + 2 * e] * factor, v[chunk * 8 + 2 * e + 1] * factor);
+      packed[e] = *reinterpret_cast<uint32_t*>(&pair);
+    }
+    *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
+template <int D>
 __global__ void __launch_bounds__(FA_THREADS, 2)      // two CTAs per SM: at most 204 registers
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                                  const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out,
@@ -107,37 +164,42 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
                                  int table_width, int num_tiles, int heads, int kv_heads, int page_size,
                                  int page_shift, int window, float scale_log2, int* queue, int* error_word,
                                  int max_parts, int tiles_per_unit, float* __restrict__ scratch,
-                                 int* __restrict__ counters) {
+                                 int* __restrict__ counters, int shared_bytes) {
+  using Shape = FaShape<D>;
+  constexpr int STAGES = Shape::STAGES;
   extern __shared__ uint8_t fa_shared_raw[];
   uint8_t* aligned = (uint8_t*)(((uintptr_t)fa_shared_raw + 1023) & ~(uintptr_t)1023);
-  bf16* q_tile = reinterpret_cast<bf16*>(aligned);                                   // [128][64]
-  uint8_t* p_tiles = aligned + FA_Q_BYTES;                                           // 2 x [128][64]
-  uint8_t* kv_ring = aligned + 3 * FA_Q_BYTES;                                       // STAGES x (K, V)
-  __shared__ uint64_t q_full, kv_full[FA_STAGES], kv_empty[FA_STAGES], s_ready[2], s_free[2], p_ready, pv_ready;
-  __shared__ uint32_t tmem_holder;
-  __shared__ int item_shared, last_shared;
+  if (aligned + Shape::DATA_BYTES + FA_CONTROL_BYTES > fa_shared_raw + shared_bytes) {
+    // the launch gave no room for the 1024-byte alignment the swizzled tiles need
+    if (threadIdx.x == 0) atomicCAS(error_word, 0, 0x6f);
+    return;
+  }
+  uint8_t* q_tile = aligned;                                                         // [halves][128][64]
+  uint8_t* p_tiles = aligned + Shape::Q_BYTES;                                       // P_BUFFERS x [128][64]
+  uint8_t* kv_ring = p_tiles + Shape::P_BUFFERS * FA_P_BYTES;                        // STAGES x (K, V), each [halves][64][64]
+  FaControl& ctl = *reinterpret_cast<FaControl*>(kv_ring + STAGES * 2 * Shape::KV_TILE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    mbar_init(&q_full, 1);
-    for (int s = 0; s < FA_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_ready[b], 1); mbar_init(&s_free[b], 4); }
-    mbar_init(&p_ready, 4);
-    mbar_init(&pv_ready, 1);
+    mbar_init(&ctl.q_full, 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl.kv_full[s], 1); mbar_init(&ctl.kv_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&ctl.s_ready[b], 1); mbar_init(&ctl.s_free[b], 4); }
+    mbar_init(&ctl.p_ready, 4);
+    mbar_init(&ctl.pv_ready, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
   }
   if (warp == 4) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_holder)), "r"(FA_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_holder)), "r"(FA_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   fa_fence_before();
   pdl_trigger();
   __syncthreads();
   fa_fence_after();
-  const uint32_t tmem_base = tmem_holder;
+  const uint32_t tmem_base = ctl.tmem_holder;
   pdl_wait();                       // before the first draw from the queue, the first read of q and the first write
 
   const int total_items = num_tiles * heads;
@@ -149,9 +211,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   bool gave_up = false;
 
   for (;;) {
-    if (threadIdx.x == 0) item_shared = atomicAdd(&queue[0], 1);
+    if (threadIdx.x == 0) ctl.item = atomicAdd(&queue[0], 1);
     __syncthreads();
-    const int unit = item_shared;
+    const int unit = ctl.item;
     if (unit >= total_units) break;
     const int part = unit / total_items, item = unit - part * total_items;
     const int tile = item / heads, head = item - tile * heads;
@@ -167,7 +229,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     const int item_begin = lowest / FA_KEYS, item_tiles = last_pos / FA_KEYS - item_begin + 1;
     const int parts = min(max_parts, (item_tiles + tiles_per_unit - 1) / tiles_per_unit);
     if (part >= parts) {
-      __syncthreads();              // item_shared is rewritten by the next draw
+      __syncthreads();              // ctl.item is rewritten by the next draw
       continue;
     }
     const int per_part = (item_tiles + parts - 1) / parts;
@@ -178,70 +240,74 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       // ------------------------------------------------------------ loads and MMAs
       auto issue_load = [&](int j) {
         const unsigned load = tiles_before + (unsigned)j;
-        const int stage = load % FA_STAGES;
-        const unsigned use = load / FA_STAGES;
-        if (use > 0) fa_wait(&kv_empty[stage], (use - 1) & 1u, error_word, 0x61, gave_up);
+        const int stage = load % STAGES;
+        const unsigned use = load / STAGES;
+        if (use > 0) fa_wait(&ctl.kv_empty[stage], (use - 1) & 1u, error_word, 0x61, gave_up);
         gave_up = __any_sync(0xffffffffu, gave_up);
         if (gave_up) return;
-        if (lane == 0) mbar_expect_tx(&kv_full[stage], 2u * FA_KV_TILE_BYTES);
+        if (lane == 0) mbar_expect_tx(&ctl.kv_full[stage], 2u * Shape::KV_TILE_BYTES);
         __syncwarp();
-        if (lane < boxes) {
-          const int key0 = (tile_begin + j) * FA_KEYS + lane * box_rows;
+        if (lane < boxes * Shape::HALVES) {
+          const int box = lane % boxes, half = lane / boxes;
+          const int key0 = (tile_begin + j) * FA_KEYS + box * box_rows;
           const int logical = key0 >> page_shift;
           int page = logical < table_width ? table[logical] : -1;
           int offset = key0 & (page_size - 1);
           if (page < 0) { page = 0; offset = 0; }
           const int y = (page * kv_heads + kv_head) * page_size + offset;
-          uint8_t* k_dst = kv_ring + (size_t)stage * 2 * FA_KV_TILE_BYTES + lane * box_rows * 128;
-          tma_load_2d(&k_map, &kv_full[stage], k_dst, 0, y);
-          tma_load_2d(&v_map, &kv_full[stage], k_dst + FA_KV_TILE_BYTES, 0, y);
+          uint8_t* k_dst = kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES + half * Shape::KV_HALF_BYTES + box * box_rows * 128;
+          tma_load_2d(&k_map, &ctl.kv_full[stage], k_dst, half * 64, y);
+          tma_load_2d(&v_map, &ctl.kv_full[stage], k_dst + Shape::KV_TILE_BYTES, half * 64, y);
         }
       };
       if (lane == 0) {
-        mbar_expect_tx(&q_full, FA_Q_BYTES);
-        tma_load_2d(&q_map, &q_full, q_tile, head * FA_D, q_start + row0);
+        mbar_expect_tx(&ctl.q_full, Shape::Q_BYTES);
+#pragma unroll
+        for (int half = 0; half < Shape::HALVES; ++half)
+          tma_load_2d(&q_map, &ctl.q_full, q_tile + half * Shape::Q_HALF_BYTES, head * D + half * 64, q_start + row0);
       }
-      for (int j = 0; j < FA_STAGES - 1 && j < tiles; ++j) issue_load(j);
+      for (int j = 0; j < STAGES - 1 && j < tiles; ++j) issue_load(j);
 
       constexpr uint32_t idesc_qk = fa_idesc(FA_ROWS, FA_KEYS, false);
-      constexpr uint32_t idesc_pv = fa_idesc(FA_ROWS, FA_D, true);
+      constexpr uint32_t idesc_pv = fa_idesc(FA_ROWS, D, true);
       const uint32_t q_addr = smem_u32(q_tile), p_addr0 = smem_u32(p_tiles);
       auto issue_qk = [&](int j) {
         const unsigned t = tiles_before + (unsigned)j;
-        const int stage = t % FA_STAGES, buffer = t & 1;
-        fa_wait(&kv_full[stage], (t / FA_STAGES) & 1u, error_word, 0x62, gave_up);
-        if (t >= 2) fa_wait(&s_free[buffer], ((t >> 1) - 1) & 1u, error_word, 0x63, gave_up);
+        const int stage = t % STAGES, buffer = t & 1;
+        fa_wait(&ctl.kv_full[stage], (t / STAGES) & 1u, error_word, 0x62, gave_up);
+        if (t >= 2) fa_wait(&ctl.s_free[buffer], ((t >> 1) - 1) & 1u, error_word, 0x63, gave_up);
         gave_up = __any_sync(0xffffffffu, gave_up);
         fa_fence_after();
         if (lane == 0 && !gave_up) {
-          const uint32_t k_addr = smem_u32(kv_ring + (size_t)stage * 2 * FA_KV_TILE_BYTES);
+          const uint32_t k_addr = smem_u32(kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES);
 #pragma unroll
-          for (int k = 0; k < FA_D / 16; ++k)
-            fa_mma(tmem_base + buffer * FA_KEYS, fa_desc_k_major(q_addr + k * 32), fa_desc_k_major(k_addr + k * 32),
-                   idesc_qk, k > 0 ? 1u : 0u);
-          fa_commit(&s_ready[buffer]);
+          for (int k = 0; k < D / 16; ++k)
+            fa_mma(tmem_base + buffer * FA_KEYS,
+                   fa_desc_k_major(q_addr + (k >> 2) * Shape::Q_HALF_BYTES + (k & 3) * 32),
+                   fa_desc_k_major(k_addr + (k >> 2) * Shape::KV_HALF_BYTES + (k & 3) * 32), idesc_qk, k > 0 ? 1u : 0u);
+          fa_commit(&ctl.s_ready[buffer]);
         }
         __syncwarp();
       };
-      fa_wait(&q_full, items_before & 1u, error_word, 0x64, gave_up);
+      fa_wait(&ctl.q_full, items_before & 1u, error_word, 0x64, gave_up);
       issue_qk(0);
       for (int j = 0; j < tiles; ++j) {
-        if (j + FA_STAGES - 1 < tiles) issue_load(j + FA_STAGES - 1);
+        if (j + STAGES - 1 < tiles) issue_load(j + STAGES - 1);
         if (j + 1 < tiles) issue_qk(j + 1);
         const unsigned t = tiles_before + (unsigned)j;
-        const int stage = t % FA_STAGES;
-        fa_wait(&p_ready, t & 1u, error_word, 0x65, gave_up);
+        const int stage = t % STAGES;
+        fa_wait(&ctl.p_ready, t & 1u, error_word, 0x65, gave_up);
         gave_up = __any_sync(0xffffffffu, gave_up);
         fa_fence_after();
         if (lane == 0 && !gave_up) {
-          const uint32_t v_addr = smem_u32(kv_ring + (size_t)stage * 2 * FA_KV_TILE_BYTES + FA_KV_TILE_BYTES);
+          const uint32_t v_addr = smem_u32(kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES + Shape::KV_TILE_BYTES);
+          const uint32_t p_addr = p_addr0 + (Shape::P_BUFFERS == 2 ? (t & 1u) : 0u) * FA_P_BYTES;
 #pragma unroll
-          const uint32_t p_addr = p_addr0 + (t & 1u) * FA_Q_BYTES;
-          for (int k = 0; k < FA_KEYS / 16; ++k)
-            fa_mma(tmem_base + (2 + (t & 1u)) * FA_KEYS, fa_desc_k_major(p_addr + k * 32),
-                   fa_desc_mn_major(v_addr + k * 2048), idesc_pv, k > 0 ? 1u : 0u);
-          fa_commit(&pv_ready);
-          fa_commit(&kv_empty[stage]);
+          for (int k = 0; k < FA_KEYS / 16; ++k)       // the output row accumulates over all key tiles of the unit
+            fa_mma(tmem_base + FA_TMEM_O, fa_desc_k_major(p_addr + k * 32),
+                   fa_desc_mn_major(v_addr + k * 2048, Shape::KV_HALF_BYTES), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          fa_commit(&ctl.pv_ready);
+          fa_commit(&ctl.kv_empty[stage]);
         }
         __syncwarp();
       }
@@ -257,16 +323,16 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       const bool warp_full = warp * 32 + 31 < rows;
       const int warp_first = first_pos + warp * 32;
       const int warp_lo = window > 0 ? max(0, first_pos + min(rows - 1, warp * 32 + 31) - window + 1) : 0;
-      float m = -INFINITY, l = 0.f;
-      float o[FA_D];
-#pragma unroll
-      for (int d = 0; d < FA_D; ++d) o[d] = 0.f;
+      float m_run = -INFINITY;      // the running max of the scaled scores (base-2 exponent)
+      float m_base = -INFINITY;     // the exponent that sum, probabilities and output are relative to
+      float l = 0.f;
+      const float2 scale2 = make_float2(scale_log2, scale_log2);
 
       for (int j = 0; j < tiles; ++j) {
         const unsigned t = tiles_before + (unsigned)j;
-        const int buffer = t & 1, stage = t % FA_STAGES;
+        const int buffer = t & 1, stage = t % STAGES;
         const int key0 = (tile_begin + j) * FA_KEYS;
-        fa_wait(&s_ready[buffer], (t >> 1) & 1u, error_word, 0x66, gave_up);
+        fa_wait(&ctl.s_ready[buffer], (t >> 1) & 1u, error_word, 0x66, gave_up);
         fa_fence_after();
         float s[FA_KEYS];
 #pragma unroll
@@ -274,11 +340,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         fa_tmem_wait_ld();
         fa_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s_free[buffer]);
+        if (lane == 0) mbar_arrive(&ctl.s_free[buffer]);
 
-        // scores stay unscaled until the exponent: p = 2^(s * scale - max), one multiply-add each
-        // (four interleaved chains for the max and the sum: a single chain of 64 dependent
-        // operations would cost more than all the exponentials)
         if (!(warp_full && key0 + FA_KEYS - 1 <= warp_first && key0 >= warp_lo)) {
 #pragma unroll
           for (int c = 0; c < FA_KEYS; ++c) {
@@ -286,61 +349,85 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
             if (!(key >= limit_lo && key <= limit_hi)) s[c] = -INFINITY;
           }
         }
-        float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        // four interleaved chains of three-input max (one chain of dependent operations would cost
+        // more than all the exponentials)
+        float part_max[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-        for (int c = 0; c < FA_KEYS; c += 4) {
+        for (int c = 4; c < FA_KEYS - 4; c += 8) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) part_max[e] = fmaxf(part_max[e], s[c + e]);
+          for (int e = 0; e < 4; ++e) part_max[e] = fa_max3(part_max[e], s[c + 2 * e], s[c + 2 * e + 1]);
         }
-        const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
-        const float m_new = fmaxf(m, tile_max * scale_log2);       // the scale is positive
-        const float base = m_new == -INFINITY ? 0.f : m_new;       // nothing visible yet: keep everything at zero
-        const float alpha = fa_exp2(m - base);                     // m = -inf gives 0
-        m = m_new;
-        float part_sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < FA_KEYS; c += 4) {
+        for (int e = 0; e < 4; ++e) part_max[e] = fmaxf(part_max[e], s[FA_KEYS - 4 + e]);
+        const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
+        m_run = fmaxf(m_run, tile_max * scale_log2);               // the scale is positive
+        // The base follows the max only in steps: (-inf) - (-inf) is NaN and compares false (nothing
+        // visible yet: no step); the first visible key gives +inf and sets the base.
+        const bool step = m_run - m_base > FA_LAZY;
+        const float alpha = step ? fa_exp2(m_base - m_run) : 1.f;   // a base of -inf gives 0
+        if (step) m_base = m_run;
+        const float base = m_base == -INFINITY ? 0.f : m_base;     // nothing visible yet: everything stays zero
+        const float2 minus_base = make_float2(-base, -base);
+        // scores stay unscaled until the exponent: p = 2^(s * scale - base), two per multiply-add
+        float2 part_sum[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+        for (int c = 0; c < FA_KEYS; c += 8) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float x = fmaf(s[c + e], scale_log2, -base);
-            s[c + e] = fa_exp2(x);
-            part_sum[e] += s[c + e];
+            const float2 x = __ffma2_rn(make_float2(s[c + 2 * e], s[c + 2 * e + 1]), scale2, minus_base);
+            s[c + 2 * e] = fa_exp2(x.x);
+            s[c + 2 * e + 1] = fa_exp2(x.y);
+            part_sum[e] = __fadd2_rn(part_sum[e], make_float2(s[c + 2 * e], s[c + 2 * e + 1]));
           }
         }
-        l = l * alpha + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
-        if (alpha != 1.f) {
-#pragma unroll
-          for (int d = 0; d < FA_D; ++d) o[d] *= alpha;
-        }
+        const float2 sum2 = __fadd2_rn(__fadd2_rn(part_sum[0], part_sum[1]), __fadd2_rn(part_sum[2], part_sum[3]));
+        l = fmaf(l, alpha, sum2.x + sum2.y);
+
+        // The output rows in tensor memory hold the sum of the earlier tiles' P V.  They are touched
+        // only when a row of this warp moved its base.  The previous tile's P V is waited for on
+        // every tile all the same (it was issued a whole tile ago): a parity wait can tell the
+        // barrier's current phase from the one before it only, so no phase may be skipped; a warp
+        // must not arrive for this tile's probabilities while the barrier still counts the previous
+        // tile's arrivals; and with one buffer of probabilities the MMA must have read it.
+        const bool rescale = j > 0 && __any_sync(0xffffffffu, step);
         if (j > 0) {
-          // the previous tile's P V, which ran while this tile's exponentials were taken; it is
-          // relative to the previous max, so it takes this tile's factor too
-          fa_wait(&pv_ready, (t - 1) & 1u, error_word, 0x67, gave_up);
+          fa_wait(&ctl.pv_ready, (t - 1) & 1u, error_word, 0x67, gave_up);
           fa_fence_after();
+        }
+        if (rescale) {
+          const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
-          for (int c = 0; c < FA_D; c += 32) {         // two loads in flight per wait
-            float pv[32];
-            fa_tmem_load16(lane_base + (2 + ((t - 1) & 1u)) * FA_KEYS + c, reinterpret_cast<uint32_t*>(pv));
-            fa_tmem_load16(lane_base + (2 + ((t - 1) & 1u)) * FA_KEYS + c + 16, reinterpret_cast<uint32_t*>(pv) + 16);
+          for (int c = 0; c < D; c += 32) {
+            float o[32];
+            fa_tmem_load16(lane_base + FA_TMEM_O + c, reinterpret_cast<uint32_t*>(o));
+            fa_tmem_load16(lane_base + FA_TMEM_O + c + 16, reinterpret_cast<uint32_t*>(o) + 16);
             fa_tmem_wait_ld();
 #pragma unroll
-            for (int d = 0; d < 32; ++d) o[c + d] = fmaf(pv[d], alpha, o[c + d]);
+            for (int d = 0; d < 32; d += 2) {
+              const float2 scaled = __fmul2_rn(make_float2(o[d], o[d + 1]), alpha2);
+              o[d] = scaled.x;
+              o[d + 1] = scaled.y;
+            }
+            fa_tmem_store16(lane_base + FA_TMEM_O + c, reinterpret_cast<const uint32_t*>(o));
+            fa_tmem_store16(lane_base + FA_TMEM_O + c + 16, reinterpret_cast<const uint32_t*>(o) + 16);
           }
+          fa_tmem_wait_st();
         }
 
         if (key0 < lowest || key0 + FA_KEYS - 1 > last_pos) {
           // ragged tile: V rows of keys outside the range become zeros (this thread takes its share of rows)
-          fa_wait(&kv_full[stage], (t / FA_STAGES) & 1u, error_word, 0x68, gave_up);
-          uint8_t* v_tile = kv_ring + (size_t)stage * 2 * FA_KV_TILE_BYTES + FA_KV_TILE_BYTES;
-          for (int idx = threadIdx.x; idx < FA_KEYS * 8; idx += FA_SOFTMAX_THREADS) {
-            const int row = idx >> 3;
+          fa_wait(&ctl.kv_full[stage], (t / STAGES) & 1u, error_word, 0x68, gave_up);
+          uint8_t* v_tile = kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES + Shape::KV_TILE_BYTES;
+          for (int idx = threadIdx.x; idx < FA_KEYS * 8 * Shape::HALVES; idx += FA_SOFTMAX_THREADS) {
+            const int half = idx / (FA_KEYS * 8), within = idx - half * (FA_KEYS * 8);
+            const int row = within >> 3;
             if (key0 + row < lowest || key0 + row > last_pos)
-              *reinterpret_cast<uint4*>(v_tile + row * 128 + (idx & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+              *reinterpret_cast<uint4*>(v_tile + half * Shape::KV_HALF_BYTES + row * 128 + (within & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
           }
         }
         // probabilities of this tile, bfloat16, row r of the swizzled A operand
         {
-          uint8_t* p_row = p_tiles + (t & 1u) * FA_Q_BYTES + r * 128;
+          uint8_t* p_row = p_tiles + (Shape::P_BUFFERS == 2 ? (t & 1u) : 0u) * FA_P_BYTES + r * 128;
 #pragma unroll
           for (int chunk = 0; chunk < 8; ++chunk) {
             uint32_t packed[4];
@@ -355,74 +442,72 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P and the zeroed V rows, for the MMA
         fa_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_ready);
+        if (lane == 0) mbar_arrive(&ctl.p_ready);
       }
-      // the last tile's P V
+      // the finished output rows, after the last tile's P V
       {
         const unsigned t = tiles_before + (unsigned)tiles - 1;
-        fa_wait(&pv_ready, t & 1u, error_word, 0x69, gave_up);
+        fa_wait(&ctl.pv_ready, t & 1u, error_word, 0x69, gave_up);
         fa_fence_after();
-        float pv[FA_D];
+        constexpr int STATE = D + 2;
+        // a part's state of row r: base exponent, sum, unnormalised output; laid out [value][row]
+        // so that the 128 threads write and read neighbouring addresses
+        float* states = scratch + (size_t)item * max_parts * STATE * FA_ROWS + r;
+        float* mine = states + (size_t)part * STATE * FA_ROWS;
+        const float inv = 1.f / l;
+        bf16* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * D;
 #pragma unroll
-        for (int c = 0; c < FA_D; c += 16) fa_tmem_load16(lane_base + (2 + (t & 1u)) * FA_KEYS + c, reinterpret_cast<uint32_t*>(pv) + c);
-        fa_tmem_wait_ld();
-        fa_fence_before();
-        if (parts == 1) {
-          if (r < rows) {
-            const float inv = 1.f / l;
-            bf16* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * FA_D;
+        for (int c = 0; c < D; c += 32) {
+          float o[32];
+          fa_tmem_load16(lane_base + FA_TMEM_O + c, reinterpret_cast<uint32_t*>(o));
+          fa_tmem_load16(lane_base + FA_TMEM_O + c + 16, reinterpret_cast<uint32_t*>(o) + 16);
+          fa_tmem_wait_ld();
+          if (parts == 1) {
+            if (r < rows) fa_store32(dst + c, o, inv);
+          } else {
 #pragma unroll
-            for (int chunk = 0; chunk < 8; ++chunk) {
-              uint32_t packed[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 pair = __floats2bfloat162_rn((o[chunk * 8 + 2 * e] + pv[chunk * 8 + 2 * e]) * inv,
-                                                            (o[chunk * 8 + 2 * e + 1] + pv[chunk * 8 + 2 * e + 1]) * inv);
-                packed[e] = *reinterpret_cast<uint32_t*>(&pair);
-              }
-              *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            }
+            for (int d = 0; d < 32; ++d) mine[(2 + c + d) * FA_ROWS] = o[d];
           }
-        } else {
-          // this part's state of row r: running max, sum, unnormalised output; laid out
-          // [value][row] so that the 128 threads write and read neighbouring addresses
-          constexpr int STATE = FA_D + 2;
-          float* states = scratch + (size_t)item * max_parts * STATE * FA_ROWS + r;
-          float* mine = states + (size_t)part * STATE * FA_ROWS;
-          mine[0] = m;
+        }
+        fa_fence_before();
+        if (parts > 1) {
+          mine[0] = m_base;
           mine[FA_ROWS] = l;
-#pragma unroll
-          for (int d = 0; d < FA_D; ++d) mine[(2 + d) * FA_ROWS] = o[d] + pv[d];
           __threadfence();
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (threadIdx.x == 0) last_shared = (atomicAdd(&counters[item], 1) == parts - 1);
+          if (threadIdx.x == 0) ctl.last = (atomicAdd(&counters[item], 1) == parts - 1);
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (last_shared) {
+          if (ctl.last) {
             __threadfence();
             float m_all = -INFINITY;
             for (int q = 0; q < parts; ++q) m_all = fmaxf(m_all, __ldcg(states + (size_t)q * STATE * FA_ROWS));
             if (r < rows && m_all != -INFINITY) {
+              float factor[8];
               float l_all = 0.f;
 #pragma unroll
-              for (int d = 0; d < FA_D; ++d) o[d] = 0.f;
-              for (int q = 0; q < parts; ++q) {              // in part order
-                const float* theirs = states + (size_t)q * STATE * FA_ROWS;
-                const float factor = fa_exp2(__ldcg(theirs) - m_all);      // a part that saw nothing: 0
-                l_all = fmaf(__ldcg(theirs + FA_ROWS), factor, l_all);
-#pragma unroll
-                for (int d = 0; d < FA_D; ++d) o[d] = fmaf(__ldcg(theirs + (2 + d) * FA_ROWS), factor, o[d]);
-              }
-              const float inv = 1.f / l_all;
-              bf16* dst = out + ((size_t)(q_start + row0 + r) * heads + head) * FA_D;
-#pragma unroll
-              for (int chunk = 0; chunk < 8; ++chunk) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  __nv_bfloat162 pair = __floats2bfloat162_rn(o[chunk * 8 + 2 * e] * inv, o[chunk * 8 + 2 * e + 1] * inv);
-                  packed[e] = *reinterpret_cast<uint32_t*>(&pair);
+              for (int q = 0; q < 8; ++q) {                 // in part order
+                factor[q] = 0.f;
+                if (q < parts) {
+                  const float* theirs = states + (size_t)q * STATE * FA_ROWS;
+                  factor[q] = fa_exp2(__ldcg(theirs) - m_all);           // a part that saw nothing: 0
+                  l_all = fmaf(__ldcg(theirs + FA_ROWS), factor[q], l_all);
                 }
-                *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              }
+              const float inv_all = 1.f / l_all;
+#pragma unroll
+              for (int c = 0; c < D; c += 32) {
+                float o[32];
+#pragma unroll
+                for (int d = 0; d < 32; ++d) o[d] = 0.f;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  if (q < parts) {
+                    const float* theirs = states + (size_t)q * STATE * FA_ROWS + (size_t)(2 + c) * FA_ROWS;
+#pragma unroll
+                    for (int d = 0; d < 32; ++d) o[d] = fmaf(__ldcg(theirs + d * FA_ROWS), factor[q], o[d]);
+                  }
+                }
+                fa_store32(dst + c, o, inv_all);
               }
             }
             if (threadIdx.x == 0) counters[item] = 0;       // ready for the next launch
@@ -432,7 +517,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     }
     tiles_before += (unsigned)tiles;
     items_before += 1;
-    __syncthreads();                // Q, P and item_shared are rewritten by the next item
+    __syncthreads();                // Q, P and ctl.item are rewritten by the next item
   }
 
   fa_fence_before();
@@ -463,41 +548,29 @@ MLR_DEFINE_PDL_SWITCH
 // Units of work aimed at per resident CTA when items are cut into parts.
 static const int units_per_cta = 2;
 
-// Prompt portions, head_dim 64, page_size a power of two >= 8.  q, out: [q_rows, heads * 64]
-// bfloat16; pools [pool_pages, kv_heads, page_size, 64]; tile_seg / tile_row0: tiles of up to 128 rows
-// of one segment, best ordered by falling key count; queue: two zeroed ints in device memory
-// (left zeroed); error_word: host-visible int that receives a code if a wait runs out; max_kv_len:
-// the longest key range of the step; scratch (scratch_bytes) and counters (counters_len zeroed ints,
-// left zeroed): room for the states of items that are cut into parts, may be null.
-MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                             const int* tile_seg, const int* tile_row0, const int* seg_q_start,
-                                             const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
-                                             int table_width, int tiles, int q_rows, int heads, int kv_heads,
-                                             int head_dim, int page_size, int pool_pages, int window, float scale,
-                                             int max_kv_len, int* queue, int* error_word, void* scratch,
-                                             long long scratch_bytes, int* counters, int counters_len,
-                                             cudaStream_t stream) {
-  if (tiles == 0) return MLR_OK;
-  if (tiles < 0 || q_rows <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 ||
-      table_width <= 0 || pool_pages <= 0 || queue == nullptr || error_word == nullptr)
-    return MLR_BAD_SIZE;
-  if (head_dim != FA_D) return MLR_BAD_SIZE;
-  if ((long long)tiles * heads >= (1ll << 30)) return MLR_TOO_LARGE;
-  const int page_shift = fa_shift_of(page_size);
-  if (page_shift < 3) return MLR_BAD_SIZE;
-  if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)q & 15)) return MLR_BAD_ALIGNMENT;
-  const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
-  if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;
+namespace mlr {
+
+template <int D>
+static int fa_launch(const void* q, const void* k_pool, const void* v_pool, void* out, const int* tile_seg,
+                     const int* tile_row0, const int* seg_q_start, const int* seg_q_len, const int* seg_pos0,
+                     const int* block_table, const int* seg_slot, int table_width, int tiles, int q_rows, int heads,
+                     int kv_heads, int page_size, int page_shift, long long pool_rows, int window, float scale,
+                     int max_kv_len, int* queue, int* error_word, void* scratch, long long scratch_bytes,
+                     int* counters, int counters_len, cudaStream_t stream) {
+  using Shape = FaShape<D>;
   const int box_rows = page_size >= FA_KEYS ? FA_KEYS : page_size;
   CUtensorMap q_map, k_map, v_map;
-  if (!cached_tile_map(&q_map, q, q_rows, (long long)heads * FA_D, FA_ROWS) ||
-      !cached_tile_map(&k_map, k_pool, pool_rows, FA_D, box_rows) ||
-      !cached_tile_map(&v_map, v_pool, pool_rows, FA_D, box_rows))
+  if (!cached_tile_map(&q_map, q, q_rows, (long long)heads * D, FA_ROWS) ||
+      !cached_tile_map(&k_map, k_pool, pool_rows, D, box_rows) ||
+      !cached_tile_map(&v_map, v_pool, pool_rows, D, box_rows))
     return MLR_BAD_SIZE;
-  const size_t shared = 1024 + 3 * (size_t)FA_Q_BYTES + (size_t)FA_STAGES * 2 * FA_KV_TILE_BYTES;
+  // With head_dim 128 two CTAs fit an SM only without the spare kilobyte for aligning the tiles:
+  // dynamic shared memory then has to start on a 1024-byte boundary, which it does when the kernel
+  // has no static shared memory; the kernel checks and reports through the error word if not.
+  const size_t shared = (D == 64 ? 1024 : 0) + (size_t)Shape::DATA_BYTES + FA_CONTROL_BYTES;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    cudaError_t err = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
@@ -513,16 +586,52 @@ MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, 
   if (tiles_per_unit < 4) tiles_per_unit = 4;
   int max_parts = (max_key_tiles + tiles_per_unit - 1) / tiles_per_unit;
   if (max_parts > 8) max_parts = 8;
-  const long long need = items * max_parts * FA_ROWS * (FA_D + 2) * (long long)sizeof(float);
+  const long long need = items * max_parts * FA_ROWS * (D + 2) * (long long)sizeof(float);
   if (max_parts > 1 && (scratch == nullptr || counters == nullptr || need > scratch_bytes || items > counters_len)) {
     max_parts = 1;
     tiles_per_unit = 1 << 30;
   }
   const long long units = items * max_parts;
   const int ctas = (int)(units < resident ? units : resident);
-  launch_kernel(prefill_attention_tcgen05_kernel, dim3(ctas), dim3(FA_THREADS), shared, stream, q_map, k_map, v_map,
+  launch_kernel(prefill_attention_tcgen05_kernel<D>, dim3(ctas), dim3(FA_THREADS), shared, stream, q_map, k_map, v_map,
                 (bf16*)out, tile_seg, tile_row0, seg_q_start, seg_q_len, seg_pos0, block_table, seg_slot, table_width, tiles, heads,
                 kv_heads, page_size, page_shift, window, scale * 1.4426950408889634f, queue, error_word, max_parts,
-                tiles_per_unit, (float*)scratch, counters);
+                tiles_per_unit, (float*)scratch, counters, (int)shared);
   return launch_status();
+}
+
+}  // namespace mlr
+
+// Prompt portions, head_dim 64 or 128, page_size a power of two >= 8.  q, out: [q_rows, heads *
+// head_dim] bfloat16; pools [pool_pages, kv_heads, page_size, head_dim]; tile_seg / tile_row0: tiles
+// of up to 128 rows of one segment, best ordered by falling key count; queue: two zeroed ints in
+// device memory (left zeroed); error_word: host-visible int that receives a code if a wait runs out;
+// max_kv_len: the longest key range of the step; scratch (scratch_bytes) and counters (counters_len
+// zeroed ints, left zeroed): room for the states of items that are cut into parts, may be null.
+MLR_EXPORT int mlr_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                             const int* tile_seg, const int* tile_row0, const int* seg_q_start,
+                                             const int* seg_q_len, const int* seg_pos0, const int* block_table, const int* seg_slot,
+                                             int table_width, int tiles, int q_rows, int heads, int kv_heads,
+                                             int head_dim, int page_size, int pool_pages, int window, float scale,
+                                             int max_kv_len, int* queue, int* error_word, void* scratch,
+                                             long long scratch_bytes, int* counters, int counters_len,
+                                             cudaStream_t stream) {
+  if (tiles == 0) return MLR_OK;
+  if (tiles < 0 || q_rows <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 ||
+      table_width <= 0 || pool_pages <= 0 || queue == nullptr || error_word == nullptr)
+    return MLR_BAD_SIZE;
+  if (head_dim != 64 && head_dim != 128) return MLR_BAD_SIZE;
+  if ((long long)tiles * heads >= (1ll << 30)) return MLR_TOO_LARGE;
+  const int page_shift = fa_shift_of(page_size);
+  if (page_shift < 3) return MLR_BAD_SIZE;
+  if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)q & 15)) return MLR_BAD_ALIGNMENT;
+  const long long pool_rows = (long long)pool_pages * kv_heads * page_size;
+  if (pool_rows >= (1ll << 31)) return MLR_TOO_LARGE;
+  if (head_dim == 64)
+    return fa_launch<64>(q, k_pool, v_pool, out, tile_seg, tile_row0, seg_q_start, seg_q_len, seg_pos0, block_table,
+                         seg_slot, table_width, tiles, q_rows, heads, kv_heads, page_size, page_shift, pool_rows, window,
+                         scale, max_kv_len, queue, error_word, scratch, scratch_bytes, counters, counters_len, stream);
+  return fa_launch<128>(q, k_pool, v_pool, out, tile_seg, tile_row0, seg_q_start, seg_q_len, seg_pos0, block_table,
+                        seg_slot, table_width, tiles, q_rows, heads, kv_heads, page_size, page_shift, pool_rows, window,
+                        scale, max_kv_len, queue, error_word, scratch, scratch_bytes, counters, counters_len, stream);
 }

@@ -70,7 +70,9 @@ def _ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
 
 
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream of the current device (the raw handle: the wrapper object of
+    ``torch.cuda.current_stream`` costs microseconds, and a step asks hundreds of times)."""
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 @dataclass
@@ -576,7 +578,7 @@ class CudaOps:
             if batch.num_decode > 0:
                 self._decode_attention(q, k_pool, v_pool, out, batch, num_heads, num_kv_heads, head_dim, scale,
                                        window, mma=True)
-            if counts["big"] > 0 and self.use_tcgen05_attention and head_dim == 64 and paged_by_tma:
+            if counts["big"] > 0 and self.use_tcgen05_attention and paged_by_tma:
                 # S = Q K^T and P V on tcgen05 with tensor-memory accumulators
                 space = self._workspace(q.device)
                 _check(build.load_library("attention_tcgen05").mlr_attention_prefill_tcgen05(

@@ -536,7 +536,7 @@ def test_prefill_attention_tensor_cores(heads, kv_heads, head_dim, page, window)
     finally:
         cuda().use_tma_attention = cuda().use_tcgen05_attention = True
     assert_close(got, other, torch.bfloat16, "default prefill kernel against the cp.async prefill kernel")
-    # head_dim 64 with such pages took the tcgen05 kernel above (S = Q K^T and P V in tensor memory, one
+    # pages of 8 keys or more took the tcgen05 kernel above (S = Q K^T and P V in tensor memory, one
     # thread per query row); the mma.sync kernel with bulk-copy loaders must agree with it
     cuda().use_tcgen05_attention = False
     try:
@@ -549,13 +549,40 @@ def test_prefill_attention_tensor_cores(heads, kv_heads, head_dim, page, window)
     assert_close(third, got, torch.bfloat16, "mma.sync prefill kernel against the default kernel")
 
 
-@pytest.mark.parametrize("heads,kv_heads,page", [(2, 1, 16), (6, 2, 64)])
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("rises", [(5.0, 12.0, 14.0, 30.0, 33.0), (40.0, 41.0, 3.0, 2.0, 1.0), (4.0, 4.5, 5.0, 5.5, 6.0)])
+def test_prefill_attention_rising_maxima(head_dim, rises):
+    """The tcgen05 kernel keeps the output rows in tensor memory relative to a base exponent that
+    follows the running max only in steps of more than 2^8.  Keys in five different key tiles are
+    given scores that rise by small and by large amounts for the last row of the prompt, so that
+    some tiles move the base (the rows are rescaled in tensor memory) and others run ahead of it."""
+    heads, kv_heads, page = 3, 1, 16
+    segments = [(0, 700), (300, 140)]
+    q, k_pool, v_pool, batch, table = make_attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, segments, 61)
+    for seg, row in ((0, 699), (1, 839)):
+        direction = q[row, :head_dim].float()
+        for place, (key, rise) in enumerate(zip((10, 130, 260, 390, 420), rises)):
+            pg, off = table[seg, key // page], key % page
+            k_pool[pg, 0, off] = (direction * (rise / direction.norm() ** 2 * math.sqrt(head_dim))).to(torch.bfloat16)
+            v_pool[pg, 0, off] = torch.full((head_dim,), 10.0 * (place + 1)).to(torch.bfloat16)
+    got, want = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+    torch.cuda.synchronize()
+    cuda().raise_if_device_error()
+    assert_close(got, want, torch.bfloat16, f"prompt attention with rising maxima {rises}")
+    cuda().use_tcgen05_attention = False
+    try:
+        other, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+    finally:
+        cuda().use_tcgen05_attention = True
+    assert_close(got, other, torch.bfloat16, "tcgen05 kernel against the mma.sync kernel")
+
+
+@pytest.mark.parametrize("heads,kv_heads,page,head_dim", [(2, 1, 16, 64), (6, 2, 64, 64), (4, 2, 16, 128), (2, 2, 128, 128)])
 @pytest.mark.parametrize("window", [None, 333])
-def test_prefill_attention_items_cut_into_parts(heads, kv_heads, page, window):
+def test_prefill_attention_items_cut_into_parts(heads, kv_heads, page, head_dim, window):
     """Few query tiles with long key ranges: the tcgen05 kernel cuts each item's keys into up to
     eight parts that different CTAs take and the last one merges.  One far key is made dominant so
     that a part that is dropped or merged with the wrong weight shows."""
-    head_dim = 64
     segments = [(0, 1500), (1900, 150), (640, 1)]
     q, k_pool, v_pool, batch, table = make_attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, segments, 57)
     if window is None:
