@@ -166,7 +166,11 @@ class ContinuousBatchEngine:
             for item in plan.items:
                 if item.kind is WorkKind.DECODE and item.request_id in covered:
                     continue
-                entries.append(StepEntry(item.request_id, item.tokens, [len(item.tokens) - 1] if item.emits else []))
+                tokens = item.tokens
+                if item.kind is not WorkKind.DECODE and len(tokens) > 16:
+                    request = self.scheduler.get_request(item.request_id)     # a prompt portion: starts at the cursor
+                    tokens = request.prompt_span(request.cursor, len(tokens))
+                entries.append(StepEntry(item.request_id, tokens, [len(tokens) - 1] if item.emits else []))
                 if item.admitted:
                     self.metrics.record_prefill_started(item.request_id, self._clock_ns())
                 if item.emits:

@@ -38,6 +38,8 @@ from dataclasses import dataclass, field
 from enum import Enum
 from typing import Protocol
 
+import numpy as np
+
 from ..sampling import GREEDY, SamplingParams
 
 
@@ -87,10 +89,19 @@ class Request:
     output: list[int] = field(default_factory=list, repr=False)
     finish_reason: FinishReason | None = None
     slot: int | None = None
+    _prompt_array: "np.ndarray | None" = field(default=None, repr=False, compare=False)
 
     @property
     def prompt_token_ids(self) -> tuple[int, ...]:
         return self.prompt
+
+    def prompt_span(self, start: int, count: int) -> "np.ndarray":
+        """``count`` prompt tokens from ``start`` as a view of one int32 array (made once: the step
+        function takes arrays as they are, while a tuple of thousands of integers costs it a
+        conversion per portion)."""
+        if self._prompt_array is None:
+            self._prompt_array = np.asarray(self.prompt, dtype=np.int32)
+        return self._prompt_array[start:start + count]
 
     @property
     def generated_token_ids(self) -> tuple[int, ...]:

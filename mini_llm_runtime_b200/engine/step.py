@@ -234,7 +234,7 @@ class ModelRunner:
         out = {}
         for name, array, offset in packer.items:
             flat = device_buffer[offset:offset + array.nbytes].view(_TORCH_OF[array.dtype])
-            out[name] = flat.view(array.shape)
+            out[name] = flat if array.ndim == 1 else flat.view(array.shape)
         return out
 
     def _pack_resident_updates(self, packer: _Packer) -> list[tuple[torch.Tensor, str, str]]:
@@ -275,13 +275,18 @@ class ModelRunner:
                 plans[key] = block.mixer.step_plan(host)
         return plans
 
-    def _pack(self, entries: Sequence[StepEntry], requests: list[RequestCache], *, want_slots: bool, fixed: bool):
+    def _pack(self, entries: Sequence[StepEntry], requests: list[RequestCache], *, want_slots: bool, fixed: bool,
+              token_arrays: list | None = None):
         """Lay the step's metadata out on the host.  ``fixed``: the layout of a captured decode step
         (the requests' slots first, then the token ids: what a replay may have to refresh)."""
         cache = self.cache
         host = self._host_batch(entries, requests)
         lengths, row_start, position_start, total = host.lengths, host.row_start, host.position_start, host.num_rows
-        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        if token_arrays is None:
+            token_arrays = [None] * len(entries)
+        pieces = [np.asarray(e.tokens, dtype=np.int32) if array is None else array
+                  for e, array in zip(entries, token_arrays)]
+        token_ids = pieces[0] if len(pieces) == 1 else np.concatenate(pieces)
         segment_of_row = np.repeat(np.arange(len(entries), dtype=np.int32), lengths)
         positions = (np.arange(total, dtype=np.int32) - row_start[segment_of_row]
                      + position_start[segment_of_row]).astype(np.int32)
@@ -313,14 +318,14 @@ class ModelRunner:
 
     def _build_context(self, entries: Sequence[StepEntry], requests: list[RequestCache], *,
                        want_slots: bool = False, fixed: bool = False, packed=None,
-                       device_buffer: torch.Tensor | None = None) -> StepContext:
+                       device_buffer: torch.Tensor | None = None, token_arrays: list | None = None) -> StepContext:
         """Host-side description of the step, sent to the device.  ``fixed``: a captured decode step
         (contexts as long as the cache allows, so that every kernel plans against the cache's
         capacity); ``device_buffer`` is that graph's own metadata buffer.  ``want_slots`` adds the
         slot of every wanted row (for sampling by slot)."""
         cache = self.cache
         packer, host, slots, wanted_rows, plans, pending = packed or self._pack(
-            entries, requests, want_slots=want_slots, fixed=fixed)
+            entries, requests, want_slots=want_slots, fixed=fixed, token_arrays=token_arrays)
         lengths, row_start, position_start, total = host.lengths, host.row_start, host.position_start, host.num_rows
         dev = self._upload(packer, device_buffer)
         self._scatter_resident_updates(pending, dev)
@@ -352,9 +357,12 @@ class ModelRunner:
         return ctx
 
     # ------------------------------------------------------------------ the step
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry]) -> list:
+        """Check the entries; returns each entry's tokens as an int32 array (converted once: a
+        prompt portion is thousands of Python integers), or None for the common decode entry."""
         if not entries:
             raise ValueError("a step needs at least one entry")
+        arrays = []
         for entry in entries:
             count = len(entry.tokens)
             if count == 0:
@@ -364,11 +372,13 @@ class ModelRunner:
                 if self.cache.get(entry.request_id).committed + 1 > self.max_positions:
                     raise ValueError(f"request {entry.request_id!r} would exceed the model's "
                                      f"{self.max_positions} positions")
-                continue                      # the common decode entry: nothing more to check
+                arrays.append(None)           # the common decode entry: nothing more to check
+                continue
             tokens = np.asarray(entry.tokens)
             if tokens.dtype.kind not in "iu" or tokens.min() < 0 or tokens.max() >= self.vocab_size:
                 raise ValueError(f"request {entry.request_id!r}: token ids must be integers in "
                                  f"[0, {self.vocab_size})")
+            arrays.append(tokens.astype(np.int32, copy=False))
             for place in entry.want:
                 if not 0 <= int(place) < count:
                     raise ValueError(f"request {entry.request_id!r}: wanted place {place} is outside "
@@ -377,6 +387,7 @@ class ModelRunner:
             if held + count > self.max_positions:
                 raise ValueError(f"request {entry.request_id!r} would reach {held + count} positions, "
                                  f"the model allows {self.max_positions}")
+        return arrays
 
     def _forward(self, ctx: StepContext, sample: bool, *, lengths_by_device: bool):
         """The model, then the choice of tokens, then the slots' new lengths.  ``lengths_by_device``:
@@ -508,7 +519,7 @@ class ModelRunner:
         overwrites (no copy is made).  ``feed=True``: every entry holds one placeholder token and the
         real input is the token the request sampled last, taken from its slot record on the device
         without the host having seen it."""
-        self._validate(entries)
+        token_arrays = self._validate(entries)
         if feed and any(len(e.tokens) != 1 for e in entries):
             raise ValueError("feed needs entries of exactly one token each")
         if sample and any(len(e.want) > 1 for e in entries):
@@ -521,7 +532,7 @@ class ModelRunner:
                     logits = logits.clone()
                     tokens = tokens.clone() if tokens is not None else None
             else:
-                ctx = self._build_context(entries, requests, want_slots=sample)
+                ctx = self._build_context(entries, requests, want_slots=sample, token_arrays=token_arrays)
                 if feed:
                     ctx.ops.decode_prepare(ctx.seg_slot, self.cache.slot_state, token_ids=ctx.token_ids)
                 logits, tokens = self._forward(ctx, sample, lengths_by_device=False)
