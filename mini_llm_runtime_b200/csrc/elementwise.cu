@@ -68,33 +68,38 @@ __global__ void rms_norm_kernel(T* residual, const T* delta,
   }
 }
 
-// bfloat16 rows whose width is a multiple of 8 (at most 256 * VECS): one warp per row, each lane
-// keeps its 16-byte pieces of the row in registers, so global memory is read once with wide loads
-// and no block-level reduction is needed.  Same arithmetic as above: float32 add rounded once and
-// stored back, float32 sum of squares, weight * (value * scale).
-template <typename W, int VECS>
+// bfloat16 rows whose width is a multiple of 8 (at most 256 * VECS * WARPS_PER_ROW): one, two or
+// four warps per row, each lane keeps its 16-byte pieces of the row in registers (at most 8 of
+// the row and 8 of the delta: a lane with more spills, and a 64 x 5120 norm then takes 31 us
+// instead of 4), so global memory is read once with wide loads.  Same arithmetic as above: float32
+// add rounded once and stored back, float32 sum of squares, weight * (value * scale).
+template <typename W, int VECS, int WARPS_PER_ROW>
 __global__ void __launch_bounds__(128)
 rms_norm_rows_kernel(bf16* residual, const bf16* delta, const W* __restrict__ weight, bf16* __restrict__ out,
                      int rows, int width, float eps) {
+  __shared__ float warp_squares[4];
   pdl_trigger();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int pieces = width >> 3;
-  uint4* stream = reinterpret_cast<uint4*>(residual + (size_t)row * width);
-  const uint4* added = delta != nullptr ? reinterpret_cast<const uint4*>(delta + (size_t)row * width) : nullptr;
-  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * width);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * (4 / WARPS_PER_ROW) + warp / WARPS_PER_ROW;
+  const int share = warp % WARPS_PER_ROW;              // this warp's pieces: lane + 32 * (share + WARPS_PER_ROW * j)
+  const bool live = row < rows;
+  const int pieces = live ? width >> 3 : 0;
+  const size_t base = (size_t)(live ? row : 0) * width;
+  uint4* stream = reinterpret_cast<uint4*>(residual + base);
+  const uint4* added = delta != nullptr ? reinterpret_cast<const uint4*>(delta + base) : nullptr;
+  uint4* dst = reinterpret_cast<uint4*>(out + base);
   uint4 raw[VECS], extra[VECS];
 #pragma unroll
   for (int j = 0; j < VECS; ++j) {
-    const int piece = lane + 32 * j;
+    const int piece = lane + 32 * (share + WARPS_PER_ROW * j);
     raw[j] = piece < pieces ? stream[piece] : make_uint4(0u, 0u, 0u, 0u);
     if (added != nullptr) extra[j] = piece < pieces ? added[piece] : make_uint4(0u, 0u, 0u, 0u);
   }
   float partial = 0.f;
 #pragma unroll
   for (int j = 0; j < VECS; ++j) {
+    const int piece = lane + 32 * (share + WARPS_PER_ROW * j);
     __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw[j]);
     if (added != nullptr) {
       const __nv_bfloat162* more = reinterpret_cast<const __nv_bfloat162*>(&extra[j]);
@@ -103,7 +108,7 @@ rms_norm_rows_kernel(bf16* residual, const bf16* delta, const W* __restrict__ we
         const float2 a = __bfloat1622float2(pairs[e]), b = __bfloat1622float2(more[e]);
         pairs[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
       }
-      if (lane + 32 * j < pieces) stream[lane + 32 * j] = raw[j];
+      if (piece < pieces) stream[piece] = raw[j];
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -111,10 +116,18 @@ rms_norm_rows_kernel(bf16* residual, const bf16* delta, const W* __restrict__ we
       partial += a.x * a.x + a.y * a.y;
     }
   }
-  const float scale = rsqrtf(warp_sum(partial) / (float)width + eps);
+  float squares = warp_sum(partial);
+  if (WARPS_PER_ROW > 1) {             // the row's warps add their sums in warp order
+    if (lane == 0) warp_squares[warp] = squares;
+    __syncthreads();
+    squares = 0.f;
+#pragma unroll
+    for (int v = 0; v < WARPS_PER_ROW; ++v) squares += warp_squares[warp / WARPS_PER_ROW * WARPS_PER_ROW + v];
+  }
+  const float scale = rsqrtf(squares / (float)width + eps);
 #pragma unroll
   for (int j = 0; j < VECS; ++j) {
-    const int piece = lane + 32 * j;
+    const int piece = lane + 32 * (share + WARPS_PER_ROW * j);
     if (piece >= pieces) continue;
     const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
     float w[8];
@@ -374,15 +387,15 @@ MLR_EXPORT int mlr_rms_norm(void* residual, const void* delta, const void* weigh
   if (dtype == MLR_F32 && weight_dtype == MLR_F32)
     return rms_norm_launch<float, float>(residual, delta, weight, out, rows, width, eps, stream);
   if (dtype == MLR_BF16 && width % 8 == 0 && width <= 8192 && (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)out) & 15) == 0) {
-    // warp-per-row kernel with the row in registers
-#define MLR_ROWS(W_, V_)                                                                                     \
-  launch_kernel(rms_norm_rows_kernel<W_, V_>, dim3((rows + 3) / 4), dim3(128), 0, stream, (bf16*)residual,   \
-                (const bf16*)delta, (const W_*)weight, (bf16*)out, rows, width, eps)
+    // the row in the registers of one, two or four warps (at most 8 pieces of 16 bytes per lane)
+#define MLR_ROWS(W_, V_, P_)                                                                                 \
+  launch_kernel(rms_norm_rows_kernel<W_, V_, P_>, dim3((rows * P_ + 3) / 4), dim3(128), 0, stream,           \
+                (bf16*)residual, (const bf16*)delta, (const W_*)weight, (bf16*)out, rows, width, eps)
 #define MLR_ROWS_BY_WIDTH(W_)                                                                                \
   do {                                                                                                       \
-    if (width <= 256) MLR_ROWS(W_, 1); else if (width <= 512) MLR_ROWS(W_, 2);                               \
-    else if (width <= 1024) MLR_ROWS(W_, 4); else if (width <= 2048) MLR_ROWS(W_, 8);                        \
-    else if (width <= 4096) MLR_ROWS(W_, 16); else MLR_ROWS(W_, 32);                                         \
+    if (width <= 256) MLR_ROWS(W_, 1, 1); else if (width <= 512) MLR_ROWS(W_, 2, 1);                         \
+    else if (width <= 1024) MLR_ROWS(W_, 4, 1); else if (width <= 2048) MLR_ROWS(W_, 8, 1);                  \
+    else if (width <= 4096) MLR_ROWS(W_, 8, 2); else MLR_ROWS(W_, 8, 4);                                     \
   } while (0)
     if (weight_dtype == MLR_F32) MLR_ROWS_BY_WIDTH(float);
     else if (weight_dtype == MLR_BF16) MLR_ROWS_BY_WIDTH(bf16);

@@ -185,8 +185,9 @@ class CudaOps:
         self.decode_max_splits: int | None = None  # None: just enough for the longest context
 
     def _workspace(self, device: torch.device) -> dict[str, torch.Tensor]:
-        index = device.index if device.index is not None else torch.cuda.current_device()
+        index = device.index if device.type == "cuda" and device.index is not None else torch.cuda.current_device()
         if index not in self._workspaces:
+            device = torch.device("cuda", index)
             self._workspaces[index] = {
                 "gemm_scratch": torch.empty(self.GEMM_SCRATCH_BYTES, dtype=torch.uint8, device=device),
                 "gemm_counters": torch.zeros(self.GEMM_COUNTERS, dtype=torch.int32, device=device),

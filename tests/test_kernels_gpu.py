@@ -54,7 +54,8 @@ def test_embedding(dtype, vocab, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width,eps", [(100, 1e-6), (896, 1e-5), (5120, 1e-6), (7, 1e-3)])
+@pytest.mark.parametrize("width,eps", [(100, 1e-6), (896, 1e-5), (5120, 1e-6), (7, 1e-3), (3584, 1e-6), (2056, 1e-5),
+                                       (8192, 1e-6), (8200, 1e-6)])
 def test_rms_norm_and_fused_add(dtype, width, eps):
     x = rnd((9, width), dtype, 3, 2.0)
     delta = rnd((9, width), dtype, 4, 0.5)
@@ -253,7 +254,7 @@ def test_few_rows_linear_with_norm_and_residual(m, n, k, eps):
     normed = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + eps)
     cuda().SKINNY_ROWS = 64
     try:
-        assert cuda()._skinny_fits(x, w) and cuda().fuses_norm(m)
+        assert cuda()._skinny_fits(x.to(DEVICE), w.to(DEVICE)) and cuda().fuses_norm(m)
         for skinny in (True, False):
             cuda().use_skinny = skinny
             got = cuda().linear(x.to(DEVICE), w.to(DEVICE), b.to(DEVICE), rms_eps=eps)
