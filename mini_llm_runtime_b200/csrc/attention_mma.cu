@@ -473,6 +473,23 @@ prefill_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
   }
 }
 
+// Thread-block clusters: barrier over all CTAs of the cluster (release / acquire), the address of a
+// peer CTA's copy of a shared-memory location, and a load from it.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_address(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ float load_cluster_shared(uint32_t address) {
+  float value;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(address) : "memory");
+  return value;
+}
+
 // The end of both decode kernels: merge the four warps' states (each saw a quarter of the keys) in
 // shared memory, write the output if the request has one chunk, else store the chunk's state and
 // let the CTA that arrives last for this (request, kv head) merge all chunks in chunk order.
@@ -480,7 +497,7 @@ template <int D>
 __device__ __forceinline__ void decode_finish(float* merge, int* last_flag_ptr, const float* m, const float* l,
                                               const float (*o)[4], bf16* out, float* scratch, int* counters,
                                               int index, int row, int heads, int kv_heads, int kv_head, int group,
-                                              int split, int splits, int max_splits) {
+                                              int split, int splits, int max_splits, int cluster_size = 0) {
   constexpr int STATE = D + 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // ---- merge the four warps (each saw a quarter of the keys)
@@ -496,6 +513,61 @@ __device__ __forceinline__ void decode_finish(float* merge, int* last_flag_ptr, 
     }
   }
   __syncthreads();
+  if (cluster_size > 1) {
+    // The chunks of one (request, kv head) are the CTAs of one cluster: each leaves its state in its
+    // own shared memory, and after one cluster barrier every CTA merges a slice of the outputs from
+    // all of them through distributed shared memory, in chunk order.  No scratch memory, fence or
+    // counter in global memory lies on the way.  A CTA without keys (a context shorter than the
+    // grid's chunks) contributes max -inf and takes part in the barriers like the others.
+    float* cta_state = merge + (size_t)ATTN_WARPS * 16 * STATE;          // [16][STATE]
+    for (int item = threadIdx.x; item < group * D; item += ATTN_THREADS) {
+      const int g = item / D, d = item - g * D;
+      float m_all = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < ATTN_WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + g) * STATE]);
+      float l_all = 0.f, a_all = 0.f;
+#pragma unroll
+      for (int w = 0; w < ATTN_WARPS; ++w) {
+        const float* state = merge + ((size_t)w * 16 + g) * STATE;
+        const float factor = m_all == -INFINITY ? 0.f : exp2f(state[0] - m_all);
+        l_all += state[1] * factor;
+        a_all += state[2 + d] * factor;
+      }
+      cta_state[g * STATE + 2 + d] = a_all;
+      if (d == 0) { cta_state[g * STATE] = m_all; cta_state[g * STATE + 1] = l_all; }
+    }
+    cluster_sync();
+    const int total = group * D, per = (total + cluster_size - 1) / cluster_size;
+    const int end = min(total, (split + 1) * per);
+    for (int item = split * per + threadIdx.x; item < end; item += ATTN_THREADS) {
+      const int g = item / D, d = item - g * D;
+      const uint32_t local = smem_u32(cta_state + g * STATE);
+      float ms[16], ls[16], as[16];
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {
+        ms[s] = -INFINITY; ls[s] = 0.f; as[s] = 0.f;
+        if (s < cluster_size) {
+          const uint32_t remote = cluster_address(local, (uint32_t)s);
+          ms[s] = load_cluster_shared(remote);
+          ls[s] = load_cluster_shared(remote + 4);
+          as[s] = load_cluster_shared(remote + 8 + (uint32_t)d * 4);
+        }
+      }
+      float m_all = -INFINITY;
+#pragma unroll
+      for (int s = 0; s < 16; ++s) m_all = fmaxf(m_all, ms[s]);
+      float l_all = 0.f, a_all = 0.f;
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {                       // in chunk order
+        const float factor = exp2f(ms[s] - m_all);         // a chunk without keys: 0
+        l_all += ls[s] * factor;
+        a_all += as[s] * factor;
+      }
+      out[((size_t)row * heads + kv_head * group + g) * D + d] = __float2bfloat16_rn(a_all / l_all);
+    }
+    cluster_sync();            // no CTA leaves while another may still read its state
+    return;
+  }
   const size_t state_base = ((size_t)index * heads + kv_head * group) * max_splits;
   for (int item = threadIdx.x; item < group * D; item += ATTN_THREADS) {
     const int g = item / D, d = item - g * D;
@@ -731,7 +803,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
                             int page_size, int page_shift, int window, float scale_log2, int chunk_arg,
                             int even_split, float* __restrict__ scratch, int* __restrict__ counters,
                             int max_splits, int* error_word, const bf16* qkv, const float* __restrict__ inv_freq,
-                            const long long* __restrict__ slots, bf16* k_pool_w, bf16* v_pool_w, int write_kv) {
+                            const long long* __restrict__ slots, bf16* k_pool_w, bf16* v_pool_w, int write_kv,
+                            int cluster_merge) {
   constexpr int HALVES = D / 64;
   constexpr int TILE_ELEMS = TKV * D;
   constexpr int NT = TKV / 8;
@@ -766,12 +839,16 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   if (even_split) chunk = max(chunk_arg, ((position + max_splits) / max_splits + TKV - 1) / TKV * TKV);
   const int first_chunk = lowest / chunk;
   const int splits = position / chunk - first_chunk + 1;
-  if (split >= splits) return;
+  // A CTA beyond the request's chunks has nothing to do; as a member of a cluster that merges
+  // through shared memory it stays, without keys, for the cluster's barriers.
+  const bool idle = split >= splits;
+  if (splits == 1) cluster_merge = 0;       // one chunk (the same answer in every CTA of the cluster): nothing to merge
+  if (idle && !cluster_merge) return;
   const int k_begin = max(lowest, (first_chunk + split) * chunk);
   const int k_end = min(position + 1, (first_chunk + split + 1) * chunk);   // exclusive
   const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
   const int tile_begin = k_begin / TKV, tile_end = (k_end - 1) / TKV;       // inclusive
-  const int tiles = tile_end - tile_begin + 1;
+  const int tiles = idle ? 0 : tile_end - tile_begin + 1;
   const int my_tiles = tiles > warp ? (tiles - warp + ATTN_WARPS - 1) / ATTN_WARPS : 0;   // tiles warp, warp + 4, ..
 
   // lane j fetches the j-th page (or the one TKV-key box) of the warp's n-th tile, K and V
@@ -807,18 +884,29 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   const bool early = !holds_new_key || inject;
   if (early)
     for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
+  // The rotation's angles depend on the position only: taken before the wait, like the new token's
+  // cache slot, so that after it only the values themselves are fetched.
+  constexpr int CHUNKS = D / 8;
+  constexpr int HALF = D / 2;
+  float sine = 0.f, cosine = 1.f;            // of pair threadIdx.x % HALF (the same for all of a thread's query items)
+  float key_sine[HALF / 32], key_cosine[HALF / 32];     // of pairs lane, lane + 32, ..: the new key's
+  long long new_slot = -1;
+  if (fused) {
+    sincosf((float)position * inv_freq[threadIdx.x % HALF], &sine, &cosine);
+    if (inject) {
+#pragma unroll
+      for (int j = 0; j < HALF / 32; ++j) sincosf((float)position * inv_freq[lane + 32 * j], &key_sine[j], &key_cosine[j]);
+      new_slot = slots[row];
+    }
+  }
   pdl_wait();
   if (!early)
     for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
 
-  constexpr int CHUNKS = D / 8;
-  constexpr int HALF = D / 2;
   const size_t qkv_width = (size_t)(heads + 2 * kv_heads) * D;
   if (fused) {
     // thread -> pair index i (the same for all its items, as 128 % HALF == 0) and rows g0, g0 + 128/HALF, ..
     const int i = threadIdx.x % HALF;
-    float sine, cosine;
-    sincosf((float)position * inv_freq[i], &sine, &cosine);
     const bf16* q_row = qkv + (size_t)row * qkv_width + (size_t)kv_head * group * D;
     for (int g = threadIdx.x / HALF; g < 16; g += ATTN_THREADS / HALF) {
       float y1 = 0.f, y2 = 0.f;
@@ -866,16 +954,16 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     if (inject && warp + n * ATTN_WARPS == newest_tile) {
       // the step's own key and value: into the pages and over the stale row of this tile
       const int r = position - key0;
-      const long long slot = slots[row];
+      const long long slot = new_slot;
       const long long page = slot / page_size;
       const size_t at = (((size_t)page * kv_heads + kv_head) * page_size + (size_t)(slot - page * page_size)) * D;
       const bf16* k_src = qkv + (size_t)row * qkv_width + (size_t)(heads + kv_head) * D;
       const bf16* v_src = k_src + (size_t)kv_heads * D;
-      for (int i = lane; i < HALF; i += 32) {
-        float sine, cosine;
-        sincosf((float)position * inv_freq[i], &sine, &cosine);
+#pragma unroll
+      for (int j = 0; j < HALF / 32; ++j) {
+        const int i = lane + 32 * j;
         float r1, r2;
-        rotate_pair(__bfloat162float(k_src[i]), __bfloat162float(k_src[i + HALF]), sine, cosine, &r1, &r2);
+        rotate_pair(__bfloat162float(k_src[i]), __bfloat162float(k_src[i + HALF]), key_sine[j], key_cosine[j], &r1, &r2);
         const bf16 y1 = __float2bfloat16_rn(r1), y2 = __float2bfloat16_rn(r2);
         tile_at<D, true, TKV>(k_tile, r, i >> 3)[i & 7] = y1;
         tile_at<D, true, TKV>(k_tile, r, (i + HALF) >> 3)[(i + HALF) & 7] = y2;
@@ -912,7 +1000,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   // No load is in flight here: every issued tile was waited for (or its wait ran out after a second).
   __syncthreads();                                               // the merge area overlays the stages
   decode_finish<D>(merge, &last_flag, m, l, o, out, scratch, counters, index, row, heads, kv_heads, kv_head, group,
-                   split, splits, max_splits);
+                   split, splits, max_splits, cluster_merge ? max_splits : 0);
 }
 
 template <typename Kernel>
@@ -1011,13 +1099,15 @@ MLR_EXPORT int mlr_attention_decode_mma(const void* q, const void* k_pool, const
 // host-visible int that receives a code if a wait runs out.  qkv != null: the fused position
 // encoding described at the kernel (q is then unused; inv_freq [head_dim/2] float32; slots [tokens]
 // int64, page * page_size + offset of each token's cache slot; write_kv = 0 leaves the pages alone).
+// cluster_merge != 0 (2 <= max_splits <= 16): the chunks merge through their cluster's shared
+// memory, and scratch and counters are not touched.
 MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out,
                                         const int* decode_seg, const int* seg_q_start, const int* seg_pos0,
                                         const int* block_table, const int* seg_slot, int table_width, int rows, int heads, int kv_heads,
                                         int head_dim, int page_size, int pool_pages, int window, float scale,
                                         int chunk, int even_split, int max_splits, int stages, void* scratch,
                                         int* counters, int* error_word, const void* qkv, const float* inv_freq,
-                                        const long long* slots, int write_kv, cudaStream_t stream) {
+                                        const long long* slots, int write_kv, int cluster_merge, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || page_size <= 0 || chunk <= 0 ||
       chunk % TILE_KV != 0 || max_splits <= 0 || table_width <= 0 || pool_pages <= 0 || error_word == nullptr)
@@ -1038,17 +1128,36 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
       !cached_tile_map(&v_map, v_pool, pool_rows, head_dim, box_rows))
     return MLR_BAD_SIZE;
   dim3 grid(max_splits, kv_heads, rows);
+  // cluster_merge: the chunks of a (request, kv head) form one thread-block cluster (the grid's x
+  // extent, at most 16 CTAs; more than 8 is the hardware's non-portable size) and merge through
+  // shared memory; otherwise through scratch memory and counters.
+  if (cluster_merge && (max_splits < 2 || max_splits > 16)) return MLR_BAD_SIZE;
   int status;
 #define MLR_LAUNCH_DECODE_TMA(D_, T_, S_)                                                                  \
   do {                                                                                                     \
     const size_t shared = 1024 + (size_t)(16 + 2 * ATTN_WARPS * S_ * T_) * D_ * 2;                         \
-    static_assert((size_t)ATTN_WARPS * 16 * (D_ + 2) * 4 <= (size_t)2 * ATTN_WARPS * S_ * T_ * D_ * 2, "merge area"); \
+    static_assert((size_t)(ATTN_WARPS + 1) * 16 * (D_ + 2) * 4 <= (size_t)2 * ATTN_WARPS * S_ * T_ * D_ * 2, "merge area"); \
     if ((status = set_shared(decode_attention_tma_kernel<D_, T_, S_>, shared)) != MLR_OK) return status;   \
-    launch_kernel(decode_attention_tma_kernel<D_, T_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream, \
+    if (cluster_merge) {                                                                                   \
+      static bool wide_clusters = false;                                                                   \
+      if (max_splits > 8 && !wide_clusters) {                                                              \
+        cudaError_t err = cudaFuncSetAttribute(decode_attention_tma_kernel<D_, T_, S_>,                     \
+                                               cudaFuncAttributeNonPortableClusterSizeAllowed, 1);        \
+        if (err != cudaSuccess) return (int)err;                                                           \
+        wide_clusters = true;                                                                              \
+      }                                                                                                    \
+      launch_kernel_clustered(decode_attention_tma_kernel<D_, T_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream, \
+                  max_splits, k_map, v_map, (const bf16*)q, (bf16*)out, decode_seg, seg_q_start, seg_pos0, block_table, seg_slot, \
+                  table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk,      \
+                  even_split, (float*)scratch, counters, max_splits, error_word, (const bf16*)qkv, inv_freq, \
+                  slots, (bf16*)const_cast<void*>(k_pool), (bf16*)const_cast<void*>(v_pool), write_kv, 1);  \
+    } else {                                                                                               \
+      launch_kernel(decode_attention_tma_kernel<D_, T_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream, \
                   k_map, v_map, (const bf16*)q, (bf16*)out, decode_seg, seg_q_start, seg_pos0, block_table, seg_slot, \
                   table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk,      \
                   even_split, (float*)scratch, counters, max_splits, error_word, (const bf16*)qkv, inv_freq, \
-                  slots, (bf16*)const_cast<void*>(k_pool), (bf16*)const_cast<void*>(v_pool), write_kv);    \
+                  slots, (bf16*)const_cast<void*>(k_pool), (bf16*)const_cast<void*>(v_pool), write_kv, 0);  \
+    }                                                                                                      \
   } while (0)
   // stages: tiles each warp keeps in flight or in use; 0 = the default.  Tiles hold 64 keys
   // (head_dim 64) or 32 keys (head_dim 128): 16 KB of K and V per stage either way.

@@ -128,6 +128,27 @@ inline void launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, 
   cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// The same for a grid of thread-block clusters of `cluster_x` CTAs along x (grid.x a multiple of it).
+template <typename... KernelArgs, typename... Args>
+inline void launch_kernel_clustered(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
+                                    cudaStream_t stream, int cluster_x, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = (unsigned)cluster_x;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 // One switch per library (each .cu is its own shared object).
 #define MLR_DEFINE_PDL_SWITCH \
   MLR_EXPORT void mlr_set_pdl(int enabled) { mlr::pdl_enabled() = enabled != 0; }

@@ -208,8 +208,8 @@ class ModelRunner:
         # milliseconds, which a size that passes by once (requests finishing one after another)
         # never earns back.
         self.graph_capture_after = 3
-        self._graphs: dict[tuple[int, bool, bool], _CapturedStep] = {}
-        self._graph_seen: dict[tuple[int, bool, bool], int] = {}
+        self._graphs: dict[tuple[int, bool, bool, int], _CapturedStep] = {}       # (batch, sample, feed, context limit)
+        self._graph_seen: dict[tuple[int, bool, bool, int], int] = {}
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ metadata
@@ -318,7 +318,8 @@ class ModelRunner:
 
     def _build_context(self, entries: Sequence[StepEntry], requests: list[RequestCache], *,
                        want_slots: bool = False, fixed: bool = False, packed=None,
-                       device_buffer: torch.Tensor | None = None, token_arrays: list | None = None) -> StepContext:
+                       device_buffer: torch.Tensor | None = None, token_arrays: list | None = None,
+                       kv_limit: int | None = None) -> StepContext:
         """Host-side description of the step, sent to the device.  ``fixed``: a captured decode step
         (contexts as long as the cache allows, so that every kernel plans against the cache's
         capacity); ``device_buffer`` is that graph's own metadata buffer.  ``want_slots`` adds the
@@ -337,7 +338,7 @@ class ModelRunner:
             token_ids=dev["token_ids"], positions=dev["positions"], wanted_rows=dev["wanted_rows"],
             seg_q_start=dev["seg_q_start"], seg_q_len=dev["seg_q_len"], seg_pos0=dev["seg_pos0"],
             seg_slot=dev["seg_slot"], max_q_len=int(lengths.max()),
-            max_kv_len=(cache.max_pages_per_request * cache.page_size if fixed
+            max_kv_len=((kv_limit or cache.max_pages_per_request * cache.page_size) if fixed
                         else int((position_start + lengths).max())),
             wanted_all_rows=(wanted_rows.shape[0] == total
                              and bool((wanted_rows == np.arange(total, dtype=np.int32)).all())))
@@ -406,12 +407,25 @@ class ModelRunner:
             kernels.advance_slots(ctx.seg_slot, state, ctx.seg_q_len, ctx.seg_pos0)
         return logits, tokens
 
-    def _graph_eligible(self, entries: Sequence[StepEntry], sample: bool, feed: bool) -> bool:
+    # A captured step plans its kernels against a context limit, not against the contexts of the
+    # step it was captured in.  Two limits: this many keys while every request is shorter (kernels
+    # may then choose plans that only pay for moderate contexts, such as the decode attention's
+    # merge through a cluster's shared memory), else the cache's capacity per request.
+    SHORT_CONTEXT = 8192
+
+    def _context_limit(self, requests: list[RequestCache]) -> int:
+        capacity = self.cache.max_pages_per_request * self.cache.page_size
+        if capacity <= self.SHORT_CONTEXT:
+            return capacity
+        longest = max(r.pending[1] for r in requests)
+        return self.SHORT_CONTEXT if longest <= self.SHORT_CONTEXT else capacity
+
+    def _graph_eligible(self, entries: Sequence[StepEntry], requests: list[RequestCache], sample: bool, feed: bool) -> bool:
         if not (self.use_graphs and len(entries) <= self.graph_max_batch
                 and isinstance(ops.current(), ops.CudaOps)
                 and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)):
             return False
-        key = (len(entries), sample, feed)
+        key = (len(entries), sample, feed, self._context_limit(requests))
         if key in self._graphs:
             return True
         seen = self._graph_seen.get(key, 0) + 1
@@ -441,7 +455,7 @@ class ModelRunner:
         size runs eagerly on the graph's fixed buffers and is then captured; later steps refresh at
         most the slots and the host's tokens, send changed table rows, and replay."""
         count = len(entries)
-        key = (count, sample, feed)
+        key = (count, sample, feed, self._context_limit(requests))
         captured = self._graphs.get(key)
         slots = tuple(r.slot for r in requests)
         if captured is not None and captured.graph is not None:
@@ -477,7 +491,7 @@ class ModelRunner:
         captured.stagings = [[torch.empty((2 * count + 8) * 4, dtype=torch.uint8, pin_memory=True), None]
                              for _ in range(3)]
         ctx = self._build_context(entries, requests, want_slots=sample, fixed=True, packed=packed,
-                                  device_buffer=captured.metadata)
+                                  device_buffer=captured.metadata, kv_limit=key[3])
         self._graphs[key] = captured
         captured.slots_now = slots
         self._prepare_decode(ctx, feed)
@@ -496,7 +510,7 @@ class ModelRunner:
 
     def launches_per_replay(self, batch: int, sampling: bool, feed: bool | None = None) -> int:
         """Kernels one replay of the captured step of this batch size launches (0 if not captured)."""
-        for (count, sample, fed), captured in self._graphs.items():
+        for (count, sample, fed, _), captured in self._graphs.items():
             if count == batch and sample == sampling and (feed is None or fed == feed) and captured.graph is not None:
                 return captured.launches
         return 0
@@ -526,7 +540,7 @@ class ModelRunner:
             raise ValueError("sampling takes at most one wanted place per request")
         requests = self.cache.begin_step([(e.request_id, len(e.tokens)) for e in entries])
         try:
-            if self._graph_eligible(entries, sample, feed):
+            if self._graph_eligible(entries, requests, sample, feed):
                 logits, tokens = self._graph_step(entries, requests, sample, feed)
                 if not borrow:
                     logits = logits.clone()

@@ -177,6 +177,7 @@ class CudaOps:
         self.use_fused_norm = True
         self.use_tma_attention = True
         self.use_fused_rope = True
+        self.use_cluster_merge = True       # chunks of a decode row merge through a cluster's shared memory
         self.split_prefill_items = True     # the tcgen05 prompt attention may cut long items into parts
         # MLR_TCGEN05_ATTENTION=0 in the environment keeps prompt attention on the mma.sync kernels
         self.use_tcgen05_attention = os.environ.get("MLR_TCGEN05_ATTENTION", "1") != "0"
@@ -453,6 +454,7 @@ class CudaOps:
     SKINNY_ROWS_SMALL_WEIGHT = 32     # rows up to which matrices of at most SKINNY_SMALL_WEIGHT elements stay with it
     SKINNY_SMALL_WEIGHT = 2 << 20
     SKINNY_LARGE_WEIGHT = 32 << 20    # elements from which 9..16 rows go to the tcgen05 kernel
+    CLUSTER_MERGE_MAX = 16            # chunks of one request and kv head that can form one thread-block cluster
     TMA_MIN_CHUNK = 256               # keys per CTA of the bulk-copy decode attention, at least
     TMA_CTAS_PER_SM = 3               # its CTAs that are resident at once on one SM
 
@@ -644,8 +646,18 @@ class CudaOps:
         if even_split:
             # the kernel divides each request's context over `splits` chunks of at least `chunk` keys
             chunk = self.TMA_MIN_CHUNK
-            splits = max(1, min(64, most_splits, self.TMA_CTAS_PER_SM * sms // max(1, batch.num_decode * num_kv_heads),
-                                -(-batch.max_kv_len // chunk)))
+            pairs = max(1, batch.num_decode * num_kv_heads)
+            resident = self.TMA_CTAS_PER_SM * sms
+            # More (request, kv head) pairs than resident CTAs: whole contexts per CTA would leave a
+            # second, nearly empty wave; four chunks each even it out (14B sizes, 64 requests:
+            # 320 -> 305 us per layer; below that number of pairs, cutting further only costs).
+            wanted = resident // pairs if pairs <= resident else 4
+            splits = max(1, min(64, most_splits, wanted, -(-batch.max_kv_len // chunk)))
+            # Up to CLUSTER_MERGE_MAX chunks merge through their cluster's shared memory, which saves
+            # several microseconds of global round trips; worth chunks of up to 512 keys instead of 256.
+            if (self.use_cluster_merge and splits > self.CLUSTER_MERGE_MAX
+                    and batch.max_kv_len <= self.CLUSTER_MERGE_MAX * 2 * chunk):
+                splits = self.CLUSTER_MERGE_MAX
         else:
             chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len, sms)
             if self.decode_chunk is not None:
@@ -670,7 +682,8 @@ class CudaOps:
                 batch.num_decode, num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
                 ctypes.c_float(scale), chunk, int(even_split), splits, int(self.decode_stages or 0),
                 _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _ptr(space["error_word"]),
-                _ptr(qkv), _ptr(inv_freq), _ptr(slots), int(bool(write_kv)), _stream()),
+                _ptr(qkv), _ptr(inv_freq), _ptr(slots), int(bool(write_kv)),
+                int(self.use_cluster_merge and 2 <= splits <= self.CLUSTER_MERGE_MAX), _stream()),
                 "decode attention (TMA)")
             return
         entry = (build.load_library("attention_mma").mlr_attention_decode_mma if mma

@@ -189,6 +189,24 @@ def test_a_batch_size_is_captured_only_once_it_recurs(setup):
         steps.append({"entries": [(rid, len(texts[rid]) - 10 + k, len(texts[rid]) - 9 + k) for rid in live],
                       "end": [rid for rid in live if k == decoded[rid] - 1]})
     results = replay(fresh, prompts, steps)
-    assert sorted(fresh.runner._graphs) == [(1, False, False)]
+    assert [key[:3] for key in fresh.runner._graphs] == [(1, False, False)]
     assert fresh.runner.graph_replays == 3          # of six steps: two eager, one captured, three replayed
     check_all(fresh, prompts, results, dtype, "captured late")
+
+
+def test_captured_steps_follow_the_context_limit(setup):
+    """A captured decode step plans against a context limit: a short one while every request is
+    below it, the cache's capacity after that.  A request that grows across the limit moves from one
+    captured step to the other; its logits stay the plain implementation's."""
+    name, dtype, engine, requests = setup
+    config, page = TINY[name]
+    fresh = TinyEngine(config, page, dtype, DEVICE, num_pages=64, max_requests=2, max_tokens=256,
+                       tensors=engine.tensors)
+    fresh.runner.SHORT_CONTEXT = 64
+    text = random_prompt(config.vocab_size, 80, 311)
+    steps = [{"entries": [("u", 0, 50)], "end": []}]
+    steps += [{"entries": [("u", 50 + k, 51 + k)], "end": ["u"] if k == 29 else []} for k in range(30)]
+    results = replay(fresh, {"u": text}, steps)
+    limits = sorted(key[3] for key in fresh.runner._graphs)
+    assert limits == [64, fresh.cache.max_pages_per_request * page], limits
+    check_all(fresh, {"u": text}, results, dtype, "across the context limit")
