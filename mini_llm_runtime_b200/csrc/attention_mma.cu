@@ -795,7 +795,7 @@ decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_poo
 // before the wait on the previous kernel (which writes this step's keys).
 // The stages are reused as the merge area once every warp has consumed its last tile.
 template <int D, int TKV, int STAGES>
-__global__ void __launch_bounds__(ATTN_THREADS)
+__global__ void __launch_bounds__(ATTN_THREADS, 3)     // three CTAs per SM with one stage: at most 168 registers
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                             const bf16* q, bf16* __restrict__ out, const int* __restrict__ decode_seg,
                             const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,

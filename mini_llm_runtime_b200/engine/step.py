@@ -411,7 +411,7 @@ class ModelRunner:
     # step it was captured in.  Two limits: this many keys while every request is shorter (kernels
     # may then choose plans that only pay for moderate contexts, such as the decode attention's
     # merge through a cluster's shared memory), else the cache's capacity per request.
-    SHORT_CONTEXT = 8192
+    SHORT_CONTEXT = 4096
 
     def _context_limit(self, requests: list[RequestCache]) -> int:
         capacity = self.cache.max_pages_per_request * self.cache.page_size

@@ -453,8 +453,20 @@ class CudaOps:
     SKINNY_ROWS = 16
     SKINNY_ROWS_SMALL_WEIGHT = 32     # rows up to which matrices of at most SKINNY_SMALL_WEIGHT elements stay with it
     SKINNY_SMALL_WEIGHT = 2 << 20
-    SKINNY_LARGE_WEIGHT = 32 << 20    # elements from which 9..16 rows go to the tcgen05 kernel
-    CLUSTER_MERGE_MAX = 16            # chunks of one request and kv head that can form one thread-block cluster
+    SKINNY_LARGE_WEIGHT = 32 << 20    # elements from which more than SKINNY_LARGE_WEIGHT_ROWS rows go to the tcgen05 kernel
+    SKINNY_LARGE_WEIGHT_ROWS = 0
+    # Chunks of one decode row and kv head that may form one thread-block cluster, and the longest
+    # chunk worth it.  A cluster lies within one GPC, one CTA per SM; with 18 SMs per GPC, 8 GPCs and
+    # three CTAs per SM only so many clusters run together, and a launch with more comes in rounds
+    # (measured: 32 clusters of 13 CTAs lose to no clusters at all, 32 clusters of 8 win).
+    CLUSTER_SIZES = (16, 8, 6, 4, 3, 2)
+    CLUSTER_MAX_CHUNK = 768
+
+    def clusters_together(self, size: int) -> int:
+        """Clusters of ``size`` CTAs that certainly run at once (a tenth below the arithmetic: launches
+        right at it measured slower than without clusters)."""
+        return 8 * (18 // size) * self.TMA_CTAS_PER_SM * 9 // 10
+
     TMA_MIN_CHUNK = 256               # keys per CTA of the bulk-copy decode attention, at least
     TMA_CTAS_PER_SM = 3               # its CTAs that are resident at once on one SM
 
@@ -468,10 +480,12 @@ class CudaOps:
         if (not self.use_skinny or weight.shape[0] >= 128 * self.sm_count(x.device)
                 or (swiglu and x.shape[1] > 2048)):
             return False
-        # More than 8 rows double this kernel's token blocks; on matrices of tens of megabytes it then
-        # loses to the tcgen05 kernel even with the separate norm and add kernels that path needs
-        # (7B down projection, 16 rows: 38.4 against 27.4 + 3 us; q|k|v and output projection stay).
-        if rows > 8 and weight.shape[0] * weight.shape[1] >= self.SKINNY_LARGE_WEIGHT:
+        # Matrices of tens of megabytes go to the tcgen05 kernel at every row count, even with the
+        # separate norm and add kernels that path needs: its operands wait in shared memory, not
+        # in registers, so its CTAs start beside the kernels before them, while this kernel's
+        # 512-thread CTAs for long rows fill a register file each and come in two rounds (7B sizes,
+        # 8 rows, down projection inside a step: 51 us against 28; the whole step 4.42 -> 3.77 ms).
+        if rows > self.SKINNY_LARGE_WEIGHT_ROWS and weight.shape[0] * weight.shape[1] >= self.SKINNY_LARGE_WEIGHT:
             return False
         if rows <= self.SKINNY_ROWS:
             return True
@@ -637,6 +651,7 @@ class CudaOps:
         sms = space["sm_count"]
         tma = mma and self.use_tma_attention and page_size >= 8 and page_size & (page_size - 1) == 0
         even_split = tma and self.decode_chunk is None
+        cluster = 0
         # float32 partial states of one split of every (row, head); the scratch buffer is fixed
         per_split = batch.num_decode * num_heads * (head_dim + 2) * 4
         most_splits = space["attention_scratch"].numel() // max(1, per_split)
@@ -653,11 +668,13 @@ class CudaOps:
             # 320 -> 305 us per layer; below that number of pairs, cutting further only costs).
             wanted = resident // pairs if pairs <= resident else 4
             splits = max(1, min(64, most_splits, wanted, -(-batch.max_kv_len // chunk)))
-            # Up to CLUSTER_MERGE_MAX chunks merge through their cluster's shared memory, which saves
-            # several microseconds of global round trips; worth chunks of up to 512 keys instead of 256.
-            if (self.use_cluster_merge and splits > self.CLUSTER_MERGE_MAX
-                    and batch.max_kv_len <= self.CLUSTER_MERGE_MAX * 2 * chunk):
-                splits = self.CLUSTER_MERGE_MAX
+            # Up to 16 chunks can merge through their thread-block cluster's shared memory, which
+            # saves several microseconds of global round trips; worth chunks of up to 768 keys.
+            for size in self.CLUSTER_SIZES:
+                if (self.use_cluster_merge and size <= splits and pairs <= self.clusters_together(size)
+                        and batch.max_kv_len <= size * self.CLUSTER_MAX_CHUNK):
+                    splits = cluster = size
+                    break
         else:
             chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len, sms)
             if self.decode_chunk is not None:
@@ -670,6 +687,7 @@ class CudaOps:
                 splits = max(1, -(-batch.max_kv_len // chunk))
         if even_split and self.decode_max_splits is not None:
             splits = min(most_splits, max(splits, self.decode_max_splits))
+            cluster = 0
         if rope is not None and not tma:
             raise KernelError("the fused position encoding needs the bulk-copy decode kernel")
         qkv, inv_freq, slots, write_kv = rope if rope is not None else (None, None, None, False)
@@ -683,7 +701,7 @@ class CudaOps:
                 ctypes.c_float(scale), chunk, int(even_split), splits, int(self.decode_stages or 0),
                 _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _ptr(space["error_word"]),
                 _ptr(qkv), _ptr(inv_freq), _ptr(slots), int(bool(write_kv)),
-                int(self.use_cluster_merge and 2 <= splits <= self.CLUSTER_MERGE_MAX), _stream()),
+                int(cluster == splits and cluster >= 2), _stream()),
                 "decode attention (TMA)")
             return
         entry = (build.load_library("attention_mma").mlr_attention_decode_mma if mma
