@@ -463,9 +463,9 @@ class CudaOps:
     CLUSTER_MAX_CHUNK = 768
 
     def clusters_together(self, size: int) -> int:
-        """Clusters of ``size`` CTAs that certainly run at once (a tenth below the arithmetic: launches
+        """Clusters of ``size`` CTAs that certainly run at once (a fifth below the arithmetic: launches
         right at it measured slower than without clusters)."""
-        return 8 * (18 // size) * self.TMA_CTAS_PER_SM * 9 // 10
+        return 8 * (18 // size) * self.TMA_CTAS_PER_SM * 8 // 10
 
     TMA_MIN_CHUNK = 256               # keys per CTA of the bulk-copy decode attention, at least
     TMA_CTAS_PER_SM = 3               # its CTAs that are resident at once on one SM
@@ -669,10 +669,10 @@ class CudaOps:
             wanted = resident // pairs if pairs <= resident else 4
             splits = max(1, min(64, most_splits, wanted, -(-batch.max_kv_len // chunk)))
             # Up to 16 chunks can merge through their thread-block cluster's shared memory, which
-            # saves several microseconds of global round trips; worth chunks of up to 768 keys.
+            # saves several microseconds of global round trips; worth fewer chunks of up to 768 keys.
             for size in self.CLUSTER_SIZES:
                 if (self.use_cluster_merge and size <= splits and pairs <= self.clusters_together(size)
-                        and batch.max_kv_len <= size * self.CLUSTER_MAX_CHUNK):
+                        and (size == splits or batch.max_kv_len <= size * self.CLUSTER_MAX_CHUNK)):
                     splits = cluster = size
                     break
         else:
