@@ -459,13 +459,13 @@ class CudaOps:
     # chunk worth it.  A cluster lies within one GPC, one CTA per SM; with 18 SMs per GPC, 8 GPCs and
     # three CTAs per SM only so many clusters run together, and a launch with more comes in rounds
     # (measured: 32 clusters of 13 CTAs lose to no clusters at all, 32 clusters of 8 win).
-    CLUSTER_SIZES = (16, 8, 6, 4, 3, 2)
+    CLUSTER_SIZES = (16, 8, 6)       # smaller clusters measured no gain: few chunks merge quickly either way
     CLUSTER_MAX_CHUNK = 768
 
     def clusters_together(self, size: int) -> int:
-        """Clusters of ``size`` CTAs that certainly run at once (a fifth below the arithmetic: launches
+        """Clusters of ``size`` CTAs that certainly run at once (a tenth below the arithmetic: launches
         right at it measured slower than without clusters)."""
-        return 8 * (18 // size) * self.TMA_CTAS_PER_SM * 8 // 10
+        return 8 * (18 // size) * self.TMA_CTAS_PER_SM * 9 // 10
 
     TMA_MIN_CHUNK = 256               # keys per CTA of the bulk-copy decode attention, at least
     TMA_CTAS_PER_SM = 3               # its CTAs that are resident at once on one SM
