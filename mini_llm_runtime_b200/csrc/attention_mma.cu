@@ -904,6 +904,22 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
 
   const size_t qkv_width = (size_t)(heads + 2 * kv_heads) * D;
+  // The warp whose tile holds the newest position fetches the step's key and value now, beside the
+  // queries, instead of when it reaches that tile.
+  const int newest_tile = position / TKV - tile_begin;          // among this chunk's tiles, if it holds it
+  const bool owns_newest = inject && newest_tile % ATTN_WARPS == warp;
+  bf16 new_key[HALF / 32][2], new_value[D / 32];
+  if (owns_newest) {
+    const bf16* k_src = qkv + (size_t)row * qkv_width + (size_t)(heads + kv_head) * D;
+    const bf16* v_src = k_src + (size_t)kv_heads * D;
+#pragma unroll
+    for (int j = 0; j < HALF / 32; ++j) {
+      new_key[j][0] = k_src[lane + 32 * j];
+      new_key[j][1] = k_src[lane + 32 * j + HALF];
+    }
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) new_value[j] = v_src[lane + 32 * j];
+  }
   if (fused) {
     // thread -> pair index i (the same for all its items, as 128 % HALF == 0) and rows g0, g0 + 128/HALF, ..
     const int i = threadIdx.x % HALF;
@@ -925,7 +941,6 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
   }
   cp_async_commit();
-  const int newest_tile = position / TKV - tile_begin;          // among this chunk's tiles, if it holds it
 
   // Rows that are no real head (the group padded to the MMA's 16 rows) have zero queries; their
   // states are computed like the others and never stored.
@@ -957,20 +972,20 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       const long long slot = new_slot;
       const long long page = slot / page_size;
       const size_t at = (((size_t)page * kv_heads + kv_head) * page_size + (size_t)(slot - page * page_size)) * D;
-      const bf16* k_src = qkv + (size_t)row * qkv_width + (size_t)(heads + kv_head) * D;
-      const bf16* v_src = k_src + (size_t)kv_heads * D;
 #pragma unroll
       for (int j = 0; j < HALF / 32; ++j) {
         const int i = lane + 32 * j;
         float r1, r2;
-        rotate_pair(__bfloat162float(k_src[i]), __bfloat162float(k_src[i + HALF]), key_sine[j], key_cosine[j], &r1, &r2);
+        rotate_pair(__bfloat162float(new_key[j][0]), __bfloat162float(new_key[j][1]), key_sine[j], key_cosine[j], &r1, &r2);
         const bf16 y1 = __float2bfloat16_rn(r1), y2 = __float2bfloat16_rn(r2);
         tile_at<D, true, TKV>(k_tile, r, i >> 3)[i & 7] = y1;
         tile_at<D, true, TKV>(k_tile, r, (i + HALF) >> 3)[(i + HALF) & 7] = y2;
         if (slot >= 0) { k_pool_w[at + i] = y1; k_pool_w[at + i + HALF] = y2; }
       }
-      for (int i = lane; i < D; i += 32) {
-        const bf16 v = v_src[i];
+#pragma unroll
+      for (int j = 0; j < D / 32; ++j) {
+        const int i = lane + 32 * j;
+        const bf16 v = new_value[j];
         tile_at<D, true, TKV>(v_tile, r, i >> 3)[i & 7] = v;
         if (slot >= 0) v_pool_w[at + i] = v;
       }
