@@ -264,7 +264,10 @@ MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, v
   // long rows (the down projection): 16 warps, or 8 where 16 would run out of registers.
   const bool long_rows = K > 2048;
   if (M <= 8) {
-    if (long_rows) return skinny_launch<16, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+    // 16 warps fill an SM's register file with one CTA; rows of up to 4,096 go to 8 warps, two CTAs
+    // per SM, so that the 224 to 288 CTAs of a 7B attention projection run in one round
+    if (K > 4096) return skinny_launch<16, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+    if (long_rows) return skinny_launch<8, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
     return skinny_launch<4, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
   }
   if (M <= 16) {

@@ -208,7 +208,8 @@ def test_tensor_core_linear_many_rows(m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32, 33, 64])
-@pytest.mark.parametrize("n,k", [(896, 896), (1152, 896), (896, 4864), (200, 72), (130, 64), (4000, 136), (5120, 5120)])
+@pytest.mark.parametrize("n,k", [(896, 896), (1152, 896), (896, 4864), (200, 72), (130, 64), (4000, 136), (5120, 5120),
+                                 (520, 3584), (72, 2056)])
 def test_few_rows_linear(m, n, k):
     """The few-rows kernel (mma.sync on 16-row weight groups, K shared by the CTA's warps) against
     float64, and against the tcgen05 kernel on the same inputs."""
@@ -240,7 +241,7 @@ def _check_few_rows(m, n, k, x, w, b, want):
 
 
 @pytest.mark.parametrize("m", [1, 7, 16, 30, 64])
-@pytest.mark.parametrize("n,k,eps", [(896, 4864, 1e-6), (1152, 896, 1e-5), (100, 72, 1e-3), (24, 4104, 1e-6)])
+@pytest.mark.parametrize("n,k,eps", [(896, 4864, 1e-6), (1152, 896, 1e-5), (100, 72, 1e-3), (24, 4104, 1e-6), (40, 3584, 1e-6)])
 def test_few_rows_linear_with_norm_and_residual(m, n, k, eps):
     """The row scale of an RMS norm taken inside the product, and the result added into a residual
     in place; alone and together, against the same operations done separately in float64.  The
