@@ -231,15 +231,21 @@ __device__ __forceinline__ void reduce_swapped_swiglu(const float* partials, int
 // SWAP = false: A (128 rows) = activations, B (BN rows) = weights; tile row = output row m.
 // SWIGLU: the weight rows come in blocks of 128 = 64 gate rows followed by the 64 up rows of the
 // same outputs; the epilogue writes silu(gate) * up, [M, N/2].
-template <int BN, bool SWAP, bool SWIGLU>
+// BM = 256 (many rows only): the CTA computes two 128-row accumulators side by side in tensor memory
+// from one load of the BN-row operand, which halves that operand's traffic from L2 per MMA (the
+// bound of the large products); no split-K in that form.
+template <int BN, bool SWAP, bool SWIGLU, int BM = TILE_ROWS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
-  constexpr uint32_t A_BYTES = TILE_ROWS * TILE_K * 2;
+  constexpr int HALVES = BM / TILE_ROWS;
+  constexpr uint32_t HALF_BYTES = TILE_ROWS * TILE_K * 2;
+  constexpr uint32_t A_BYTES = BM * TILE_K * 2;
   constexpr uint32_t B_BYTES = BN * TILE_K * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t TMEM_COLS = BN * HALVES < 32 ? 32 : BN * HALVES;
   static_assert(!SWIGLU || SWAP || BN % 128 == 0, "fused SwiGLU needs gate and up columns in one tile");
+  static_assert(BM == TILE_ROWS || (BM == 2 * TILE_ROWS && !SWAP && BN * HALVES <= 512), "two accumulators: many rows, 512 columns");
 
   extern __shared__ uint8_t raw_shared[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)raw_shared + 1023) & ~(uintptr_t)1023);
@@ -249,7 +255,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
-  const int a_row0 = blockIdx.x * TILE_ROWS;   // first row of the 128-row operand
+  const int a_row0 = blockIdx.x * BM;          // first row of the 128-row (or 256-row) operand
   const int b_row0 = blockIdx.y * BN;          // first row of the BN-row operand
   const int split = blockIdx.z;
   const int total_kb = (p.K + TILE_K - 1) / TILE_K;
@@ -291,8 +297,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int i = 0; i < ahead; ++i) {
       uint8_t* stage = tiles + (size_t)i * STAGE_BYTES;
       const int k = (kb_begin + i) * TILE_K;
-      if (SWAP) tma_load_2d(&map_b, &full_bar[i], stage + A_BYTES, k, b_row0);
-      else tma_load_2d(&map_a, &full_bar[i], stage, k, a_row0);
+      if (SWAP) {
+        tma_load_2d(&map_b, &full_bar[i], stage + A_BYTES, k, b_row0);
+      } else {
+#pragma unroll
+        for (int half = 0; half < HALVES; ++half)
+          tma_load_2d(&map_a, &full_bar[i], stage + half * HALF_BYTES, k, a_row0 + half * TILE_ROWS);
+      }
     }
     int s = ahead == stages ? 0 : ahead, round = ahead == stages ? 1 : 0;
     for (int i = ahead; i < num_kb; ++i) {
@@ -300,7 +311,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_expect_tx(&full_bar[s], STAGE_BYTES);
       uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
       const int k = (kb_begin + i) * TILE_K;
-      tma_load_2d(&map_a, &full_bar[s], stage, k, a_row0);
+#pragma unroll
+      for (int half = 0; half < HALVES; ++half)
+        tma_load_2d(&map_a, &full_bar[s], stage + half * HALF_BYTES, k, a_row0 + half * TILE_ROWS);
       tma_load_2d(&map_b, &full_bar[s], stage + A_BYTES, k, b_row0);
       if (++s == stages) { s = 0; ++round; }
     }
@@ -315,8 +328,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
       for (int k = 0; k < TILE_K / MMA_K; ++k)
-        umma(tmem_base, smem_descriptor(a_addr + k * MMA_K * 2), smem_descriptor(b_addr + k * MMA_K * 2), idesc,
-             (i > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int half = 0; half < HALVES; ++half)
+          umma(tmem_base + half * BN, smem_descriptor(a_addr + half * HALF_BYTES + k * MMA_K * 2),
+               smem_descriptor(b_addr + k * MMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
       umma_commit(&empty_bar[s]);
       if (++s == stages) { s = 0; ++round; }
     }
@@ -377,17 +392,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // not swapped: each group of 128 columns holds 64 gate columns, then the 64 up columns of
       // the same outputs, all in this thread's TMEM lane.
       // tcgen05.ld is warp-collective: every lane runs the loads, only the stores depend on m.
-      const int m = a_row0 + row;
       const int half = p.N >> 1;
       if (finish) {
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 2; cc += 32) {
-          const int block = cc >> 6, c0 = cc & 63;           // which 128-column group, offset in it
+        for (int cc = 0; cc < HALVES * (BN / 2); cc += 32) {
+          const int accumulator = cc / (BN / 2), within = cc - accumulator * (BN / 2);
+          const int block = within >> 6, c0 = within & 63;   // which 128-column group, offset in it
+          const int m = a_row0 + accumulator * TILE_ROWS + row;
+          const uint32_t from = lane_base + accumulator * BN + block * 128;
           uint32_t g[32], u[32];
-          tmem_issue_load16(lane_base + block * 128 + c0, g);
-          tmem_issue_load16(lane_base + block * 128 + c0 + 16, g + 16);
-          tmem_issue_load16(lane_base + block * 128 + 64 + c0, u);
-          tmem_issue_load16(lane_base + block * 128 + 64 + c0 + 16, u + 16);
+          tmem_issue_load16(from + c0, g);
+          tmem_issue_load16(from + c0 + 16, g + 16);
+          tmem_issue_load16(from + 64 + c0, u);
+          tmem_issue_load16(from + 64 + c0 + 16, u + 16);
           tmem_wait_loads();
           if (m >= p.M) continue;
 #pragma unroll
@@ -418,17 +435,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // (a load and its wait per 16 columns made the epilogue as long as a short main loop)
       constexpr int ROUND = BN >= 64 ? 64 : BN;
 #pragma unroll 1
-      for (int c00 = 0; c00 < BN; c00 += ROUND) {
+      for (int cc = 0; cc < HALVES * BN; cc += ROUND) {
+        const int accumulator = cc / BN, c00 = cc - accumulator * BN;
         float v[ROUND];
         if (reduce) {
 #pragma unroll
           for (int q = 0; q < ROUND; q += 16) reduce_partials<BN>(partials, p.splits, c00 + q, row, v + q);
         } else {
 #pragma unroll
-          for (int q = 0; q < ROUND; q += 16) tmem_issue_load16(lane_base + c00 + q, reinterpret_cast<uint32_t*>(v) + q);
+          for (int q = 0; q < ROUND; q += 16)
+            tmem_issue_load16(lane_base + accumulator * BN + c00 + q, reinterpret_cast<uint32_t*>(v) + q);
           tmem_wait_loads();
         }
-        const int m = a_row0 + row;
+        const int m = a_row0 + accumulator * TILE_ROWS + row;
         if (m >= p.M) continue;
 #pragma unroll
         for (int q = 0; q < ROUND; q += 16) {
@@ -472,12 +491,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 
 // ---------------------------------------------------------------- host side
-template <int BN, bool SWAP, bool SWIGLU>
+template <int BN, bool SWAP, bool SWIGLU, int BM = TILE_ROWS>
 static int launch(const void* x, const void* w, const GemmParams& p, int splits, cudaStream_t stream) {
-  const size_t shared = (size_t)p.stages * (TILE_ROWS * TILE_K * 2 + BN * TILE_K * 2) + 1024;
+  const size_t shared = (size_t)p.stages * (BM * TILE_K * 2 + BN * TILE_K * 2) + 1024;
+  if (BM != TILE_ROWS && splits != 1) return MLR_BAD_SIZE;
   static size_t configured = 0;
   if (shared > configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, SWAP, SWIGLU>,
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, SWAP, SWIGLU, BM>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;
     configured = shared;
@@ -488,16 +508,16 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
   CUtensorMap map_a, map_b;
   if (!cached_tile_map(&map_a, a_base, a_rows, p.K, TILE_ROWS) || !cached_tile_map(&map_b, b_base, b_rows, p.K, BN))
     return MLR_BAD_ALIGNMENT;
-  dim3 grid((a_rows + TILE_ROWS - 1) / TILE_ROWS, (b_rows + BN - 1) / BN, splits);
-  launch_kernel(gemm_tcgen05_kernel<BN, SWAP, SWIGLU>, dim3(grid), dim3(GEMM_THREADS), shared, stream, map_a, map_b, p);
+  dim3 grid((a_rows + BM - 1) / BM, (b_rows + BN - 1) / BN, splits);
+  launch_kernel(gemm_tcgen05_kernel<BN, SWAP, SWIGLU, BM>, dim3(grid), dim3(GEMM_THREADS), shared, stream, map_a, map_b, p);
   return launch_status();
 }
 
 // Tile shape, split count and ring depth for a product of this shape.
-struct GemmPlan { int bn, tiles, splits, stages, kb_per_split; };
+struct GemmPlan { int bn, tiles, splits, stages, kb_per_split, bm; };
 
 // Overrides for measurements (0 = the planner decides): tile width and ring depth of many-row products.
-static int forced_bn = 0, forced_stages = 0, forced_splits = 0;
+static int forced_bn = 0, forced_stages = 0, forced_splits = 0, forced_bm = 0;
 
 // Many rows (M > 128): tile width, ring depth and split count by a small model of the kernel,
 // in microseconds.  A CTA costs a fixed 1.5 us (barriers, tensor-memory allocation, first loads)
@@ -516,23 +536,27 @@ static int forced_bn = 0, forced_stages = 0, forced_splits = 0;
 static GemmPlan plan_many_rows(int M, int N, int K, bool swiglu, int sms) {
   const int total_kb = (K + TILE_K - 1) / TILE_K;
   const int tiles_m = (M + TILE_ROWS - 1) / TILE_ROWS;
-  GemmPlan best = {128, tiles_m * ((N + 127) / 128), 1, 2, total_kb};
+  GemmPlan best = {128, tiles_m * ((N + 127) / 128), 1, 2, total_kb, TILE_ROWS};
   double best_cost = 1e30;
-  for (int bn = 128; bn <= 256; bn += 128) {
+  for (int shape = 0; shape < 3; ++shape) {
+    // 128 x 128, 128 x 256, and 256 x 256 (two accumulators per CTA; no split-K)
+    const int bn = shape == 0 ? 128 : 256, bm = shape == 2 ? 2 * TILE_ROWS : TILE_ROWS;
     if (bn == 256 && N < 256) continue;
+    if (bm > TILE_ROWS && M < 2 * bm) continue;
     if (forced_bn != 0 && forced_bn != bn) continue;
-    const size_t stage_bytes = TILE_ROWS * TILE_K * 2 + (size_t)bn * TILE_K * 2;
-    const int tiles = tiles_m * ((N + bn - 1) / bn);
+    if (forced_bm != 0 && forced_bm != bm) continue;
+    const size_t stage_bytes = (size_t)bm * TILE_K * 2 + (size_t)bn * TILE_K * 2;
+    const int tiles = ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
     for (int stages = 2; stages <= MAX_STAGES; ++stages) {
       const size_t shared = stages * stage_bytes + 2048;
       if (shared > 225 * 1024) break;
       if (forced_stages >= 2 && forced_stages != stages) continue;
       int per_sm = (int)((227 * 1024) / shared);
-      const int by_tensor_memory = 512 / bn;
+      const int by_tensor_memory = 512 / (bn * (bm / TILE_ROWS));
       if (per_sm > by_tensor_memory) per_sm = by_tensor_memory;
       if (per_sm > 3) per_sm = 3;
       for (int splits = 1; splits <= 4; ++splits) {
-        if (splits > 1 && (swiglu || M > 1024 || total_kb < 8 * splits)) break;   // that epilogue reads tensor memory only
+        if (splits > 1 && (swiglu || M > 1024 || total_kb < 8 * splits || bm > TILE_ROWS)) break;   // that epilogue reads tensor memory only
         if (forced_splits >= 1 && forced_splits != splits) continue;
         if (splits > 1 && (long long)tiles * splits * bn * TILE_ROWS * 4 > (24ll << 20)) break;
         const long long ctas = (long long)tiles * splits;
@@ -541,14 +565,14 @@ static GemmPlan plan_many_rows(int M, int N, int K, bool swiglu, int sms) {
         const int sharing = (int)(ctas < resident ? (ctas + sms - 1) / sms : per_sm);   // CTAs that really share an SM
         const double kb = (double)((total_kb + splits - 1) / splits);
         const double stage_kb = (double)stage_bytes / 1024.0;
-        double per_kb = 0.14 * (bn / 128) * sharing;                                   // tensor pipe
+        double per_kb = 0.14 * (bn / 128) * (bm / TILE_ROWS) * sharing;                // tensor pipe
         if ((0.5 + 0.03 * stage_kb) / stages > per_kb) per_kb = (0.5 + 0.03 * stage_kb) / stages;   // load latency
         if (sharing * stage_kb / 112.0 > per_kb) per_kb = sharing * stage_kb / 112.0;  // operand bandwidth of the SM
-        double cost = rounds * (1.5 + kb * per_kb + 1.5 * (bn / 128) + ((per_sm == 1 && rounds > 1) ? 4.0 : 0.0));
+        double cost = rounds * (1.5 + kb * per_kb + 1.5 * (bn / 128) * (bm / TILE_ROWS) + ((per_sm == 1 && rounds > 1) ? 4.0 : 0.0));
         if (splits > 1) cost += 4.0 + (double)splits * bn * 512.0 / 50e3;
         if (cost < best_cost) {
           best_cost = cost;
-          best.bn = bn; best.tiles = tiles; best.splits = splits; best.stages = stages;
+          best.bn = bn; best.tiles = tiles; best.splits = splits; best.stages = stages; best.bm = bm;
         }
       }
     }
@@ -562,6 +586,7 @@ static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
   const int sms = sm_count();
   if (M > 128) return plan_many_rows(M, N, K, swiglu, sms);
   GemmPlan plan;
+  plan.bm = TILE_ROWS;
   const int total_kb = (K + TILE_K - 1) / TILE_K;
   plan.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   plan.tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
@@ -615,10 +640,11 @@ using namespace mlr;
 MLR_DEFINE_PDL_SWITCH
 
 // For measurements only (the engine never calls it): overrides of the planner; 0 leaves a choice to it.
-MLR_EXPORT void mlr_gemm_tcgen05_debug(int bn, int stages, int splits) {
+MLR_EXPORT void mlr_gemm_tcgen05_debug(int bn, int stages, int splits, int bm) {
   forced_bn = bn;
   forced_stages = stages;
   forced_splits = splits;
+  forced_bm = bm;
 }
 
 // Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
@@ -660,6 +686,7 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
     if (M <= 32) return launch<32, true, true>(x, w, p, plan.splits, stream);
     if (M <= 64) return launch<64, true, true>(x, w, p, plan.splits, stream);
     if (M <= 128) return launch<128, true, true>(x, w, p, plan.splits, stream);
+    if (plan.bm == 2 * TILE_ROWS) return launch<256, false, true, 2 * TILE_ROWS>(x, w, p, plan.splits, stream);
     if (plan.bn == 256) return launch<256, false, true>(x, w, p, plan.splits, stream);
     return launch<128, false, true>(x, w, p, plan.splits, stream);
   }
@@ -667,6 +694,7 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
   if (M <= 32) return launch<32, true, false>(x, w, p, plan.splits, stream);
   if (M <= 64) return launch<64, true, false>(x, w, p, plan.splits, stream);
   if (M <= 128) return launch<128, true, false>(x, w, p, plan.splits, stream);
+  if (plan.bm == 2 * TILE_ROWS) return launch<256, false, false, 2 * TILE_ROWS>(x, w, p, plan.splits, stream);
   if (plan.bn == 256) return launch<256, false, false>(x, w, p, plan.splits, stream);
   return launch<128, false, false>(x, w, p, plan.splits, stream);
 }
