@@ -266,7 +266,9 @@ MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, v
   if (M <= 8) {
     // 16 warps fill an SM's register file with one CTA; rows of up to 4,096 go to 8 warps, two CTAs
     // per SM, so that the 224 to 288 CTAs of a 7B attention projection run in one round
-    if (K > 4096) return skinny_launch<16, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+    // (longer rows too when there are more CTAs than SMs: one 16-warp CTA per SM would come in three rounds)
+    if (K > 4096 && (N + 15) / 16 <= sm_count())
+      return skinny_launch<16, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
     if (long_rows) return skinny_launch<8, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
     return skinny_launch<4, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
   }
