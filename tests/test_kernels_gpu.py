@@ -509,6 +509,40 @@ def test_decode_attention_split_kv(heads, kv_heads, head_dim, page, chunk):
     assert_close(both, generic, torch.bfloat16, "tensor-core kernels against the generic kernel")
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (28, 4, 128, 16), (5, 1, 128, 64)])
+def test_decode_attention_merges_through_clusters_of_every_size(heads, kv_heads, head_dim, page):
+    """Contexts of up to 4,096 keys for few requests: the chunks of a (request, kv head) form a
+    thread-block cluster of 16, 8 or 6 CTAs (by the number of pairs) that merges through shared
+    memory.  Short contexts in the same launch leave most of their cluster's CTAs without keys;
+    one far key is made dominant so that a chunk merged with the wrong weight shows.  Against the
+    plain stand-in and against the merge through scratch memory."""
+    contexts_by_rows = {4: [4095, 100, 2600, 257], 9: [4000, 3, 255, 256, 1023, 3071, 2048, 64, 700],
+                        20: [4095] + [137 * i % 3900 + 1 for i in range(19)],
+                        28: [4095] + [211 * i % 4000 + 1 for i in range(27)]}
+    for rows, contexts in contexts_by_rows.items():
+        if rows * kv_heads > 64:          # more pairs than clusters of 6 that run together
+            continue
+        segments = [(c, 1) for c in contexts]
+        q, k_pool, v_pool, batch, table = make_attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, segments, 70 + rows)
+        direction = q[0, :head_dim].float()                      # request 0, head 0: key 70 dominates
+        pg, off = table[0, 70 // page], 70 % page
+        k_pool[pg, 0, off] = (direction * (40.0 / direction.norm() ** 2 * math.sqrt(head_dim))).to(torch.bfloat16)
+        v_pool[pg, 0, off] = torch.full((head_dim,), 100.0).to(torch.bfloat16)
+        got, want = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+        torch.cuda.synchronize()
+        cuda().raise_if_device_error()
+        assert_close(got, want, torch.bfloat16, f"decode attention, {rows} rows, cluster merge")
+        assert float(got[0, :head_dim].float().mean()) > 90.0, "the dominant far key was lost"
+        again, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+        assert torch.equal(got, again), "chunks are merged in chunk order: same bits every time"
+        cuda().use_cluster_merge = False
+        try:
+            other, _ = run_attention_both(torch.bfloat16, q, k_pool, v_pool, batch, heads, kv_heads, head_dim, None)
+        finally:
+            cuda().use_cluster_merge = True
+        assert_close(got, other, torch.bfloat16, "cluster merge against the merge through scratch memory")
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (3, 1, 128, 8), (8, 8, 64, 64), (8, 2, 128, 32), (5, 1, 64, 256)])
 @pytest.mark.parametrize("write_kv", [True, False])
 def test_decode_attention_with_fused_position_encoding(heads, kv_heads, head_dim, page, write_kv):
