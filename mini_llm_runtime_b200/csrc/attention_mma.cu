@@ -678,7 +678,6 @@ decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_poo
                             int* __restrict__ counters, int max_splits) {
   pdl_trigger();
   pdl_wait();
-  constexpr int STATE = D + 2;
   extern __shared__ __align__(128) uint8_t attn_shared[];
   bf16* q_tile = reinterpret_cast<bf16*>(attn_shared);            // [16][D], rows >= group are zeros
   bf16* k_tiles = q_tile + 16 * D;                                 // STAGES x [64][D]
@@ -1018,11 +1017,20 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
                    split, splits, max_splits, cluster_merge ? max_splits : 0);
 }
 
+// Opt in to more than 48 KB of dynamic shared memory, once per kernel and size (the attribute call
+// costs the host a microsecond or two, and eager steps launch these kernels once per layer).
 template <typename Kernel>
 static int set_shared(Kernel kernel, size_t bytes) {
   if (bytes <= 48 * 1024) return MLR_OK;
+  static Kernel known[16];
+  static size_t granted[16];
+  static int count = 0;
+  for (int i = 0; i < count; ++i)
+    if (known[i] == kernel && granted[i] >= bytes) return MLR_OK;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-  return err == cudaSuccess ? MLR_OK : (int)err;
+  if (err != cudaSuccess) return (int)err;
+  if (count < 16) { known[count] = kernel; granted[count] = bytes; ++count; }
+  return MLR_OK;
 }
 
 }  // namespace mlr
