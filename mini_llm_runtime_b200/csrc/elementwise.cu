@@ -185,6 +185,9 @@ __global__ void rope_kv_write_kernel(const T* qkv, const int* __restrict__ posit
                                      const long long* __restrict__ slots, T* __restrict__ q_out,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, int heads,
                                      int kv_heads, int head_dim, int page_size, int write_kv) {
+  // The token's sines and cosines (one per pair index) are taken once, into shared memory: every
+  // head uses the same head_dim/2 angles.
+  __shared__ float sines[128], cosines[128];
   pdl_trigger();
   pdl_wait();
   const int token = blockIdx.x;
@@ -196,55 +199,67 @@ __global__ void rope_kv_write_kernel(const T* qkv, const int* __restrict__ posit
   const long long page = slot >= 0 ? slot / page_size : 0;
   const int offset = slot >= 0 ? (int)(slot - page * page_size) : 0;
   const bool store = write_kv != 0 && slot >= 0;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(position * inv_freq[i], &sines[i], &cosines[i]);
+  __syncthreads();
 
   const int rotated_heads = heads + kv_heads;
-  if ((half & 1) == 0) {
-    // two adjacent pair indices per item (4-byte accesses for 16-bit types); the angle depends on
-    // the index only, so a thread that keeps its index across items evaluates sine and cosine once
-    const int half_pairs = half >> 1;
-    int cached = -1;
-    float sine[2] = {0.f, 0.f}, cosine[2] = {1.f, 1.f};
-    for (int item = threadIdx.x; item < rotated_heads * half_pairs; item += blockDim.x) {
-      const int head = item / half_pairs, i = (item - head * half_pairs) * 2;
-      if (i != cached) {
-        sincosf(position * inv_freq[i], &sine[0], &cosine[0]);
-        sincosf(position * inv_freq[i + 1], &sine[1], &cosine[1]);
-        cached = i;
-      }
-      const T* src = row + head * head_dim + i;
-      float y1[2], y2[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) rotate_pair(to_float(src[e]), to_float(src[e + half]), sine[e], cosine[e], &y1[e], &y2[e]);
+  constexpr int VEC = 16 / sizeof(T);            // elements per 16-byte access
+  const bool wide = half % VEC == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+                    ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0;
+  if (wide) {
+    // an item: VEC adjacent pair indices of one head, i.e. 16 bytes of the first half of the head
+    // and the matching 16 bytes of the second
+    const int chunks = half / VEC;
+    for (int item = threadIdx.x; item < rotated_heads * chunks; item += blockDim.x) {
+      const int head = item / chunks, i0 = (item - head * chunks) * VEC;
       T* dst = nullptr;
       if (head < heads) dst = q_out + ((size_t)token * heads + head) * head_dim;
       else if (store) dst = k_pool + (((size_t)page * kv_heads + (head - heads)) * page_size + offset) * head_dim;
-      if (dst != nullptr) {
+      if (dst == nullptr) continue;
+      const T* src = row + head * head_dim + i0;
+      const uint4 lo = *reinterpret_cast<const uint4*>(src);
+      const uint4 hi = *reinterpret_cast<const uint4*>(src + half);
+      const T* x1 = reinterpret_cast<const T*>(&lo);
+      const T* x2 = reinterpret_cast<const T*>(&hi);
+      uint4 out_lo, out_hi;
+      T* y1 = reinterpret_cast<T*>(&out_lo);
+      T* y2 = reinterpret_cast<T*>(&out_hi);
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          dst[i + e] = from_float<T>(y1[e]);
-          dst[i + e + half] = from_float<T>(y2[e]);
-        }
+      for (int e = 0; e < VEC; ++e) {
+        float r1, r2;
+        rotate_pair(to_float(x1[e]), to_float(x2[e]), sines[i0 + e], cosines[i0 + e], &r1, &r2);
+        y1[e] = from_float<T>(r1);
+        y2[e] = from_float<T>(r2);
+      }
+      *reinterpret_cast<uint4*>(dst + i0) = out_lo;
+      *reinterpret_cast<uint4*>(dst + i0 + half) = out_hi;
+    }
+    if (store) {
+      const T* v_row = row + (size_t)(heads + kv_heads) * head_dim;
+      const int per_head = head_dim / VEC;
+      for (int item = threadIdx.x; item < kv_heads * per_head; item += blockDim.x) {
+        const int kv_head = item / per_head, i0 = (item - kv_head * per_head) * VEC;
+        *reinterpret_cast<uint4*>(v_pool + (((size_t)page * kv_heads + kv_head) * page_size + offset) * head_dim + i0) =
+            *reinterpret_cast<const uint4*>(v_row + kv_head * head_dim + i0);
       }
     }
-  } else {
-    for (int item = threadIdx.x; item < rotated_heads * half; item += blockDim.x) {
-      const int head = item / half, i = item - head * half;
-      float sine, cosine;
-      sincosf(position * inv_freq[i], &sine, &cosine);
-      const float x1 = to_float(row[head * head_dim + i]);
-      const float x2 = to_float(row[head * head_dim + i + half]);
-      float y1, y2;
-      rotate_pair(x1, x2, sine, cosine, &y1, &y2);
-      if (head < heads) {
-        T* dst = q_out + ((size_t)token * heads + head) * head_dim;
-        dst[i] = from_float<T>(y1);
-        dst[i + half] = from_float<T>(y2);
-      } else if (store) {
-        const int kv_head = head - heads;
-        T* dst = k_pool + (((size_t)page * kv_heads + kv_head) * page_size + offset) * head_dim;
-        dst[i] = from_float<T>(y1);
-        dst[i + half] = from_float<T>(y2);
-      }
+    return;
+  }
+  for (int item = threadIdx.x; item < rotated_heads * half; item += blockDim.x) {
+    const int head = item / half, i = item - head * half;
+    const float x1 = to_float(row[head * head_dim + i]);
+    const float x2 = to_float(row[head * head_dim + i + half]);
+    float y1, y2;
+    rotate_pair(x1, x2, sines[i], cosines[i], &y1, &y2);
+    if (head < heads) {
+      T* dst = q_out + ((size_t)token * heads + head) * head_dim;
+      dst[i] = from_float<T>(y1);
+      dst[i + half] = from_float<T>(y2);
+    } else if (store) {
+      const int kv_head = head - heads;
+      T* dst = k_pool + (((size_t)page * kv_heads + kv_head) * page_size + offset) * head_dim;
+      dst[i] = from_float<T>(y1);
+      dst[i + half] = from_float<T>(y2);
     }
   }
   if (store) {
@@ -312,9 +327,10 @@ int rope_kv_write_launch(const void* qkv, const int* positions, const float* inv
                          const long long* slots, void* q_out, void* k_pool, void* v_pool,
                          int tokens, int heads, int kv_heads, int head_dim, int page_size,
                          int write_kv, cudaStream_t stream) {
-  // items of two adjacent pairs; few enough threads that each keeps its pair index over its items
-  int work = (heads + kv_heads) * (head_dim / 4);
-  int threads = work >= 512 ? 256 : (work >= 256 ? 128 : 64);
+  // items of 16 bytes of a head's first half and the 16 bytes they pair with (scalar pairs where
+  // the head size does not allow that)
+  int work = (heads + kv_heads) * (head_dim / 2) / (int)(16 / sizeof(T));
+  int threads = work >= 192 ? 256 : (work >= 96 ? 128 : 64);
   launch_kernel(rope_kv_write_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 
       (const T*)qkv, positions, inv_freq, slots, (T*)q_out, (T*)k_pool, (T*)v_pool, heads,
       kv_heads, head_dim, page_size, write_kv);
@@ -449,6 +465,7 @@ MLR_EXPORT int mlr_rope_kv_write(const void* qkv, const int* positions, const fl
   if (tokens == 0) return MLR_OK;
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || page_size <= 0)
     return MLR_BAD_SIZE;
+  if (head_dim > 256) return MLR_TOO_LARGE;       // the kernel keeps head_dim/2 sines and cosines in shared memory
   if (dtype == MLR_F32)
     return rope_kv_write_launch<float>(qkv, positions, inv_freq, slots, q_out, k_pool, v_pool, tokens,
                                        heads, kv_heads, head_dim, page_size, write_kv, stream);
