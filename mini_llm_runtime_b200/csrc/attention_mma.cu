@@ -791,8 +791,19 @@ decode_attention_mma_kernel(const bf16* q, const bf16* k_pool, const bf16* v_poo
 // of each replay.
 //
 // Chunks other than a request's last hold no key of this step, so their first loads are issued
-// before the wait on the previous kernel (which writes this step's keys).
+// before the wait on the previous kernel (which writes this step's keys); the rotation's angles and
+// the new token's cache slot are taken before that wait too, and the step's key and value are
+// fetched right after it, beside the queries.
 // The stages are reused as the merge area once every warp has consumed its last tile.
+//
+// Merge of a request's chunks.  With cluster_merge the launch's chunks of one (request, kv head)
+// are the CTAs of one thread-block cluster (2..16 of them): each leaves its state in its own
+// shared memory, and after one cluster barrier every CTA merges a slice of the outputs from all of
+// them through distributed shared memory, in chunk order; a second barrier keeps every CTA's
+// memory alive until the others have read it.  Inside a captured decode step of the 0.5B sizes this
+// costs 10.7 us per layer against 15.2 us for the other way: partial states to scratch memory, a
+// fence, a counter, and the CTA that arrives last merging them.  That way remains for launches
+// with more chunks or more clusters than run together.
 template <int D, int TKV, int STAGES>
 __global__ void __launch_bounds__(ATTN_THREADS, 3)     // three CTAs per SM with one stage: at most 168 registers
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
