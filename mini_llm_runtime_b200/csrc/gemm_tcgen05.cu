@@ -9,6 +9,8 @@
 //   warps 2..5         epilogue: tcgen05.ld the accumulator (one TMEM lane = one tile row per
 //                      thread), add bias, convert, store
 // Both operands are K-major, as activations [M,K] and checkpoint weights [N,K] are stored.
+// For products of many rows a CTA may also compute two such tiles (256 x 256) side by side in tensor
+// memory from one load of the BN-row operand: half the traffic of that operand per MMA.
 //
 // Orientation.  With many rows (prefill) x is the 128-row operand and 128 weight rows form the
 // N side.  With few rows (decode) the roles swap: 128 weight rows fill the MMA's M side and the
