@@ -694,15 +694,25 @@ class CudaOps:
         decode_seg = batch.plan["decode_seg"]
         if tma:
             # pages arrive by the tensor memory accelerator, one bulk copy per page and kv head
-            _check(build.load_library("attention_mma").mlr_attention_decode_tma(
-                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(decode_seg), _ptr(batch.seg_q_start),
-                _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1],
-                batch.num_decode, num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
-                ctypes.c_float(scale), chunk, int(even_split), splits, int(self.decode_stages or 0),
-                _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _ptr(space["error_word"]),
-                _ptr(qkv), _ptr(inv_freq), _ptr(slots), int(bool(write_kv)),
-                int(cluster == splits and cluster >= 2), _stream()),
-                "decode attention (TMA)")
+            entry = build.load_library("attention_mma").mlr_attention_decode_tma
+
+            def launch(clustered: bool) -> int:
+                return entry(
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(decode_seg), _ptr(batch.seg_q_start),
+                    _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1],
+                    batch.num_decode, num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
+                    ctypes.c_float(scale), chunk, int(even_split), splits, int(self.decode_stages or 0),
+                    _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _ptr(space["error_word"]),
+                    _ptr(qkv), _ptr(inv_freq), _ptr(slots), int(bool(write_kv)), int(clustered), _stream())
+
+            clustered = cluster == splits and cluster >= 2
+            status = launch(clustered)
+            if status > 0 and clustered:
+                # the device refused clusters of this size (a partitioned GPU, say): the merge through
+                # scratch memory serves from now on
+                self.use_cluster_merge = False
+                status = launch(False)
+            _check(status, "decode attention (TMA)")
             return
         entry = (build.load_library("attention_mma").mlr_attention_decode_mma if mma
                  else build.load_library("attention_decode").mlr_attention_decode)
