@@ -1201,7 +1201,7 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
       case 1: MLR_LAUNCH_DECODE_TMA(64, 64, 1); break;
       case 2: MLR_LAUNCH_DECODE_TMA(64, 64, 2); break;
       case 3: MLR_LAUNCH_DECODE_TMA(64, 64, 3); break;
-      case 12: MLR_LAUNCH_DECODE_TMA(64, 32, 2); break;    // 32-key tiles, for measurements
+      case 12: MLR_LAUNCH_DECODE_TMA(64, 32, 2); break;    // 32-key tiles, two in flight: for chunks of many tiles
       case 13: MLR_LAUNCH_DECODE_TMA(64, 32, 3); break;
       case 14: MLR_LAUNCH_DECODE_TMA(64, 32, 4); break;
       default: return MLR_BAD_SIZE;

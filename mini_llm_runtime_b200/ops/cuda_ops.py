@@ -701,11 +701,18 @@ class CudaOps:
                     _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(decode_seg), _ptr(batch.seg_q_start),
                     _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1],
                     batch.num_decode, num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
-                    ctypes.c_float(scale), chunk, int(even_split), splits, int(self.decode_stages or 0),
+                    ctypes.c_float(scale), chunk, int(even_split), splits, stages,
                     _ptr(space["attention_scratch"]), _ptr(space["attention_counters"]), _ptr(space["error_word"]),
                     _ptr(qkv), _ptr(inv_freq), _ptr(slots), int(bool(write_kv)), int(clustered), _stream())
 
             clustered = cluster == splits and cluster >= 2
+            # head_dim 64: a warp that walks more than two 64-key tiles does better with 32-key tiles
+            # and two of them in flight (same shared memory; measured 2 to 3 % of a decode step
+            # from 24 requests on, slower below, and slower at contexts of 32k)
+            stages = int(self.decode_stages or 0)
+            if (self.decode_stages is None and head_dim == 64 and batch.max_kv_len <= 8192
+                    and -(-batch.max_kv_len // splits) > 2 * self.TMA_MIN_CHUNK):
+                stages = 12
             status = launch(clustered)
             if status > 0 and clustered:
                 # the device refused clusters of this size (a partitioned GPU, say): the merge through

@@ -558,9 +558,12 @@ def test_decode_attention_with_fused_position_encoding(heads, kv_heads, head_dim
     slots = torch.tensor([int(table[s, c // page]) * page + c % page for s, c in enumerate(contexts)], dtype=torch.int64)
     inv_freq = 1.0 / (10000.0 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
     results = {}
-    for fused in (False, True):
+    for fused in (False, True, "32-key tiles"):
+        if fused == "32-key tiles" and head_dim != 64:
+            continue
         k_dev, v_dev = k_pool.clone().to(DEVICE), v_pool.clone().to(DEVICE)
-        cuda().use_fused_rope = fused
+        cuda().use_fused_rope = bool(fused)
+        cuda().decode_stages = 12 if fused == "32-key tiles" else None      # 32-key tiles, two in flight per warp
         try:
             for window in (None, 100):
                 before = cuda_ops.launches
@@ -571,11 +574,17 @@ def test_decode_attention_with_fused_position_encoding(heads, kv_heads, head_dim
                 results[fused, window] = out
         finally:
             cuda().use_fused_rope = True
+            cuda().decode_stages = None
         results[fused, "k"], results[fused, "v"] = k_dev, v_dev
     torch.cuda.synchronize()
     cuda().raise_if_device_error()
     for key in (None, 100, "k", "v"):
         assert torch.equal(results[True, key], results[False, key]), f"fused and separate kernels differ in {key}"
+    if head_dim == 64:
+        for key in ("k", "v"):
+            assert torch.equal(results["32-key tiles", key], results[False, key]), "pages written with 32-key tiles differ"
+        for key in (None, 100):
+            assert_close(results["32-key tiles", key], results[True, key], torch.bfloat16, "32-key tiles against 64-key tiles")
     if not write_kv:
         assert torch.equal(results[True, "k"].cpu(), k_pool) and torch.equal(results[True, "v"].cpu(), v_pool)
     # and against the plain stand-in, which rotates and attends in float32
