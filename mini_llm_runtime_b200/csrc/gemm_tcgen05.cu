@@ -10,15 +10,21 @@
 //                      thread), add bias, convert, store
 // Both operands are K-major, as activations [M,K] and checkpoint weights [N,K] are stored.
 // For products of many rows a CTA may also compute two such tiles (256 x 256) side by side in tensor
-// memory from one load of the BN-row operand: half the traffic of that operand per MMA.
+// memory from one load of the BN-row operand: half the traffic of that operand per MMA.  Or the
+// 256 x 256 tile lies over an SM pair (a cluster of two CTAs, tcgen05 cta_group::2): each CTA loads
+// its 128 rows and half of the BN-row operand, one thread of the even CTA issues MMAs of 256 rows
+// for both, each CTA holds and writes out the accumulator of its rows; with half the shared and
+// tensor memory per CTA, two CTAs fit an SM and one's epilogue overlaps the other's MMAs.
 //
 // Orientation.  With many rows (prefill) x is the 128-row operand and 128 weight rows form the
 // N side.  With few rows (decode) the roles swap: 128 weight rows fill the MMA's M side and the
 // BN = 16..128 token rows its N side, so that a step streams every weight byte exactly once through
 // full-width tiles.  K may be split over gridDim.z CTAs; partial tiles go to a float32 scratch
 // buffer and the CTA that arrives last for a tile adds them in split order (deterministic) and
-// writes the output.  No CTA waits for another CTA.
-//
+// writes the output.
+// No CTA waits for another CTA, the two of a pair excepted: they meet at the hardware cluster barrier
+// after their barriers are set up and before tensor memory is freed, and the odd CTA's loads and
+// the even CTA's MMAs signal each other's mbarriers.
 // Every wait on an mbarrier is bounded; a wait that runs out stores a code into the error word
 // (host-visible memory), the CTA stops issuing work, frees its tensor memory and returns.
 // TMA loads use no cluster multicast.  Requirements: K % 8 == 0 (16-byte row pitch for TMA) and
@@ -77,6 +83,43 @@ __device__ __forceinline__ void tmem_issue_load16(uint32_t taddr, uint32_t* r) {
       : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- two CTAs on one tile (a cluster of two: an SM pair).  Each CTA holds its own 128 rows of the
+// 128-row operand and half of the BN-row operand; one thread of the even CTA issues MMAs of 256
+// rows that read both CTAs' shared memory and write both CTAs' tensor memory.  Loads of both CTAs
+// count on the even CTA's barrier; a commit arrives on the barriers of both.
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t address_in_cta(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+// `barrier`: shared::cluster address of the barrier that counts the bytes (the even CTA's)
+__device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_t barrier, void* dst, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(barrier), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives, once the MMAs issued so far have finished, on the barrier at this address in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
 
 struct GemmParams {
   int M, N, K;
@@ -236,18 +279,22 @@ __device__ __forceinline__ void reduce_swapped_swiglu(const float* partials, int
 // BM = 256 (many rows only): the CTA computes two 128-row accumulators side by side in tensor memory
 // from one load of the BN-row operand, which halves that operand's traffic from L2 per MMA (the
 // bound of the large products); no split-K in that form.
-template <int BN, bool SWAP, bool SWIGLU, int BM = TILE_ROWS>
+// PAIR (many rows only): the tile is 256 x BN over two CTAs as described above; the grid's x
+// extent counts 128-row halves, consecutive CTAs forming a cluster.
+template <int BN, bool SWAP, bool SWIGLU, int BM = TILE_ROWS, bool PAIR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
   constexpr int HALVES = BM / TILE_ROWS;
   constexpr uint32_t HALF_BYTES = TILE_ROWS * TILE_K * 2;
   constexpr uint32_t A_BYTES = BM * TILE_K * 2;
-  constexpr uint32_t B_BYTES = BN * TILE_K * 2;
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;               // rows of the BN-row operand this CTA loads
+  constexpr uint32_t B_BYTES = B_ROWS * TILE_K * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = BN * HALVES < 32 ? 32 : BN * HALVES;
   static_assert(!SWIGLU || SWAP || BN % 128 == 0, "fused SwiGLU needs gate and up columns in one tile");
   static_assert(BM == TILE_ROWS || (BM == 2 * TILE_ROWS && !SWAP && BN * HALVES <= 512), "two accumulators: many rows, 512 columns");
+  static_assert(!PAIR || (BM == TILE_ROWS && !SWAP && BN % 32 == 0), "an SM pair: many rows, one accumulator per CTA");
 
   extern __shared__ uint8_t raw_shared[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)raw_shared + 1023) & ~(uintptr_t)1023);
@@ -259,6 +306,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int stages = p.stages;
   const int a_row0 = blockIdx.x * BM;          // first row of the 128-row (or 256-row) operand
   const int b_row0 = blockIdx.y * BN;          // first row of the BN-row operand
+  const uint32_t pair_rank = PAIR ? cluster_cta_rank() : 0u;
   const int split = blockIdx.z;
   const int total_kb = (p.K + TILE_K - 1) / TILE_K;
   const int kb_begin = split * p.k_blocks_per_split;
@@ -274,11 +322,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_holder)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {      // the same warp of both CTAs: the same columns in both SMs' tensor memory
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_holder)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_holder)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();        // the other CTA's barriers exist before anything is sent to them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_holder;
 
@@ -287,41 +341,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ---------------- producer
     // The weight tiles of the first ring-full of k blocks do not depend on the kernel before this
     // one: request them at once, then wait for that kernel and request the activation tiles.
-    const int ahead = min(stages, num_kb);
-    for (int i = 0; i < ahead; ++i) {
-      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-      uint8_t* stage = tiles + (size_t)i * STAGE_BYTES;
-      const int k = (kb_begin + i) * TILE_K;
-      if (SWAP) tma_load_2d(&map_a, &full_bar[i], stage, k, a_row0);
-      else tma_load_2d(&map_b, &full_bar[i], stage + A_BYTES, k, b_row0);
-    }
-    pdl_wait();
-    for (int i = 0; i < ahead; ++i) {
-      uint8_t* stage = tiles + (size_t)i * STAGE_BYTES;
-      const int k = (kb_begin + i) * TILE_K;
-      if (SWAP) {
-        tma_load_2d(&map_b, &full_bar[i], stage + A_BYTES, k, b_row0);
+    // In a pair both CTAs load (their rows of the one operand, their half of the other) and all bytes
+    // count on the even CTA's barrier, which alone expects them.
+    auto load_a = [&](int s, int k) {
+      uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+      if (PAIR) {
+        tma_load_2d_pair(&map_a, address_in_cta(smem_u32(&full_bar[s]), 0), stage, k, a_row0);
       } else {
 #pragma unroll
         for (int half = 0; half < HALVES; ++half)
-          tma_load_2d(&map_a, &full_bar[i], stage + half * HALF_BYTES, k, a_row0 + half * TILE_ROWS);
+          tma_load_2d(&map_a, &full_bar[s], stage + half * HALF_BYTES, k, a_row0 + half * TILE_ROWS);
       }
+    };
+    auto load_b = [&](int s, int k) {
+      uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+      if (PAIR) tma_load_2d_pair(&map_b, address_in_cta(smem_u32(&full_bar[s]), 0), stage + A_BYTES, k, b_row0 + (int)pair_rank * B_ROWS);
+      else tma_load_2d(&map_b, &full_bar[s], stage + A_BYTES, k, b_row0);
+    };
+    auto expect = [&](int s) {
+      if (!PAIR) mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      else if (pair_rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+    };
+    const int ahead = min(stages, num_kb);
+    for (int i = 0; i < ahead; ++i) {
+      expect(i);
+      const int k = (kb_begin + i) * TILE_K;
+      if (SWAP) load_a(i, k); else load_b(i, k);
+    }
+    pdl_wait();
+    for (int i = 0; i < ahead; ++i) {
+      const int k = (kb_begin + i) * TILE_K;
+      if (SWAP) load_b(i, k); else load_a(i, k);
     }
     int s = ahead == stages ? 0 : ahead, round = ahead == stages ? 1 : 0;
     for (int i = ahead; i < num_kb; ++i) {
       if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, p.error_word, 1)) break;
-      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-      uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+      expect(s);
       const int k = (kb_begin + i) * TILE_K;
-#pragma unroll
-      for (int half = 0; half < HALVES; ++half)
-        tma_load_2d(&map_a, &full_bar[s], stage + half * HALF_BYTES, k, a_row0 + half * TILE_ROWS);
-      tma_load_2d(&map_b, &full_bar[s], stage + A_BYTES, k, b_row0);
+      load_a(s, k);
+      load_b(s, k);
       if (++s == stages) { s = 0; ++round; }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
-    constexpr uint32_t idesc = instruction_descriptor(TILE_ROWS, BN);
+  } else if (warp == 1 && lane == 0 && pair_rank == 0) {
+    // ---------------- MMA issuer (of a pair: the even CTA's, for both)
+    constexpr uint32_t idesc = instruction_descriptor(PAIR ? 2 * TILE_ROWS : TILE_ROWS, BN);
     int s = 0, round = 0;
     for (int i = 0; i < num_kb; ++i) {
       if (!mbar_wait(&full_bar[s], round & 1, p.error_word, 2)) break;
@@ -329,15 +392,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
       const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-      for (int k = 0; k < TILE_K / MMA_K; ++k)
+      for (int k = 0; k < TILE_K / MMA_K; ++k) {
+        if (PAIR) {
+          umma_pair(tmem_base, smem_descriptor(a_addr + k * MMA_K * 2), smem_descriptor(b_addr + k * MMA_K * 2), idesc,
+                    (i > 0 || k > 0) ? 1u : 0u);
+        } else {
 #pragma unroll
-        for (int half = 0; half < HALVES; ++half)
-          umma(tmem_base + half * BN, smem_descriptor(a_addr + half * HALF_BYTES + k * MMA_K * 2),
-               smem_descriptor(b_addr + k * MMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
-      umma_commit(&empty_bar[s]);
+          for (int half = 0; half < HALVES; ++half)
+            umma(tmem_base + half * BN, smem_descriptor(a_addr + half * HALF_BYTES + k * MMA_K * 2),
+                 smem_descriptor(b_addr + k * MMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+      }
+      if (PAIR) umma_commit_pair(&empty_bar[s]); else umma_commit(&empty_bar[s]);
       if (++s == stages) { s = 0; ++round; }
     }
-    umma_commit(&accumulator_bar);   // arrives once every MMA issued above has finished
+    // arrives once every MMA issued above has finished (in a pair: on both CTAs' barriers)
+    if (PAIR) umma_commit_pair(&accumulator_bar); else umma_commit(&accumulator_bar);
   } else if (warp >= 2) {
     // ---------------- epilogue: thread <-> TMEM lane <-> tile row
     const int quarter = warp & 3;
@@ -485,9 +555,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();        // both CTAs are done with tensor memory and with each other's shared memory
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -515,11 +587,32 @@ static int launch(const void* x, const void* w, const GemmParams& p, int splits,
   return launch_status();
 }
 
-// Tile shape, split count and ring depth for a product of this shape.
-struct GemmPlan { int bn, tiles, splits, stages, kb_per_split, bm; };
+// A 256 x BN tile over an SM pair: a cluster of two CTAs, 128 rows and BN/2 weight rows each.
+template <int BN, bool SWIGLU>
+static int launch_pair(const void* x, const void* w, const GemmParams& p, cudaStream_t stream) {
+  const size_t shared = (size_t)p.stages * (TILE_ROWS * TILE_K * 2 + BN / 2 * TILE_K * 2) + 1024;
+  static size_t configured = 0;
+  if (shared > configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false, SWIGLU, TILE_ROWS, true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return (int)err;
+    configured = shared;
+  }
+  CUtensorMap map_a, map_b;
+  if (!cached_tile_map(&map_a, x, p.M, p.K, TILE_ROWS) || !cached_tile_map(&map_b, w, p.N, p.K, BN / 2))
+    return MLR_BAD_ALIGNMENT;
+  dim3 grid(2 * ((p.M + 2 * TILE_ROWS - 1) / (2 * TILE_ROWS)), (p.N + BN - 1) / BN, 1);
+  launch_kernel_clustered(gemm_tcgen05_kernel<BN, false, SWIGLU, TILE_ROWS, true>, grid, dim3(GEMM_THREADS), shared, stream, 2,
+                          map_a, map_b, p);
+  return launch_status();
+}
+
+// Tile shape, split count and ring depth for a product of this shape.  pair: the 256 x 256 tile lies
+// over two CTAs (one accumulator of 256 columns each) instead of in one CTA with two accumulators.
+struct GemmPlan { int bn, tiles, splits, stages, kb_per_split, bm; bool pair; };
 
 // Overrides for measurements (0 = the planner decides): tile width and ring depth of many-row products.
-static int forced_bn = 0, forced_stages = 0, forced_splits = 0, forced_bm = 0;
+static int forced_bn = 0, forced_stages = 0, forced_splits = 0, forced_bm = 0, forced_pair = 0;
 
 // Many rows (M > 128): tile width, ring depth and split count by a small model of the kernel,
 // in microseconds.  A CTA costs a fixed 1.5 us (barriers, tensor-memory allocation, first loads)
@@ -538,7 +631,7 @@ static int forced_bn = 0, forced_stages = 0, forced_splits = 0, forced_bm = 0;
 static GemmPlan plan_many_rows(int M, int N, int K, bool swiglu, int sms) {
   const int total_kb = (K + TILE_K - 1) / TILE_K;
   const int tiles_m = (M + TILE_ROWS - 1) / TILE_ROWS;
-  GemmPlan best = {128, tiles_m * ((N + 127) / 128), 1, 2, total_kb, TILE_ROWS};
+  GemmPlan best = {128, tiles_m * ((N + 127) / 128), 1, 2, total_kb, TILE_ROWS, false};
   double best_cost = 1e30;
   for (int shape = 0; shape < 3; ++shape) {
     // 128 x 128, 128 x 256, and 256 x 256 (two accumulators per CTA; no split-K)
@@ -581,6 +674,20 @@ static GemmPlan plan_many_rows(int M, int N, int K, bool swiglu, int sms) {
   }
   best.kb_per_split = (total_kb + best.splits - 1) / best.splits;
   best.splits = (total_kb + best.kb_per_split - 1) / best.kb_per_split;      // no empty split
+  // The 256 x 256 tile over an SM pair, with rings of three stages so that two CTAs share an SM and
+  // one's epilogue runs under the other's MMAs: that pays where the epilogue is long, which is the
+  // SwiGLU one (the gate/up product of 37888 x 3584 at 2,048 rows: 400 us against 424 us in one CTA
+  // and 433 us as 128 x 256 tiles; at 520 rows 151 against 162 and 155; 27648 x 5120 at 4,096 rows
+  // 825 against 838 and 845; at 384 rows the padding to 512 eats the gain).  The other products are
+  // as fast or faster in one CTA with its ring of 64 KB stages.
+  const bool pair_fits = N >= 256 && M > 2 * TILE_ROWS;
+  const bool pair_pays = swiglu && best.bn == 256 && M > 3 * TILE_ROWS;
+  if (pair_fits && (forced_pair > 0 || (forced_pair == 0 && pair_pays))) {
+    best.bn = 256; best.bm = 2 * TILE_ROWS; best.pair = true;
+    best.tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    best.splits = 1; best.kb_per_split = total_kb;
+    best.stages = forced_stages >= 2 ? (forced_stages > 6 ? 6 : forced_stages) : (forced_pair == 1 ? 6 : 3);
+  }
   return best;
 }
 
@@ -589,6 +696,7 @@ static GemmPlan plan_gemm(int M, int N, int K, bool swiglu) {
   if (M > 128) return plan_many_rows(M, N, K, swiglu, sms);
   GemmPlan plan;
   plan.bm = TILE_ROWS;
+  plan.pair = false;
   const int total_kb = (K + TILE_K - 1) / TILE_K;
   plan.bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   plan.tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
@@ -648,6 +756,9 @@ MLR_EXPORT void mlr_gemm_tcgen05_debug(int bn, int stages, int splits, int bm) {
   forced_splits = splits;
   forced_bm = bm;
 }
+// 0: the planner decides whether 256 x 256 tiles lie over SM pairs; -1: never; 1: wherever the shape
+// allows, with rings of six stages (one CTA per SM); 2: the same with three stages (two CTAs per SM).
+MLR_EXPORT void mlr_gemm_tcgen05_debug_pair(int pair) { forced_pair = pair; }
 
 // Scratch needed for a product of this shape (bytes of float32 partial tiles); 0 without split-K.
 // `splits_out` receives the split count the launcher will use, `tiles_out` the number of tiles.
@@ -688,6 +799,7 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
     if (M <= 32) return launch<32, true, true>(x, w, p, plan.splits, stream);
     if (M <= 64) return launch<64, true, true>(x, w, p, plan.splits, stream);
     if (M <= 128) return launch<128, true, true>(x, w, p, plan.splits, stream);
+    if (plan.pair) return launch_pair<256, true>(x, w, p, stream);
     if (plan.bm == 2 * TILE_ROWS) return launch<256, false, true, 2 * TILE_ROWS>(x, w, p, plan.splits, stream);
     if (plan.bn == 256) return launch<256, false, true>(x, w, p, plan.splits, stream);
     return launch<128, false, true>(x, w, p, plan.splits, stream);
@@ -696,6 +808,7 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
   if (M <= 32) return launch<32, true, false>(x, w, p, plan.splits, stream);
   if (M <= 64) return launch<64, true, false>(x, w, p, plan.splits, stream);
   if (M <= 128) return launch<128, true, false>(x, w, p, plan.splits, stream);
+  if (plan.pair) return launch_pair<256, false>(x, w, p, stream);
   if (plan.bm == 2 * TILE_ROWS) return launch<256, false, false, 2 * TILE_ROWS>(x, w, p, plan.splits, stream);
   if (plan.bn == 256) return launch<256, false, false>(x, w, p, plan.splits, stream);
   return launch<128, false, false>(x, w, p, plan.splits, stream);

@@ -193,6 +193,49 @@ def test_two_accumulators_per_cta(m, n, k, tcgen05_only):
                      torch.bfloat16, "256 x 256 tiles with SwiGLU")
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(600, 300, 72), (1000, 1290, 3584), (257, 256, 64), (2049, 896, 200)])
+def test_tile_over_an_sm_pair(m, n, k, mode, tcgen05_only):
+    """The 256 x 256 tile over a cluster of two CTAs (each loads its 128 rows and half of the weight
+    rows; one thread of the even CTA issues MMAs for both; commits arrive in both), forced through
+    the debug entry with long rings (one CTA per SM) and short ones (two): tails in M (the odd CTA
+    partly or wholly empty), N (the odd CTA's weight half partly or wholly outside) and K; plain,
+    float32 and SwiGLU epilogues; and the same bits as the tile computed by one CTA."""
+    from mini_llm_runtime_b200.ops import build
+
+    lib = build.load_library("gemm_tcgen05")
+    x = rnd((m, k), torch.bfloat16, 180 + m % 5)
+    w = rnd((n, k), torch.bfloat16, 181, 0.1)
+    b = rnd((n,), torch.bfloat16, 182)
+    inner = (n // 128) * 64
+    xd, wd, bd = x.to(DEVICE), w.to(DEVICE), b.to(DEVICE)
+    lib.mlr_gemm_tcgen05_debug_pair(-1)
+    lib.mlr_gemm_tcgen05_debug(256, 0, 1, 128)
+    try:
+        alone = cuda().linear(xd, wd, bd)
+        lib.mlr_gemm_tcgen05_debug(0, 0, 0, 0)
+        lib.mlr_gemm_tcgen05_debug_pair(mode)
+        got = cuda().linear(xd, wd, bd)
+        got32 = cuda().linear(xd, wd, None, out_dtype=torch.float32)
+        if inner >= 128:
+            gate = rnd((inner, k), torch.bfloat16, 183, 0.1)
+            up = rnd((inner, k), torch.bfloat16, 184, 0.1)
+            stacked = torch.cat([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k)
+            act = cuda().linear_swiglu(xd, stacked.to(DEVICE), 64)
+        torch.cuda.synchronize()
+        cuda().raise_if_device_error()
+    finally:
+        lib.mlr_gemm_tcgen05_debug(0, 0, 0, 0)
+        lib.mlr_gemm_tcgen05_debug_pair(0)
+    want = x.double() @ w.double().T
+    assert torch.equal(got, alone), "an SM pair and one CTA differ"
+    assert_close(got, want + b.double(), torch.bfloat16, f"SM pair {m}x{n}x{k}")
+    assert float((got32.double().cpu() - want).abs().max()) <= 1e-4 * float(want.abs().max()) + 1e-5
+    if inner >= 128:
+        assert_close(act, torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T),
+                     torch.bfloat16, "SM pair with SwiGLU")
+
+
 @pytest.mark.parametrize("m,inner,k", [(2048, 4864, 896), (777, 1216, 200), (1300, 2560, 4864)])
 def test_many_row_swiglu(m, inner, k, tcgen05_only):
     x = rnd((m, k), torch.bfloat16, 150)
