@@ -827,6 +827,27 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   __shared__ int last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Step metadata was copied to the device before the first kernel of the step: safe to read at
+  // once, and asked for before the barriers are set up, since every round trip to memory up to the
+  // first bulk copy lies on the launch's critical path.
+  const int group = heads / kv_heads;
+  const int split = blockIdx.x, kv_head = blockIdx.y, index = blockIdx.z;
+  // decode_seg null: every segment of the step is one decoded row, so segment and row are the index
+  // itself (one round trip less)
+  const int seg = decode_seg != nullptr ? decode_seg[index] : index;
+  const int row = decode_seg != nullptr ? seg_q_start[seg] : index;
+  const int position = seg_pos0[seg];
+  const int table_row = seg_slot != nullptr ? seg_slot[seg] : seg;
+  // the rotation's frequencies (of pair threadIdx.x % HALF for the queries; of pairs lane, lane + 32, ..
+  // for the step's key, should this CTA turn out to hold it)
+  constexpr int HALF = D / 2;
+  const bool fused = qkv != nullptr;
+  float query_frequency = 0.f, key_frequency[HALF / 32];
+  if (fused) {
+    query_frequency = inv_freq[threadIdx.x % HALF];
+#pragma unroll
+    for (int j = 0; j < HALF / 32; ++j) key_frequency[j] = inv_freq[lane + 32 * j];
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < ATTN_WARPS * STAGES; ++i) mbar_init(&full_bar[0][0] + i, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -835,13 +856,6 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   }
   pdl_trigger();
   __syncthreads();
-
-  // Step metadata was copied to the device before the first kernel of the step: safe to read now.
-  const int group = heads / kv_heads;
-  const int split = blockIdx.x, kv_head = blockIdx.y, index = blockIdx.z;
-  const int seg = decode_seg[index];
-  const int row = seg_q_start[seg];
-  const int position = seg_pos0[seg];
   const int lowest = window > 0 ? max(0, position - window + 1) : 0;
   // even_split: the request's own context divided over the grid's chunks (at least chunk_arg keys
   // each), so that one captured launch fits every context length; else chunks of chunk_arg keys
@@ -856,7 +870,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   if (idle && !cluster_merge) return;
   const int k_begin = max(lowest, (first_chunk + split) * chunk);
   const int k_end = min(position + 1, (first_chunk + split + 1) * chunk);   // exclusive
-  const int* table = block_table + (size_t)(seg_slot != nullptr ? seg_slot[seg] : seg) * table_width;
+  const int* table = block_table + (size_t)table_row * table_width;
   const int tile_begin = k_begin / TKV, tile_end = (k_end - 1) / TKV;       // inclusive
   const int tiles = idle ? 0 : tile_end - tile_begin + 1;
   const int my_tiles = tiles > warp ? (tiles - warp + ATTN_WARPS - 1) / ATTN_WARPS : 0;   // tiles warp, warp + 4, ..
@@ -865,18 +879,23 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   const int boxes = page_size >= TKV ? 1 : TKV >> page_shift;
   const int box_rows = page_size >= TKV ? TKV : page_size;
   bf16* my_stages = kv_tiles + (size_t)warp * STAGES * 2 * TILE_ELEMS;
-  auto issue = [&](int n) {
+  // The pool row (the bulk copy's y) of this lane's box of the warp's n-th tile: one read of the
+  // block table, asked for ahead of the copy so that its round trip does not delay the copy.
+  auto lookup = [&](int n) -> int {
+    if (lane >= boxes) return 0;
+    const int key0 = (tile_begin + warp + n * ATTN_WARPS) * TKV + lane * box_rows;
+    const int logical = key0 >> page_shift;
+    int page = logical < table_width ? table[logical] : -1;
+    int offset = key0 & (page_size - 1);
+    if (page < 0) { page = 0; offset = 0; }
+    return (page * kv_heads + kv_head) * page_size + offset;
+  };
+  auto issue = [&](int n, int y) {
     const int stage = n % STAGES;
     uint64_t* bar = &full_bar[warp][stage];
     if (lane == 0) mbar_expect_tx(bar, 2u * TILE_ELEMS * 2u);
     __syncwarp();
     if (lane < boxes) {
-      const int key0 = (tile_begin + warp + n * ATTN_WARPS) * TKV + lane * box_rows;
-      const int logical = key0 >> page_shift;
-      int page = logical < table_width ? table[logical] : -1;
-      int offset = key0 & (page_size - 1);
-      if (page < 0) { page = 0; offset = 0; }
-      const int y = (page * kv_heads + kv_head) * page_size + offset;
       bf16* k_dst = my_stages + (size_t)stage * 2 * TILE_ELEMS + lane * box_rows * 64;
       bf16* v_dst = k_dst + TILE_ELEMS;
 #pragma unroll
@@ -887,31 +906,39 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
   };
   const bool holds_new_key = split == splits - 1;
-  const bool fused = qkv != nullptr;
   const bool inject = fused && write_kv != 0 && holds_new_key;   // this CTA stores the step's key and value
   // The newest key's row is stale in the pool until this step stores it: a CTA that reads it from
   // the pool waits for the previous kernel first; one that overwrites it in shared memory need not.
   const bool early = !holds_new_key || inject;
-  if (early)
-    for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
+  // The first ring-full of tiles: all table reads, then all copies.
+  int first_rows[STAGES];
+#pragma unroll
+  for (int n = 0; n < STAGES; ++n) first_rows[n] = n < my_tiles ? lookup(n) : 0;
+  if (early) {
+#pragma unroll
+    for (int n = 0; n < STAGES; ++n)
+      if (n < my_tiles) issue(n, first_rows[n]);
+  }
   // The rotation's angles depend on the position only: taken before the wait, like the new token's
   // cache slot, so that after it only the values themselves are fetched.
   constexpr int CHUNKS = D / 8;
-  constexpr int HALF = D / 2;
   float sine = 0.f, cosine = 1.f;            // of pair threadIdx.x % HALF (the same for all of a thread's query items)
   float key_sine[HALF / 32], key_cosine[HALF / 32];     // of pairs lane, lane + 32, ..: the new key's
   long long new_slot = -1;
   if (fused) {
-    sincosf((float)position * inv_freq[threadIdx.x % HALF], &sine, &cosine);
+    if (inject) new_slot = slots[row];
+    sincosf((float)position * query_frequency, &sine, &cosine);
     if (inject) {
 #pragma unroll
-      for (int j = 0; j < HALF / 32; ++j) sincosf((float)position * inv_freq[lane + 32 * j], &key_sine[j], &key_cosine[j]);
-      new_slot = slots[row];
+      for (int j = 0; j < HALF / 32; ++j) sincosf((float)position * key_frequency[j], &key_sine[j], &key_cosine[j]);
     }
   }
   pdl_wait();
-  if (!early)
-    for (int n = 0; n < STAGES && n < my_tiles; ++n) issue(n);
+  if (!early) {
+#pragma unroll
+    for (int n = 0; n < STAGES; ++n)
+      if (n < my_tiles) issue(n, first_rows[n]);
+  }
 
   const size_t qkv_width = (size_t)(heads + 2 * kv_heads) * D;
   // The warp whose tile holds the newest position fetches the step's key and value now, beside the
@@ -934,11 +961,20 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     // thread -> pair index i (the same for all its items, as 128 % HALF == 0) and rows g0, g0 + 128/HALF, ..
     const int i = threadIdx.x % HALF;
     const bf16* q_row = qkv + (size_t)row * qkv_width + (size_t)kv_head * group * D;
-    for (int g = threadIdx.x / HALF; g < 16; g += ATTN_THREADS / HALF) {
-      float y1 = 0.f, y2 = 0.f;
-      if (g < group) {
-        rotate_pair(__bfloat162float(q_row[g * D + i]), __bfloat162float(q_row[g * D + i + HALF]), sine, cosine, &y1, &y2);
-      }
+    constexpr int STEP = ATTN_THREADS / HALF, MINE = 16 / STEP;     // this thread's rows: g0, g0 + STEP, ..
+    const int g0 = threadIdx.x / HALF;
+    bf16 low[MINE], high[MINE];                                     // every load before the first store
+#pragma unroll
+    for (int j = 0; j < MINE; ++j) {
+      const int g = g0 + j * STEP;
+      low[j] = g < group ? q_row[g * D + i] : __float2bfloat16_rn(0.f);
+      high[j] = g < group ? q_row[g * D + i + HALF] : __float2bfloat16_rn(0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < MINE; ++j) {
+      const int g = g0 + j * STEP;
+      float y1, y2;
+      rotate_pair(__bfloat162float(low[j]), __bfloat162float(high[j]), sine, cosine, &y1, &y2);
       tile_at<D>(q_tile, g, i >> 3)[i & 7] = __float2bfloat16_rn(y1);
       tile_at<D>(q_tile, g, (i + HALF) >> 3)[(i + HALF) & 7] = __float2bfloat16_rn(y2);
     }
@@ -971,6 +1007,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   bool gave_up = false;       // after one wait ran out, later waits are skipped: the kernel ends, the host raises
   for (int n = 0; n < my_tiles; ++n) {
     const int stage = n % STAGES;
+    const int refill_row = n + STAGES < my_tiles ? lookup(n + STAGES) : 0;     // in flight during this tile
     if (!gave_up) gave_up = !mbar_wait(&full_bar[warp][stage], (uint32_t)(n / STAGES) & 1u, error_word, 0x41);
     gave_up = __any_sync(0xffffffffu, gave_up);                  // warp-uniform: the warp issues as one
     bf16* k_tile = my_stages + (size_t)stage * 2 * TILE_ELEMS;
@@ -1020,7 +1057,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
     warp_pv<D, NT, true, TKV>(o, s, v_tile, 0, lane);
     __syncwarp();                                                // every lane is done with this stage
-    if (n + STAGES < my_tiles && !gave_up) issue(n + STAGES);
+    if (n + STAGES < my_tiles && !gave_up) issue(n + STAGES, refill_row);
   }
   // No load is in flight here: every issued tile was waited for (or its wait ran out after a second).
   __syncthreads();                                               // the merge area overlays the stages
@@ -1261,3 +1298,4 @@ MLR_EXPORT int mlr_attention_prefill_tma(const void* q, const void* k_pool, cons
 #undef MLR_LAUNCH_PREFILL_TMA
   return launch_status();
 }
+

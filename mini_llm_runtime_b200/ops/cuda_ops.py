@@ -696,9 +696,12 @@ class CudaOps:
             # pages arrive by the tensor memory accelerator, one bulk copy per page and kv head
             entry = build.load_library("attention_mma").mlr_attention_decode_tma
 
+            # every segment one decoded row: segment and row are the index itself, the kernel skips the list
+            listed = None if batch.num_decode == batch.num_segments else decode_seg
+
             def launch(clustered: bool) -> int:
                 return entry(
-                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(decode_seg), _ptr(batch.seg_q_start),
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(listed), _ptr(batch.seg_q_start),
                     _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1],
                     batch.num_decode, num_heads, num_kv_heads, head_dim, page_size, k_pool.shape[0], int(window or 0),
                     ctypes.c_float(scale), chunk, int(even_split), splits, stages,
