@@ -1217,7 +1217,7 @@ MLR_EXPORT int mlr_attention_decode_tma(const void* q, const void* k_pool, const
         if (err != cudaSuccess) return (int)err;                                                           \
         wide_clusters = true;                                                                              \
       }                                                                                                    \
-      launch_kernel_clustered(decode_attention_tma_kernel<D_, T_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream, \
+      launch_kernel_clustered_balanced(decode_attention_tma_kernel<D_, T_, S_>, dim3(grid), dim3(ATTN_THREADS), shared, stream, \
                   max_splits, k_map, v_map, (const bf16*)q, (bf16*)out, decode_seg, seg_q_start, seg_pos0, block_table, seg_slot, \
                   table_width, heads, kv_heads, page_size, page_shift, window, scale * LOG2_E, chunk,      \
                   even_split, (float*)scratch, counters, max_splits, error_word, (const bf16*)qkv, inv_freq, \
@@ -1298,4 +1298,5 @@ MLR_EXPORT int mlr_attention_prefill_tma(const void* q, const void* k_pool, cons
 #undef MLR_LAUNCH_PREFILL_TMA
   return launch_status();
 }
+
 

@@ -129,24 +129,47 @@ inline void launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, 
 }
 
 // The same for a grid of thread-block clusters of `cluster_x` CTAs along x (grid.x a multiple of it).
+// `balanced`: the blocks of a cluster may go wherever the hardware finds room for them, instead of
+// being spread one per SM: large clusters then find room sooner beside the kernel before them (the
+// decode attention's clusters of 16 in a step of 8 requests: 646 -> 633 us per step).  Not for
+// kernels whose CTAs must sit on the two SMs of a pair.
 template <typename... KernelArgs, typename... Args>
-inline void launch_kernel_clustered(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
-                                    cudaStream_t stream, int cluster_x, Args&&... args) {
+inline void launch_clustered(bool balanced, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
+                             cudaStream_t stream, int cluster_x, Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
   config.dynamicSmemBytes = shared;
   config.stream = stream;
-  cudaLaunchAttribute attribute[2];
+  cudaLaunchAttribute attribute[3];
   attribute[0].id = cudaLaunchAttributeClusterDimension;
   attribute[0].val.clusterDim.x = (unsigned)cluster_x;
   attribute[0].val.clusterDim.y = 1;
   attribute[0].val.clusterDim.z = 1;
-  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  int count = 1;
+  if (balanced) {
+    attribute[count].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+    attribute[count].val.clusterSchedulingPolicyPreference = cudaClusterSchedulingPolicyLoadBalancing;
+    ++count;
+  }
+  if (pdl_enabled()) {
+    attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
   config.attrs = attribute;
-  config.numAttrs = pdl_enabled() ? 2 : 1;
+  config.numAttrs = count;
   cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+template <typename... KernelArgs, typename... Args>
+inline void launch_kernel_clustered(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
+                                    cudaStream_t stream, int cluster_x, Args&&... args) {
+  launch_clustered(false, kernel, grid, block, shared, stream, cluster_x, static_cast<Args&&>(args)...);
+}
+template <typename... KernelArgs, typename... Args>
+inline void launch_kernel_clustered_balanced(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared,
+                                             cudaStream_t stream, int cluster_x, Args&&... args) {
+  launch_clustered(true, kernel, grid, block, shared, stream, cluster_x, static_cast<Args&&>(args)...);
 }
 
 // One switch per library (each .cu is its own shared object).

@@ -27,6 +27,13 @@ namespace mlr {
 
 // k blocks (of 32) whose loads are in flight together: fewer when more tokens need registers
 __host__ __device__ constexpr int skinny_batch(int tokens8) { return tokens8 <= 2 ? 8 : (tokens8 == 4 ? 4 : 2); }
+// CTAs per SM the compiler is asked to leave registers for.  The fused gate/up product of up to 8
+// tokens with a batch of 7 fits 168 registers, so that three of its CTAs share an SM: with two, the
+// 304 CTAs of a 4864-wide product were 8 more than 148 SMs hold, and those 8 ran as a second round
+// that doubled the kernel's time (7.1 instead of 3.6 us inside a decode step).
+__host__ __device__ constexpr int skinny_ctas_per_sm(int warps, int groups, int tokens8, int batch) {
+  return (warps == 4 && groups == 2 && tokens8 == 1 && batch <= 7) ? 3 : 0;     // 0: no request
+}
 
 __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                             uint32_t b0, uint32_t b1) {
@@ -38,11 +45,18 @@ __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, 
 
 // GROUPS: 16-row groups per CTA (2 for the fused gate/up product: the gate rows and their up rows).
 // TOKENS8: token blocks of 8 (1 for M <= 8, 2 for M <= 16, 4 for M <= 32, 8 for M <= 64).
-template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU>
-__global__ void __launch_bounds__(WARPS * 32)
+// SKINNY_BATCH: k blocks per warp whose loads are in flight together.
+// ROWS8: the CTA owns 8 weight rows instead of 16 (the MMA's other 8 rows are zeros): twice the CTAs
+// and, in the registers of the missing rows, more k blocks in flight per warp, for long rows of few outputs
+// (a down projection of 896 outputs: 112 CTAs with their whole rows in flight instead of 56 CTAs
+// that fetch theirs in two batches, one after the other).
+template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU, int SKINNY_BATCH = skinny_batch(TOKENS8), bool ROWS8 = false>
+__global__ void __launch_bounds__(WARPS * 32, skinny_ctas_per_sm(WARPS, GROUPS, TOKENS8, SKINNY_BATCH))
 skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __restrict__ bias, void* out,
                    const bf16* residual, int M, int N, int K, int out_f32, float rms_eps) {
-  constexpr int SKINNY_BATCH = skinny_batch(TOKENS8);
+  constexpr int ROWS = ROWS8 ? 8 : 16;               // weight rows (output columns) per group
+  constexpr int HALVES = ROWS8 ? 1 : 2;              // of the MMA's two row halves, those that hold rows
+  static_assert(!ROWS8 || (GROUPS == 1 && !SWIGLU), "8-row CTAs: plain products only");
   extern __shared__ float partial_raw[];
   float (*partial)[GROUPS * TOKENS8 * 4][32] = reinterpret_cast<float (*)[GROUPS * TOKENS8 * 4][32]>(partial_raw);
   __shared__ float squares[WARPS][TOKENS8 * 8];     // per warp: sum of x^2 over its share of K, per token
@@ -59,14 +73,14 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
     row0[0] = (o0 / 64) * 128 + (o0 % 64);                // its gate rows
     row0[GROUPS - 1] = row0[0] + 64;                      // and the up rows of the same outputs
   } else {
-    row0[0] = blockIdx.x * 16;
+    row0[0] = blockIdx.x * ROWS;
   }
-  const uint4* w_row[GROUPS][2];
-  bool w_valid[GROUPS][2];
+  const uint4* w_row[GROUPS][HALVES];
+  bool w_valid[GROUPS][HALVES];
 #pragma unroll
   for (int r = 0; r < GROUPS; ++r)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < HALVES; ++h) {
       const int row = row0[r] + g + 8 * h;
       w_valid[r][h] = row < N;
       w_row[r][h] = reinterpret_cast<const uint4*>(w + (size_t)(w_valid[r][h] ? row : 0) * K);
@@ -80,6 +94,15 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
     x_row[n] = reinterpret_cast<const uint4*>(x + (size_t)(x_valid[n] ? token : 0) * K);
   }
 
+  // the epilogue's bias (rows g and g + 8 of warp 0's lanes): asked for now, not after the reduction
+  float bias_value[2] = {0.f, 0.f};
+  if (!SWIGLU && bias != nullptr && warp == 0) {
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h)
+      if (row0[0] + g + 8 * h < N) bias_value[h] = to_float(bias[row0[0] + g + 8 * h]);
+  }
+  bf16 residual_value[TOKENS8][4];          // likewise the residual, as soon as the previous kernel is done
+
   float acc[GROUPS][TOKENS8][4];
 #pragma unroll
   for (int r = 0; r < GROUPS; ++r)
@@ -91,8 +114,18 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
   for (int n = 0; n < TOKENS8; ++n) square_sum[n] = 0.f;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   bool waited = false;
+  auto fetch_residual = [&]() {
+    if (SWIGLU || residual == nullptr || warp != 0) return;
+#pragma unroll
+    for (int n = 0; n < TOKENS8; ++n)
+#pragma unroll
+      for (int e = 0; e < 2 * HALVES; ++e) {
+        const int token = n * 8 + 2 * t + (e & 1), row = row0[0] + g + 8 * (e >> 1);
+        if (token < M && row < N) residual_value[n][e] = residual[(size_t)token * N + row];
+      }
+  };
   for (int first = warp; first < k_blocks; first += WARPS * SKINNY_BATCH) {
-    uint4 wv[SKINNY_BATCH][GROUPS][2], xv[SKINNY_BATCH][TOKENS8];
+    uint4 wv[SKINNY_BATCH][GROUPS][HALVES], xv[SKINNY_BATCH][TOKENS8];
 #pragma unroll
     for (int i = 0; i < SKINNY_BATCH; ++i) {
       const int piece = (first + i * WARPS) * 4 + t;          // index of this lane's 16 bytes in the row
@@ -100,11 +133,12 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
 #pragma unroll
       for (int r = 0; r < GROUPS; ++r)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) wv[i][r][h] = (in_range && w_valid[r][h]) ? __ldg(w_row[r][h] + piece) : zero;
+        for (int h = 0; h < HALVES; ++h) wv[i][r][h] = (in_range && w_valid[r][h]) ? __ldg(w_row[r][h] + piece) : zero;
     }
     if (!waited) {
       pdl_wait();                                             // x comes from the kernel before this one
       waited = true;
+      fetch_residual();
     }
 #pragma unroll
     for (int i = 0; i < SKINNY_BATCH; ++i) {
@@ -133,11 +167,15 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
 #pragma unroll
         for (int n = 0; n < TOKENS8; ++n) {
           // the lane's 8 k values: (x, y) feed one MMA, (z, w) the next, same order in A and B
-          mma_16x8x16(acc[r][n], wv[i][r][0].x, wv[i][r][1].x, wv[i][r][0].y, wv[i][r][1].y, xv[i][n].x, xv[i][n].y);
-          mma_16x8x16(acc[r][n], wv[i][r][0].z, wv[i][r][1].z, wv[i][r][0].w, wv[i][r][1].w, xv[i][n].z, xv[i][n].w);
+          const uint4 lower = wv[i][r][0], upper = ROWS8 ? zero : wv[i][r][HALVES - 1];
+          mma_16x8x16(acc[r][n], lower.x, upper.x, lower.y, upper.y, xv[i][n].x, xv[i][n].y);
+          mma_16x8x16(acc[r][n], lower.z, upper.z, lower.w, upper.w, xv[i][n].z, xv[i][n].w);
         }
   }
-  if (!waited) pdl_wait();
+  if (!waited) {
+    pdl_wait();
+    fetch_residual();
+  }
 
   // ---- add the warps' partial tiles in warp order
 #pragma unroll
@@ -199,10 +237,11 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
           out_bf16[(size_t)token * half + column] = __float2bfloat16_rn(gate / (1.f + __expf(-gate)) * up);
         }
       } else {
+        if (ROWS8 && e >= 2) continue;                     // the MMA's upper rows hold nothing
         const int row = row0[0] + g + 8 * (e >> 1);
         if (row < N) {
-          float value = acc[0][n][e] * scale + (bias != nullptr ? to_float(bias[row]) : 0.f);
-          if (residual != nullptr) value += to_float(residual[(size_t)token * N + row]);
+          float value = acc[0][n][e] * scale + bias_value[e >> 1];
+          if (residual != nullptr) value += to_float(residual_value[n][e]);
           if (out_f32) out_f32p[(size_t)token * N + row] = value;
           else out_bf16[(size_t)token * N + row] = __float2bfloat16_rn(value);
         }
@@ -210,20 +249,20 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
     }
 }
 
-template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU>
+template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU, int BATCH = skinny_batch(TOKENS8), bool ROWS8 = false>
 static int skinny_launch_one(const void* x, const void* w, const void* bias, void* out, const void* residual, int M,
                              int N, int K, int out_f32, float rms_eps, int groups_of_rows, cudaStream_t stream) {
   const size_t shared = (size_t)WARPS * GROUPS * TOKENS8 * 4 * 32 * sizeof(float);
   if (shared > 48 * 1024) {
     static bool configured = false;
     if (!configured) {
-      cudaError_t err = cudaFuncSetAttribute(skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU>,
+      cudaError_t err = cudaFuncSetAttribute(skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU, BATCH, ROWS8>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
       if (err != cudaSuccess) return (int)err;
       configured = true;
     }
   }
-  launch_kernel(skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU>, dim3(groups_of_rows), dim3(WARPS * 32), shared,
+  launch_kernel(skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU, BATCH, ROWS8>, dim3(groups_of_rows), dim3(WARPS * 32), shared,
                 stream, (const bf16*)x, (const bf16*)w, (const bf16*)bias, out, (const bf16*)residual, M, N, K, out_f32,
                 rms_eps);
   return launch_status();
@@ -233,9 +272,16 @@ template <int WARPS, int TOKENS8>
 static int skinny_launch(const void* x, const void* w, const void* bias, void* out, const void* residual, int M, int N,
                          int K, int out_f32, int swiglu, float rms_eps, cudaStream_t stream) {
   if constexpr (WARPS <= 8) {
-    if (swiglu)
+    if (swiglu) {
+      if constexpr (WARPS == 4 && TOKENS8 == 1) {
+        // rows of at most 7 k blocks per warp (896 wide): a batch of 7 leaves registers for a third CTA per SM
+        if ((K + 31) / 32 <= 7 * WARPS)
+          return skinny_launch_one<WARPS, 2, TOKENS8, true, 7>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
+                                                               (N / 2 + 15) / 16, stream);
+      }
       return skinny_launch_one<WARPS, 2, TOKENS8, true>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
                                                         (N / 2 + 15) / 16, stream);
+    }
   }
   return skinny_launch_one<WARPS, 1, TOKENS8, false>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
                                                      (N + 15) / 16, stream);
@@ -267,6 +313,10 @@ MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, v
     // 16 warps fill an SM's register file with one CTA; rows of up to 4,096 go to 8 warps, two CTAs
     // per SM, so that the 224 to 288 CTAs of a 7B attention projection run in one round
     // (longer rows too when there are more CTAs than SMs: one 16-warp CTA per SM would come in three rounds)
+    // and where 8-row CTAs still fit one round and hold a whole row in one batch, those (see ROWS8)
+    if (!swiglu && K > 4096 && (N + 7) / 8 <= sm_count() && (K + 31) / 32 <= 16 * 10)
+      return skinny_launch_one<16, 1, 1, false, 10, true>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
+                                                          (N + 7) / 8, stream);
     if (K > 4096 && (N + 15) / 16 <= sm_count())
       return skinny_launch<16, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
     if (long_rows) return skinny_launch<8, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
@@ -279,3 +329,4 @@ MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, v
   if (M <= 32) return skinny_launch<8, 4>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
   return skinny_launch<8, 8>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
 }
+

@@ -408,17 +408,20 @@ class ModelRunner:
         return logits, tokens
 
     # A captured step plans its kernels against a context limit, not against the contexts of the
-    # step it was captured in.  Two limits: this many keys while every request is shorter (kernels
-    # may then choose plans that only pay for moderate contexts, such as the decode attention's
-    # merge through a cluster's shared memory), else the cache's capacity per request.
-    SHORT_CONTEXT = 4096
+    # step it was captured in.  The limits: the first of these that no request exceeds (kernels may
+    # then choose plans that only pay for such contexts: the decode attention sizes the thread-block
+    # clusters that merge its chunks by it), else the cache's capacity per request.
+    CONTEXT_LIMITS = (1024, 2048, 4096)
 
     def _context_limit(self, requests: list[RequestCache]) -> int:
         capacity = self.cache.max_pages_per_request * self.cache.page_size
-        if capacity <= self.SHORT_CONTEXT:
-            return capacity
         longest = max(r.pending[1] for r in requests)
-        return self.SHORT_CONTEXT if longest <= self.SHORT_CONTEXT else capacity
+        for limit in self.CONTEXT_LIMITS:
+            if limit >= capacity:
+                break
+            if longest <= limit:
+                return limit
+        return capacity
 
     def _graph_eligible(self, entries: Sequence[StepEntry], requests: list[RequestCache], sample: bool, feed: bool) -> bool:
         if not (self.use_graphs and len(entries) <= self.graph_max_batch

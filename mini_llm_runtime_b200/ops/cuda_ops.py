@@ -459,7 +459,11 @@ class CudaOps:
     # chunk worth it.  A cluster lies within one GPC, one CTA per SM; with 18 SMs per GPC, 8 GPCs and
     # three CTAs per SM only so many clusters run together, and a launch with more comes in rounds
     # (measured: 32 clusters of 13 CTAs lose to no clusters at all, 32 clusters of 8 win).
-    CLUSTER_SIZES = (16, 8, 6)       # smaller clusters measured no gain: few chunks merge quickly either way
+    # The smallest of these sizes that leaves a CTA at most CLUSTER_CHUNK keys is taken, else the
+    # largest that fits (a step of 8 requests at 0.5B sizes: contexts of 1,024 keys 582 us with
+    # clusters of 6, 598 with 8, 624 with 16; contexts of 3,072 keys 661, 653 and 646 us).
+    CLUSTER_SIZES = (4, 6, 8, 16)
+    CLUSTER_CHUNK = 256
     CLUSTER_MAX_CHUNK = 768
 
     def clusters_together(self, size: int) -> int:
@@ -673,8 +677,11 @@ class CudaOps:
             for size in self.CLUSTER_SIZES:
                 if (self.use_cluster_merge and size <= splits and pairs <= self.clusters_together(size)
                         and (size == splits or batch.max_kv_len <= size * self.CLUSTER_MAX_CHUNK)):
-                    splits = cluster = size
-                    break
+                    cluster = size
+                    if batch.max_kv_len <= size * self.CLUSTER_CHUNK:
+                        break
+            if cluster:
+                splits = cluster
         else:
             chunk, splits = self.plan_decode(batch.num_decode, num_kv_heads, batch.max_kv_len, sms)
             if self.decode_chunk is not None:

@@ -202,7 +202,7 @@ def test_captured_steps_follow_the_context_limit(setup):
     config, page = TINY[name]
     fresh = TinyEngine(config, page, dtype, DEVICE, num_pages=64, max_requests=2, max_tokens=256,
                        tensors=engine.tensors)
-    fresh.runner.SHORT_CONTEXT = 64
+    fresh.runner.CONTEXT_LIMITS = (64,)
     text = random_prompt(config.vocab_size, 80, 311)
     steps = [{"entries": [("u", 0, 50)], "end": []}]
     steps += [{"entries": [("u", 50 + k, 51 + k)], "end": ["u"] if k == 29 else []} for k in range(30)]

@@ -286,7 +286,7 @@ def test_tensor_core_linear_many_rows(m, n, k):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32, 33, 64])
 @pytest.mark.parametrize("n,k", [(896, 896), (1152, 896), (896, 4864), (200, 72), (130, 64), (4000, 136), (5120, 5120),
-                                 (520, 3584), (72, 2056)])
+                                 (520, 3584), (72, 2056), (99, 4360)])
 def test_few_rows_linear(m, n, k):
     """The few-rows kernel (mma.sync on 16-row weight groups, K shared by the CTA's warps) against
     float64, and against the tcgen05 kernel on the same inputs."""
@@ -318,7 +318,7 @@ def _check_few_rows(m, n, k, x, w, b, want):
 
 
 @pytest.mark.parametrize("m", [1, 7, 16, 30, 64])
-@pytest.mark.parametrize("n,k,eps", [(896, 4864, 1e-6), (1152, 896, 1e-5), (100, 72, 1e-3), (24, 4104, 1e-6), (40, 3584, 1e-6)])
+@pytest.mark.parametrize("n,k,eps", [(896, 4864, 1e-6), (1152, 896, 1e-5), (100, 72, 1e-3), (24, 4104, 1e-6), (40, 3584, 1e-6), (99, 4360, 1e-6)])
 def test_few_rows_linear_with_norm_and_residual(m, n, k, eps):
     """The row scale of an RMS norm taken inside the product, and the result added into a residual
     in place; alone and together, against the same operations done separately in float64.  The
@@ -555,11 +555,12 @@ def test_decode_attention_split_kv(heads, kv_heads, head_dim, page, chunk):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(14, 2, 64, 16), (28, 4, 128, 16), (5, 1, 128, 64)])
 def test_decode_attention_merges_through_clusters_of_every_size(heads, kv_heads, head_dim, page):
     """Contexts of up to 4,096 keys for few requests: the chunks of a (request, kv head) form a
-    thread-block cluster of 16, 8 or 6 CTAs (by the number of pairs) that merges through shared
+    thread-block cluster of 16, 8 or 6 CTAs (by the number of pairs and the longest context) that merges through shared
     memory.  Short contexts in the same launch leave most of their cluster's CTAs without keys;
     one far key is made dominant so that a chunk merged with the wrong weight shows.  Against the
     plain stand-in and against the merge through scratch memory."""
     contexts_by_rows = {4: [4095, 100, 2600, 257], 9: [4000, 3, 255, 256, 1023, 3071, 2048, 64, 700],
+                        5: [1000, 3, 700, 256, 999], 6: [2047, 80, 1025, 512, 1900, 71],     # clusters of 6 and of 8
                         20: [4095] + [137 * i % 3900 + 1 for i in range(19)],
                         28: [4095] + [211 * i % 4000 + 1 for i in range(27)]}
     for rows, contexts in contexts_by_rows.items():
