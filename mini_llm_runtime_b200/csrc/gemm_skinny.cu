@@ -251,7 +251,8 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
 
 template <int WARPS, int GROUPS, int TOKENS8, bool SWIGLU, int BATCH = skinny_batch(TOKENS8), bool ROWS8 = false>
 static int skinny_launch_one(const void* x, const void* w, const void* bias, void* out, const void* residual, int M,
-                             int N, int K, int out_f32, float rms_eps, int groups_of_rows, cudaStream_t stream) {
+                             int N, int K, int out_f32, float rms_eps, int groups_of_rows, cudaStream_t stream,
+                             int* rounds_out) {
   const size_t shared = (size_t)WARPS * GROUPS * TOKENS8 * 4 * 32 * sizeof(float);
   if (shared > 48 * 1024) {
     static bool configured = false;
@@ -262,6 +263,21 @@ static int skinny_launch_one(const void* x, const void* w, const void* bias, voi
       configured = true;
     }
   }
+  if (rounds_out != nullptr) {
+    // a question, not a launch: in how many rounds would this grid's CTAs run (by what the device
+    // says it holds of this instantiation)
+    static int per_sm = 0;
+    if (per_sm == 0) {
+      int blocks = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU, BATCH, ROWS8>,
+                                                        WARPS * 32, shared) != cudaSuccess || blocks < 1)
+        blocks = 1;
+      per_sm = blocks;
+    }
+    const int together = per_sm * sm_count();
+    *rounds_out = (groups_of_rows + together - 1) / together;
+    return MLR_OK;
+  }
   launch_kernel(skinny_gemm_kernel<WARPS, GROUPS, TOKENS8, SWIGLU, BATCH, ROWS8>, dim3(groups_of_rows), dim3(WARPS * 32), shared,
                 stream, (const bf16*)x, (const bf16*)w, (const bf16*)bias, out, (const bf16*)residual, M, N, K, out_f32,
                 rms_eps);
@@ -270,21 +286,21 @@ static int skinny_launch_one(const void* x, const void* w, const void* bias, voi
 
 template <int WARPS, int TOKENS8>
 static int skinny_launch(const void* x, const void* w, const void* bias, void* out, const void* residual, int M, int N,
-                         int K, int out_f32, int swiglu, float rms_eps, cudaStream_t stream) {
+                         int K, int out_f32, int swiglu, float rms_eps, cudaStream_t stream, int* rounds_out) {
   if constexpr (WARPS <= 8) {
     if (swiglu) {
       if constexpr (WARPS == 4 && TOKENS8 == 1) {
         // rows of at most 7 k blocks per warp (896 wide): a batch of 7 leaves registers for a third CTA per SM
         if ((K + 31) / 32 <= 7 * WARPS)
           return skinny_launch_one<WARPS, 2, TOKENS8, true, 7>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
-                                                               (N / 2 + 15) / 16, stream);
+                                                               (N / 2 + 15) / 16, stream, rounds_out);
       }
       return skinny_launch_one<WARPS, 2, TOKENS8, true>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
-                                                        (N / 2 + 15) / 16, stream);
+                                                        (N / 2 + 15) / 16, stream, rounds_out);
     }
   }
   return skinny_launch_one<WARPS, 1, TOKENS8, false>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
-                                                     (N + 15) / 16, stream);
+                                                     (N + 15) / 16, stream, rounds_out);
 }
 
 }  // namespace mlr
@@ -293,13 +309,9 @@ using namespace mlr;
 
 MLR_DEFINE_PDL_SWITCH
 
-// x [M,K], w [N,K], bias [N] or null (bfloat16); out [M,N] bfloat16 or float32 (out_f32).
-// swiglu != 0: w interleaves blocks of 64 gate rows with the 64 up rows of the same outputs
-// (N % 128 == 0, no bias); out is silu(gate) * up, [M, N/2] bfloat16.  M <= 64, K % 8 == 0.
-// rms_eps >= 0: the product acts on the RMS-normalised rows of x.  residual: [M,N] bfloat16 added
-// to the result (it may be `out`), or null; not with swiglu.
-MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, void* out, const void* residual,
-                               int M, int N, int K, int out_f32, int swiglu, float rms_eps, cudaStream_t stream) {
+static int skinny_dispatch(const void* x, const void* w, const void* bias, void* out, const void* residual,
+                           int M, int N, int K, int out_f32, int swiglu, float rms_eps, cudaStream_t stream,
+                           int* rounds_out) {
   if (M == 0) return MLR_OK;
   if (M < 0 || N <= 0 || K <= 0) return MLR_BAD_SIZE;
   if (M > 64) return MLR_TOO_LARGE;
@@ -316,17 +328,36 @@ MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, v
     // and where 8-row CTAs still fit one round and hold a whole row in one batch, those (see ROWS8)
     if (!swiglu && K > 4096 && (N + 7) / 8 <= sm_count() && (K + 31) / 32 <= 16 * 10)
       return skinny_launch_one<16, 1, 1, false, 10, true>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
-                                                          (N + 7) / 8, stream);
+                                                          (N + 7) / 8, stream, rounds_out);
     if (K > 4096 && (N + 15) / 16 <= sm_count())
-      return skinny_launch<16, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
-    if (long_rows) return skinny_launch<8, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
-    return skinny_launch<4, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+      return skinny_launch<16, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream, rounds_out);
+    if (long_rows) return skinny_launch<8, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream, rounds_out);
+    return skinny_launch<4, 1>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream, rounds_out);
   }
   if (M <= 16) {
-    if (long_rows) return skinny_launch<8, 2>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
-    return skinny_launch<4, 2>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+    if (long_rows) return skinny_launch<8, 2>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream, rounds_out);
+    return skinny_launch<4, 2>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream, rounds_out);
   }
-  if (M <= 32) return skinny_launch<8, 4>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
-  return skinny_launch<8, 8>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream);
+  if (M <= 32) return skinny_launch<8, 4>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream, rounds_out);
+  return skinny_launch<8, 8>(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream, rounds_out);
 }
 
+
+// x [M,K], w [N,K], bias [N] or null (bfloat16); out [M,N] bfloat16 or float32 (out_f32).
+// swiglu != 0: w interleaves blocks of 64 gate rows with the 64 up rows of the same outputs
+// (N % 128 == 0, no bias); out is silu(gate) * up, [M, N/2] bfloat16.  M <= 64, K % 8 == 0.
+// rms_eps >= 0: the product acts on the RMS-normalised rows of x.  residual: [M,N] bfloat16 added
+// to the result (it may be `out`), or null; not with swiglu.
+MLR_EXPORT int mlr_gemm_skinny(const void* x, const void* w, const void* bias, void* out, const void* residual,
+                               int M, int N, int K, int out_f32, int swiglu, float rms_eps, cudaStream_t stream) {
+  return skinny_dispatch(x, w, bias, out, residual, M, N, K, out_f32, swiglu, rms_eps, stream, nullptr);
+}
+
+// Rounds in which the CTAs of that product would run on this device (1: all of them at once), or a
+// negative number if the kernel does not take the shape.  Launches nothing.
+MLR_EXPORT int mlr_gemm_skinny_rounds(int M, int N, int K, int swiglu) {
+  int rounds = 0;
+  alignas(16) static const char aligned[16] = {0};
+  const int status = skinny_dispatch(aligned, aligned, nullptr, nullptr, nullptr, M, N, K, 0, swiglu, -1.f, nullptr, &rounds);
+  return status == MLR_OK ? rounds : -1;
+}

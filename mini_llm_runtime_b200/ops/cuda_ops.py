@@ -454,7 +454,10 @@ class CudaOps:
     SKINNY_ROWS_SMALL_WEIGHT = 32     # rows up to which matrices of at most SKINNY_SMALL_WEIGHT elements stay with it
     SKINNY_SMALL_WEIGHT = 2 << 20
     SKINNY_LARGE_WEIGHT = 32 << 20    # elements from which more than SKINNY_LARGE_WEIGHT_ROWS rows go to the tcgen05 kernel
+    SKINNY_LARGE_WEIGHT_ONE_ROW = 64 << 20   # the same for a single row (14B sizes, one request: 6.26 -> 6.14 ms per step)
     SKINNY_LARGE_WEIGHT_ROWS = 0
+    skinny_one_round = True
+    SKINNY_ROUNDS_WEIGHT = 4 << 20    # elements from which a grid of more than one round goes to the tcgen05 kernel
     # Chunks of one decode row and kv head that may form one thread-block cluster, and the longest
     # chunk worth it.  A cluster lies within one GPC, one CTA per SM; with 18 SMs per GPC, 8 GPCs and
     # three CTAs per SM only so many clusters run together, and a launch with more comes in rounds
@@ -489,12 +492,33 @@ class CudaOps:
         # in registers, so its CTAs start beside the kernels before them, while this kernel's
         # 512-thread CTAs for long rows fill a register file each and come in two rounds (7B sizes,
         # 8 rows, down projection inside a step: 51 us against 28; the whole step 4.42 -> 3.77 ms).
-        if rows > self.SKINNY_LARGE_WEIGHT_ROWS and weight.shape[0] * weight.shape[1] >= self.SKINNY_LARGE_WEIGHT:
+        elements = weight.shape[0] * weight.shape[1]
+        if rows > self.SKINNY_LARGE_WEIGHT_ROWS and elements >= (self.SKINNY_LARGE_WEIGHT if rows > 1
+                                                                 else self.SKINNY_LARGE_WEIGHT_ONE_ROW):
             return False
         if rows <= self.SKINNY_ROWS:
+            # Its CTAs keep their operands in registers, so a grid that the device does not hold at once
+            # runs in rounds, the last of them nearly empty and as long as the first; with more than
+            # one token row such products do better in the tcgen05 kernel once the matrix is more
+            # than a few megabytes.  Decode steps, one-round rule off and on: 14B sizes 2 rows 6.43 ->
+            # 6.31 ms, 4 rows 6.72 -> 6.55, 8 rows 7.19 -> 6.83, 16 rows 8.50 -> 7.80; 7B sizes 16 rows
+            # 3.77 -> 3.64; but 14B sizes 1 row 6.22 -> 6.37 (a single row's x costs no traffic), and the
+            # fused gate/up product of the 0.5B sizes at 9 to 16 rows 0.89 -> 0.92 ms.
+            if (self.skinny_one_round and rows > 1 and not swiglu and elements >= self.SKINNY_ROUNDS_WEIGHT
+                    and self._skinny_rounds(rows, weight.shape[0], weight.shape[1], swiglu) > 1):
+                return False
             return True
         return (not swiglu and rows <= self.SKINNY_ROWS_SMALL_WEIGHT
                 and weight.shape[0] * weight.shape[1] <= self.SKINNY_SMALL_WEIGHT)
+
+    def _skinny_rounds(self, rows: int, n: int, k: int, swiglu: bool) -> int:
+        """Rounds in which the few-rows kernel's CTAs for this product would run on this device."""
+        key = (min(rows, 64) if rows > 16 else (8 if rows <= 8 else 16), n, k, bool(swiglu))
+        cache = self.__dict__.setdefault("_rounds_cache", {})
+        if key not in cache:
+            lib = build.load_library("gemm_skinny")
+            cache[key] = int(lib.mlr_gemm_skinny_rounds(int(rows), int(n), int(k), int(bool(swiglu))))
+        return cache[key]
 
     def _linear_skinny(self, x, weight, bias, out_dtype, swiglu, rms_eps=None, residual=None):
         M, K = x.shape

@@ -295,10 +295,37 @@ def test_few_rows_linear(m, n, k):
     b = rnd((n,), torch.bfloat16, 92)
     want = x.double() @ w.double().T + b.double()
     cuda().SKINNY_ROWS = 64          # the kernel takes up to 64 rows; the dispatcher stops at 16
+    cuda().skinny_one_round = False  # and leaves grids of more than one round to the tcgen05 kernel
     try:
         _check_few_rows(m, n, k, x, w, b, want)
     finally:
         del cuda().SKINNY_ROWS
+        del cuda().skinny_one_round
+
+
+def test_few_rows_kernel_is_left_when_its_grid_takes_more_than_one_round():
+    """The dispatcher asks the few-rows kernel in how many rounds its CTAs would run (the device's own
+    occupancy figure) and, with more than one token row and a matrix of megabytes, gives a grid of
+    more than one round to the tcgen05 kernel; the answer does not change the result."""
+    ops_ = cuda()
+    assert ops_._skinny_rounds(8, 1152, 896, False) == 1            # 72 CTAs
+    assert ops_._skinny_rounds(8, 9728, 896, True) == 1             # 304 CTAs, three per SM
+    wide = 16 * (2 * ops_.sm_count(torch.device(DEVICE)) + 8)       # 8 warps per CTA, two CTAs per SM: 8 CTAs too many
+    assert ops_._skinny_rounds(8, wide, 5120, False) >= 2
+    x = rnd((8, 5120), torch.bfloat16, 410)
+    w = rnd((wide, 5120), torch.bfloat16, 411, 0.1)
+    xd, wd = x.to(DEVICE), w.to(DEVICE)
+    assert not ops_._skinny_fits(xd, wd) and ops_._skinny_fits(xd[:1], wd)
+    by_rule = ops_.linear(xd, wd)
+    ops_.skinny_one_round = False
+    try:
+        assert ops_._skinny_fits(xd, wd)
+        few_rows = ops_.linear(xd, wd)
+    finally:
+        del ops_.skinny_one_round
+    want = x.double() @ w.double().T
+    assert_close(by_rule, want, torch.bfloat16, "the tcgen05 kernel by the one-round rule")
+    assert_close(few_rows, want, torch.bfloat16, "the few-rows kernel in rounds")
 
 
 def _check_few_rows(m, n, k, x, w, b, want):
@@ -331,6 +358,7 @@ def test_few_rows_linear_with_norm_and_residual(m, n, k, eps):
     xd = x.double()
     normed = xd * torch.rsqrt((xd * xd).mean(-1, keepdim=True) + eps)
     cuda().SKINNY_ROWS = 64
+    cuda().skinny_one_round = False
     try:
         assert cuda()._skinny_fits(x.to(DEVICE), w.to(DEVICE)) and cuda().fuses_norm(m)
         for skinny in (True, False):
@@ -348,6 +376,7 @@ def test_few_rows_linear_with_norm_and_residual(m, n, k, eps):
     finally:
         cuda().use_skinny = True
         del cuda().SKINNY_ROWS
+        del cuda().skinny_one_round
 
 
 @pytest.mark.parametrize("m", [2, 16, 40])
