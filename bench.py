@@ -313,8 +313,11 @@ def time_prefill(bench, repeats=REPEATS, warmup=3):
 
     from mini_llm_runtime_b200.engine import StepEntry
 
+    import numpy as np
+
     runner = bench.runner(2, PREFILL_TOKENS)
-    tokens = random_tokens(PREFILL_TOKENS, bench.config.vocab_size, 99)
+    # as the engine hands a prompt's portion to the step: an int32 array, not a list of Python integers
+    tokens = np.asarray(random_tokens(PREFILL_TOKENS, bench.config.vocab_size, 99), dtype=np.int32)
     samples = []
     for attempt in range(warmup + repeats):
         runner.cache.create_request("p")

@@ -196,6 +196,7 @@ class ModelRunner:
         self.max_positions = model.spec.max_positions
         self._ring = _PinnedRing(self.device)
         self._device_meta: torch.Tensor | None = None
+        self._typed_views: dict[int, tuple] = {}       # by a metadata buffer's address: (the buffer, its typed views)
         self.steps_run = 0
         self.bytes_sent = 0        # host-to-device bytes of all steps so far (metadata and changed rows)
         # Decode-only steps (one token per request, its logits wanted) are captured into CUDA
@@ -231,9 +232,18 @@ class ModelRunner:
         device_buffer[:nbytes].copy_(staging[:nbytes], non_blocking=True)
         self._ring.sent(index)
         self.bytes_sent += nbytes
+        # views of the whole buffer by element type, made once per buffer: one slice per array then
+        typed = self._typed_views.get(device_buffer.data_ptr())
+        if typed is None or typed[0] is not device_buffer:
+            typed = (device_buffer, {dtype: device_buffer[:device_buffer.numel() // 8 * 8].view(dtype)
+                                     for dtype in set(_TORCH_OF.values())})
+            if len(self._typed_views) > 64:
+                self._typed_views.clear()
+            self._typed_views[device_buffer.data_ptr()] = typed
         out = {}
         for name, array, offset in packer.items:
-            flat = device_buffer[offset:offset + array.nbytes].view(_TORCH_OF[array.dtype])
+            size = array.itemsize
+            flat = typed[1][_TORCH_OF[array.dtype]][offset // size:(offset + array.nbytes) // size]
             out[name] = flat if array.ndim == 1 else flat.view(array.shape)
         return out
 
@@ -411,7 +421,7 @@ class ModelRunner:
     # step it was captured in.  The limits: the first of these that no request exceeds (kernels may
     # then choose plans that only pay for such contexts: the decode attention sizes the thread-block
     # clusters that merge its chunks by it), else the cache's capacity per request.
-    CONTEXT_LIMITS = (1024, 2048, 4096)
+    CONTEXT_LIMITS = (1024, 1536, 2048, 4096)
 
     def _context_limit(self, requests: list[RequestCache]) -> int:
         capacity = self.cache.max_pages_per_request * self.cache.page_size
