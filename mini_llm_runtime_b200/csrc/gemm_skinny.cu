@@ -3,7 +3,7 @@
 // give every SM a 128-row tcgen05 tile: there the cost is a chain of latencies, not bandwidth, and
 // this kernel keeps the chain short.
 //
-// One CTA owns 16 weight rows (output columns).  Its warps split K between them in blocks of 32;
+// One CTA owns 16 weight rows (output columns; 8 in one variant).  Its warps split K between them in blocks of 32;
 // every lane fetches its pieces of W and x with plain 16-byte loads - all loads of a batch of
 // k blocks are issued before any is used - and feeds them to mma.sync.m16n8k16 with the 16 weight
 // rows on the M side and up to 8 tokens on the N side.  The 16 bytes a lane loads from a row are 8
@@ -19,8 +19,13 @@
 // folded into w).  (2) Residual: with a residual pointer the result is added to it (it may be the
 // output itself: every element is read and written by the same thread).
 //
-// Weight loads of the first batch are issued before the programmatic dependency wait: they do
-// not depend on the previous kernel.  Requires K % 8 == 0 and 16-byte aligned rows.
+// Weight loads of the first batch and the bias are issued before the programmatic dependency wait:
+// they do not depend on the previous kernel; the residual is asked for right after it, beside x,
+// not after the reduction.  The kernel's time inside a decode step is a few round trips to memory,
+// so two things are arranged by shape: long rows of few outputs get CTAs of 8 weight rows (ROWS8),
+// which hold a whole row in one batch of loads, and register budgets are set so that a product's
+// CTAs are all resident at once; mlr_gemm_skinny_rounds tells a caller whether they are.
+// Requires K % 8 == 0 and 16-byte aligned rows.
 #include "common.cuh"
 
 namespace mlr {
