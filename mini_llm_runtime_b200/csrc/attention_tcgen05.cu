@@ -38,7 +38,7 @@ namespace mlr {
 constexpr int FA_ROWS = 128;        // query rows per item = MMA M
 constexpr int FA_KEYS = 64;         // keys per tile = MMA N of S, K of P V
 constexpr int FA_SOFTMAX_THREADS = 128;
-constexpr int FA_THREADS = FA_SOFTMAX_THREADS + 32;
+constexpr int FA_THREADS = FA_SOFTMAX_THREADS + 64;      // + the warp that issues MMAs and the warp that loads
 constexpr uint32_t FA_TMEM_COLS = 256;   // S0 | S1 | O (head_dim columns)
 constexpr uint32_t FA_TMEM_O = 2 * FA_KEYS;
 constexpr int FA_P_BYTES = FA_ROWS * FA_KEYS * 2;          // one tile of probabilities
@@ -49,8 +49,8 @@ constexpr float FA_LAZY = 8.f;      // the base exponent follows the running max
 template <int D>
 struct FaShape {
   static constexpr int HALVES = D / 64;                      // 64-wide (128-byte) column blocks of a row
-  static constexpr int STAGES = D == 64 ? 3 : 2;
-  static constexpr int P_BUFFERS = D == 64 ? 2 : 1;
+  static constexpr int STAGES = D == 64 ? 4 : 2;
+  static constexpr int P_BUFFERS = 1;
   static constexpr int Q_BYTES = FA_ROWS * D * 2;
   static constexpr int Q_HALF_BYTES = FA_ROWS * 128;
   static constexpr int KV_TILE_BYTES = FA_KEYS * D * 2;      // one K or V tile
@@ -60,7 +60,7 @@ struct FaShape {
 
 // Barriers and the few words the warps share; behind the tiles in dynamic shared memory.
 struct FaControl {
-  uint64_t q_full, kv_full[3], kv_empty[3], s_ready[2], s_free[2], p_ready, pv_ready;
+  uint64_t q_full, k_full[4], k_empty[4], v_full[4], v_empty[4], s_ready[2], s_free[2], p_ready, pv_ready;
   uint32_t tmem_holder;
   int item, last;
 };
@@ -182,7 +182,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(&ctl.q_full, 1);
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl.kv_full[s], 1); mbar_init(&ctl.kv_empty[s], 1); }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl.k_full[s], 1); mbar_init(&ctl.k_empty[s], 1);
+      mbar_init(&ctl.v_full[s], 1); mbar_init(&ctl.v_empty[s], 1);
+    }
     for (int b = 0; b < 2; ++b) { mbar_init(&ctl.s_ready[b], 1); mbar_init(&ctl.s_free[b], 4); }
     mbar_init(&ctl.p_ready, 4);
     mbar_init(&ctl.pv_ready, 1);
@@ -236,28 +239,37 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     const int tile_begin = item_begin + part * per_part;
     const int tiles = min(per_part, item_tiles - part * per_part);
 
-    if (warp == 4) {
-      // ------------------------------------------------------------ loads and MMAs
-      auto issue_load = [&](int j) {
+    if (warp == 5) {
+      // ------------------------------------------------------------ loads
+      // K and V tiles have rings of their own.  A K stage is free again once the scores that read it
+      // exist, a V stage once the P V product that read it is done; so with S stages the K tile
+      // j + S + 1 is on its way while tile j is in the softmax.  The block-table read that a copy
+      // needs is made at least a key tile before the copy.  (This warp does nothing else: table
+      // reads, waits and the issue of up to 16 bulk copies per key tile took the MMA warp longer
+      // than the softmax takes, when it did both.)
+      auto lookup = [&](int j) -> int {                     // the page, or -1
+        if (j >= tiles || lane >= boxes * Shape::HALVES) return -1;
+        const int logical = ((tile_begin + j) * FA_KEYS + (lane % boxes) * box_rows) >> page_shift;
+        return logical < table_width ? table[logical] : -1;
+      };
+      auto load_tile = [&](int j, int page, bool values) {
         const unsigned load = tiles_before + (unsigned)j;
         const int stage = load % STAGES;
         const unsigned use = load / STAGES;
-        if (use > 0) fa_wait(&ctl.kv_empty[stage], (use - 1) & 1u, error_word, 0x61, gave_up);
+        uint64_t* full = values ? &ctl.v_full[stage] : &ctl.k_full[stage];
+        if (use > 0) fa_wait(values ? &ctl.v_empty[stage] : &ctl.k_empty[stage], (use - 1) & 1u, error_word, 0x61, gave_up);
         gave_up = __any_sync(0xffffffffu, gave_up);
         if (gave_up) return;
-        if (lane == 0) mbar_expect_tx(&ctl.kv_full[stage], 2u * Shape::KV_TILE_BYTES);
+        if (lane == 0) mbar_expect_tx(full, (uint32_t)Shape::KV_TILE_BYTES);
         __syncwarp();
         if (lane < boxes * Shape::HALVES) {
           const int box = lane % boxes, half = lane / boxes;
-          const int key0 = (tile_begin + j) * FA_KEYS + box * box_rows;
-          const int logical = key0 >> page_shift;
-          int page = logical < table_width ? table[logical] : -1;
-          int offset = key0 & (page_size - 1);
+          int offset = ((tile_begin + j) * FA_KEYS + box * box_rows) & (page_size - 1);
           if (page < 0) { page = 0; offset = 0; }
           const int y = (page * kv_heads + kv_head) * page_size + offset;
-          uint8_t* k_dst = kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES + half * Shape::KV_HALF_BYTES + box * box_rows * 128;
-          tma_load_2d(&k_map, &ctl.kv_full[stage], k_dst, half * 64, y);
-          tma_load_2d(&v_map, &ctl.kv_full[stage], k_dst + Shape::KV_TILE_BYTES, half * 64, y);
+          uint8_t* dst = kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES + (values ? Shape::KV_TILE_BYTES : 0)
+                         + half * Shape::KV_HALF_BYTES + box * box_rows * 128;
+          tma_load_2d(values ? &v_map : &k_map, full, dst, half * 64, y);
         }
       };
       if (lane == 0) {
@@ -266,15 +278,39 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         for (int half = 0; half < Shape::HALVES; ++half)
           tma_load_2d(&q_map, &ctl.q_full, q_tile + half * Shape::Q_HALF_BYTES, head * D + half * 64, q_start + row0);
       }
-      for (int j = 0; j < STAGES - 1 && j < tiles; ++j) issue_load(j);
-
+      // pages[i]: of tile j + STAGES - 1 + i in iteration j (i = 0: its V is asked for then, i = 2: its K)
+      int pages[3];
+      {
+        int first_pages[STAGES];            // the first ring-full: all table reads, then all copies
+#pragma unroll
+        for (int j = 0; j < STAGES; ++j) first_pages[j] = lookup(j);
+        pages[0] = first_pages[STAGES - 1];
+        pages[1] = lookup(STAGES);
+        pages[2] = lookup(STAGES + 1);
+#pragma unroll
+        for (int j = 0; j < STAGES; ++j)
+          if (j < tiles) { load_tile(j, first_pages[j], false); load_tile(j, first_pages[j], true); }
+      }
+      if (STAGES < tiles) load_tile(STAGES, pages[1], false);       // where tile 0's K was
+      for (int j = 0; j < tiles; ++j) {
+        const int page_after = lookup(j + STAGES + 2);         // in flight during this iteration
+        // in the order in which the MMA warp frees the stages: V of tile j + STAGES - 1 goes where tile
+        // j - 1's was, K of tile j + STAGES + 1 where tile j + 1's was
+        if (j >= 1 && j + STAGES - 1 < tiles) load_tile(j + STAGES - 1, pages[0], true);
+        if (j + STAGES + 1 < tiles) load_tile(j + STAGES + 1, pages[2], false);
+        pages[0] = pages[1];
+        pages[1] = pages[2];
+        pages[2] = page_after;
+      }
+    } else if (warp == 4) {
+      // ------------------------------------------------------------ MMAs
       constexpr uint32_t idesc_qk = fa_idesc(FA_ROWS, FA_KEYS, false);
       constexpr uint32_t idesc_pv = fa_idesc(FA_ROWS, D, true);
       const uint32_t q_addr = smem_u32(q_tile), p_addr0 = smem_u32(p_tiles);
       auto issue_qk = [&](int j) {
         const unsigned t = tiles_before + (unsigned)j;
         const int stage = t % STAGES, buffer = t & 1;
-        fa_wait(&ctl.kv_full[stage], (t / STAGES) & 1u, error_word, 0x62, gave_up);
+        fa_wait(&ctl.k_full[stage], (t / STAGES) & 1u, error_word, 0x62, gave_up);
         if (t >= 2) fa_wait(&ctl.s_free[buffer], ((t >> 1) - 1) & 1u, error_word, 0x63, gave_up);
         gave_up = __any_sync(0xffffffffu, gave_up);
         fa_fence_after();
@@ -286,17 +322,22 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
                    fa_desc_k_major(q_addr + (k >> 2) * Shape::Q_HALF_BYTES + (k & 3) * 32),
                    fa_desc_k_major(k_addr + (k >> 2) * Shape::KV_HALF_BYTES + (k & 3) * 32), idesc_qk, k > 0 ? 1u : 0u);
           fa_commit(&ctl.s_ready[buffer]);
+          fa_commit(&ctl.k_empty[stage]);
         }
         __syncwarp();
       };
+      // The scores run two key tiles ahead of the softmax (both score buffers in use), so that the
+      // softmax of a tile does not wait for this warp: per tile it waits for the probabilities,
+      // issues P V at once (the softmax of the next tile needs it done midway), then the scores of
+      // the tile after next.
       fa_wait(&ctl.q_full, items_before & 1u, error_word, 0x64, gave_up);
       issue_qk(0);
+      if (tiles > 1) issue_qk(1);
       for (int j = 0; j < tiles; ++j) {
-        if (j + STAGES - 1 < tiles) issue_load(j + STAGES - 1);
-        if (j + 1 < tiles) issue_qk(j + 1);
         const unsigned t = tiles_before + (unsigned)j;
         const int stage = t % STAGES;
         fa_wait(&ctl.p_ready, t & 1u, error_word, 0x65, gave_up);
+        fa_wait(&ctl.v_full[stage], (t / STAGES) & 1u, error_word, 0x6a, gave_up);
         gave_up = __any_sync(0xffffffffu, gave_up);
         fa_fence_after();
         if (lane == 0 && !gave_up) {
@@ -307,9 +348,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
             fa_mma(tmem_base + FA_TMEM_O, fa_desc_k_major(p_addr + k * 32),
                    fa_desc_mn_major(v_addr + k * 2048, Shape::KV_HALF_BYTES), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
           fa_commit(&ctl.pv_ready);
-          fa_commit(&ctl.kv_empty[stage]);
+          fa_commit(&ctl.v_empty[stage]);
         }
         __syncwarp();
+        if (j + 2 < tiles) issue_qk(j + 2);
       }
     } else {
       // ------------------------------------------------------------ softmax, one thread per query row
@@ -416,7 +458,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
 
         if (key0 < lowest || key0 + FA_KEYS - 1 > last_pos) {
           // ragged tile: V rows of keys outside the range become zeros (this thread takes its share of rows)
-          fa_wait(&ctl.kv_full[stage], (t / STAGES) & 1u, error_word, 0x68, gave_up);
+          fa_wait(&ctl.v_full[stage], (t / STAGES) & 1u, error_word, 0x68, gave_up);
           uint8_t* v_tile = kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES + Shape::KV_TILE_BYTES;
           for (int idx = threadIdx.x; idx < FA_KEYS * 8 * Shape::HALVES; idx += FA_SOFTMAX_THREADS) {
             const int half = idx / (FA_KEYS * 8), within = idx - half * (FA_KEYS * 8);
