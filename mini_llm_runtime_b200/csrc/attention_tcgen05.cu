@@ -2,7 +2,7 @@
 // tensor cores (head_dim 64 or 128): S = Q K^T and O += P V run as tcgen05.mma with their results
 // in tensor memory; the online softmax runs on the CUDA cores, one thread per query row.
 //
-// One work item is 128 query rows of one head.  A CTA has five warps:
+// One work item is 128 query rows of one head.  A CTA has six warps:
 //   warps 0..3  softmax: thread r owns query row r (tensor-memory lane r).  Per 64-key tile it reads
 //               its row of S from tensor memory (64 values), masks (causal limit, window, rows past
 //               the portion), keeps the running max and sum, and writes the probabilities as
@@ -16,12 +16,20 @@
 //               the paired float32 instructions (two multiply-adds or adds per issue slot) and the
 //               three-input max, because the instruction stream, not a pipe, bounds this loop.
 //               No shuffles: a row lives in one thread.
-//   warp 4      loads and issues: Q by bulk tensor copies per item, K and V page by page (one
-//               copy per page, kv head and 64-wide half of the head, as in the other attention
-//               kernels) into a ring of stages; one lane issues the MMAs: S_{j+1} = Q K_{j+1}^T
-//               goes out before the warp waits for tile j's probabilities (two S buffers), then
-//               O += P_j V_j.  K is the K-major B operand; V ([keys][head_dim], head_dim
-//               contiguous) is the MN-major B operand.
+//   warp 4      issues the MMAs (one lane).  The scores run two key tiles ahead of the softmax (two
+//               S buffers): per tile the warp waits for the tile's probabilities, issues O += P_j V_j
+//               at once (the next tile's softmax needs it done midway), then S_{j+2} = Q K_{j+2}^T.
+//               K is the K-major B operand; V ([keys][head_dim], head_dim contiguous) is the
+//               MN-major B operand.  One commit per product: the same barrier tells the softmax
+//               that the product exists and the load warp that the product's stage is free.
+//   warp 5      loads: Q by bulk tensor copies per item, K and V page by page (one copy per page, kv
+//               head and 64-wide half of the head, as in the other attention kernels) into a K ring
+//               and a V ring of their own: a K stage is free once the scores that read it exist, a V
+//               stage once its P V product is done, so K runs further ahead than V could.  The
+//               block-table read that a copy needs is made a key tile before the copy.  (Table reads,
+//               waits and the issue of up to 16 copies per key tile took the MMA warp longer than
+//               the softmax takes, when one warp did both: 2,600 to 3,600 cycles per key tile, of
+//               which the softmax waited 1,000 to 1,900 for its scores; now 2,200 to 2,300.)
 // Items are drawn heaviest-first from a counter in global memory by the resident CTAs (two per SM,
 // so one CTA's MMAs run under the other's softmax).
 //
@@ -60,7 +68,9 @@ struct FaShape {
 
 // Barriers and the few words the warps share; behind the tiles in dynamic shared memory.
 struct FaControl {
-  uint64_t q_full, k_full[4], k_empty[4], v_full[4], v_empty[4], s_ready[2], s_free[2], p_ready, pv_ready;
+  // qk_done[stage]: the scores that read this K stage exist (the softmax waits for it, and the load
+  // warp before it refills the stage); pv_done[stage]: likewise the P V product and the V stage
+  uint64_t q_full, k_full[4], v_full[4], qk_done[4], pv_done[4], s_free[2], p_ready;
   uint32_t tmem_holder;
   int item, last;
 };
@@ -183,12 +193,11 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   if (threadIdx.x == 0) {
     mbar_init(&ctl.q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&ctl.k_full[s], 1); mbar_init(&ctl.k_empty[s], 1);
-      mbar_init(&ctl.v_full[s], 1); mbar_init(&ctl.v_empty[s], 1);
+      mbar_init(&ctl.k_full[s], 1); mbar_init(&ctl.qk_done[s], 1);
+      mbar_init(&ctl.v_full[s], 1); mbar_init(&ctl.pv_done[s], 1);
     }
-    for (int b = 0; b < 2; ++b) { mbar_init(&ctl.s_ready[b], 1); mbar_init(&ctl.s_free[b], 4); }
+    for (int b = 0; b < 2; ++b) mbar_init(&ctl.s_free[b], 4);
     mbar_init(&ctl.p_ready, 4);
-    mbar_init(&ctl.pv_ready, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
@@ -257,7 +266,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         const int stage = load % STAGES;
         const unsigned use = load / STAGES;
         uint64_t* full = values ? &ctl.v_full[stage] : &ctl.k_full[stage];
-        if (use > 0) fa_wait(values ? &ctl.v_empty[stage] : &ctl.k_empty[stage], (use - 1) & 1u, error_word, 0x61, gave_up);
+        if (use > 0) fa_wait(values ? &ctl.pv_done[stage] : &ctl.qk_done[stage], (use - 1) & 1u, error_word, 0x61, gave_up);
         gave_up = __any_sync(0xffffffffu, gave_up);
         if (gave_up) return;
         if (lane == 0) mbar_expect_tx(full, (uint32_t)Shape::KV_TILE_BYTES);
@@ -307,6 +316,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       constexpr uint32_t idesc_qk = fa_idesc(FA_ROWS, FA_KEYS, false);
       constexpr uint32_t idesc_pv = fa_idesc(FA_ROWS, D, true);
       const uint32_t q_addr = smem_u32(q_tile), p_addr0 = smem_u32(p_tiles);
+      // descriptors differ from tile to tile in their address field only (bytes / 16 in the low bits)
+      const uint64_t q_desc = fa_desc_k_major(q_addr), kv_desc = fa_desc_k_major(smem_u32(kv_ring));
+      const uint64_t v_desc = fa_desc_mn_major(smem_u32(kv_ring) + Shape::KV_TILE_BYTES, Shape::KV_HALF_BYTES);
+      const uint64_t p_desc = fa_desc_k_major(p_addr0);
       auto issue_qk = [&](int j) {
         const unsigned t = tiles_before + (unsigned)j;
         const int stage = t % STAGES, buffer = t & 1;
@@ -315,14 +328,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         gave_up = __any_sync(0xffffffffu, gave_up);
         fa_fence_after();
         if (lane == 0 && !gave_up) {
-          const uint32_t k_addr = smem_u32(kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES);
+          const uint64_t k_desc = kv_desc + (uint64_t)((stage * 2 * Shape::KV_TILE_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < D / 16; ++k)
-            fa_mma(tmem_base + buffer * FA_KEYS,
-                   fa_desc_k_major(q_addr + (k >> 2) * Shape::Q_HALF_BYTES + (k & 3) * 32),
-                   fa_desc_k_major(k_addr + (k >> 2) * Shape::KV_HALF_BYTES + (k & 3) * 32), idesc_qk, k > 0 ? 1u : 0u);
-          fa_commit(&ctl.s_ready[buffer]);
-          fa_commit(&ctl.k_empty[stage]);
+            fa_mma(tmem_base + buffer * FA_KEYS, q_desc + (uint64_t)(((k >> 2) * Shape::Q_HALF_BYTES + (k & 3) * 32) >> 4),
+                   k_desc + (uint64_t)(((k >> 2) * Shape::KV_HALF_BYTES + (k & 3) * 32) >> 4), idesc_qk, k > 0 ? 1u : 0u);
+          fa_commit(&ctl.qk_done[stage]);
         }
         __syncwarp();
       };
@@ -341,14 +352,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         gave_up = __any_sync(0xffffffffu, gave_up);
         fa_fence_after();
         if (lane == 0 && !gave_up) {
-          const uint32_t v_addr = smem_u32(kv_ring + (size_t)stage * 2 * Shape::KV_TILE_BYTES + Shape::KV_TILE_BYTES);
-          const uint32_t p_addr = p_addr0 + (Shape::P_BUFFERS == 2 ? (t & 1u) : 0u) * FA_P_BYTES;
+          const uint64_t v_tile = v_desc + (uint64_t)((stage * 2 * Shape::KV_TILE_BYTES) >> 4);
+          const uint64_t p_tile = p_desc + (uint64_t)(((Shape::P_BUFFERS == 2 ? (t & 1u) : 0u) * FA_P_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < FA_KEYS / 16; ++k)       // the output row accumulates over all key tiles of the unit
-            fa_mma(tmem_base + FA_TMEM_O, fa_desc_k_major(p_addr + k * 32),
-                   fa_desc_mn_major(v_addr + k * 2048, Shape::KV_HALF_BYTES), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-          fa_commit(&ctl.pv_ready);
-          fa_commit(&ctl.v_empty[stage]);
+            fa_mma(tmem_base + FA_TMEM_O, p_tile + (uint64_t)((k * 32) >> 4), v_tile + (uint64_t)((k * 2048) >> 4), idesc_pv,
+                   (j > 0 || k > 0) ? 1u : 0u);
+          fa_commit(&ctl.pv_done[stage]);
         }
         __syncwarp();
         if (j + 2 < tiles) issue_qk(j + 2);
@@ -374,7 +384,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         const unsigned t = tiles_before + (unsigned)j;
         const int buffer = t & 1, stage = t % STAGES;
         const int key0 = (tile_begin + j) * FA_KEYS;
-        fa_wait(&ctl.s_ready[buffer], (t >> 1) & 1u, error_word, 0x66, gave_up);
+        fa_wait(&ctl.qk_done[stage], (t / STAGES) & 1u, error_word, 0x66, gave_up);
         fa_fence_after();
         float s[FA_KEYS];
 #pragma unroll
@@ -427,13 +437,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
 
         // The output rows in tensor memory hold the sum of the earlier tiles' P V.  They are touched
         // only when a row of this warp moved its base.  The previous tile's P V is waited for on
-        // every tile all the same (it was issued a whole tile ago): a parity wait can tell the
-        // barrier's current phase from the one before it only, so no phase may be skipped; a warp
-        // must not arrive for this tile's probabilities while the barrier still counts the previous
-        // tile's arrivals; and with one buffer of probabilities the MMA must have read it.
+        // every tile all the same (it was issued a whole tile ago): a warp must not arrive for this
+        // tile's probabilities while the barrier still counts the previous tile's arrivals, and
+        // with one buffer of probabilities the MMA must have read it.
         const bool rescale = j > 0 && __any_sync(0xffffffffu, step);
         if (j > 0) {
-          fa_wait(&ctl.pv_ready, (t - 1) & 1u, error_word, 0x67, gave_up);
+          fa_wait(&ctl.pv_done[(t - 1) % STAGES], ((t - 1) / STAGES) & 1u, error_word, 0x67, gave_up);
           fa_fence_after();
         }
         if (rescale) {
@@ -489,7 +498,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       // the finished output rows, after the last tile's P V
       {
         const unsigned t = tiles_before + (unsigned)tiles - 1;
-        fa_wait(&ctl.pv_ready, t & 1u, error_word, 0x69, gave_up);
+        fa_wait(&ctl.pv_done[t % STAGES], (t / STAGES) & 1u, error_word, 0x69, gave_up);
         fa_fence_after();
         constexpr int STATE = D + 2;
         // a part's state of row r: base exponent, sum, unnormalised output; laid out [value][row]
