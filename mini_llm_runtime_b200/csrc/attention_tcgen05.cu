@@ -70,7 +70,7 @@ struct FaShape {
 struct FaControl {
   // qk_done[stage]: the scores that read this K stage exist (the softmax waits for it, and the load
   // warp before it refills the stage); pv_done[stage]: likewise the P V product and the V stage
-  uint64_t q_full, k_full[4], v_full[4], qk_done[4], pv_done[4], s_free[2], p_ready;
+  uint64_t q_full, k_full[4], v_full[4], qk_done[4], pv_done[4], p_ready;
   uint32_t tmem_holder;
   int item, last;
 };
@@ -196,7 +196,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       mbar_init(&ctl.k_full[s], 1); mbar_init(&ctl.qk_done[s], 1);
       mbar_init(&ctl.v_full[s], 1); mbar_init(&ctl.pv_done[s], 1);
     }
-    for (int b = 0; b < 2; ++b) mbar_init(&ctl.s_free[b], 4);
     mbar_init(&ctl.p_ready, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
@@ -324,7 +323,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         const unsigned t = tiles_before + (unsigned)j;
         const int stage = t % STAGES, buffer = t & 1;
         fa_wait(&ctl.k_full[stage], (t / STAGES) & 1u, error_word, 0x62, gave_up);
-        if (t >= 2) fa_wait(&ctl.s_free[buffer], ((t >> 1) - 1) & 1u, error_word, 0x63, gave_up);
+        // The score buffer is free: scores go out two tiles ahead, after the probabilities of tile
+        // j - 2 arrived, and a softmax warp arrives there only after it has read that tile's scores
+        // (the same buffer); a unit's first two tiles follow the previous unit's end.
         gave_up = __any_sync(0xffffffffu, gave_up);
         fa_fence_after();
         if (lane == 0 && !gave_up) {
@@ -391,8 +392,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         for (int c = 0; c < FA_KEYS; c += 16) fa_tmem_load16(lane_base + buffer * FA_KEYS + c, reinterpret_cast<uint32_t*>(s) + c);
         fa_tmem_wait_ld();
         fa_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl.s_free[buffer]);
 
         if (!(warp_full && key0 + FA_KEYS - 1 <= warp_first && key0 >= warp_lo)) {
 #pragma unroll
