@@ -239,7 +239,7 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
         const int half = N >> 1;
         if (column < half) {
           const float gate = acc[0][n][e] * scale, up = acc[GROUPS - 1][n][e] * scale;
-          out_bf16[(size_t)token * half + column] = __float2bfloat16_rn(gate / (1.f + __expf(-gate)) * up);
+          out_bf16[(size_t)token * half + column] = __float2bfloat16_rn(silu_times(gate, up));
         }
       } else {
         if (ROWS8 && e >= 2) continue;                     // the MMA's upper rows hold nothing

@@ -136,7 +136,6 @@ struct GemmParams {
 
 constexpr int MAX_STAGES = 8;
 
-__device__ __forceinline__ float silu_times(float gate, float up) { return gate / (1.f + __expf(-gate)) * up; }
 
 // Sum of the splits' partial values of 16 columns of one tile row, in split order.  Loads of four
 // splits are issued together so that their latencies overlap; a missing split adds zeros.
@@ -621,7 +620,9 @@ static int forced_bn = 0, forced_stages = 0, forced_splits = 0, forced_bm = 0, f
 //   the load latency spread over the ring: (0.5 + 0.03 per KB of a stage) / stages
 //     (56 k blocks, one CTA per SM: 4 stages of 32 KB 23.5 us, 4 stages of 48 KB 31.6 us);
 //   the SM's operand bandwidth from L2, about 112 GB/s, shared by its CTAs
-//     (8,192^3 with two CTAs per SM and 48 KB stages: 0.43 us per k block and SM).
+//     (8,192^3 with two CTAs per SM and 48 KB stages: 0.43 us per k block and SM); 90 GB/s when three
+//     CTAs with 32 KB stages share it (9728 x 896 with SwiGLU at 2,048 rows: 53.7 us as 128 x 128
+//     tiles in two stages, 43.8 as 128 x 256 in two stages, 46.0 as 128 x 128 in three).
 // CTAs per SM follow from shared and tensor memory; a launch takes ceil(CTAs / resident) rounds; with
 // a single CTA per SM nothing hides a CTA's start and end, which costs about 4 us more per round.
 // Checked against: 9728 x 896 at 2,048 rows 45 (measured 44.6); 4608 x 3584 at 520 rows, 128 wide,
@@ -662,8 +663,11 @@ static GemmPlan plan_many_rows(int M, int N, int K, bool swiglu, int sms) {
         const double stage_kb = (double)stage_bytes / 1024.0;
         double per_kb = 0.14 * (bn / 128) * (bm / TILE_ROWS) * sharing;                // tensor pipe
         if ((0.5 + 0.03 * stage_kb) / stages > per_kb) per_kb = (0.5 + 0.03 * stage_kb) / stages;   // load latency
-        if (sharing * stage_kb / 112.0 > per_kb) per_kb = sharing * stage_kb / 112.0;  // operand bandwidth of the SM
-        double cost = rounds * (1.5 + kb * per_kb + 1.5 * (bn / 128) * (bm / TILE_ROWS) + ((per_sm == 1 && rounds > 1) ? 4.0 : 0.0));
+        const double sm_gbs = sharing >= 3 ? 90.0 : 112.0;     // three small rings take in less than two larger ones
+        if (sharing * stage_kb / sm_gbs > per_kb) per_kb = sharing * stage_kb / sm_gbs;  // operand bandwidth of the SM
+        // per 128 columns; SwiGLU writes half as many, but two accumulators per CTA leave nobody to run under
+        const double epilogue = (swiglu && bm == TILE_ROWS) ? 1.0 : 1.5;
+        double cost = rounds * (1.5 + kb * per_kb + epilogue * (bn / 128) * (bm / TILE_ROWS) + ((per_sm == 1 && rounds > 1) ? 4.0 : 0.0));
         if (splits > 1) cost += 4.0 + (double)splits * bn * 512.0 / 50e3;
         if (cost < best_cost) {
           best_cost = cost;
@@ -681,7 +685,10 @@ static GemmPlan plan_many_rows(int M, int N, int K, bool swiglu, int sms) {
   // 825 against 838 and 845; at 384 rows the padding to 512 eats the gain).  The other products are
   // as fast or faster in one CTA with its ring of 64 KB stages.
   const bool pair_fits = N >= 256 && M > 2 * TILE_ROWS;
-  const bool pair_pays = swiglu && best.bn == 256 && M > 3 * TILE_ROWS;
+  // (With 14 k blocks, 9728 x 896, the pair's longer start and end cost more than its epilogue's
+  // overlap brings: 46.4 us against 43.8 us as 128 x 256 tiles in two stages; with 24, 17920 x 1536,
+  // 90.9 against 92.4.)
+  const bool pair_pays = swiglu && best.bn == 256 && M > 3 * TILE_ROWS && total_kb >= 24;
   if (pair_fits && (forced_pair > 0 || (forced_pair == 0 && pair_pays))) {
     best.bn = 256; best.bm = 2 * TILE_ROWS; best.pair = true;
     best.tiles = ((M + 255) / 256) * ((N + 255) / 256);
