@@ -595,9 +595,9 @@ using namespace mlr;
 
 MLR_DEFINE_PDL_SWITCH
 
-// Units of work aimed at per resident CTA when items are cut into parts.  One: measured with the
-// output rows in tensor memory, a 2,048-row prompt takes 40 us at 14 heads of 64 and 72 us at 28 heads
-// of 128 against 48 and 83 us with two (more, shorter units mean more starts, ends and merges).
+// Units of work aimed at per resident CTA when items are cut into parts.  One: a 2,048-row prompt
+// takes 38 us at 14 heads of 64 and 52 us at 28 heads of 128 against 43 and 67 us with two (more,
+// shorter units mean more starts, ends and merges).
 static const int units_per_cta = 1;
 
 namespace mlr {
