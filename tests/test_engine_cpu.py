@@ -76,6 +76,33 @@ def test_step_validation():
     assert engine.cache.get("a").committed == 3
 
 
+def test_a_captured_steps_context_limit_is_the_first_that_no_request_exceeds():
+    """The limit a captured decode step plans its kernels against: the first of the runner's limits
+    that holds every request's length after the step, limits at or beyond the cache's capacity per
+    request do not count, and beyond the last one the capacity itself."""
+    config, page = TINY["A"]
+    engine = TinyEngine(config, page, torch.float32, "cpu", num_pages=64, max_requests=2, max_tokens=40 * page)
+    runner, cache = engine.runner, engine.cache
+    capacity = cache.max_pages_per_request * page
+    runner.CONTEXT_LIMITS = (2 * page, 5 * page, 10 * capacity)
+    cache.create_request("a")
+    cache.create_request("b")
+    runner.step([StepEntry("a", [1] * (2 * page - 1), []), StepEntry("b", [2, 3], [])])
+
+    def limit_after(tokens_a, tokens_b):
+        requests = cache.begin_step([("a", tokens_a), ("b", tokens_b)])
+        try:
+            return runner._context_limit(requests)
+        finally:
+            cache.abort_step()
+
+    assert limit_after(1, 1) == 2 * page                    # a reaches exactly the first limit
+    assert limit_after(2, 1) == 5 * page                    # one token more: the next
+    assert limit_after(3 * page + 1, 1) == 5 * page
+    assert limit_after(3 * page + 2, 1) == capacity         # beyond the last limit below the capacity
+    assert limit_after(1, 5 * page) == capacity             # the longest request decides
+
+
 def build_engine(name, **options):
     config, page = TINY[name]
     model = build_model(config, torch.float32)
