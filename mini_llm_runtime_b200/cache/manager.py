@@ -278,7 +278,7 @@ class CacheManager:
                 raise ValueError(f"request {request_id!r} would hold {request.committed + count} tokens, "
                                  f"more than max_tokens_per_request={self.max_tokens_per_request}")
             plan.append((request, count))
-        taken: list[tuple[RequestCache, CacheGroup, int, int]] = []   # (request, group, logical, id)
+        taken: list[tuple[RequestCache, CacheGroup, int, list[int]]] = []   # (request, group, first logical page, ids)
         try:
             for request, count in plan:
                 end = request.committed + count
@@ -292,20 +292,20 @@ class CacheManager:
                     if limit and request.held(group.index) + missing > limit:
                         raise OutOfPages(f"request {request.request_id!r} would exceed the {limit} pages "
                                          f"promised to it in group {group.index}")
-                    new_ids = group.allocator.allocate(missing, promised=bool(limit))
-                    for page_id in new_ids:
-                        pages.append(page_id)
-                        taken.append((request, group, len(pages) - 1, page_id))
+                    new_ids = list(group.allocator.allocate(missing, promised=bool(limit)))
+                    taken.append((request, group, len(pages), new_ids))
+                    pages.extend(new_ids)
         except OutOfPages:
-            for request, group, logical, page_id in reversed(taken):
-                popped = request.pages[group.index].pop()
-                assert popped == page_id and len(request.pages[group.index]) == logical
-                group.allocator.free([page_id], promised=bool(request.promised[group.index]))
+            for request, group, first, new_ids in reversed(taken):
+                pages = request.pages[group.index]
+                assert pages[first:] == new_ids
+                del pages[first:]
+                group.allocator.free(new_ids, promised=bool(request.promised[group.index]))
             raise
-        for request, group, logical, page_id in taken:
-            group.table[request.slot, logical] = page_id
+        for request, group, first, new_ids in taken:
+            group.table[request.slot, first:first + len(new_ids)] = new_ids       # a prompt portion brings a hundred pages
             group.dirty.add(request.slot)
-            request.step_new_pages[group.index].append(page_id)
+            request.step_new_pages[group.index].extend(new_ids)
         for request, count in plan:
             request.pending = (request.committed, request.committed + count)
         self._step = plan

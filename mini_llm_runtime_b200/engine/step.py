@@ -297,9 +297,13 @@ class ModelRunner:
         pieces = [np.asarray(e.tokens, dtype=np.int32) if array is None else array
                   for e, array in zip(entries, token_arrays)]
         token_ids = pieces[0] if len(pieces) == 1 else np.concatenate(pieces)
-        segment_of_row = np.repeat(np.arange(len(entries), dtype=np.int32), lengths)
-        positions = (np.arange(total, dtype=np.int32) - row_start[segment_of_row]
-                     + position_start[segment_of_row]).astype(np.int32)
+        if len(entries) == 1:
+            segment_of_row = np.zeros(total, dtype=np.int32)
+            positions = np.arange(position_start[0], position_start[0] + total, dtype=np.int32)
+        else:
+            segment_of_row = np.repeat(np.arange(len(entries), dtype=np.int32), lengths)
+            positions = (np.arange(total, dtype=np.int32) - row_start[segment_of_row]
+                         + position_start[segment_of_row]).astype(np.int32)
         wanted = [row_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
         wanted_rows = np.concatenate(wanted).astype(np.int32) if wanted else np.zeros(0, dtype=np.int32)
         slots = np.array([r.slot for r in requests], dtype=np.int32)

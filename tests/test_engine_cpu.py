@@ -76,6 +76,32 @@ def test_step_validation():
     assert engine.cache.get("a").committed == 3
 
 
+def test_attention_work_lists_of_one_portion_equal_the_general_construction():
+    """A step of one prompt portion takes a short way to its attention work lists; they are the
+    lists the general construction (cut every segment into tiles, heaviest first) gives."""
+    import numpy as np
+
+    from mini_llm_runtime_b200.ops import cuda_ops
+
+    def general(count, start):
+        lengths, starts = np.array([count], dtype=np.int32), np.array([start], dtype=np.int32)
+        segments = np.array([0], dtype=np.int32)
+        lists = {}
+        for prefix, rows, order in (("tile", cuda_ops.GENERIC_TILE_ROWS, None), ("wide_tile", cuda_ops.MMA_TILE_ROWS, starts),
+                                    ("big_tile", cuda_ops.TCGEN05_TILE_ROWS, starts)):
+            lists[prefix + "_seg"], lists[prefix + "_row0"] = cuda_ops._tiles(lengths, segments, rows, order)
+        return lists
+
+    for count in (2, 3, 15, 16, 17, 63, 64, 65, 127, 128, 129, 777, 2048, 2049):
+        for start in (0, 5, 1000):
+            arrays, counts = cuda_ops.plan_attention([count], [start])
+            for name, want in general(count, start).items():
+                assert arrays[name].dtype == want.dtype and np.array_equal(arrays[name], want), (count, start, name)
+            assert arrays["decode_seg"].shape == (0,) and counts["decode"] == 0
+            assert (counts["tiles"], counts["wide"], counts["big"]) == tuple(
+                len(arrays[name]) for name in ("tile_seg", "wide_tile_seg", "big_tile_seg"))
+
+
 def test_a_captured_steps_context_limit_is_the_first_that_no_request_exceeds():
     """The limit a captured decode step plans its kernels against: the first of the runner's limits
     that holds every request's length after the step, limits at or beyond the cache's capacity per
