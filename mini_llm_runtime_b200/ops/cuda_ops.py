@@ -146,7 +146,7 @@ def plan_attention(lengths: np.ndarray, position_start: np.ndarray) -> tuple[dic
             count = -(-rows // tile_rows)
             row0 = np.arange(count, dtype=np.int32) * np.int32(tile_rows)
             arrays[prefix + "_seg"] = np.zeros(count, dtype=np.int32)
-            arrays[prefix + "_row0"] = np.ascontiguousarray(row0[::-1]) if heavy_first else row0
+            arrays[prefix + "_row0"] = row0[::-1].copy() if heavy_first else row0
             counts[count_name] = count
         return arrays, counts
     decode_seg = np.flatnonzero(lengths == 1).astype(np.int32)

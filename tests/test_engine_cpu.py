@@ -97,6 +97,7 @@ def test_attention_work_lists_of_one_portion_equal_the_general_construction():
             arrays, counts = cuda_ops.plan_attention([count], [start])
             for name, want in general(count, start).items():
                 assert arrays[name].dtype == want.dtype and np.array_equal(arrays[name], want), (count, start, name)
+                assert all(stride > 0 for stride in arrays[name].strides), "a tensor cannot be made from it"
             assert arrays["decode_seg"].shape == (0,) and counts["decode"] == 0
             assert (counts["tiles"], counts["wide"], counts["big"]) == tuple(
                 len(arrays[name]) for name in ("tile_seg", "wide_tile_seg", "big_tile_seg"))
